@@ -1,0 +1,227 @@
+"""ctypes binding of include/arcsample.h. Tensors are torch CUDA tensors; every call enqueues
+on torch's current stream of the tensors' device and returns without synchronising."""
+import ctypes as C
+import os
+
+import numpy as np
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libarcsample.so")
+
+KCAP = 256
+HEAD = 512
+F32, BF16 = 0, 1
+FLAG_TIE_TOPK, FLAG_FIRST_REFUSED, FLAG_TAIL_SKIPPED, FLAG_TAIL_USED = 1, 2, 4, 8
+
+# arcs_row_params: SamplingParams of the reference (tools/sampler.h:15-26) without seed / logit_bias
+PARAMS_DTYPE = np.dtype(
+    [
+        ("temperature", "<f4"),
+        ("top_p", "<f4"),
+        ("min_p", "<f4"),
+        ("presence_penalty", "<f4"),
+        ("frequency_penalty", "<f4"),
+        ("repeat_penalty", "<f4"),
+        ("repeat_last_n", "<i4"),
+        ("top_k", "<i4"),
+    ]
+)
+
+
+class ArcsError(RuntimeError):
+    pass
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `make -C arcinfer_b200/csrc` "
+            "(or __graft_entry__.build()); there is no CPU fallback"
+        )
+    return C.CDLL(LIB_PATH)
+
+
+lib = _load()
+
+
+class SampleArgs(C.Structure):
+    _fields_ = [
+        ("logits", C.c_void_p), ("dtype", C.c_int32), ("B", C.c_int32), ("V", C.c_int32),
+        ("row_stride", C.c_int64), ("params", C.c_void_p),
+        ("hist_off", C.c_void_p), ("hist_ids", C.c_void_p),
+        ("bias_off", C.c_void_p), ("bias_ids", C.c_void_p), ("bias_vals", C.c_void_p),
+        ("u", C.c_void_p), ("mask", C.c_void_p), ("mask_row", C.c_void_p), ("mask_stride", C.c_int64),
+        ("max_hist", C.c_int32), ("max_bias", C.c_int32), ("id_base", C.c_int32), ("v_global", C.c_int32),
+        ("token", C.c_void_p), ("n_cand", C.c_void_p), ("n_kept", C.c_void_p), ("flags", C.c_void_p),
+        ("cand_id", C.c_void_p), ("cand_val", C.c_void_p), ("cand_pr", C.c_void_p), ("cand_stride", C.c_int32),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
+    ]  # fmt: skip
+
+
+class ArgmaxArgs(C.Structure):
+    _fields_ = [
+        ("logits", C.c_void_p), ("dtype", C.c_int32), ("R", C.c_int32), ("V", C.c_int32),
+        ("row_stride", C.c_int64), ("argmax", C.c_void_p), ("max_sumexp", C.c_void_p),
+        ("slots", C.c_int32), ("row_off", C.c_void_p), ("draft", C.c_void_p), ("draft_off", C.c_void_p),
+        ("accepted", C.c_void_p), ("next", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
+    ]  # fmt: skip
+
+
+lib.arcs_last_error.restype = C.c_char_p
+lib.arcs_version.restype = C.c_int
+lib.arcs_sample_workspace_bytes.restype = C.c_size_t
+lib.arcs_sample_workspace_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int32]
+lib.arcs_sample_batch.restype = C.c_int
+lib.arcs_sample_batch.argtypes = [C.POINTER(SampleArgs), C.c_void_p]
+lib.arcs_argmax_workspace_bytes.restype = C.c_size_t
+lib.arcs_argmax_workspace_bytes.argtypes = [C.c_int32, C.c_int32]
+lib.arcs_argmax_batch.restype = C.c_int
+lib.arcs_argmax_batch.argtypes = [C.POINTER(ArgmaxArgs), C.c_void_p]
+lib.arcs_dfa_mask.restype = C.c_int
+lib.arcs_dfa_mask.argtypes = [
+    C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
+    C.c_int32, C.c_int32, C.c_void_p, C.c_int64, C.c_void_p,
+]  # fmt: skip
+
+
+def _check(rc, what):
+    if rc != 0:
+        raise ArcsError(f"{what}: status {rc}: {lib.arcs_last_error().decode()}")
+
+
+def _ptr(t):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(device):
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _dtype_code(t):
+    if t.dtype == torch.float32:
+        return F32
+    if t.dtype == torch.bfloat16:
+        return BF16
+    raise ArcsError(f"logits must be float32 or bfloat16, not {t.dtype}")
+
+
+def make_params(n=1, **kw):
+    """n rows of SamplingParams defaults (tools/sampler.h:16-22), fields overridden by kw."""
+    p = np.zeros(n, PARAMS_DTYPE)
+    p["temperature"], p["top_p"], p["repeat_penalty"], p["repeat_last_n"], p["top_k"] = 1.0, 0.95, 1.0, 64, 20
+    for k, v in kw.items():
+        p[k] = v
+    return p
+
+
+def params_to_device(p, device):
+    return torch.from_numpy(np.ascontiguousarray(p).view(np.uint8).copy()).to(device)
+
+
+_workspaces = {}
+
+
+def _workspace(kind, device, nbytes):
+    """One zero-initialised scratch buffer per (kind, device), grown on demand. The kernels leave
+    it zeroed again, so it is cleared only when (re)allocated."""
+    key = (kind, str(device))
+    w = _workspaces.get(key)
+    if w is None or w.numel() < nbytes:
+        w = torch.zeros(max(nbytes, 1024), dtype=torch.uint8, device=device)
+        _workspaces[key] = w
+    return w
+
+
+def reset_workspaces():
+    """Zero every cached scratch buffer (needed after a launch that reported a device status)."""
+    for w in _workspaces.values():
+        w.zero_()
+
+
+def sample_batch(logits, params, u, hist_off=None, hist_ids=None, bias_off=None, bias_ids=None, bias_vals=None,
+                 mask=None, mask_row=None, max_hist=0, max_bias=0, id_base=0, v_global=0, V=None,
+                 want_cands=False, status=None):
+    """arcs_sample_batch on device tensors. logits: [B, >=V] float32/bfloat16 (row stride =
+    logits.stride(0)); params: uint8 tensor holding B arcs_row_params; u: float64 [B]."""
+    assert logits.is_cuda and logits.dim() == 2 and logits.stride(1) == 1
+    dev = logits.device
+    B = logits.shape[0]
+    V = logits.shape[1] if V is None else V
+    out = {
+        "token": torch.empty(B, dtype=torch.int32, device=dev),
+        "n_cand": torch.empty(B, dtype=torch.int32, device=dev),
+        "n_kept": torch.empty(B, dtype=torch.int32, device=dev),
+        "flags": torch.empty(B, dtype=torch.int32, device=dev),
+    }
+    if want_cands:
+        out["cand_id"] = torch.empty(B, KCAP, dtype=torch.int32, device=dev)
+        out["cand_val"] = torch.empty(B, KCAP, dtype=torch.float32, device=dev)
+        out["cand_pr"] = torch.empty(B, KCAP, dtype=torch.float32, device=dev)
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out["status"] = status
+    masked = mask is not None
+    nbytes = lib.arcs_sample_workspace_bytes(B, V, int(masked))
+    ws = _workspace("sample", dev, nbytes)
+    a = SampleArgs()
+    a.logits, a.dtype, a.B, a.V, a.row_stride = logits.data_ptr(), _dtype_code(logits), B, V, logits.stride(0)
+    a.params = params.data_ptr()
+    a.hist_off, a.hist_ids = _ptr(hist_off), _ptr(hist_ids)
+    a.bias_off, a.bias_ids, a.bias_vals = _ptr(bias_off), _ptr(bias_ids), _ptr(bias_vals)
+    a.u = u.data_ptr()
+    a.mask, a.mask_row = _ptr(mask), _ptr(mask_row)
+    a.mask_stride = mask.stride(0) if masked else 0
+    a.max_hist, a.max_bias, a.id_base, a.v_global = max_hist, max_bias, id_base, v_global
+    a.token, a.n_cand, a.n_kept, a.flags = (out[k].data_ptr() for k in ("token", "n_cand", "n_kept", "flags"))
+    if want_cands:
+        a.cand_id, a.cand_val, a.cand_pr = out["cand_id"].data_ptr(), out["cand_val"].data_ptr(), out["cand_pr"].data_ptr()
+    a.cand_stride = KCAP
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
+    a.status = status.data_ptr()
+    _check(lib.arcs_sample_batch(C.byref(a), _stream(dev)), "arcs_sample_batch")
+    return out
+
+
+def argmax_batch(logits, V=None, want_lse=False, row_off=None, draft=None, draft_off=None, status=None):
+    """arcs_argmax_batch: first maximum per row, optional (max, sumexp), optional greedy
+    acceptance for rows grouped into slots (row_off / draft / draft_off int32 device tensors)."""
+    assert logits.is_cuda and logits.dim() == 2 and logits.stride(1) == 1
+    dev = logits.device
+    R = logits.shape[0]
+    V = logits.shape[1] if V is None else V
+    out = {"argmax": torch.empty(R, dtype=torch.int32, device=dev)}
+    if want_lse:
+        out["max_sumexp"] = torch.empty(R, 2, dtype=torch.float32, device=dev)
+    slots = 0 if row_off is None else row_off.numel() - 1
+    if slots:
+        out["accepted"] = torch.empty(slots, dtype=torch.int32, device=dev)
+        out["next"] = torch.empty(slots, dtype=torch.int32, device=dev)
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out["status"] = status
+    ws = _workspace("argmax", dev, lib.arcs_argmax_workspace_bytes(R, V))
+    a = ArgmaxArgs()
+    a.logits, a.dtype, a.R, a.V, a.row_stride = logits.data_ptr(), _dtype_code(logits), R, V, logits.stride(0)
+    a.argmax, a.max_sumexp = out["argmax"].data_ptr(), _ptr(out.get("max_sumexp"))
+    a.slots, a.row_off, a.draft, a.draft_off = slots, _ptr(row_off), _ptr(draft), _ptr(draft_off)
+    a.accepted, a.next = _ptr(out.get("accepted")), _ptr(out.get("next"))
+    a.workspace, a.workspace_bytes, a.status = ws.data_ptr(), ws.numel(), status.data_ptr()
+    _check(lib.arcs_argmax_batch(C.byref(a), _stream(dev)), "arcs_argmax_batch")
+    return out
+
+
+def dfa_mask(table, dead, states, byte_off, bytes_, special=None, special_ok=False, V=None):
+    """arcs_dfa_mask: table [S,256] uint16-as-int16 tensor, states int32 [n], byte_off
+    uint32-as-int32 [V+1], bytes_ uint8. Returns int32 [n, ceil(V/32)] packed bits."""
+    dev = table.device
+    V = byte_off.numel() - 1 if V is None else V
+    W = (V + 31) // 32
+    out = torch.zeros(states.numel(), W, dtype=torch.int32, device=dev)
+    _check(
+        lib.arcs_dfa_mask(table.data_ptr(), table.shape[0], dead, states.data_ptr(), states.numel(), byte_off.data_ptr(),
+                          bytes_.data_ptr(), _ptr(special), int(special_ok), V, out.data_ptr(), W, _stream(dev)),
+        "arcs_dfa_mask",
+    )
+    return out

@@ -1,0 +1,148 @@
+/*
+ * libarcsample — per-step token selection on NVIDIA B200 (sm_100a), C ABI.
+ *
+ * This is the boundary a host application binds instead of running the reference's
+ * single-threaded host sampler over a logits row read back from the GPU. Every entry point
+ * takes plain pointers and sizes; device pointers are owned by the caller; nothing throws;
+ * the return value is an arcs_status. Calls enqueue work on the caller's stream (passed as
+ * void*, a cudaStream_t) and do not synchronise unless the name ends in _host.
+ *
+ * Citations name files of the reference project (rizagp/arcinfer) by their path inside it.
+ *
+ * Ordering rule everywhere: candidates are ranked by (logit descending, token id ascending).
+ * The reference leaves the order among exactly equal logits to the C++ standard library's
+ * heap code; with distinct logits both orders are the same.
+ */
+#ifndef ARCSAMPLE_H
+#define ARCSAMPLE_H
+#include <stddef.h>
+#include <stdint.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define ARCS_VERSION 1
+#define ARCS_KCAP 256          /* most candidates a row can keep (top_k <= 0 means 256) */
+#define ARCS_HEAD 512          /* sample_allowed: ranks examined before the tail rule */
+#define ARCS_BANNED (-1e30f)   /* Sampler::kBanned, tools/sampler.h:32 */
+
+typedef enum {
+  ARCS_OK = 0,
+  ARCS_ERR_ARG = 1,        /* null pointer, negative size, unknown dtype, V == 0 ... */
+  ARCS_ERR_TOPK = 2,       /* a row asks for more than ARCS_KCAP candidates */
+  ARCS_ERR_WORKSPACE = 3,  /* workspace missing or smaller than arcs_*_workspace_bytes says */
+  ARCS_ERR_CUDA = 4,       /* a CUDA call failed; arcs_last_error() has the text */
+  ARCS_ERR_LIST = 5,       /* a row's history / bias list is longer than max_hist / max_bias */
+  ARCS_ERR_TIMEOUT = 6,    /* device side: a bounded wait ran out (status word only) */
+  ARCS_ERR_INJECTED = 7    /* host-side fault injection (ARCS_FAIL_CALL=N environment variable) */
+} arcs_status;
+
+typedef enum { ARCS_F32 = 0, ARCS_BF16 = 1 } arcs_dtype;
+
+/* One row's sampling parameters: SamplingParams (tools/sampler.h:15-26) field for field,
+ * without the seed (the uniform draw u is an explicit input) and without the logit_bias
+ * list (a CSR list beside it). Defaults there: temperature 1, top_p .95, min_p 0,
+ * presence 0, frequency 0, repeat_penalty 1, repeat_last_n 64, top_k 20. */
+typedef struct {
+  float temperature, top_p, min_p, presence_penalty, frequency_penalty, repeat_penalty;
+  int32_t repeat_last_n, top_k;
+} arcs_row_params;
+
+/* per-row result flags */
+enum {
+  ARCS_FLAG_TIE_TOPK = 1,      /* two equal logits among the candidates kept */
+  ARCS_FLAG_FIRST_REFUSED = 2, /* constrained: the most likely token was not allowed (tools/server_chat.h:542) */
+  ARCS_FLAG_TAIL_SKIPPED = 4,  /* constrained: e^-20 stop at rank 512 applied (tools/sampler.h:111) */
+  ARCS_FLAG_TAIL_USED = 8      /* constrained: candidates beyond rank 512 were needed */
+};
+
+const char* arcs_last_error(void); /* text of the calling thread's last failure */
+int arcs_version(void);
+
+/* ------------------------------------------------------------------------------------------
+ * sample_batch: Sampler::adjusted + Sampler::sample for B rows in one launch
+ * (tools/sampler.h:36-78, :147-176); with a mask, Sampler::sample_allowed (:82-144) where
+ * the predicate ok(t) is bit t of the row's mask.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  /* inputs (device pointers) */
+  const void* logits;        /* [B][row_stride] of dtype; row b starts at b*row_stride elements */
+  int32_t dtype;             /* arcs_dtype */
+  int32_t B, V;
+  int64_t row_stride;        /* in elements, >= V */
+  const arcs_row_params* params; /* [B] */
+  const int32_t* hist_off;   /* [B+1] CSR offsets into hist_ids, or NULL: no history (`recent`) */
+  const int32_t* hist_ids;   /* token ids generated so far, oldest first; ids outside [0,V) ignored */
+  const int32_t* bias_off;   /* [B+1] CSR offsets of the logit_bias lists, or NULL */
+  const int32_t* bias_ids;
+  const float* bias_vals;    /* <= -100 bans the token (tools/sampler.h:24) */
+  const double* u;           /* [B] uniform draws in [0,1); the reference's draw is u*tot */
+  const uint32_t* mask;      /* NULL: unconstrained. Else packed allowed-token bits, rows of mask_stride words */
+  const int32_t* mask_row;   /* [B] mask row used by each batch row, or NULL: row b uses mask row b */
+  int64_t mask_stride;       /* words per mask row, >= ceil(V/32) */
+  int32_t max_hist, max_bias;/* upper bounds on any row's list length (sizes the on-chip tables) */
+  int32_t id_base;           /* global id of column 0 (vocabulary shards); 0 otherwise */
+  int32_t v_global;          /* whole vocabulary size when sharded; 0 means V */
+  /* outputs (device pointers; optional ones may be NULL) */
+  int32_t* token;            /* [B] chosen id, -1 when no token is allowed */
+  int32_t* n_cand;           /* [B] optional: candidates after top-k / banned trimming */
+  int32_t* n_kept;           /* [B] optional: candidates left after min-p / top-p */
+  int32_t* flags;            /* [B] optional: ARCS_FLAG_* */
+  int32_t* cand_id;          /* [B][cand_stride] optional: candidate ids in order */
+  float* cand_val;           /* [B][cand_stride] optional: their adjusted logits */
+  float* cand_pr;            /* [B][cand_stride] optional: their probabilities pr[i]/z */
+  int32_t cand_stride;       /* >= ARCS_KCAP when any cand_* is given */
+  /* scratch */
+  void* workspace;           /* arcs_sample_workspace_bytes() bytes, zeroed once before first use */
+  size_t workspace_bytes;
+  int32_t* status;           /* optional device word: 0 or an arcs_status set by the kernels */
+} arcs_sample_args;
+
+size_t arcs_sample_workspace_bytes(int32_t B, int32_t V, int32_t masked);
+int arcs_sample_batch(const arcs_sample_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * argmax_batch: first maximum of each row (tools/sampler.h:38; zero/runz.cpp:283;
+ * zero/engine_drafters.h:80-81, :632-633), optionally with (max, sum exp(l - max)) per row
+ * (softmax_den, zero/engine_drafters.h:380-389) and, for rows grouped by slot, the greedy
+ * draft acceptance of zero/runz.cpp:699-708 / :361-374: accepted[s] = number of leading
+ * drafts equal to the row argmax, next[s] = argmax of row accepted[s] of the slot.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* logits;
+  int32_t dtype;
+  int32_t R, V;
+  int64_t row_stride;
+  int32_t* argmax;           /* [R] */
+  float* max_sumexp;         /* [R][2] optional */
+  int32_t slots;             /* 0: no verification */
+  const int32_t* row_off;    /* [slots+1] first row of each slot (rows of a slot are contiguous) */
+  const int32_t* draft;      /* draft tokens of all slots */
+  const int32_t* draft_off;  /* [slots+1] */
+  int32_t* accepted;         /* [slots] */
+  int32_t* next;             /* [slots] */
+  void* workspace;           /* arcs_argmax_workspace_bytes(), zeroed once before first use */
+  size_t workspace_bytes;
+  int32_t* status;
+} arcs_argmax_args;
+
+size_t arcs_argmax_workspace_bytes(int32_t R, int32_t V);
+int arcs_argmax_batch(const arcs_argmax_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * dfa_mask: allowed(t) for every token of a vocabulary under a byte automaton, packed.
+ * Replaces the per-candidate predicate calls of tools/server_chat.h:539-557
+ * (piece(t) not empty, not special unless special_ok, check(text + piece) != FAIL) by one
+ * pass over the vocabulary per distinct automaton state: token t is allowed iff its byte
+ * string is not empty and walking it from the state never reaches `dead`.
+ * table: [n_table_states][256] uint16 next state; states: [n_states] start states;
+ * out: [n_states][out_stride] words. vocabulary: byte_off[V+1] offsets into bytes.
+ * ---------------------------------------------------------------------------------------- */
+int arcs_dfa_mask(const uint16_t* table, int32_t n_table_states, int32_t dead, const int32_t* states,
+                  int32_t n_states, const uint32_t* byte_off, const uint8_t* bytes, const uint8_t* special,
+                  int32_t special_ok, int32_t V, uint32_t* out, int64_t out_stride, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

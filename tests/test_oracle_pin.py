@@ -1,0 +1,111 @@
+"""Pins the plain-C oracle to the reference's own code: oracle/_ref/libarcs_ref.so is the
+reference's Sampler compiled from its sources (built where the reference tree is present; it
+travels with the repository's built files). Rows in which two candidates have exactly equal
+logits are counted separately: there the reference's order is whatever its standard library's
+heap code produces, and the oracle uses (value desc, id asc) instead."""
+import numpy as np
+import pytest
+
+import orc
+from cases import rand_logits, rand_mask, rand_params, rand_recent
+
+needs_ref = pytest.mark.skipif(orc.ref is None, reason="oracle/_ref/libarcs_ref.so not built")
+
+
+@needs_ref
+def test_uniform_draw_matches_libstdcxx():
+    g = np.random.default_rng(1)
+    for _ in range(200):
+        seed = int(g.integers(1, 2**63))
+        tot = float(g.random()) + 1e-3
+        a = orc.u_from_seed(seed, 8) * tot
+        b = orc.ref_uniform(seed, tot, 8)
+        assert np.array_equal(a, b)
+
+
+@needs_ref
+def test_adjusted_bit_exact():
+    g = np.random.default_rng(2)
+    for c in range(300):
+        V = int(g.integers(2, 3000))
+        l = rand_logits(g, V, c % 3)
+        p, bias = rand_params(g, V, True)
+        rec = rand_recent(g, V)
+        if c % 5 == 0:  # duplicate bias entries, ids out of range, a ban lifted by nothing
+            bias += [(bias[0][0] if bias else 0, 1.25), (-3, 2.0), (V + 5, -100.0)]
+            rec = np.concatenate([rec, np.array([-1, V, V + 7], np.int32)])
+        assert np.array_equal(orc.adjusted(l, p, rec, bias).view(np.uint32), orc.ref_adjusted(l, p, rec, bias).view(np.uint32))
+
+
+def _run_sample_cases(pen, n_cases, seed):
+    g = np.random.default_rng(seed)
+    bad = ties = n = 0
+    for c in range(n_cases):
+        V = 151936 if c % 40 == 0 else int(g.integers(64, 6064))
+        l = rand_logits(g, V, 0 if pen else c % 3)
+        p, bias = rand_params(g, V, pen)
+        rec = list(rand_recent(g, V))
+        s = int(g.integers(1, 2**62)) | 1
+        want = orc.ref_sample_seq(l, p, np.array(rec, np.int32), s, ndraws=4, append=True, bias=bias)
+        us = orc.u_from_seed(s, 4)
+        draw = 0
+        for d in range(4):
+            r = orc.sample(l, p, np.array(rec, np.int32), us[draw], bias)
+            if p["temperature"][0] > 0:
+                draw += 1
+            n += 1
+            if r["flags"] & 1:
+                ties += 1
+                rec.append(int(want[d]))
+                continue
+            bad += r["token"] != want[d]
+            rec.append(int(want[d]))
+    return n, bad, ties
+
+
+@needs_ref
+@pytest.mark.parametrize("pen", [False, True])
+def test_sample_matches_reference(pen):
+    n, bad, ties = _run_sample_cases(pen, 160, 3 + pen)
+    print(f"sample(): {n} draws, {ties} with tied candidates (not compared), {bad} differ")
+    assert bad == 0
+    assert n - ties > n // 3
+
+
+@needs_ref
+@pytest.mark.parametrize("pen", [False, True])
+def test_sample_allowed_matches_reference(pen):
+    g = np.random.default_rng(7 + pen)
+    bad = badfirst = ties = n = tails = skipped = 0
+    for c in range(200):
+        V = 151936 if c % 50 == 0 else (int(g.integers(1, 600)) if c % 7 == 0 else int(g.integers(64, 20000)))
+        l = rand_logits(g, V, 0 if pen else c % 3)
+        p, bias = rand_params(g, V, pen, allow_k0=True)
+        if p["top_k"][0] == 0 and V < 256:
+            p["top_k"] = 20
+        den = float(g.choice([1.0, 0.5, 0.05, 0.005, 0.001, 0.0]))
+        mask = rand_mask(g, V, den)
+        rec = list(rand_recent(g, V))
+        s = int(g.integers(1, 2**62)) | 1
+        want, calls, first = orc.ref_sample_seq(l, p, np.array(rec, np.int32), s, ndraws=3, append=True, bias=bias, mask=mask)
+        us = orc.u_from_seed(s, 3)
+        draw = 0
+        for d in range(3):
+            r = orc.sample(l, p, np.array(rec, np.int32), us[draw], bias, mask)
+            if p["temperature"][0] > 0 and r["n_cand"] > 1:
+                draw += 1  # the reference draws only when it has at least two candidates
+            n += 1
+            tails += bool(r["flags"] & 8)
+            skipped += bool(r["flags"] & 4)
+            if r["flags"] & (1 | 16):
+                ties += 1
+            else:
+                bad += r["token"] != want[d]
+                if calls[d] > 0:
+                    badfirst += bool(r["flags"] & 2) != bool(first[d])
+            if want[d] >= 0:
+                rec.append(int(want[d]))
+    print(f"sample_allowed(): {n} draws, {ties} tied (not compared), {tails} used the tail, {skipped} skipped it, "
+          f"{bad} tokens differ, {badfirst} first-refused flags differ")
+    assert bad == 0 and badfirst == 0
+    assert tails > 0 and n - ties > n // 3
