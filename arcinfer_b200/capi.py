@@ -225,3 +225,110 @@ def dfa_mask(table, dead, states, byte_off, bytes_, special=None, special_ok=Fal
         "arcs_dfa_mask",
     )
     return out
+
+
+# ---------------------------------------------------------------- host-buffer entry points
+lib.arcs_host_create.restype = C.c_int
+lib.arcs_host_create.argtypes = [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_int64]
+lib.arcs_host_destroy.restype = None
+lib.arcs_host_destroy.argtypes = [C.c_void_p]
+lib.arcs_sample_batch_host.restype = C.c_int
+lib.arcs_sample_batch_host.argtypes = [C.c_void_p, C.POINTER(SampleArgs)]
+lib.arcs_argmax_batch_host.restype = C.c_int
+lib.arcs_argmax_batch_host.argtypes = [C.c_void_p, C.POINTER(ArgmaxArgs)]
+lib.arcs_host_last_status.restype = C.c_int
+lib.arcs_host_last_status.argtypes = [C.c_void_p]
+
+
+def _hp(a):
+    """host pointer of a numpy array or a (pinned) CPU torch tensor"""
+    if a is None:
+        return None
+    if isinstance(a, np.ndarray):
+        assert a.flags["C_CONTIGUOUS"]
+        return a.ctypes.data
+    assert not a.is_cuda and a.is_contiguous()
+    return a.data_ptr()
+
+
+class HostContext:
+    """arcs_host_ctx: the call a host application makes when its logits live in host memory.
+    Inputs and outputs are numpy arrays or CPU torch tensors (pinned memory lets the copies of
+    one chunk of rows overlap the kernel of the previous chunk)."""
+
+    def __init__(self, device, max_B, max_V, bf16, max_hist_total=0, max_bias_total=0, max_mask_words=0):
+        self._h = C.c_void_p()
+        _check(lib.arcs_host_create(C.byref(self._h), device, max_B, max_V, BF16 if bf16 else F32, max_hist_total,
+                                    max_bias_total, max_mask_words), "arcs_host_create")
+        self.bf16 = bf16
+
+    def close(self):
+        if self._h:
+            lib.arcs_host_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        self.close()
+
+    def sample(self, logits, params, u, token, V=None, hist_off=None, hist_ids=None, bias_off=None, bias_ids=None,
+               bias_vals=None, mask=None, mask_row=None, max_hist=0, max_bias=0, n_cand=None, n_kept=None, flags=None,
+               cand_id=None, cand_val=None, cand_pr=None):
+        B = logits.shape[0]
+        a = SampleArgs()
+        a.logits, a.dtype, a.B = _hp(logits), BF16 if self.bf16 else F32, B
+        a.V = logits.shape[1] if V is None else V
+        a.row_stride = logits.shape[1]
+        a.params, a.u, a.token = _hp(params), _hp(u), _hp(token)
+        a.hist_off, a.hist_ids, a.bias_off, a.bias_ids, a.bias_vals = _hp(hist_off), _hp(hist_ids), _hp(bias_off), _hp(bias_ids), _hp(bias_vals)
+        a.mask, a.mask_row = _hp(mask), _hp(mask_row)
+        a.mask_stride = mask.shape[1] if mask is not None else 0
+        a.max_hist, a.max_bias = max_hist, max_bias
+        a.n_cand, a.n_kept, a.flags = _hp(n_cand), _hp(n_kept), _hp(flags)
+        a.cand_id, a.cand_val, a.cand_pr, a.cand_stride = _hp(cand_id), _hp(cand_val), _hp(cand_pr), KCAP
+        _check(lib.arcs_sample_batch_host(self._h, C.byref(a)), "arcs_sample_batch_host")
+
+    def argmax(self, logits, argmax, V=None, max_sumexp=None, row_off=None, draft=None, draft_off=None, accepted=None, next_=None):
+        a = ArgmaxArgs()
+        a.logits, a.dtype, a.R = _hp(logits), BF16 if self.bf16 else F32, logits.shape[0]
+        a.V = logits.shape[1] if V is None else V
+        a.row_stride = logits.shape[1]
+        a.argmax, a.max_sumexp = _hp(argmax), _hp(max_sumexp)
+        a.slots = 0 if row_off is None else len(row_off) - 1
+        a.row_off, a.draft, a.draft_off, a.accepted, a.next = _hp(row_off), _hp(draft), _hp(draft_off), _hp(accepted), _hp(next_)
+        _check(lib.arcs_argmax_batch_host(self._h, C.byref(a)), "arcs_argmax_batch_host")
+
+
+class SamplePlan:
+    """A prepared arcs_sample_batch call: the argument block and the output tensors are built
+    once, launch() only enqueues the kernel (what a serving loop does every step)."""
+
+    def __init__(self, logits, params, u, hist_off=None, hist_ids=None, max_hist=0, mask=None, mask_row=None, V=None,
+                 id_base=0, v_global=0, want_cands=False):
+        dev = logits.device
+        B = logits.shape[0]
+        V = logits.shape[1] if V is None else V
+        self.device = dev
+        self.keep = (logits, params, u, hist_off, hist_ids, mask, mask_row)
+        self.out = {k: torch.empty(B, dtype=torch.int32, device=dev) for k in ("token", "n_cand", "n_kept", "flags")}
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        masked = mask is not None
+        self.ws = _workspace("sample", dev, lib.arcs_sample_workspace_bytes(B, V, int(masked)))
+        a = SampleArgs()
+        a.logits, a.dtype, a.B, a.V, a.row_stride = logits.data_ptr(), _dtype_code(logits), B, V, logits.stride(0)
+        a.params, a.u = params.data_ptr(), u.data_ptr()
+        a.hist_off, a.hist_ids, a.max_hist = _ptr(hist_off), _ptr(hist_ids), max_hist
+        a.mask, a.mask_row, a.mask_stride = _ptr(mask), _ptr(mask_row), (mask.stride(0) if masked else 0)
+        a.id_base, a.v_global = id_base, v_global
+        a.token, a.n_cand, a.n_kept, a.flags = (self.out[k].data_ptr() for k in ("token", "n_cand", "n_kept", "flags"))
+        if want_cands:
+            for k, dt in (("cand_id", torch.int32), ("cand_val", torch.float32), ("cand_pr", torch.float32)):
+                self.out[k] = torch.empty(B, KCAP, dtype=dt, device=dev)
+            a.cand_id, a.cand_val, a.cand_pr = (self.out[k].data_ptr() for k in ("cand_id", "cand_val", "cand_pr"))
+        a.cand_stride = KCAP
+        a.workspace, a.workspace_bytes, a.status = self.ws.data_ptr(), self.ws.numel(), self.status.data_ptr()
+        self.args = a
+
+    def launch(self, stream=None):
+        s = _stream(self.device) if stream is None else stream
+        _check(lib.arcs_sample_batch(C.byref(self.args), s), "arcs_sample_batch")
+        return self.out

@@ -1,0 +1,307 @@
+#!/usr/bin/env python
+"""Benchmark of the token-selection hot path on B200.
+
+Workload (config.workload = "wide-batch"): B=1024 rows x V=262144 bf16 logits ~N(0,3^2), top-k 50,
+top-p .95, repetition penalty 1.1 over each row's whole 512-token history, one uniform draw per
+row: the fused penalty + top-k/top-p sampling pass, one kernel launch per step. Rows are
+independent, so with N GPUs every rank runs its own 1024-row batch (weak scaling, no data-path
+collective) and the value is the rows all ranks sampled per second.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints one JSON line (rank 0). `value` is timed with CUDA events over K launches with the
+inputs resident in HBM (512 MiB of logits per step: larger than L2); `e2e` is the same metric
+through the host-buffer entry point (pinned host logits copied in every step, token ids copied
+back); `roofline` is the kernel's algorithmic bytes over its average launch time against the
+measured copy bandwidth of this pool's B200s; `cpu_baseline` is the reference's own CPU sampler
+(compiled from its sources into oracle/_ref) timed on this box's host cores.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+B_ROWS, VOCAB, HIST = 1024, 262144, 512
+METRIC, UNIT = "sampled_rows_per_sec", "rows/s"
+
+
+def algorithmic_bytes(B, V, H, elt):
+    """bytes one launch must read: every logit once, every history id once"""
+    return B * V * elt + B * H * 4
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+def ncu_traffic(key):
+    """DRAM bytes per launch from the committed ncu summary (profiles/traffic.json), if any"""
+    try:
+        with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+            return json.load(f).get(key)
+    except Exception:
+        return None
+
+
+class ClockSampler:
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                       "-i", str(index)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except Exception:
+            self.p.kill()
+        self.f.flush()
+        self.f.seek(0)
+        sm, mx, reasons = [], [], set()
+        for line in self.f.read().splitlines():
+            c = [x.strip() for x in line.split(",")]
+            if len(c) < 9:
+                continue
+            try:
+                sm.append(float(c[1]))
+                mx.append(float(c[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        self.f.close()
+        os.unlink(self.f.name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_reference_rate(logits_f32, params, hist_off, hist_ids, seeds, threads, min_seconds):
+    """rows/s of the reference's Sampler::sample over the given rows, repeated until min_seconds"""
+    import ctypes as C
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import numpy as np
+
+    import orc
+
+    if orc.ref is None:
+        return None
+    rows = logits_f32.shape[0]
+    out = np.zeros(rows, np.int32)
+    total_t, total_rows = 0.0, 0
+    while total_rows == 0 or total_t < min_seconds:
+        t = orc.ref.ref_sample_batch(params.ctypes.data_as(C.c_void_p), seeds.ctypes.data_as(C.c_void_p),
+                                     logits_f32.ctypes.data_as(C.c_void_p), C.c_int64(rows), logits_f32.shape[1],
+                                     hist_off.ctypes.data_as(C.c_void_p), hist_ids.ctypes.data_as(C.c_void_p), None,
+                                     C.c_int64(0), threads, out.ctypes.data_as(C.c_void_p))
+        total_t += t
+        total_rows += rows
+    return total_rows / total_t, out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--rows", type=int, default=B_ROWS, help="rows per GPU (default: the measured workload)")
+    ap.add_argument("--vocab", type=int, default=VOCAB)
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import numpy as np
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    B, V, H = args.rows, args.vocab, HIST
+    config = {"workload": "wide-batch", "rows_per_gpu": B, "vocab": V, "history": H, "top_k": 50, "top_p": 0.95,
+              "repeat_penalty": 1.1, "logits": "bf16 ~N(0,3^2)", "partition": f"rows x{world}",
+              "l2": "inputs (512 MiB per step) larger than L2"}
+
+    from arcinfer_b200 import synth
+
+    params = synth.make_params(B, top_k=50, top_p=0.95, repeat_penalty=1.1, repeat_last_n=-1)
+
+    if args.impl == "reference":
+        # the reference's own CPU sampler on this box's host cores; rank 0 only
+        if rank != 0:
+            return
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import orc
+
+        if orc.ref is None:
+            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libarcs_ref.so not built (reference tree absent at build time)"}))
+            return
+        threads = int(orc.ref.ref_hardware_threads()) or os.cpu_count() or 1
+        S = max(threads, min(B, 128))  # rows per step: a bounded sample of the 1024-row batch
+        g = synth.rng(synth.BASE_SEED + 5)
+        x = synth.bf16_bits_to_f32(synth.normal_logits(g, S, V, 3.0, bf16=True))
+        hist = g.integers(0, V, (S, H)).astype(np.int32)
+        hoff = (np.arange(S + 1) * H).astype(np.int32)
+        seeds = g.integers(1, 2**62, S).astype(np.uint64)
+        p = params[:1].repeat(S)
+        for _ in range(min(args.warmup, 1)):
+            cpu_reference_rate(x, p, hoff, hist.reshape(-1), seeds, threads, 0.0)
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            cpu_reference_rate(x, p, hoff, hist.reshape(-1), seeds, threads, 0.0)
+        dt = time.perf_counter() - t0
+        val = S * args.steps / dt
+        sample = f"{S} rows of the workload per step (widened to fp32), {threads} threads, one Sampler per row"
+        print(json.dumps({"impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+                          "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
+                          "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
+                          "data": "synthetic", "config": config,
+                          "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "reference", "sample": sample},
+                          "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}))
+        return
+
+    import arcinfer_b200 as ab
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device: there is no CPU fallback"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- synthetic inputs, generated on the device from a per-rank seed
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(synth.BASE_SEED + 5 + 1000 * rank)
+    logits = torch.empty(B, V, dtype=torch.bfloat16, device=dev)
+    for r0 in range(0, B, 128):
+        r1 = min(B, r0 + 128)
+        logits[r0:r1] = (torch.randn(r1 - r0, V, generator=gen, device=dev) * 3.0).to(torch.bfloat16)
+    hist = torch.randint(0, V, (B, H), generator=gen, device=dev, dtype=torch.int32)
+    hist_off = (torch.arange(B + 1, device=dev, dtype=torch.int32) * H).contiguous()
+    u = torch.rand(B, generator=gen, device=dev, dtype=torch.float64)
+    p_dev = ab.capi.params_to_device(params, dev)
+    plan = ab.capi.SamplePlan(logits, p_dev, u, hist_off=hist_off, hist_ids=hist.reshape(-1), max_hist=H)
+
+    for _ in range(args.warmup):
+        plan.launch()
+    barrier()
+    clocks = ClockSampler(local) if rank == 0 else None
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        out = plan.launch()
+    ev1.record()
+    barrier()
+    ms = ev0.elapsed_time(ev1)
+    status = int(plan.status.item())
+    tok = out["token"]
+    assert status == 0, f"device status {status}"
+    assert int(tok.min()) >= 0 and int(tok.max()) < V
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_step = ms / args.steps
+    value = world * B / (ms_step * 1e-3)
+
+    # ---- end to end through the host-buffer entry point: pinned host logits in, token ids out
+    e2e = None
+    if not args.no_e2e:
+        h_logits = torch.empty(B, V, dtype=torch.bfloat16).pin_memory()
+        h_logits.copy_(logits)
+        h_hist = hist.reshape(-1).cpu().pin_memory()
+        h_off = hist_off.cpu().pin_memory()
+        h_u = u.cpu().pin_memory()
+        h_tok = torch.empty(B, dtype=torch.int32).pin_memory()
+        ctx = ab.capi.HostContext(local, B, V, True, max_hist_total=B * H)
+        esteps = max(3, min(args.steps, 10))
+        for _ in range(2):
+            ctx.sample(h_logits, params, h_u, h_tok, hist_off=h_off, hist_ids=h_hist, max_hist=H)
+        same = bool((h_tok.to(dev) == tok).all())
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(esteps):
+            ctx.sample(h_logits, params, h_u, h_tok, hist_off=h_off, hist_ids=h_hist, max_hist=H)
+        barrier()
+        dt = time.perf_counter() - t0
+        if world > 1:
+            t = torch.tensor([dt], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            dt = float(t.item())
+        h2d = B * V * 2 + B * H * 4 + (B + 1) * 4 + B * 8 + B * 32
+        e2e = {"value": world * B * esteps / dt, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": B * 4 + 4,
+               "steps": esteps, "ms_per_step": 1e3 * dt / esteps, "same_tokens_as_device_path": same}
+        ctx.close()
+        del h_logits
+    clk = clocks.stop() if clocks else None
+
+    # ---- the reference's CPU sampler on this box's host cores (rank 0, one GPU only)
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import orc
+
+        if orc.ref is not None:
+            threads = int(orc.ref.ref_hardware_threads()) or os.cpu_count() or 1
+            S = min(B, max(64, threads))
+            x = logits[:S].float().cpu().numpy()
+            hh = hist[:S].cpu().numpy().reshape(-1)
+            hoff = (np.arange(S + 1) * H).astype(np.int32)
+            seeds = np.arange(1, S + 1, dtype=np.uint64)
+            rate_all, _ = cpu_reference_rate(x, params[:S].copy(), hoff, hh, seeds, threads, 8.0)
+            rate_one, _ = cpu_reference_rate(x[:8], params[:8].copy(), hoff[:9], hh[: 8 * H], seeds[:8], 1, 2.0)
+            cpu = {"value": rate_all, "unit": UNIT, "cores": threads, "kind": "reference",
+                   "sample": f"first {S} rows of the batch (widened to fp32), repeated for >= 8 s, {threads} threads",
+                   "single_thread_value": rate_one}
+        else:
+            cpu = {"value": None, "unit": UNIT, "cores": 0, "kind": "reference", "sample": "oracle/_ref not built"}
+
+    if rank == 0:
+        peak, which = measured_peak()
+        abytes = algorithmic_bytes(B, V, H, 2)
+        achieved = abytes / (ms_step * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": config, "gpu_launches": args.steps, "clocks": clk, "e2e": e2e,
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": ncu_traffic("sample_kernel_bf16_wide_batch"), "peak_source": f"of {which}",
+                         "algorithmic_bytes_per_launch": abytes, "frac_of_8TBs_nominal": achieved / 8000.0},
+            "cpu_baseline": cpu,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

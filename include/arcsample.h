@@ -142,6 +142,27 @@ int arcs_dfa_mask(const uint16_t* table, int32_t n_table_states, int32_t dead, c
                   int32_t n_states, const uint32_t* byte_off, const uint8_t* bytes, const uint8_t* special,
                   int32_t special_ok, int32_t V, uint32_t* out, int64_t out_stride, void* stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Host-buffer entry points: what a host application that keeps its logits in host memory
+ * (the reference reads every row back from the GPU, zero/engine.h:255-258, and hands
+ * Sampler::sample a std::vector<float>, tools/server_chat.h:561) calls instead of
+ * Sampler::sample / sample_allowed. All pointers in `host_args` are HOST pointers (pinned
+ * memory makes the copies asynchronous); workspace / status are ignored. The context owns
+ * the device buffers, two streams and the scratch; rows are copied and processed in chunks so
+ * that the host-to-device copy of one chunk overlaps the kernel of the previous one. The call
+ * returns after the results are in the host output arrays. A context is not thread-safe (the
+ * reference's Sampler is not either, tools/sampler.h:204-206).
+ * ---------------------------------------------------------------------------------------- */
+typedef struct arcs_host_ctx arcs_host_ctx;
+int arcs_host_create(arcs_host_ctx** out, int32_t device, int32_t max_B, int32_t max_V, int32_t dtype,
+                     int64_t max_hist_total, int64_t max_bias_total, int64_t max_mask_words);
+void arcs_host_destroy(arcs_host_ctx* ctx);
+int arcs_sample_batch_host(arcs_host_ctx* ctx, const arcs_sample_args* host_args);
+/* greedy selection + acceptance with host buffers (zero/runz.cpp:683-715) */
+int arcs_argmax_batch_host(arcs_host_ctx* ctx, const arcs_argmax_args* host_args);
+/* device status word of the last host call (0 = fine) */
+int arcs_host_last_status(arcs_host_ctx* ctx);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,84 @@
+"""GPU parity: batched first-maximum, (max, sumexp) and greedy draft acceptance through the C ABI
+against the CPU oracle (bit-exact ids and counts)."""
+import numpy as np
+import pytest
+import torch
+
+import orc
+from arcinfer_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(x, bf16, stride=None, offset=0, **kw):
+    import arcinfer_b200 as ab
+    from gpuutil import to_dev_logits
+
+    lg, V = to_dev_logits(x, bf16, stride, offset)
+    out = ab.argmax_batch(lg, V=V, **kw)
+    torch.cuda.synchronize()
+    return {k: v.cpu().numpy() for k, v in out.items()}
+
+
+@pytest.mark.parametrize("bf16", [False, True])
+def test_argmax_edge_sizes(bf16):
+    g = np.random.default_rng(11)
+    for V in [1, 2, 7, 8, 9, 31, 32, 33, 127, 128, 129, 1000, 2047, 2048, 2049, 4097, 8191, 8192, 8193, 20000, 40961]:
+        for R in [1, 2, 3]:
+            for mode in range(3):
+                if mode == 0:
+                    x = (g.standard_normal((R, V), dtype=np.float32) * 3).astype(np.float32)
+                elif mode == 1:  # few levels: many exact ties, the lowest id must win
+                    x = (0.5 * g.integers(0, 8, (R, V))).astype(np.float32)
+                else:
+                    x = np.full((R, V), -np.inf, np.float32)
+                    x[:, V // 2 :] = -3.0
+                xb = synth.f32_to_bf16_bits(x) if bf16 else x
+                xf = synth.bf16_bits_to_f32(xb) if bf16 else x
+                want = np.array([orc.argmax(xf[r]) for r in range(R)], np.int32)
+                for stride, off in [(None, 0), (V + 3, 1)]:
+                    got = _run(xb, bf16, stride, off)
+                    assert got["status"][0] == 0
+                    assert np.array_equal(got["argmax"], want), (V, R, mode, stride)
+
+
+def test_spec_verify_config3():
+    c = synth.config3()
+    xf = synth.bf16_bits_to_f32(c["logits"])
+    sel = np.array([orc.argmax(r) for r in xf], np.int32)
+    acc, nxt = orc.verify_greedy(sel, c["row_off"], c["draft"], c["draft_off"])
+    for rep in range(3):  # the scratch must come back clean for the next call
+        got = _run(c["logits"], True, row_off=torch.from_numpy(c["row_off"]).cuda(), draft=torch.from_numpy(c["draft"]).cuda(),
+                   draft_off=torch.from_numpy(c["draft_off"]).cuda(), want_lse=True)
+        assert got["status"][0] == 0
+        assert np.array_equal(got["argmax"], sel)
+        assert np.array_equal(got["accepted"], acc) and np.array_equal(got["next"], nxt)
+    assert 0 < acc.sum() < 7 * 8
+    for r in range(0, 64, 7):
+        mx = xf[r].max()
+        assert got["max_sumexp"][r, 0] == mx
+        z = orc.softmax_den(xf[r], mx, exact=True)
+        assert abs(got["max_sumexp"][r, 1] - z) <= 1e-6 * z
+        assert abs(got["max_sumexp"][r, 1] - orc.softmax_den(xf[r], mx)) <= 5e-6 * z  # the reference's float blocks
+
+
+def test_verify_ragged_slots():
+    g = np.random.default_rng(5)
+    V = 5000
+    rows = [1, 3, 8, 2]
+    R = sum(rows)
+    x = (g.standard_normal((R, V), dtype=np.float32) * 2).astype(np.float32)
+    sel = x.argmax(axis=1).astype(np.int32)
+    row_off = np.concatenate([[0], np.cumsum(rows)]).astype(np.int32)
+    drafts = []
+    for s, n in enumerate(rows):
+        d = sel[row_off[s] : row_off[s] + n - 1].copy()
+        if s == 2:
+            d[4] = (d[4] + 1) % V
+        drafts.append(d)
+    draft_off, draft = synth.csr(drafts)
+    acc, nxt = orc.verify_greedy(sel, row_off, draft, draft_off)
+    got = _run(x, False, row_off=torch.from_numpy(row_off).cuda(), draft=torch.from_numpy(draft if len(draft) else np.zeros(1, np.int32)).cuda(),
+               draft_off=torch.from_numpy(draft_off).cuda())
+    assert np.array_equal(got["accepted"], acc) and np.array_equal(got["next"], nxt)
+    assert list(acc) == [0, 2, 4, 1]
