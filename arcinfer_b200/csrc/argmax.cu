@@ -43,7 +43,7 @@ __device__ __forceinline__ void lse_merge(float& m, float& s, float m2, float s2
 
 template <typename T, bool LSE>
 __global__ void __launch_bounds__(kThreads) argmax_kernel(const ArgmaxDev a) {
-  __shared__ __align__(128) char stage[kStages * kTileBytes];
+  extern __shared__ __align__(128) char stage[];  // kStages * kTileBytes
   __shared__ __align__(8) uint64_t bars[kStages];
   __shared__ unsigned long long red_c[kThreads / 32];
   __shared__ float red_m[kThreads / 32], red_s[kThreads / 32];
@@ -80,10 +80,14 @@ __global__ void __launch_bounds__(kThreads) argmax_kernel(const ArgmaxDev a) {
     const int slot = t % kStages;
     if (!mbar_wait(&bars[slot], (uint32_t)((t / kStages) & 1))) failed = true;
     const uint32_t nbytes = tile_bytes(p, t);
-    const bool have = (uint32_t)tid * 16u < nbytes;
-    uint4 q = make_uint4(0, 0, 0, 0);
-    if (have && !failed) q = lds128(stage + (size_t)slot * kTileBytes + tid * 16);
-    // every thread has taken its chunk: the slot can be refilled
+    constexpr int kChunks = kTileBytes / 16 / kThreads;
+    uint4 q[kChunks];
+#pragma unroll
+    for (int j = 0; j < kChunks; ++j) {
+      const uint32_t off = (uint32_t)(j * kThreads + tid) * 16u;
+      q[j] = off < nbytes && !failed ? lds128(stage + (size_t)slot * kTileBytes + off) : make_uint4(0, 0, 0, 0);
+    }
+    // every thread has taken its chunks: the slot can be refilled
     if (__syncthreads_or(failed)) {
       if (tid == 0) {
         raise_status(a.status, ARCS_ERR_TIMEOUT);
@@ -93,21 +97,24 @@ __global__ void __launch_bounds__(kThreads) argmax_kernel(const ArgmaxDev a) {
       return;
     }
     if (tid == 0 && t + kStages < p.tiles) issue_tile(p, t + kStages, stage, bars);
-    if (have) {
-      const float m = Elem<T>::chunk_max(q);
-      if (m > bv || bi < 0) {
-        const int32_t id0 = p.body_first + (t * kTileBytes + tid * 16) / (int)sizeof(T);
 #pragma unroll
-        for (int j = 0; j < E; ++j) {
-          const float v = Elem<T>::get(q, j);
-          if (v > bv || (bi < 0 && v == v)) { bv = v; bi = id0 + j; }
+    for (int j = 0; j < kChunks; ++j) {  // a thread's chunks come in increasing id order
+      const uint32_t off = (uint32_t)(j * kThreads + tid) * 16u;
+      if (off >= nbytes) continue;
+      const float m = Elem<T>::chunk_max(q[j]);
+      if (m > bv || bi < 0) {
+        const int32_t id0 = p.body_first + (int32_t)(((uint32_t)t * kTileBytes + off) / sizeof(T));
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+          const float v = Elem<T>::get(q[j], e);
+          if (v > bv || (bi < 0 && v == v)) { bv = v; bi = id0 + e; }
         }
       }
       if (LSE) {
         if (m > lm) { ls *= expf(lm - m); lm = m; }
 #pragma unroll
-        for (int j = 0; j < E; ++j) {
-          const float v = Elem<T>::get(q, j);
+        for (int e = 0; e < E; ++e) {
+          const float v = Elem<T>::get(q[j], e);
           if (v == v && lm > -INFINITY) ls += expf(v - lm);
         }
       }
@@ -220,12 +227,20 @@ extern "C" int arcs_argmax_batch(const arcs_argmax_args* g, void* stream) {
   const dim3 grid((unsigned)a.nseg * (unsigned)a.R);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const bool lse = g->max_sumexp != nullptr;
+  constexpr int smem = kStages * kTileBytes;
+#define ARCS_LAUNCH(T, L)                                                                                  \
+  do {                                                                                                     \
+    cudaError_t e = cudaFuncSetAttribute(argmax_kernel<T, L>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+    if (e != cudaSuccess) return set_error(ARCS_ERR_CUDA, cudaGetErrorString(e));                          \
+    argmax_kernel<T, L><<<grid, kThreads, smem, st>>>(a);                                                  \
+  } while (0)
   if (g->dtype == ARCS_F32) {
-    if (lse) argmax_kernel<float, true><<<grid, kThreads, 0, st>>>(a);
-    else argmax_kernel<float, false><<<grid, kThreads, 0, st>>>(a);
+    if (lse) ARCS_LAUNCH(float, true);
+    else ARCS_LAUNCH(float, false);
   } else {
-    if (lse) argmax_kernel<__nv_bfloat16, true><<<grid, kThreads, 0, st>>>(a);
-    else argmax_kernel<__nv_bfloat16, false><<<grid, kThreads, 0, st>>>(a);
+    if (lse) ARCS_LAUNCH(__nv_bfloat16, true);
+    else ARCS_LAUNCH(__nv_bfloat16, false);
   }
+#undef ARCS_LAUNCH
   return check_launch("argmax_batch");
 }

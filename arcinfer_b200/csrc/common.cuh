@@ -9,8 +9,8 @@
 namespace arcs {
 
 constexpr int kThreads = 256;          // threads per CTA of the streaming kernels
-constexpr int kTileBytes = 4096;       // one 16-byte chunk per thread per tile
-constexpr int kStages = 8;             // tiles in flight per CTA (bulk-copy ring)
+constexpr int kTileBytes = 16384;      // four 16-byte chunks per thread per tile
+constexpr int kStages = 3;             // tiles in the bulk-copy ring of a CTA
 constexpr uint32_t kWaitLimit = 1u << 22;  // bounded mbarrier wait (tries)
 
 // ---------------------------------------------------------------- order-preserving keys
@@ -37,6 +37,7 @@ template <typename T> struct Elem;
 template <> struct Elem<float> {
   static constexpr int kPerChunk = 4;
   static __device__ __forceinline__ float load(const float* p) { return __ldg(p); }
+  static __device__ __forceinline__ float from_smem(const char* p) { return *reinterpret_cast<const float*>(p); }
   // value j of a 16-byte chunk
   static __device__ __forceinline__ float get(const uint4& q, int j) {
     return __uint_as_float(j == 0 ? q.x : j == 1 ? q.y : j == 2 ? q.z : q.w);
@@ -50,6 +51,9 @@ template <> struct Elem<__nv_bfloat16> {
   static constexpr int kPerChunk = 8;
   static __device__ __forceinline__ float load(const __nv_bfloat16* p) {
     return __uint_as_float((uint32_t)__ldg(reinterpret_cast<const unsigned short*>(p)) << 16);
+  }
+  static __device__ __forceinline__ float from_smem(const char* p) {
+    return __uint_as_float((uint32_t)*reinterpret_cast<const unsigned short*>(p) << 16);
   }
   static __device__ __forceinline__ float get(const uint4& q, int j) {
     const uint32_t w = (j >> 1) == 0 ? q.x : (j >> 1) == 1 ? q.y : (j >> 1) == 2 ? q.z : q.w;

@@ -11,8 +11,9 @@
 
 namespace arcs {
 
-constexpr int kCapB = 2560;   // candidate buffer: prune trigger (<= 512) + one tile of bf16 elements
-constexpr int kCapA = 3072;   // constrained head select (k = 512, trigger 1024)
+constexpr int kChunks = kTileBytes / 16 / kThreads;  // 16-byte chunks per thread per tile
+constexpr int kCapB = 1024;   // candidate buffer: prune trigger (<= 512) + one round of pushes (<= 256); holds a tile's chunk maxima
+constexpr int kCapA = 1280;   // constrained head select (k = 512, trigger 1024)
 constexpr uint32_t kEmpty = 0xFFFFFFFFu;
 // per touched token: occurrences in the history (low 20 bits) and what applies to it
 constexpr uint32_t kInfoCount = 0xFFFFFu, kInfoWindow = 1u << 31, kInfoBias = 1u << 30, kInfoBan = 1u << 29;
@@ -72,6 +73,7 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const SampleDev a) {
   int32_t* aid = reinterpret_cast<int32_t*>(akey + (MASKED ? kCapA : 0));
   uint32_t* hkey = reinterpret_cast<uint32_t*>(aid + (MASKED ? kCapA : 0));  // [hash_slots] token ids
   uint32_t* hinfo = hkey + a.hash_slots;                                      // [hash_slots]
+  uint16_t* hotl = reinterpret_cast<uint16_t*>(hinfo + a.hash_slots);         // [kTileBytes / 16] chunks to examine
   // after streaming, the tile ring is reused for the sorted candidates
   float* sv = reinterpret_cast<float*>(stage);
   int32_t* sid = reinterpret_cast<int32_t*>(sv + ARCS_KCAP);
@@ -79,7 +81,7 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const SampleDev a) {
   unsigned long long* s64 = reinterpret_cast<unsigned long long*>(spr + ARCS_KCAP);  // [2]
 
   // sh[] indices
-  enum { S_CNT_B = 0, S_TAU_B, S_CNT_A, S_TAU_A, S_LAST, S_FLAGS, S_NCAND, S_NKEPT, S_TOKEN, S_PICK };
+  enum { S_CNT_B = 0, S_TAU_B, S_CNT_A, S_TAU_A, S_LAST, S_FLAGS, S_NCAND, S_NKEPT, S_TOKEN, S_PICK, S_HOT0, S_HOT1 };
 
   constexpr int E = Elem<T>::kPerChunk;
   const int tid = threadIdx.x, seg = blockIdx.x % a.nseg, b = blockIdx.x / a.nseg;
@@ -120,6 +122,9 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const SampleDev a) {
     sh[S_TAU_A] = 0;
     sh[S_LAST] = 0;
     sh[S_FLAGS] = 0;
+    sh[S_PICK] = 0;
+    sh[S_HOT0] = 0;
+    sh[S_HOT1] = 0;
     if (k_bad) raise_status(a.status, ARCS_ERR_TOPK);
     if (!lists_ok) raise_status(a.status, ARCS_ERR_LIST);
   }
@@ -203,50 +208,118 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const SampleDev a) {
     if (pa) sel_prune(selA, selA.k, ps);
   };
 
-  // ---- head elements (before the first 16-byte boundary)
-  {
-    const bool valid = tid < p.head_n;
-    const float v = valid ? Elem<T>::load(row + lo + tid) : 0.0f;
-    consider(valid, v, lo + tid, 0u, 0u, false);
-  }
-
-  // ---- the stream
+  // ---- the stream. Per tile: (A) every thread looks at its 16-byte chunks and lists the few
+  // whose maximum reaches the current threshold; (B) the listed chunks are examined one
+  // element per thread. Nearly all chunks fail (A), which costs a handful of instructions.
   bool failed = false;
   for (int t = 0; t < p.tiles; ++t) {
     const int slot = t % kStages;
+    const char* tile = stage + (size_t)slot * kTileBytes;
     if (!mbar_wait(&bars[slot], (uint32_t)((t / kStages) & 1))) failed = true;
-    const uint32_t nbytes = tile_bytes(p, t);
-    const bool have = (uint32_t)tid * 16u < nbytes && !failed;
-    uint4 q = make_uint4(0, 0, 0, 0);
-    if (have) q = lds128(stage + (size_t)slot * kTileBytes + tid * 16);
-    // One barrier per tile: every thread holds its chunk in registers (the slot can be
-    // refilled) and the pushes of the previous tile are complete (the buffer can be pruned).
-    const int any = __syncthreads_or((hot ? 1 : 0) | (failed ? 2 : 0));
-    if (any) {
-      if (__syncthreads_or(failed)) {
+    const int nchunk = (int)(tile_bytes(p, t) / 16u);
+    if (t == 0) {
+      // Bootstrap of the threshold: the k-th largest chunk maximum is a lower bound of the
+      // k-th largest element. Tokens of this tile that the table replaces may own a chunk
+      // maximum without counting as candidates, so that many extra maxima are skipped.
+      Sel& s0 = MASKED ? selA : selB;
+      if (touched_on) {
+        int extra = 0;
+        const int32_t c_lo = p.body_first, c_hi = p.body_first + nchunk * E;
+        for (int i = tid; i < a.hash_slots; i += kThreads) {
+          const uint32_t ck = hkey[i];
+          extra += ck != kEmpty && (int32_t)ck >= c_lo && (int32_t)ck < c_hi;
+        }
+        if (extra) atomicAdd(&sh[S_PICK], extra);
+      }
+      const int fail0 = __syncthreads_or(failed);
+      const int kth = s0.k + sh[S_PICK];
+      if (!fail0 && kth <= nchunk && nchunk <= s0.cap) {
+#pragma unroll
+        for (int j = 0; j < kChunks; ++j) {
+          const int ci = j * kThreads + tid;
+          if (ci < nchunk) {
+            s0.key[ci] = key_of(Elem<T>::chunk_max(lds128(tile + ci * 16)));
+            s0.id[ci] = ci;
+          }
+        }
+        if (tid == 0) *s0.cnt = nchunk;
+        __syncthreads();
+        sel_prune(s0, kth, ps);
         if (tid == 0) {
-          raise_status(a.status, ARCS_ERR_TIMEOUT);
-          drain_tiles(p, t, bars);
+          const uint32_t tk0 = *s0.tau_key;  // 1 + smallest kept maximum (0: nothing was dropped)
+          *s0.tau_key = tk0 > 0u && tk0 != 0xFFFFFFFFu ? tk0 - 1u : tk0;
+          *s0.cnt = 0;
         }
         __syncthreads();
-        return;
       }
     }
+    const uint32_t tauB = *selB.tau_key, tauA = MASKED ? *selA.tau_key : 0xFFFFFFFFu;
+    const uint32_t tmin = min(tauB, tauA);
+    const float tf = value_of(tmin < 0x007FFFFFu ? 0x007FFFFFu : tmin);  // -inf while nothing has been dropped
+    int* hot_n = &sh[S_HOT0 + (t & 1)];
+    // (A)
+#pragma unroll
+    for (int j = 0; j < kChunks; ++j) {
+      const int ci = j * kThreads + tid;
+      bool h = false;
+      if (ci < nchunk && !failed) h = Elem<T>::chunk_max(lds128(tile + ci * 16)) >= tf;
+      const unsigned bal = __ballot_sync(0xFFFFFFFFu, h);
+      if (bal) {
+        const int lane = tid & 31, leader = __ffs(bal) - 1;
+        int base = 0;
+        if (lane == leader) base = atomicAdd(hot_n, __popc(bal));
+        base = __shfl_sync(0xFFFFFFFFu, base, leader);
+        if (h) hotl[base + __popc(bal & ((1u << lane) - 1u))] = (uint16_t)ci;
+      }
+    }
+    if (__syncthreads_or(failed)) {
+      if (tid == 0) {
+        raise_status(a.status, ARCS_ERR_TIMEOUT);
+        drain_tiles(p, t, bars);
+      }
+      __syncthreads();
+      return;
+    }
+    // (B)
+    const int nhot = *hot_n;
+    if (tid == 0) sh[S_HOT0 + ((t + 1) & 1)] = 0;
+    const int32_t col0 = p.body_first + t * (kTileBytes / (int)sizeof(T));
+    uint32_t tb = tauB, ta = tauA;
+    for (int r0 = 0; r0 < nhot; r0 += kThreads / E) {
+      const int qi = r0 + tid / E, e = tid % E;
+      const bool valid = qi < nhot;
+      float v = 0.0f;
+      int32_t c = 0;
+      if (valid) {
+        const int ci = hotl[qi];
+        v = Elem<T>::from_smem(tile + ci * 16 + e * (int)sizeof(T));
+        c = col0 + ci * E + e;
+      }
+      consider(valid, v, c, tb, ta, false);
+      if (r0 + kThreads / E < nhot) {  // more rounds: keep the buffer below its capacity
+        if (__syncthreads_or(hot)) {
+          maybe_prune();
+          hot = false;
+          // the entries kept may now come from this tile, and the chunks still listed are in no
+          // particular order: a tie with the smallest kept key can still win on its id
+          tb = *selB.tau_key;
+          tb = tb ? tb - 1u : 0u;
+          ta = MASKED ? *selA.tau_key : 0xFFFFFFFFu;
+          ta = MASKED && ta ? ta - 1u : ta;
+        }
+      }
+    }
+    // every thread is done with the tile: refill the slot, prune if the buffer has grown
+    const int any = __syncthreads_or(hot);
     if (tid == 0 && t + kStages < p.tiles) issue_tile(p, t + kStages, stage, bars);
     if (any) {
       maybe_prune();
       hot = false;
     }
-    const uint32_t tauB = *selB.tau_key, tauA = MASKED ? *selA.tau_key : 0xFFFFFFFFu;
-    const float tf = value_of(min(tauB, tauA) < 0x007FFFFFu ? 0x007FFFFFu : min(tauB, tauA));  // -inf when nothing dropped yet
-    const bool enter = have && Elem<T>::chunk_max(q) >= tf;
-    if (__any_sync(0xFFFFFFFFu, enter)) {
-      const int32_t c0 = p.body_first + (t * kTileBytes + tid * 16) / (int)sizeof(T);
-#pragma unroll
-      for (int j = 0; j < E; ++j) consider(enter, Elem<T>::get(q, j), c0 + j, tauB, tauA, false);
-    }
   }
-  // ---- tail elements (after the last 16-byte boundary)
+  // ---- the scalar elements after the last and before the first 16-byte boundary. The tail
+  // follows the stream in id order; the head has the lowest ids of the segment, so there a tie
+  // with the smallest kept key must still be taken.
   {
     __syncthreads();
     maybe_prune();
@@ -254,6 +327,13 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const SampleDev a) {
     const bool valid = tid < p.tail_n;
     const float v = valid ? Elem<T>::load(row + p.tail_first + tid) : 0.0f;
     consider(valid, v, p.tail_first + tid, *selB.tau_key, MASKED ? *selA.tau_key : 0u, false);
+    __syncthreads();
+    maybe_prune();
+    hot = false;
+    const bool hvalid = tid < p.head_n;
+    const float hv = hvalid ? Elem<T>::load(row + lo + tid) : 0.0f;
+    const uint32_t tb = *selB.tau_key, ta = MASKED ? *selA.tau_key : 0u;
+    consider(hvalid, hv, lo + tid, tb ? tb - 1u : 0u, ta ? ta - 1u : 0u, false);
   }
 
   // ---- touched tokens: exact fp32 arithmetic of Sampler::adjusted, one token per thread
@@ -475,6 +555,7 @@ static size_t sample_smem_bytes(bool masked, int hash_slots) {
   n += (size_t)kCapB * 8;
   if (masked) n += (size_t)kCapA * 8;
   n += (size_t)hash_slots * 8;
+  n += (size_t)(kTileBytes / 16) * 2;
   return n + 128;
 }
 

@@ -53,7 +53,7 @@ def run_gpu_sample(x, bf16, params, hists, us, biases=None, masks=None, mask_row
     return {k: v.cpu().numpy() for k, v in out.items()}
 
 
-def check_rows(out, x, bf16, params, hists, us, biases=None, masks=None, mask_row=None, rows=None, pr_rtol=1e-6):
+def check_rows(out, x, bf16, params, hists, us, biases=None, masks=None, mask_row=None, rows=None, pr_rtol=1e-6, tag=""):
     """Bit-exact ids / counts / adjusted logits, probabilities within pr_rtol relative."""
     B = x.shape[0]
     assert int(out["status"][0]) == 0
@@ -62,7 +62,7 @@ def check_rows(out, x, bf16, params, hists, us, biases=None, masks=None, mask_ro
         m = None if masks is None else masks[b if mask_row is None else mask_row[b]]
         r = orc.sample(xf[b], params[b : b + 1], hists[b] if hists is not None else np.zeros(0, np.int32), float(us[b]),
                        biases[b] if biases is not None else None, m)
-        ctx = f"row {b} params {params[b]}"
+        ctx = f"{tag} V={x.shape[1]} row {b} params {params[b]} got token {out['token'][b]} want {r['token']} n_cand {out['n_cand'][b]}/{r['n_cand']}"
         assert out["token"][b] == r["token"], ctx
         assert out["n_cand"][b] == r["n_cand"], ctx
         assert out["n_kept"][b] == r["n_kept"], ctx

@@ -39,7 +39,7 @@ def test_sample_random_battery(bf16, pen):
         xb = synth.f32_to_bf16_bits(x) if bf16 else x
         for stride, off in [(None, 0), (V + 5, 3)]:
             out = run_gpu_sample(xb, bf16, params, hists, us, biases, stride=stride, offset=off)
-            check_rows(out, xb, bf16, params, hists, us, biases)
+            check_rows(out, xb, bf16, params, hists, us, biases, tag=f"stride={stride} off={off}")
 
 
 @pytest.mark.parametrize("bf16", [False, True])
