@@ -1,19 +1,39 @@
 // sample_batch: penalties + temperature / top-k / top-p / min-p (+ allowed-token mask) in one
-// pass over the logits. One CTA streams one segment of one row through a ring of bulk-copied
-// shared-memory tiles, keeps the exact k best (value desc, id asc) in a shared-memory buffer
-// with a rising threshold, handles the few tokens touched by penalties / bias separately from
-// their exact fp32 arithmetic, and finishes the row (softmax over the candidates in fp64, the
-// cuts and the draw) without another launch. Rows cut into several segments are merged by the
-// CTA that finishes the row last.
+// pass over the logits.
+//
+// One persistent CTA per SM walks a list of work items (a row, or a segment of a row when
+// there are few rows). Its warps have fixed roles and never meet at a CTA-wide barrier:
+//   producer   one thread keeps a ring of 16 KB tiles filled with 1-D bulk copies (TMA);
+//   scanners   16 warps take every tile from the ring; a 16-byte chunk whose maximum is
+//              below the item's current threshold costs a handful of instructions, the few
+//              other chunks are tested element by element and the survivors queued;
+//   examiner   one warp owns the candidate buffers: it applies the exact rules to the queued
+//              elements (penalised tokens are skipped here), keeps the k best under (value
+//              desc, id asc) by radix select and raises the threshold the scanners read;
+//   finishers  256 threads prepare the next item (table of penalised / biased tokens, first
+//              threshold) and finish the previous one (exact fp32 penalty arithmetic for the
+//              few touched tokens, final order, fp64 softmax, cuts, draw) while the ring keeps
+//              streaming the current one.
+// Items alternate between two sets of per-item state (parity), so HBM is read without pause.
 #include "plan.h"
 #include "select.cuh"
 #include "stream.cuh"
 
 namespace arcs {
 
-constexpr int kChunks = kTileBytes / 16 / kThreads;  // 16-byte chunks per thread per tile
-constexpr int kCapB = 1024;   // candidate buffer: prune trigger (<= 512) + one round of pushes (<= 256); holds a tile's chunk maxima
+constexpr int kScanW = 16;                                 // scanner warps
+constexpr int kExamWarp = kScanW;                          // examiner warp
+constexpr int kProdWarp = kScanW + 1;                      // producer warp (lane 0 works)
+constexpr int kFinWarp0 = kScanW + 2;                      // first finisher warp
+constexpr int kThreadsP = (kFinWarp0 + kGroup / 32) * 32;  // 832 threads
+constexpr int kRing = kScanW;                              // tiles in the ring: scanner w owns slot w
+constexpr int kSTile = 8192;                               // bytes per tile (512 chunks: 16 per lane)
+constexpr int kQueue = 1024;                               // queued elements between scanners and examiner
+constexpr uint32_t kIdMask = 0x3FFFFFFFu;                  // queue entry word y: id | eligible-for-B << 30 | parity << 31
+constexpr uint32_t kMarker = kIdMask;                      // id field of a scanner's end-of-item entry
+constexpr int kCapB = 1024;   // candidate buffer: prune trigger (<= 512) + one round of pushes (<= 256)
 constexpr int kCapA = 1280;   // constrained head select (k = 512, trigger 1024)
+constexpr int kBootBytes = 8192;  // prefix of an item read ahead to seed its threshold
 constexpr uint32_t kEmpty = 0xFFFFFFFFu;
 // per touched token: occurrences in the history (low 20 bits) and what applies to it
 constexpr uint32_t kInfoCount = 0xFFFFFu, kInfoWindow = 1u << 31, kInfoBias = 1u << 30, kInfoBan = 1u << 29;
@@ -54,514 +74,1025 @@ __host__ __device__ inline int32_t seg_block_bytes(bool masked) {
   return 16 + ARCS_KCAP * 8 + (masked ? ARCS_HEAD * 8 : 0);
 }
 
+// Optional role timing (build with -DARCS_ROLE_TIMING): cycles each role of CTA 0 spends in its
+// phases, accumulated in registers and added to g_role[] once at the end.
+#ifdef ARCS_ROLE_TIMING
+__device__ unsigned long long g_role[32];
+#define RT_DECL long long rt_last = clock64(); unsigned long long rt0 = 0, rt1 = 0, rt2 = 0, rt3 = 0
+#define RT(i) do { const long long n_ = clock64(); const unsigned long long d_ = (unsigned long long)(n_ - rt_last); rt_last = n_; if (i == 0) rt0 += d_; else if (i == 1) rt1 += d_; else if (i == 2) rt2 += d_; else rt3 += d_; } while (0)
+#define RT_FLUSH(base, cond) do { if (blockIdx.x == 0 && (cond)) { atomicAdd(&g_role[base], rt0); atomicAdd(&g_role[base + 1], rt1); atomicAdd(&g_role[base + 2], rt2); atomicAdd(&g_role[base + 3], rt3); } } while (0)
+#else
+#define RT_DECL
+#define RT(i)
+#define RT_FLUSH(base, cond)
+#endif
+
 __device__ __forceinline__ uint32_t hash_of(int32_t id, int shift) { return ((uint32_t)id * 2654435761u) >> shift; }
 
-template <typename T, bool MASKED>
-__global__ void __launch_bounds__(kThreads) sample_kernel(const SampleDev a) {
-  extern __shared__ __align__(128) char smem[];
-  // ---- carve shared memory
-  char* stage = smem;                                                  // kStages * kTileBytes
-  uint64_t* bars = reinterpret_cast<uint64_t*>(stage + kStages * kTileBytes);
-  uint32_t* hist = reinterpret_cast<uint32_t*>(bars + kStages);        // [2][256]
-  uint32_t* tk = hist + 512;
-  int32_t* ti = reinterpret_cast<int32_t*>(tk + kTmpCap);
-  int* misc = reinterpret_cast<int*>(ti + kTmpCap);                    // [8] prune scratch
-  int* sh = misc + 8;                                                  // [24] kernel scalars
-  uint32_t* bkey = reinterpret_cast<uint32_t*>(sh + 24);
-  int32_t* bid = reinterpret_cast<int32_t*>(bkey + kCapB);
-  uint32_t* akey = reinterpret_cast<uint32_t*>(bid + kCapB);
-  int32_t* aid = reinterpret_cast<int32_t*>(akey + (MASKED ? kCapA : 0));
-  uint32_t* hkey = reinterpret_cast<uint32_t*>(aid + (MASKED ? kCapA : 0));  // [hash_slots] token ids
-  uint32_t* hinfo = hkey + a.hash_slots;                                      // [hash_slots]
-  uint16_t* hotl = reinterpret_cast<uint16_t*>(hinfo + a.hash_slots);         // [kTileBytes / 16] chunks to examine
-  // after streaming, the tile ring is reused for the sorted candidates
-  float* sv = reinterpret_cast<float*>(stage);
-  int32_t* sid = reinterpret_cast<int32_t*>(sv + ARCS_KCAP);
-  double* spr = reinterpret_cast<double*>(sid + ARCS_KCAP);
-  unsigned long long* s64 = reinterpret_cast<unsigned long long*>(spr + ARCS_KCAP);  // [2]
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
 
-  // sh[] indices
-  enum { S_CNT_B = 0, S_TAU_B, S_CNT_A, S_TAU_A, S_LAST, S_FLAGS, S_NCAND, S_NKEPT, S_TOKEN, S_PICK, S_HOT0, S_HOT1 };
+// what every role derives from an item number
+template <typename T>
+struct Item {
+  int32_t b, seg, lo, hi;
+  const T* row;
+  SegPlan p;
+};
+template <typename T>
+__device__ __forceinline__ Item<T> item_of(const SampleDev& a, int item) {
+  Item<T> it;
+  it.b = item / a.nseg;
+  it.seg = item % a.nseg;
+  it.row = reinterpret_cast<const T*>(a.logits) + (size_t)it.b * a.row_stride;
+  it.lo = it.seg * a.seg_len;
+  it.hi = min(a.V, it.lo + a.seg_len);
+  it.p = make_plan(it.row, it.lo, it.hi);
+  return it;
+}
+
+__device__ __forceinline__ int s_tiles(const SegPlan& p) { return (p.body_bytes + kSTile - 1) / kSTile; }
+__device__ __forceinline__ uint32_t s_tile_bytes(const SegPlan& p, int t) {
+  const int32_t rem = p.body_bytes - t * kSTile;
+  return (uint32_t)(rem < kSTile ? rem : kSTile);
+}
+
+// element `el` of the 16-byte chunk held as four words
+template <typename T>
+__device__ __forceinline__ float elem_of_words(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, int el);
+template <>
+__device__ __forceinline__ float elem_of_words<float>(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, int el) {
+  return __uint_as_float(el == 0 ? w0 : el == 1 ? w1 : el == 2 ? w2 : w3);
+}
+template <>
+__device__ __forceinline__ float elem_of_words<__nv_bfloat16>(uint32_t w0, uint32_t w1, uint32_t w2, uint32_t w3, int el) {
+  const uint32_t w = (el >> 1) == 0 ? w0 : (el >> 1) == 1 ? w1 : (el >> 1) == 2 ? w2 : w3;
+  return __uint_as_float((el & 1) ? (w & 0xFFFF0000u) : (w << 16));
+}
+
+// indices into the shared scalar arrays
+enum { S_ABORT = 0, S_QTAIL, S_QHEAD, S_PREPARED, S_STREAMED, S_LAST, S_FLAGS, S_NCAND, S_PICK,
+       S_CNT_B /* [2] */ = 10, S_CNT_A = 12, S_K = 14, S_TRIG = 16, S_TOUCHED = 18, S_BANS = 20, S_BASE_B = 22, S_BASE_A = 24,
+       S_END = 28 };
+enum { L_TAU_B = 0 /* [2] */, L_TAU_A = 2, L_PRUNE_MIN = 4, L_TOP, L_LOW, L_MROW /* [2] */ = 8, L_END = 12 };
+
+// ---- the scanners' rare path, kept out of line so that the streaming loop stays small
+struct ScanCtx {
+  const uint32_t* hk;      // the item's table of replaced tokens (columns)
+  int32_t hash_slots, hash_shift;
+  int32_t touched, bans, par;
+  const uint32_t* mrow;
+  uint32_t* histB;         // coarse histograms of the item
+  uint32_t* histA;
+  uint32_t baseB, baseA;
+  int* sh;                 // shared scalars (queue head / tail, abort flag)
+  uint2* q_ent;
+  uint32_t* q_seq;
+  int32_t* status;
+  int32_t col0, id_base;   // global id of the tile's first element
+  uint64_t tcB, tcA;       // thresholds the chunk was listed against
+};
+
+__device__ __forceinline__ bool table_has(const uint32_t* hk, int32_t slots, int32_t shift, int32_t c) {
+  uint32_t h = hash_of(c, shift);
+  for (int probe = 0; probe < slots; ++probe) {
+    const uint32_t kx = hk[h];
+    if (kx == kEmpty) return false;
+    if (kx == (uint32_t)c) return true;
+    h = (h + 1) & (uint32_t)(slots - 1);
+  }
+  return false;
+}
+
+// append one entry to the scanner -> examiner queue (the caller holds reservation e)
+__device__ __forceinline__ void queue_write(int* sh, uint2* q_ent, uint32_t* q_seq, int32_t* status, uint32_t e,
+                                            uint32_t key, uint32_t idp) {
+  volatile int* vsh = sh;
+  uint32_t spins = 0;  // bounded wait for room
+  while ((int32_t)(e - (uint32_t)vsh[S_QHEAD]) >= kQueue && !vsh[S_ABORT]) {
+    if (++spins > kWaitLimit) {
+      vsh[S_ABORT] = 1;
+      raise_status(status, ARCS_ERR_TIMEOUT);
+    }
+    __nanosleep(32);
+  }
+  q_ent[e % kQueue] = make_uint2(key, idp);
+  __threadfence_block();
+  *reinterpret_cast<volatile uint32_t*>(&q_seq[e % kQueue]) = e + 1u;
+}
+
+// The chunks of one warp-wide load whose maximum reached the threshold (bits of `bal`, chunk
+// cbase + lane held in q) are examined one element per lane, up to 32/E chunks per pass.
+template <typename T, bool MASKED>
+__device__ __noinline__ void scan_examine(const ScanCtx& c, uint4 q, int cbase, unsigned bal) {
+  constexpr int E = Elem<T>::kPerChunk;
+  const int lane = threadIdx.x & 31;
+  while (bal) {
+    const int jj = lane / E, el = lane % E;
+    const unsigned src = __fns(bal, 0, jj + 1);
+    const bool valid = src < 32u;
+    const int sl = valid ? (int)src : 0;
+    const uint32_t w0 = __shfl_sync(0xFFFFFFFFu, q.x, sl), w1 = __shfl_sync(0xFFFFFFFFu, q.y, sl);
+    const uint32_t w2 = __shfl_sync(0xFFFFFFFFu, q.z, sl), w3 = __shfl_sync(0xFFFFFFFFu, q.w, sl);
+    const float v = elem_of_words<T>(w0, w1, w2, w3, el);
+    const int32_t gid = c.col0 + (cbase + sl) * E + el;
+    const uint32_t ky = key_of(v);
+    const uint64_t cm = comp_of(ky, gid);
+    // eligible for the selection proper (B) / for the constrained head ranking (A)
+    bool okB = valid && ky != 0u && cm > c.tcB;
+    bool okA = MASKED && valid && ky != 0u && cm > c.tcA;
+    if (MASKED && okB)
+      okB = ((__ldg(&c.mrow[gid >> 5]) >> (gid & 31)) & 1u) && !(c.bans && v + 0.0f <= ARCS_BANNED);  // tools/sampler.h:118-119
+    // tokens the table replaces are taken from it when the item is finished, not from the stream
+    if ((okB || okA) && c.touched && table_has(c.hk, c.hash_slots, c.hash_shift, gid - c.id_base)) okB = okA = false;
+    // count the survivors by the upper 16 bits of their keys: the examiner reads thresholds off these counts
+    if (okB) atomicAdd(&c.histB[coarse_bin(ky, c.baseB)], 1u);
+    if (okA) atomicAdd(&c.histA[coarse_bin(ky, c.baseA)], 1u);
+    const bool pass = okB || okA;
+    const unsigned pb = __ballot_sync(0xFFFFFFFFu, pass);
+    if (pb) {
+      const int leader = __ffs(pb) - 1;
+      uint32_t base = 0;
+      if (lane == leader) base = atomicAdd(reinterpret_cast<unsigned int*>(&c.sh[S_QTAIL]), (unsigned)__popc(pb));
+      base = __shfl_sync(0xFFFFFFFFu, base, leader);
+      if (pass)
+        queue_write(c.sh, c.q_ent, c.q_seq, c.status, base + __popc(pb & ((1u << lane) - 1u)), ky,
+                    (uint32_t)gid | ((uint32_t)okB << 30) | ((uint32_t)c.par << 31));
+    }
+    const int done = min(__popc(bal), 32 / E);
+    for (int i = 0; i < done; ++i) bal &= bal - 1u;
+  }
+}
+
+template <typename T, bool MASKED>
+__global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a) {
+  extern __shared__ __align__(128) char smem[];
+  // ---- carve shared memory (ordered by alignment)
+  char* ring = smem;                                                          // kRing * kSTile
+  uint2* q_ent = reinterpret_cast<uint2*>(ring + (size_t)kRing * kSTile);  // [kQueue] (key, id | parity << 31)
+  uint64_t* full = reinterpret_cast<uint64_t*>(q_ent + kQueue);               // [kRing] tile has landed
+  uint64_t* empty = full + kRing;                                             // [kRing] tile has been scanned
+  unsigned long long* s64 = reinterpret_cast<unsigned long long*>(empty + kRing);  // [L_END]
+  double* spr = reinterpret_cast<double*>(s64 + L_END);                       // [ARCS_KCAP + 1]
+  uint32_t* q_seq = reinterpret_cast<uint32_t*>(spr + ARCS_KCAP + 1);         // [kQueue] entry number + 1 once written
+  uint32_t* hist = q_seq + kQueue;                                            // [512] finishers' radix histograms
+  uint32_t* xhist = hist + 512;                                               // [256] examiner's radix histogram
+  uint32_t* xh = xhist + 256;                                                 // [2 parities][B, A][256] coarse histograms
+  uint32_t* tk = xh + 4 * 256;                                                 // [kTmpCap] finishers' scratch
+  int32_t* ti = reinterpret_cast<int32_t*>(tk + kTmpCap);
+  uint32_t* xtk = reinterpret_cast<uint32_t*>(ti + kTmpCap);                  // [kTmpCap] examiner's scratch
+  int32_t* xti = reinterpret_cast<int32_t*>(xtk + kTmpCap);
+  int* misc = reinterpret_cast<int*>(xti + kTmpCap);                          // [8]
+  int* sh = misc + 8;                                                         // [S_END]
+  float* sv = reinterpret_cast<float*>(sh + S_END);                           // [ARCS_KCAP] sorted candidates
+  int32_t* sid = reinterpret_cast<int32_t*>(sv + ARCS_KCAP);
+  uint32_t* bkey = reinterpret_cast<uint32_t*>(sid + ARCS_KCAP);              // [2][kCapB]
+  int32_t* bid = reinterpret_cast<int32_t*>(bkey + 2 * kCapB);
+  uint32_t* akey = reinterpret_cast<uint32_t*>(bid + 2 * kCapB);              // [2][kCapA] when MASKED
+  int32_t* aid = reinterpret_cast<int32_t*>(akey + (MASKED ? 2 * kCapA : 0));
+  uint32_t* hkey = reinterpret_cast<uint32_t*>(aid + (MASKED ? 2 * kCapA : 0));  // [2][hash_slots] token columns
+  uint32_t* hinfo = hkey + 2 * a.hash_slots;                                  // [2][hash_slots]
+  volatile int* vsh = sh;
+  volatile unsigned long long* v64 = s64;
 
   constexpr int E = Elem<T>::kPerChunk;
-  const int tid = threadIdx.x, seg = blockIdx.x % a.nseg, b = blockIdx.x / a.nseg;
-  const T* row = reinterpret_cast<const T*>(a.logits) + (size_t)b * a.row_stride;
-  const int32_t lo = seg * a.seg_len, hi = min(a.V, lo + a.seg_len);
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int n_items = a.B * a.nseg;
+  const int my_n = (n_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
   const int32_t Vg = a.v_global > 0 ? a.v_global : a.V;
-  const SegPlan p = make_plan(row, lo, hi);
-  const PruneScratch ps{hist, tk, ti, misc};
-
-  // ---- row parameters
-  const arcs_row_params prm = a.params[b];
-  const bool greedy = prm.temperature <= 0.0f;
-  int kB;
-  if (MASKED) kB = greedy ? 1 : (prm.top_k > 0 ? min(prm.top_k, Vg) : 40);       // `need`, tools/sampler.h:86
-  else kB = greedy ? 1 : min(prm.top_k > 0 ? min(prm.top_k, Vg) : 256, Vg);      // tools/sampler.h:38-40
-  const bool k_bad = kB > ARCS_KCAP;
-  if (k_bad) kB = ARCS_KCAP;
-  const bool fp_on = prm.frequency_penalty != 0.0f;
-  const bool rp_on = prm.repeat_penalty != 1.0f && prm.repeat_penalty > 0.0f && prm.repeat_last_n != 0;
-  const bool pp_on = prm.presence_penalty != 0.0f;
-  const int32_t h0 = a.hist_off ? a.hist_off[b] : 0, H = a.hist_off ? a.hist_off[b + 1] - h0 : 0;
-  const int32_t q0 = a.bias_off ? a.bias_off[b] : 0, NB = a.bias_off ? a.bias_off[b + 1] - q0 : 0;
-  const bool pen_on = (fp_on || rp_on || pp_on) && H > 0;
-  const bool lists_ok = H <= a.max_hist && NB <= a.max_bias;
-  const bool touched_on = (pen_on || NB > 0) && lists_ok;
-  const uint32_t* mrow = nullptr;
-  if (MASKED) mrow = a.mask + (size_t)(a.mask_row ? a.mask_row[b] : b) * a.mask_stride;
-
-  Sel selB{bkey, bid, &sh[S_CNT_B], reinterpret_cast<uint32_t*>(&sh[S_TAU_B]), kB, min(512, max(2 * kB, kB + 128)), kCapB};
-  Sel selA{akey, aid, &sh[S_CNT_A], reinterpret_cast<uint32_t*>(&sh[S_TAU_A]), ARCS_HEAD, 1024, kCapA};
 
   if (tid == 0) {
-    for (int i = 0; i < kStages; ++i) mbar_init(&bars[i], 1);
+    for (int i = 0; i < kRing; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
     mbar_init_fence();
-    sh[S_CNT_B] = 0;
-    sh[S_TAU_B] = 0;
-    sh[S_CNT_A] = 0;
-    sh[S_TAU_A] = 0;
-    sh[S_LAST] = 0;
-    sh[S_FLAGS] = 0;
-    sh[S_PICK] = 0;
-    sh[S_HOT0] = 0;
-    sh[S_HOT1] = 0;
-    if (k_bad) raise_status(a.status, ARCS_ERR_TOPK);
-    if (!lists_ok) raise_status(a.status, ARCS_ERR_LIST);
+    for (int i = 0; i < S_END; ++i) sh[i] = 0;
+    for (int i = 0; i < L_END; ++i) s64[i] = 0ull;
   }
-  __syncthreads();
-  if (tid == 0)
-    for (int t = 0; t < p.tiles && t < kStages; ++t) issue_tile(p, t, stage, bars);
+  for (int i = tid; i < kQueue; i += kThreadsP) q_seq[i] = 0u;
+  for (int i = tid; i < 4 * 256; i += kThreadsP) xh[i] = 0u;
+  __syncthreads();  // the only CTA-wide barrier
 
-  // ---- table of the tokens this segment must not take from the stream: every id of the
-  // history that a penalty applies to and every id of the bias list (tools/sampler.h:154-174)
-  bool bans = false;  // Sampler::bans_: any bias entry <= -100, in range or not (tools/sampler.h:34)
-  if (touched_on) {
-    for (int i = tid; i < a.hash_slots; i += kThreads) {
-      hkey[i] = kEmpty;
-      hinfo[i] = 0;
-    }
-    __syncthreads();
-    auto insert = [&](int32_t t) -> int {  // global id -> slot, -1 when it is not this segment's
-      if (t < 0 || t >= Vg) return -1;
-      const int32_t c = t - a.id_base;
-      if (c < lo || c >= hi) return -1;
-      uint32_t h = hash_of(c, a.hash_shift);
-      for (int probe = 0; probe < a.hash_slots; ++probe) {
-        const uint32_t old = atomicCAS(&hkey[h], kEmpty, (uint32_t)c);
-        if (old == kEmpty || old == (uint32_t)c) return (int)h;
-        h = (h + 1) & (uint32_t)(a.hash_slots - 1);
-      }
-      return -1;
-    };
-    if (pen_on) {
-      const int32_t nwin = prm.repeat_last_n < 0 ? H : min(H, prm.repeat_last_n);  // tools/sampler.h:163
-      for (int i = tid; i < H; i += kThreads) {
-        const int s = insert(a.hist_ids[h0 + i]);
-        if (s >= 0) atomicAdd(&hinfo[s], 1u);
-        if (s >= 0 && i >= H - nwin) atomicOr(&hinfo[s], kInfoWindow);
-      }
-    }
-    for (int i = tid; i < NB; i += kThreads) {
-      const float bv = a.bias_vals[q0 + i];
-      bans = bans || bv <= -100.0f;
-      const int s = insert(a.bias_ids[q0 + i]);
-      if (s >= 0) atomicOr(&hinfo[s], bv > -100.0f ? kInfoBias : kInfoBan);
-    }
-    bans = __syncthreads_or(bans);
-  }
-  auto is_touched = [&](int32_t c) -> bool {
+  auto abort_now = [&]() {
+    vsh[S_ABORT] = 1;
+    raise_status(a.status, ARCS_ERR_TIMEOUT);
+  };
+  auto is_touched = [&](int par, int32_t c) -> bool {
+    const uint32_t* hk = hkey + par * a.hash_slots;
     uint32_t h = hash_of(c, a.hash_shift);
     for (int probe = 0; probe < a.hash_slots; ++probe) {
-      const uint32_t kx = hkey[h];
+      const uint32_t kx = hk[h];
       if (kx == kEmpty) return false;
       if (kx == (uint32_t)c) return true;
       h = (h + 1) & (uint32_t)(a.hash_slots - 1);
     }
     return false;
   };
-
-  // ---- one element of the stream (all lanes of a warp call this together)
-  // v: logit as read; c: column; `in_order`: the element arrives in increasing id order, so an
-  // element equal to the smallest kept key loses to it (threshold tau_key); otherwise ties with
-  // the smallest kept key must still be taken (threshold tau_key - 1).
-  bool hot = false;
-  auto consider = [&](bool valid, float v, int32_t c, uint32_t tauB, uint32_t tauA, bool from_table) {
-    v = v + 0.0f;
-    const uint32_t ky = key_of(v);
-    bool okB = valid && ky >= tauB && ky != 0u;
-    bool okA = MASKED && valid && ky >= tauA && ky != 0u;
-    if ((okB || okA) && touched_on && !from_table && is_touched(c)) okB = okA = false;
-    if (MASKED && okB) {
-      const int32_t g = c + a.id_base;
-      okB = ((__ldg(&mrow[g >> 5]) >> (g & 31)) & 1u) && !(bans && v <= ARCS_BANNED);  // tools/sampler.h:118-119
+  if (warp == kProdWarp) {
+    // =================================================================== producer
+    if (lane == 0) {
+      RT_DECL;
+      uint32_t g = 0;
+      for (int j = 0; j < my_n && !vsh[S_ABORT]; ++j) {
+        const Item<T> it = item_of<T>(a, (int)blockIdx.x + j * (int)gridDim.x);
+        const int T_ = s_tiles(it.p);
+        for (int t = 0; t < T_; ++t, ++g) {
+          const int slot = (int)(g % kRing);
+          if (vsh[S_ABORT]) break;
+          RT(0);
+          if (!mbar_wait(&empty[slot], ((g / kRing) & 1u) ^ 1u)) {
+            abort_now();
+            break;
+          }
+          RT(1);
+          const uint32_t n = s_tile_bytes(it.p, t);
+          mbar_expect_tx(&full[slot], n);
+          bulk_load(ring + (size_t)slot * kSTile, it.p.body + (size_t)t * kSTile, n, &full[slot]);
+        }
+      }
+      RT_FLUSH(0, true);
+      if (vsh[S_ABORT]) {  // give the copies in flight a bounded chance to land before the CTA ends
+        const uint32_t first = g > (uint32_t)kRing ? g - kRing : 0u;
+        for (uint32_t x = first; x < g; ++x) mbar_wait(&full[x % kRing], (x / kRing) & 1u);
+      }
     }
-    sel_push(selB, okB, ky, c + a.id_base, hot, a.status);
-    if (MASKED) sel_push(selA, okA, ky, c + a.id_base, hot, a.status);
-  };
-  // Called by all threads after a barrier behind which no thread is pushing. The counts are
-  // read before a second barrier so that every thread takes the same branches even though
-  // threads that leave early start pushing again.
-  auto maybe_prune = [&]() {
-    const bool pb = sh[S_CNT_B] > selB.trig, pa = MASKED && sh[S_CNT_A] > selA.trig;
-    __syncthreads();
-    if (pb) sel_prune(selB, selB.k, ps);
-    if (pa) sel_prune(selA, selA.k, ps);
-  };
+  } else if (warp < kScanW) {
+    // =================================================================== scanners
+    // Scanner w consumes the tiles whose running number is w modulo kScanW (its own ring slot),
+    // so sixteen tiles are in work at once and no warp waits for another.
+    uint32_t G0 = 0;  // running number of the item's first tile
+    RT_DECL;
+    for (int j = 0; j < my_n; ++j) {
+      const int par = j & 1;
+      const Item<T> it = item_of<T>(a, (int)blockIdx.x + j * (int)gridDim.x);
+      const int T_ = s_tiles(it.p);
+      RT(0);
+      {  // the item's table and first threshold must be ready
+        uint32_t spins = 0;
+        while (vsh[S_PREPARED] <= j && !vsh[S_ABORT]) {
+          if (++spins > kWaitLimit) abort_now();
+          __nanosleep(64);
+        }
+        __threadfence_block();
+      }
+      RT(1);
+      if (vsh[S_ABORT]) break;
+      const uint32_t* mrow = MASKED ? reinterpret_cast<const uint32_t*>(s64[L_MROW + par]) : nullptr;
+      const bool touched = sh[S_TOUCHED + par] != 0, bans = MASKED && sh[S_BANS + par] != 0;
+      ScanCtx ctx;
+      ctx.hk = hkey + par * a.hash_slots;
+      ctx.hash_slots = a.hash_slots;
+      ctx.hash_shift = a.hash_shift;
+      ctx.touched = touched;
+      ctx.bans = bans;
+      ctx.par = par;
+      ctx.mrow = mrow;
+      ctx.histB = xh + (2 * par) * 256;
+      ctx.histA = xh + (2 * par + 1) * 256;
+      ctx.baseB = (uint32_t)sh[S_BASE_B + par];
+      ctx.baseA = (uint32_t)sh[S_BASE_A + par];
+      ctx.sh = sh;
+      ctx.q_ent = q_ent;
+      ctx.q_seq = q_seq;
+      ctx.status = a.status;
+      ctx.id_base = a.id_base;
+      const char* tile = ring + (size_t)warp * kSTile;
+      for (int t = (int)(((uint32_t)warp - G0) % kRing); t < T_; t += kRing) {
+        const uint32_t g = G0 + (uint32_t)t;
+        if (vsh[S_ABORT]) break;
+        RT(0);
+        if (!mbar_wait(&full[warp], (g / kRing) & 1u)) {
+          abort_now();
+          break;
+        }
+        RT(2);
+        const int nchunk = (int)(s_tile_bytes(it.p, t) / 16u);
+        const int32_t col0 = it.p.body_first + t * (kSTile / (int)sizeof(T)) + a.id_base;  // global id of the tile's first element
+        // thresholds are re-read for every group of chunks: the examiner raises them all the time
+        uint64_t tcB = 0, tcA = 0;
+        float tfB = 0.0f, tfA = 0.0f;
+        auto refresh = [&]() {
+          tcB = v64[L_TAU_B + par];
+          tcA = MASKED ? v64[L_TAU_A + par] : 0xFFFFFFFFFFFFFFFFull;
+          // chunk-level test in float: inclusive on the threshold's value (ids are settled per element)
+          const uint32_t kB32 = (uint32_t)(tcB >> 32), kA32 = (uint32_t)(tcA >> 32);
+          tfB = value_of(kB32 < 0x007FFFFFu ? 0x007FFFFFu : kB32);
+          tfA = MASKED ? value_of(kA32 < 0x007FFFFFu ? 0x007FFFFFu : kA32) : INFINITY;
+        };
+        ctx.col0 = col0;
+#ifndef ARCS_X_NOSCAN
+        for (int c0 = 0; c0 < nchunk; c0 += 4 * 32) {
+          uint4 q[4];
+          bool h[4];
+          refresh();
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int ci = c0 + u * 32 + lane;
+            q[u] = ci < nchunk ? lds128(tile + ci * 16) : make_uint4(0, 0, 0, 0);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int ci = c0 + u * 32 + lane;
+            const float m = Elem<T>::chunk_max(q[u]);
+            h[u] = ci < nchunk && m >= tfB;
+            if (MASKED) {
+              bool hb = h[u];
+              if (hb) {
+                const int32_t gid = col0 + ci * E;
+                uint32_t bits = __ldg(&mrow[gid >> 5]) >> (gid & 31);
+                if ((gid & 31) + E > 32) bits |= __ldg(&mrow[(gid >> 5) + 1]) << (32 - (gid & 31));
+                hb = (bits & ((1u << E) - 1u)) != 0u;
+              }
+              h[u] = hb || (ci < nchunk && m >= tfA);
+            }
+#ifdef ARCS_X_NOHOT
+            h[u] = h[u] && a.V < 0;  // never true, but the test above is still evaluated
+#endif
+          }
+          if (__any_sync(0xFFFFFFFFu, h[0] || h[1] || h[2] || h[3])) {
+            ctx.tcB = tcB;
+            ctx.tcA = tcA;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const unsigned bal = __ballot_sync(0xFFFFFFFFu, h[u]);
+              if (bal) scan_examine<T, MASKED>(ctx, q[u], c0 + u * 32, bal);
+            }
+          }
+        }
+#endif
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[warp]);
+      }
+      if (vsh[S_ABORT]) break;
+      __syncwarp();
+      if (lane == 0) {  // this warp has queued everything it found in the item
+        const uint32_t e = atomicAdd(reinterpret_cast<unsigned int*>(&sh[S_QTAIL]), 1u);
+        queue_write(sh, q_ent, q_seq, a.status, e, 0u, kMarker | ((uint32_t)par << 31));
+      }
+      G0 += (uint32_t)T_;
+    }
+    RT(0);
+    RT_FLUSH(4, tid == 0);
+  } else if (warp == kExamWarp) {
+    // =================================================================== examiner
+    // Owns the candidate buffers while an item streams: moves the queued survivors into them,
+    // reads a new threshold off the coarse histograms the scanners keep (the lower edge of the
+    // bin that holds the k-th best survivor so far: at least k survivors are at or above it),
+    // and drops buffer entries the threshold has overtaken. The exact radix select runs only
+    // when a buffer still overflows, i.e. when one bin holds very many equal or close keys.
+    uint32_t head = 0, idle = 0, polls = 0;
+    int cB[2] = {0, 0}, cA[2] = {0, 0}, marks[2] = {0, 0}, streamed = 0;
+    int kk[2] = {0, 0};
+    uint32_t baseB[2] = {0, 0}, baseA[2] = {0, 0};
+    bool loaded[2] = {false, false};
+    constexpr int kStep = 128;     // queue entries taken per step, four per lane
+    constexpr int kFullB = 512, kFullA = 1024;  // buffer fill at which stale entries are dropped
+    RT_DECL;
+    unsigned long long xsteps = 0, xents = 0;
+    // drop what the threshold has overtaken; if the buffer is still too full, select exactly
+    auto shrink = [&](const Sel& sel, int& cnt, int full) {
+      const uint64_t tc = *reinterpret_cast<volatile unsigned long long*>(sel.tau);
+      int out = 0;
+      for (int i0 = 0; i0 < cnt; i0 += 32) {
+        const int i = i0 + lane;
+        uint32_t ky = 0;
+        int32_t id = 0;
+        bool keep = false;
+        if (i < cnt) {
+          ky = sel.key[i];
+          id = sel.id[i];
+          keep = comp_of(ky, id) > tc;
+        }
+        const unsigned b = __ballot_sync(0xFFFFFFFFu, keep);  // (every lane has read its entry before any write below)
+        if (keep) {
+          const int pos = out + __popc(b & ((1u << lane) - 1u));
+          sel.key[pos] = ky;
+          sel.id[pos] = id;
+        }
+        out += __popc(b);
+        __syncwarp();
+      }
+      cnt = out;
+      if (cnt > full - kStep) cnt = sel_prune_warp(sel, cnt, sel.k, xhist, xtk, xti);
+    };
+    // threshold from the scanners' counts
+    auto raise = [&](const Sel& sel, const uint32_t* hst, uint32_t base) {
+      int d, kr;
+      bool ex;
+      find_bin(hst, sel.k, d, kr, ex);
+      if (d <= 0) return;
+      const unsigned long long tc = (unsigned long long)((base + (uint32_t)d) << 16) << 32;  // comp > tc <=> key >= edge of bin d
+      if (lane == 0 && tc > *reinterpret_cast<volatile unsigned long long*>(sel.tau))
+        *reinterpret_cast<volatile unsigned long long*>(sel.tau) = tc;
+      __syncwarp();
+    };
+    while (streamed < my_n) {
+      if (vsh[S_ABORT]) break;
+      const uint32_t tail = (uint32_t)vsh[S_QTAIL];
+      const int avail = (int)(tail - head);
+      if (avail == 0) {
+        if (++idle > kWaitLimit) {
+          abort_now();
+          break;
+        }
+        __nanosleep(32);
+        continue;
+      }
+      if (avail < kStep && polls < 4) {  // let a fuller batch build up
+        ++polls;
+        __nanosleep(32);
+        continue;
+      }
+      idle = 0;
+      polls = 0;
+      RT(0);
+      const int nb = min(avail, kStep);
+      uint2 ent[kStep / 32];
+#pragma unroll
+      for (int u = 0; u < kStep / 32; ++u) {
+        const uint32_t e = head + (uint32_t)(u * 32 + lane);
+        if (u * 32 + lane < nb) {
+          uint32_t spins = 0;  // the entry is reserved; its writer publishes it right after
+          while (*reinterpret_cast<volatile uint32_t*>(&q_seq[e % kQueue]) != e + 1u && !vsh[S_ABORT])
+            if (++spins > kWaitLimit) abort_now();
+        }
+      }
+      __syncwarp();
+      __threadfence_block();
+#pragma unroll
+      for (int u = 0; u < kStep / 32; ++u) {
+        const uint32_t e = head + (uint32_t)(u * 32 + lane);
+        ent[u] = u * 32 + lane < nb ? q_ent[e % kQueue] : make_uint2(0u, 0u);
+      }
+      __syncwarp();
+      __threadfence_block();
+      head += (uint32_t)nb;
+      if (lane == 0) vsh[S_QHEAD] = (int)head;
+#pragma unroll
+      for (int par = 0; par < 2; ++par) {
+        const Sel sB{bkey + par * kCapB, bid + par * kCapB, &sh[S_CNT_B + par], &s64[L_TAU_B + par], kk[par], 0, kCapB};
+        const Sel sA{akey + par * kCapA, aid + par * kCapA, &sh[S_CNT_A + par], &s64[L_TAU_A + par], ARCS_HEAD, 0, kCapA};
+        bool seen = false;
+        int nmark = 0;
+#pragma unroll
+        for (int u = 0; u < kStep / 32; ++u) {
+          const bool valid = u * 32 + lane < nb && (int)(ent[u].y >> 31) == par;
+          const uint32_t gid = ent[u].y & kIdMask;
+          const bool marker = valid && gid == kMarker;
+          const bool mine = valid && !marker;
+          nmark += __popc(__ballot_sync(0xFFFFFFFFu, marker));
+          if (!__any_sync(0xFFFFFFFFu, mine)) continue;
+          if (!loaded[par]) {  // first entry of a new item: its settings were published before it could be queued
+            loaded[par] = true;
+            kk[par] = sh[S_K + par];
+            baseB[par] = (uint32_t)sh[S_BASE_B + par];
+            baseA[par] = (uint32_t)sh[S_BASE_A + par];
+          }
+          seen = true;
+          const uint64_t cm = comp_of(ent[u].x, (int32_t)gid);
+          const bool okB = mine && ((ent[u].y >> 30) & 1u) && cm > v64[L_TAU_B + par];
+          const unsigned bb = __ballot_sync(0xFFFFFFFFu, okB);
+          if (okB) {
+            const int pos = cB[par] + __popc(bb & ((1u << lane) - 1u));
+            sB.key[pos] = ent[u].x;
+            sB.id[pos] = (int32_t)gid;
+          }
+          cB[par] += __popc(bb);
+          if (MASKED) {
+            const bool okA = mine && cm > v64[L_TAU_A + par];
+            const unsigned ba = __ballot_sync(0xFFFFFFFFu, okA);
+            if (okA) {
+              const int pos = cA[par] + __popc(ba & ((1u << lane) - 1u));
+              sA.key[pos] = ent[u].x;
+              sA.id[pos] = (int32_t)gid;
+            }
+            cA[par] += __popc(ba);
+          }
+        }
+        if (seen) {
+          const Sel sBk{sB.key, sB.id, sB.cnt, sB.tau, kk[par], 0, kCapB};
+          raise(sBk, xh + (2 * par) * 256, baseB[par]);
+          if (cB[par] > kFullB - kStep) shrink(sBk, cB[par], kFullB);
+          if (MASKED) {
+            raise(sA, xh + (2 * par + 1) * 256, baseA[par]);
+            if (cA[par] > kFullA - kStep) shrink(sA, cA[par], kFullA);
+          }
+        }
+        marks[par] += nmark;
+        if (marks[par] == kScanW) {  // every scanner has closed the item: hand its buffers to the finishers
+          marks[par] = 0;
+          __syncwarp();
+          if (lane == 0) {
+            sh[S_CNT_B + par] = cB[par];
+            if (MASKED) sh[S_CNT_A + par] = cA[par];
+            __threadfence_block();
+            vsh[S_STREAMED] = streamed + 1;
+          }
+          cB[par] = cA[par] = 0;
+          loaded[par] = false;
+#pragma unroll
+          for (int x = 0; x < 16; ++x) xh[(2 * par) * 256 + x * 32 + lane] = 0;  // both histograms of this parity
+          ++streamed;
+        }
+      }
+      RT(1);
+      xsteps += 1;
+      xents += nb;
+    }
+#ifdef ARCS_ROLE_TIMING
+    rt2 = xsteps;
+    rt3 = xents;
+#endif
+    RT_FLUSH(8, lane == 0);
+  } else {
+    // =================================================================== finishers
+    const int gt = tid - kFinWarp0 * 32;
+    RT_DECL;
+    const PruneScratch ps{hist, tk, ti, misc, &s64[L_PRUNE_MIN]};
 
-  // ---- the stream. Per tile: (A) every thread looks at its 16-byte chunks and lists the few
-  // whose maximum reaches the current threshold; (B) the listed chunks are examined one
-  // element per thread. Nearly all chunks fail (A), which costs a handful of instructions.
-  bool failed = false;
-  for (int t = 0; t < p.tiles; ++t) {
-    const int slot = t % kStages;
-    const char* tile = stage + (size_t)slot * kTileBytes;
-    if (!mbar_wait(&bars[slot], (uint32_t)((t / kStages) & 1))) failed = true;
-    const int nchunk = (int)(tile_bytes(p, t) / 16u);
-    if (t == 0) {
-      // Bootstrap of the threshold: the k-th largest chunk maximum is a lower bound of the
-      // k-th largest element. Tokens of this tile that the table replaces may own a chunk
-      // maximum without counting as candidates, so that many extra maxima are skipped.
-      Sel& s0 = MASKED ? selA : selB;
-      if (touched_on) {
+    struct RowCfg {
+      arcs_row_params prm;
+      int kB;
+      bool greedy, k_bad, fp_on, rp_on, pp_on, pen_on, lists_ok, touched_on;
+      int32_t h0, H, q0, NB;
+    };
+    auto row_cfg = [&](int b) {
+      RowCfg r;
+      r.prm = a.params[b];
+      r.greedy = r.prm.temperature <= 0.0f;
+      if (MASKED) r.kB = r.greedy ? 1 : (r.prm.top_k > 0 ? min(r.prm.top_k, Vg) : 40);     // `need`, tools/sampler.h:86
+      else r.kB = r.greedy ? 1 : min(r.prm.top_k > 0 ? min(r.prm.top_k, Vg) : 256, Vg);    // tools/sampler.h:38-40
+      r.k_bad = r.kB > ARCS_KCAP;
+      if (r.k_bad) r.kB = ARCS_KCAP;
+      r.fp_on = r.prm.frequency_penalty != 0.0f;
+      r.rp_on = r.prm.repeat_penalty != 1.0f && r.prm.repeat_penalty > 0.0f && r.prm.repeat_last_n != 0;
+      r.pp_on = r.prm.presence_penalty != 0.0f;
+      r.h0 = a.hist_off ? a.hist_off[b] : 0;
+      r.H = a.hist_off ? a.hist_off[b + 1] - r.h0 : 0;
+      r.q0 = a.bias_off ? a.bias_off[b] : 0;
+      r.NB = a.bias_off ? a.bias_off[b + 1] - r.q0 : 0;
+      r.pen_on = (r.fp_on || r.rp_on || r.pp_on) && r.H > 0;
+      r.lists_ok = r.H <= a.max_hist && r.NB <= a.max_bias;
+      r.touched_on = (r.pen_on || r.NB > 0) && r.lists_ok;
+      return r;
+    };
+
+    // ---- prepare item j: table of the tokens the stream must not supply (every id of the
+    // history a penalty applies to, every id of the bias list: tools/sampler.h:154-174) and a
+    // first threshold from a short prefix of the item, read ahead of the ring.
+    auto prepare = [&](int j) {
+      const int par = j & 1;
+      const Item<T> it = item_of<T>(a, (int)blockIdx.x + j * (int)gridDim.x);
+      const RowCfg r = row_cfg(it.b);
+      uint32_t* hk = hkey + par * a.hash_slots;
+      uint32_t* hi_ = hinfo + par * a.hash_slots;
+      bool bans = false;  // Sampler::bans_: any bias entry <= -100, in range or not (tools/sampler.h:34)
+      if (gt == 0) {
+        if (r.k_bad) raise_status(a.status, ARCS_ERR_TOPK);
+        if (!r.lists_ok) raise_status(a.status, ARCS_ERR_LIST);
+        sh[S_PICK] = 0;
+      }
+      if (r.touched_on) {
+        for (int i = gt; i < a.hash_slots; i += kGroup) {
+          hk[i] = kEmpty;
+          hi_[i] = 0;
+        }
+        group_sync();
+        auto insert = [&](int32_t t) -> int {  // global id -> slot, -1 when it is not this segment's
+          if (t < 0 || t >= Vg) return -1;
+          const int32_t c = t - a.id_base;
+          if (c < it.lo || c >= it.hi) return -1;
+          uint32_t h = hash_of(c, a.hash_shift);
+          for (int probe = 0; probe < a.hash_slots; ++probe) {
+            const uint32_t old = atomicCAS(&hk[h], kEmpty, (uint32_t)c);
+            if (old == kEmpty || old == (uint32_t)c) return (int)h;
+            h = (h + 1) & (uint32_t)(a.hash_slots - 1);
+          }
+          return -1;
+        };
+        if (r.pen_on) {
+          const int32_t nwin = r.prm.repeat_last_n < 0 ? r.H : min(r.H, r.prm.repeat_last_n);  // tools/sampler.h:163
+          for (int i = gt; i < r.H; i += kGroup) {
+            const int s = insert(a.hist_ids[r.h0 + i]);
+            if (s >= 0) atomicAdd(&hi_[s], 1u);
+            if (s >= 0 && i >= r.H - nwin) atomicOr(&hi_[s], kInfoWindow);
+          }
+        }
+        for (int i = gt; i < r.NB; i += kGroup) {
+          const float bv = a.bias_vals[r.q0 + i];
+          bans = bans || bv <= -100.0f;
+          const int s = insert(a.bias_ids[r.q0 + i]);
+          if (s >= 0) atomicOr(&hi_[s], bv > -100.0f ? kInfoBias : kInfoBan);
+        }
+      }
+      bans = group_sync_or(bans);
+      // first threshold: the k-th largest of 256 (or, constrained, 1024) maxima over disjoint
+      // pieces of the prefix is a lower bound of the k-th best element. Tokens of the prefix that
+      // the table replaces may own a maximum without counting, so that many more are skipped.
+      const int nchunk = min(it.p.body_bytes, MASKED ? 2 * kBootBytes : kBootBytes) / 16;
+      if (r.touched_on) {
         int extra = 0;
-        const int32_t c_lo = p.body_first, c_hi = p.body_first + nchunk * E;
-        for (int i = tid; i < a.hash_slots; i += kThreads) {
-          const uint32_t ck = hkey[i];
+        const int32_t c_lo = it.p.body_first, c_hi = it.p.body_first + nchunk * E;
+        for (int i = gt; i < a.hash_slots; i += kGroup) {
+          const uint32_t ck = hk[i];
           extra += ck != kEmpty && (int32_t)ck >= c_lo && (int32_t)ck < c_hi;
         }
         if (extra) atomicAdd(&sh[S_PICK], extra);
+        group_sync();
       }
-      const int fail0 = __syncthreads_or(failed);
-      const int kth = s0.k + sh[S_PICK];
-      if (!fail0 && kth <= nchunk && nchunk <= s0.cap) {
-#pragma unroll
-        for (int j = 0; j < kChunks; ++j) {
-          const int ci = j * kThreads + tid;
-          if (ci < nchunk) {
-            s0.key[ci] = key_of(Elem<T>::chunk_max(lds128(tile + ci * 16)));
-            s0.id[ci] = ci;
+      const int kth = (MASKED ? ARCS_HEAD : r.kB) + sh[S_PICK];
+      unsigned long long tau0B = 0ull, tau0A = 0ull;
+      if (!MASKED) {
+        float m = -INFINITY;
+        bool any = false;
+        for (int ci = gt; ci < nchunk; ci += kGroup) {
+          m = fmaxf(m, Elem<T>::chunk_max(ldg128_stream(it.p.body + (size_t)ci * 16)));
+          any = true;
+        }
+        const uint32_t my = any ? key_of(m) : 0u;
+        tk[gt] = my;
+        if (gt == 0) s64[L_PRUNE_MIN] = 0ull;  // hand-over word of the rank search below
+        group_sync();
+        if (kth <= min(nchunk, kGroup)) {
+          int gtc = 0, gec = 0;
+          for (int x = 0; x < kGroup; ++x) {
+            const uint32_t o = tk[x];
+            gtc += o > my;
+            gec += o >= my;
           }
+          if (gtc < kth && kth <= gec && my != 0u) s64[L_PRUNE_MIN] = (unsigned long long)my << 32;  // keeps ties with it
         }
-        if (tid == 0) *s0.cnt = nchunk;
-        __syncthreads();
-        sel_prune(s0, kth, ps);
-        if (tid == 0) {
-          const uint32_t tk0 = *s0.tau_key;  // 1 + smallest kept maximum (0: nothing was dropped)
-          *s0.tau_key = tk0 > 0u && tk0 != 0xFFFFFFFFu ? tk0 - 1u : tk0;
-          *s0.cnt = 0;
+        group_sync();
+      }
+      if (MASKED) {
+        const Sel sA{akey + par * kCapA, aid + par * kCapA, &sh[S_CNT_A + par], &s64[L_TAU_A + par], ARCS_HEAD, 1024, kCapA};
+        if (kth <= nchunk && nchunk <= kCapA) {
+          for (int ci = gt; ci < nchunk; ci += kGroup) {
+            sA.key[ci] = key_of(Elem<T>::chunk_max(ldg128_stream(it.p.body + (size_t)ci * 16)));
+            sA.id[ci] = ci;
+          }
+          if (gt == 0) {
+            *sA.cnt = nchunk;
+            *sA.tau = 0ull;
+          }
+          group_sync();
+          sel_prune(sA, kth, ps, gt);
+          tau0A = (*sA.tau >> 32) << 32;
+          group_sync();
         }
-        __syncthreads();
       }
-    }
-    const uint32_t tauB = *selB.tau_key, tauA = MASKED ? *selA.tau_key : 0xFFFFFFFFu;
-    const uint32_t tmin = min(tauB, tauA);
-    const float tf = value_of(tmin < 0x007FFFFFu ? 0x007FFFFFu : tmin);  // -inf while nothing has been dropped
-    int* hot_n = &sh[S_HOT0 + (t & 1)];
-    // (A)
-#pragma unroll
-    for (int j = 0; j < kChunks; ++j) {
-      const int ci = j * kThreads + tid;
-      bool h = false;
-      if (ci < nchunk && !failed) h = Elem<T>::chunk_max(lds128(tile + ci * 16)) >= tf;
-      const unsigned bal = __ballot_sync(0xFFFFFFFFu, h);
-      if (bal) {
-        const int lane = tid & 31, leader = __ffs(bal) - 1;
-        int base = 0;
-        if (lane == leader) base = atomicAdd(hot_n, __popc(bal));
-        base = __shfl_sync(0xFFFFFFFFu, base, leader);
-        if (h) hotl[base + __popc(bal & ((1u << lane) - 1u))] = (uint16_t)ci;
+      if (gt == 0) {
+        if (!MASKED) {
+          tau0B = s64[L_PRUNE_MIN];
+        }
+        s64[L_TAU_B + par] = tau0B;
+        s64[L_TAU_A + par] = tau0A;
+        sh[S_CNT_B + par] = 0;
+        sh[S_CNT_A + par] = 0;
+        sh[S_K + par] = r.kB;
+        sh[S_TRIG + par] = min(512, max(2 * r.kB, r.kB + 128));
+        sh[S_TOUCHED + par] = r.touched_on;
+        sh[S_BANS + par] = bans;
+        sh[S_BASE_B + par] = (int)(tau0B >> 48);
+        sh[S_BASE_A + par] = (int)(tau0A >> 48);
+        if (MASKED)
+          s64[L_MROW + par] = reinterpret_cast<unsigned long long>(a.mask + (size_t)(a.mask_row ? a.mask_row[it.b] : it.b) * a.mask_stride);
+        __threadfence_block();
+        vsh[S_PREPARED] = j + 1;
       }
-    }
-    if (__syncthreads_or(failed)) {
-      if (tid == 0) {
-        raise_status(a.status, ARCS_ERR_TIMEOUT);
-        drain_tiles(p, t, bars);
+      group_sync();
+    };
+
+    // ---- finish item j once the examiner has handed its buffers over. Returns false when the
+    // kernel is being abandoned (uniform over the group).
+    auto finish = [&](int j) -> bool {
+      const int par = j & 1;
+      bool bad = false;
+      if (gt == 0) {
+        uint32_t spins = 0;
+        while (vsh[S_STREAMED] <= j && !vsh[S_ABORT]) {
+          if (++spins > kWaitLimit) abort_now();
+          __nanosleep(64);
+        }
+        bad = vsh[S_ABORT] != 0;
+        __threadfence_block();
       }
-      __syncthreads();
-      return;
-    }
-    // (B)
-    const int nhot = *hot_n;
-    if (tid == 0) sh[S_HOT0 + ((t + 1) & 1)] = 0;
-    const int32_t col0 = p.body_first + t * (kTileBytes / (int)sizeof(T));
-    uint32_t tb = tauB, ta = tauA;
-    for (int r0 = 0; r0 < nhot; r0 += kThreads / E) {
-      const int qi = r0 + tid / E, e = tid % E;
-      const bool valid = qi < nhot;
-      float v = 0.0f;
-      int32_t c = 0;
-      if (valid) {
-        const int ci = hotl[qi];
-        v = Elem<T>::from_smem(tile + ci * 16 + e * (int)sizeof(T));
-        c = col0 + ci * E + e;
+      if (group_sync_or(bad)) return false;
+      RT(3);
+      const Item<T> it = item_of<T>(a, (int)blockIdx.x + j * (int)gridDim.x);
+      const RowCfg r = row_cfg(it.b);
+      const int b = it.b;
+      const T* row = it.row;
+      const SegPlan& p = it.p;
+      const uint32_t* hk = hkey + par * a.hash_slots;
+      const uint32_t* hi_ = hinfo + par * a.hash_slots;
+      bool bans = sh[S_BANS + par] != 0;
+      const uint32_t* mrow = MASKED ? reinterpret_cast<const uint32_t*>(s64[L_MROW + par]) : nullptr;
+      const Sel selB{bkey + par * kCapB, bid + par * kCapB, &sh[S_CNT_B + par], &s64[L_TAU_B + par], r.kB,
+                     min(512, max(2 * r.kB, r.kB + 128)), kCapB};
+      const Sel selA{akey + par * kCapA, aid + par * kCapA, &sh[S_CNT_A + par], &s64[L_TAU_A + par], ARCS_HEAD, 1024, kCapA};
+
+      bool hot = false;
+      // one more element for the selections (all lanes of every finisher warp call it together);
+      // v is the final (adjusted) logit, c the column; from_table: the element comes from the table
+      auto consider = [&](bool valid, float v, int32_t c, bool from_table) {
+        const uint32_t ky = key_of(v);
+        const uint64_t cm = comp_of(ky, c + a.id_base);
+        bool okB = valid && ky != 0u && cm > *selB.tau;
+        bool okA = MASKED && valid && ky != 0u && cm > *selA.tau;
+        if ((okB || okA) && r.touched_on && !from_table && is_touched(par, c)) okB = okA = false;
+        if (MASKED && okB) {
+          const int32_t g = c + a.id_base;
+          okB = ((__ldg(&mrow[g >> 5]) >> (g & 31)) & 1u) && !(bans && v + 0.0f <= ARCS_BANNED);  // tools/sampler.h:118-119
+        }
+        sel_push(selB, okB, ky, c + a.id_base, hot, a.status);
+        if (MASKED) sel_push(selA, okA, ky, c + a.id_base, hot, a.status);
+      };
+      // called by the whole group after a barrier behind which nobody pushes
+      auto maybe_prune = [&]() {
+        const bool pb = *selB.cnt > selB.trig, pa = MASKED && *selA.cnt > selA.trig;
+        group_sync();
+        if (pb) sel_prune(selB, selB.k, ps, gt);
+        if (pa) sel_prune(selA, selA.k, ps, gt);
+      };
+
+      // the scalar elements before the first and after the last 16-byte boundary
+      {
+        const bool hv = gt < p.head_n;
+        consider(hv, hv ? Elem<T>::load(row + it.lo + gt) : 0.0f, it.lo + gt, false);
+        const bool tv = gt < p.tail_n;
+        consider(tv, tv ? Elem<T>::load(row + p.tail_first + gt) : 0.0f, p.tail_first + gt, false);
       }
-      consider(valid, v, c, tb, ta, false);
-      if (r0 + kThreads / E < nhot) {  // more rounds: keep the buffer below its capacity
-        if (__syncthreads_or(hot)) {
+      // touched tokens: exact fp32 arithmetic of Sampler::adjusted, one token per thread
+      if (r.touched_on) {
+        for (int s0 = 0; s0 < a.hash_slots; s0 += kGroup) {
+          group_sync();
           maybe_prune();
           hot = false;
-          // the entries kept may now come from this tile, and the chunks still listed are in no
-          // particular order: a tie with the smallest kept key can still win on its id
-          tb = *selB.tau_key;
-          tb = tb ? tb - 1u : 0u;
-          ta = MASKED ? *selA.tau_key : 0xFFFFFFFFu;
-          ta = MASKED && ta ? ta - 1u : ta;
+          const int s = s0 + gt;
+          const uint32_t ck = hk[s];
+          const bool valid = ck != kEmpty;
+          float v = 0.0f;
+          if (valid) {
+            const uint32_t info = hi_[s];
+            const uint32_t cnt = info & kInfoCount;
+            v = Elem<T>::load(row + (int32_t)ck);
+            if (info & kInfoBias) {  // :154-155 in list order, duplicates add again
+              const int32_t g = (int32_t)ck + a.id_base;
+              for (int i = 0; i < r.NB; ++i)
+                if (a.bias_ids[r.q0 + i] == g && a.bias_vals[r.q0 + i] > -100.0f) v = __fadd_rn(v, a.bias_vals[r.q0 + i]);
+            }
+            if (r.pen_on && cnt > 0) {
+              if (r.fp_on) v = __fsub_rn(v, __fmul_rn(r.prm.frequency_penalty, (float)cnt));             // :160
+              if (r.rp_on && (info & kInfoWindow))
+                v = v > 0.0f ? __fdiv_rn(v, r.prm.repeat_penalty) : __fmul_rn(v, r.prm.repeat_penalty);   // :166
+              if (r.pp_on) v = __fsub_rn(v, r.prm.presence_penalty);                                      // :171
+            }
+            if (info & kInfoBan) v = ARCS_BANNED;                                                         // :174
+          }
+          consider(valid, v, (int32_t)ck, true);
         }
       }
-    }
-    // every thread is done with the tile: refill the slot, prune if the buffer has grown
-    const int any = __syncthreads_or(hot);
-    if (tid == 0 && t + kStages < p.tiles) issue_tile(p, t + kStages, stage, bars);
-    if (any) {
-      maybe_prune();
-      hot = false;
-    }
-  }
-  // ---- the scalar elements after the last and before the first 16-byte boundary. The tail
-  // follows the stream in id order; the head has the lowest ids of the segment, so there a tie
-  // with the smallest kept key must still be taken.
-  {
-    __syncthreads();
-    maybe_prune();
-    hot = false;
-    const bool valid = tid < p.tail_n;
-    const float v = valid ? Elem<T>::load(row + p.tail_first + tid) : 0.0f;
-    consider(valid, v, p.tail_first + tid, *selB.tau_key, MASKED ? *selA.tau_key : 0u, false);
-    __syncthreads();
-    maybe_prune();
-    hot = false;
-    const bool hvalid = tid < p.head_n;
-    const float hv = hvalid ? Elem<T>::load(row + lo + tid) : 0.0f;
-    const uint32_t tb = *selB.tau_key, ta = MASKED ? *selA.tau_key : 0u;
-    consider(hvalid, hv, lo + tid, tb ? tb - 1u : 0u, ta ? ta - 1u : 0u, false);
-  }
+      group_sync();
+      if (MASKED) sel_prune(selA, selA.k, ps, gt);
 
-  // ---- touched tokens: exact fp32 arithmetic of Sampler::adjusted, one token per thread
-  if (touched_on) {
-    for (int s0 = 0; s0 < a.hash_slots; s0 += kThreads) {
-      __syncthreads();
-      maybe_prune();
-      hot = false;
-      const int s = s0 + tid;
-      const uint32_t ck = hkey[s];
-      const bool valid = ck != kEmpty;
-      float v = 0.0f;
-      if (valid) {
-        const uint32_t info = hinfo[s];
-        const uint32_t cnt = info & kInfoCount;
-        v = Elem<T>::load(row + (int32_t)ck);
-        if (info & kInfoBias) {  // :154-155 in list order, duplicates add again
-          const int32_t g = (int32_t)ck + a.id_base;
-          for (int i = 0; i < NB; ++i)
-            if (a.bias_ids[q0 + i] == g && a.bias_vals[q0 + i] > -100.0f) v = __fadd_rn(v, a.bias_vals[q0 + i]);
+      // rows cut into segments: publish this segment's survivors; the CTA that arrives last merges
+      if (a.nseg > 1) {
+        sel_prune(selB, selB.k, ps, gt);
+        char* blk = a.ws_seg + ((size_t)b * a.nseg + it.seg) * a.seg_block;
+        int32_t* hdr = reinterpret_cast<int32_t*>(blk);
+        uint32_t* wk = reinterpret_cast<uint32_t*>(blk + 16);
+        int32_t* wi = reinterpret_cast<int32_t*>(wk + ARCS_KCAP);
+        const int nb = min(*selB.cnt, ARCS_KCAP), na = MASKED ? min(*selA.cnt, ARCS_HEAD) : 0;
+        for (int i = gt; i < nb; i += kGroup) {
+          wk[i] = selB.key[i];
+          wi[i] = selB.id[i];
         }
-        if (pen_on && cnt > 0) {
-          if (fp_on) v = __fsub_rn(v, __fmul_rn(prm.frequency_penalty, (float)cnt));             // :160
-          if (rp_on && (info & kInfoWindow))
-            v = v > 0.0f ? __fdiv_rn(v, prm.repeat_penalty) : __fmul_rn(v, prm.repeat_penalty);   // :166
-          if (pp_on) v = __fsub_rn(v, prm.presence_penalty);                                      // :171
-        }
-        if (info & kInfoBan) v = ARCS_BANNED;                                                     // :174
-      }
-      // these ids are not in stream order: a tie with the smallest kept key must still be taken
-      const uint32_t tb = *selB.tau_key, ta = MASKED ? *selA.tau_key : 0u;
-      consider(valid, v, (int32_t)ck, tb ? tb - 1u : 0u, ta ? ta - 1u : 0u, true);
-    }
-  }
-  __syncthreads();
-  sel_prune(selB, selB.k, ps);
-  if (MASKED) sel_prune(selA, selA.k, ps);
-  __syncthreads();
-
-  // ---- rows cut into segments: publish this segment's survivors; the last CTA merges them
-  if (a.nseg > 1) {
-    char* blk = a.ws_seg + ((size_t)b * a.nseg + seg) * a.seg_block;
-    int32_t* hdr = reinterpret_cast<int32_t*>(blk);
-    uint32_t* wk = reinterpret_cast<uint32_t*>(blk + 16);
-    int32_t* wi = reinterpret_cast<int32_t*>(wk + ARCS_KCAP);
-    const int nb = min(sh[S_CNT_B], ARCS_KCAP), na = MASKED ? min(sh[S_CNT_A], ARCS_HEAD) : 0;
-    for (int i = tid; i < nb; i += kThreads) {
-      wk[i] = bkey[i];
-      wi[i] = bid[i];
-    }
-    if (MASKED) {
-      uint32_t* xk = reinterpret_cast<uint32_t*>(wi + ARCS_KCAP);
-      int32_t* xi = reinterpret_cast<int32_t*>(xk + ARCS_HEAD);
-      for (int i = tid; i < na; i += kThreads) {
-        xk[i] = akey[i];
-        xi[i] = aid[i];
-      }
-    }
-    if (tid == 0) {
-      hdr[0] = nb;
-      hdr[1] = na;
-      hdr[2] = bans;
-    }
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-      const unsigned int old = atomicAdd(&a.ws_arrive[b], 1u);
-      sh[S_LAST] = old == (unsigned int)a.nseg - 1u;
-      if (sh[S_LAST]) a.ws_arrive[b] = 0u;  // ready for the next launch
-    }
-    __syncthreads();
-    if (!sh[S_LAST]) return;
-    __threadfence();
-    if (tid == 0) {
-      sh[S_CNT_B] = 0;
-      sh[S_TAU_B] = 0;
-      sh[S_CNT_A] = 0;
-      sh[S_TAU_A] = 0;
-    }
-    hot = false;
-    for (int g = 0; g < a.nseg; ++g) {
-      const char* gb = a.ws_seg + ((size_t)b * a.nseg + g) * a.seg_block;
-      const int32_t* gh = reinterpret_cast<const int32_t*>(gb);
-      const uint32_t* gk = reinterpret_cast<const uint32_t*>(gb + 16);
-      const int32_t* gi = reinterpret_cast<const int32_t*>(gk + ARCS_KCAP);
-      const int gnb = __ldcg(&gh[0]), gna = __ldcg(&gh[1]);
-      bans = bans || __ldcg(&gh[2]) != 0;
-      const int rounds = MASKED ? (ARCS_HEAD + kThreads - 1) / kThreads : 1;
-      for (int r = 0; r < rounds; ++r) {
-        __syncthreads();
-        maybe_prune();
-        hot = false;
-        const int i = r * kThreads + tid;
-        const uint32_t tb = *selB.tau_key;
-        const bool pb = i < gnb;
-        uint32_t ky = pb ? __ldcg(&gk[i]) : 0u;
-        sel_push(selB, pb && ky >= (tb ? tb - 1u : 0u), ky, pb ? __ldcg(&gi[i]) : 0, hot, a.status);
         if (MASKED) {
-          const uint32_t* xk = reinterpret_cast<const uint32_t*>(gi + ARCS_KCAP);
-          const int32_t* xi = reinterpret_cast<const int32_t*>(xk + ARCS_HEAD);
-          const uint32_t ta = *selA.tau_key;
-          const bool pa = i < gna;
-          ky = pa ? __ldcg(&xk[i]) : 0u;
-          sel_push(selA, pa && ky >= (ta ? ta - 1u : 0u), ky, pa ? __ldcg(&xi[i]) : 0, hot, a.status);
-        }
-      }
-    }
-    __syncthreads();
-    sel_prune(selB, selB.k, ps);
-    if (MASKED) sel_prune(selA, selA.k, ps);
-    __syncthreads();
-  }
-
-  // ---- finish the row: candidates best first, then tools/sampler.h:54-77 (or :105-143)
-  int nB = min(sh[S_CNT_B], selB.k);
-  sel_sort(selB, nB, sv, sid);
-  if (tid == 0) {
-    s64[0] = 0ull;                    // best composite among head entries that are not skipped as banned
-    s64[1] = 0xFFFFFFFFFFFFFFFFull;   // smallest composite of the head
-  }
-  __syncthreads();
-  int flags = 0, nc = nB;
-  if (MASKED) {
-    const int nA = min(sh[S_CNT_A], ARCS_HEAD);
-    for (int i = tid; i < nA; i += kThreads) {
-      const uint64_t c = comp_of(akey[i], aid[i]);
-      if (!(bans && value_of(akey[i]) <= ARCS_BANNED)) atomicMax(&s64[0], (unsigned long long)c);
-      atomicMin(&s64[1], (unsigned long long)c);
-    }
-    __syncthreads();
-    if (tid == 0) {
-      const uint64_t top = s64[0], low = s64[1];
-      if (top != 0ull && (nB == 0 || comp_of(key_of(sv[0]), sid[0]) != top)) flags |= ARCS_FLAG_FIRST_REFUSED;
-      if (Vg > ARCS_HEAD && nA == ARCS_HEAD) {  // the scan reaches rank 512 (tools/sampler.h:106-116)
-        int nh = 0;
-        while (nh < nB && comp_of(key_of(sv[nh]), sid[nh]) >= low) ++nh;
-        if (nh < selB.k) {
-          const float l512 = value_of(comp_key(low));
-          if (!greedy && nh > 0 && __fdiv_rn(__fsub_rn(sv[0], l512), prm.temperature) > 20.0f) {  // :111
-            nc = nh;
-            flags |= ARCS_FLAG_TAIL_SKIPPED;
-          } else {
-            flags |= ARCS_FLAG_TAIL_USED;
+          uint32_t* xk = reinterpret_cast<uint32_t*>(wi + ARCS_KCAP);
+          int32_t* xi = reinterpret_cast<int32_t*>(xk + ARCS_HEAD);
+          for (int i = gt; i < na; i += kGroup) {
+            xk[i] = selA.key[i];
+            xi[i] = selA.id[i];
           }
         }
+        if (gt == 0) {
+          hdr[0] = nb;
+          hdr[1] = na;
+          hdr[2] = bans;
+        }
+        __threadfence();
+        group_sync();
+        if (gt == 0) {
+          const unsigned int old = atomicAdd(&a.ws_arrive[b], 1u);
+          sh[S_LAST] = old == (unsigned int)a.nseg - 1u;
+          if (sh[S_LAST]) a.ws_arrive[b] = 0u;  // ready for the next launch
+        }
+        group_sync();
+        if (!sh[S_LAST]) {
+          group_sync();
+          return true;
+        }
+        __threadfence();
+        if (gt == 0) {
+          *selB.cnt = 0;
+          *selA.cnt = 0;
+          *selB.tau = 0ull;
+          *selA.tau = 0ull;
+        }
+        hot = false;
+        for (int g = 0; g < a.nseg; ++g) {
+          const char* gb = a.ws_seg + ((size_t)b * a.nseg + g) * a.seg_block;
+          const int32_t* gh = reinterpret_cast<const int32_t*>(gb);
+          const uint32_t* gk = reinterpret_cast<const uint32_t*>(gb + 16);
+          const int32_t* gi = reinterpret_cast<const int32_t*>(gk + ARCS_KCAP);
+          const int gnb = __ldcg(&gh[0]), gna = __ldcg(&gh[1]);
+          bans = bans || __ldcg(&gh[2]) != 0;
+          const int rounds = MASKED ? (ARCS_HEAD + kGroup - 1) / kGroup : 1;
+          for (int rr = 0; rr < rounds; ++rr) {
+            group_sync();
+            maybe_prune();
+            hot = false;
+            const int i = rr * kGroup + gt;
+            const bool pb = i < gnb;
+            uint32_t ky = pb ? __ldcg(&gk[i]) : 0u;
+            int32_t id = pb ? __ldcg(&gi[i]) : 0;
+            sel_push(selB, pb && comp_of(ky, id) > *selB.tau, ky, id, hot, a.status);
+            if (MASKED) {
+              const uint32_t* xk = reinterpret_cast<const uint32_t*>(gi + ARCS_KCAP);
+              const int32_t* xi = reinterpret_cast<const int32_t*>(xk + ARCS_HEAD);
+              const bool pa = i < gna;
+              ky = pa ? __ldcg(&xk[i]) : 0u;
+              id = pa ? __ldcg(&xi[i]) : 0;
+              sel_push(selA, pa && comp_of(ky, id) > *selA.tau, ky, id, hot, a.status);
+            }
+          }
+        }
+        group_sync();
+        if (MASKED) sel_prune(selA, selA.k, ps, gt);
       }
-      sh[S_NCAND] = nc;
-      sh[S_FLAGS] = flags;
-    }
-    __syncthreads();
-    nc = sh[S_NCAND];
-  } else {
-    if (tid == 0) {
-      if (bans)  // tools/sampler.h:54-55
-        while (nc > 1 && sv[nc - 1] <= ARCS_BANNED) --nc;
-      sh[S_NCAND] = nc;
-    }
-    __syncthreads();
-    nc = sh[S_NCAND];
-  }
-  // equal logits among the candidates kept: the reference's order there is not defined
-  {
-    bool tie = false;
-    for (int i = tid; i + 1 < nc; i += kThreads) tie = tie || sv[i] == sv[i + 1];
-    if (tie) atomicOr(&sh[S_FLAGS], ARCS_FLAG_TIE_TOPK);
-  }
-  const bool draw = !greedy && nc > 1 || (!MASKED && !greedy && nc == 1);
-  if (draw) {
-    const float mx = sv[0];
-    for (int i = tid; i < nc; i += kThreads) {
-      const float x = __fdiv_rn(__fsub_rn(sv[i], mx), prm.temperature);  // :60 float arithmetic
-      spr[i] = (double)(float)exp((double)x);                            // float exp, widened
-    }
-  }
-  __syncthreads();
-  if (tid == 0) {
-    int token = nc > 0 ? sid[0] : -1, n = nc > 0 ? 1 : 0;
-    if (draw) {
-      double z = 0.0;
-      for (int i = 0; i < nc; ++i) z = __dadd_rn(z, spr[i]);
-      for (int i = 0; i < nc; ++i) spr[i] = __ddiv_rn(spr[i], z);
-      n = nc;
-      double cum = 0.0;
-      const double mp = __dmul_rn((double)prm.min_p, spr[0]);
-      for (int i = 0; i < nc; ++i) {
-        if (prm.min_p > 0.0f && spr[i] < mp) { n = max(1, i); break; }          // :65
-        cum = __dadd_rn(cum, spr[i]);
-        if (cum >= (double)prm.top_p) { n = i + 1; break; }                     // :67
+
+      // ---- candidates best first. Up to 512 entries are ranked by counting, which selects the k
+      // best and sorts them in one step; a longer buffer is cut by the radix select first.
+      if (*selB.cnt > 2 * kGroup) sel_prune(selB, selB.k, ps, gt);
+      group_sync();
+      const int nbuf = min(*selB.cnt, 2 * kGroup);
+      const int nB = min(nbuf, selB.k);
+      for (int i = gt; i < nbuf; i += kGroup) {
+        const uint32_t ky = selB.key[i];
+        const int32_t id = selB.id[i];
+        const uint64_t c = comp_of(ky, id);
+        int rank = 0;
+        for (int x = 0; x < nbuf; ++x) rank += comp_of(selB.key[x], selB.id[x]) > c;
+        if (rank < nB) {
+          sv[rank] = value_of(ky);
+          sid[rank] = id;
+        }
       }
-      double tot = 0.0;
-      for (int i = 0; i < n; ++i) tot = __dadd_rn(tot, spr[i]);
-      double r = __dmul_rn(a.u[b], tot);                                        // :71-72
-      int pick = n - 1;
-      for (int i = 0; i < n; ++i) {
-        r = __dsub_rn(r, spr[i]);
-        if (r <= 0.0) { pick = i; break; }
+      if (gt == 0) {
+        s64[L_TOP] = 0ull;                    // best composite among head entries that are not skipped as banned
+        s64[L_LOW] = 0xFFFFFFFFFFFFFFFFull;   // smallest composite of the head
+        sh[S_FLAGS] = 0;
       }
-      token = sid[pick];
+      group_sync();
+      // ---- tools/sampler.h:54-77 (or :105-143)
+      int flags = 0, nc = nB;
+      if (MASKED) {
+        const int nA = min(*selA.cnt, ARCS_HEAD);
+        for (int i = gt; i < nA; i += kGroup) {
+          const uint64_t c = comp_of(selA.key[i], selA.id[i]);
+          if (!(bans && value_of(selA.key[i]) <= ARCS_BANNED)) atomicMax(&s64[L_TOP], (unsigned long long)c);
+          atomicMin(&s64[L_LOW], (unsigned long long)c);
+        }
+        group_sync();
+        if (gt == 0) {
+          const uint64_t top = s64[L_TOP], low = s64[L_LOW];
+          if (top != 0ull && (nB == 0 || comp_of(key_of(sv[0]), sid[0]) != top)) flags |= ARCS_FLAG_FIRST_REFUSED;
+          if (Vg > ARCS_HEAD && nA == ARCS_HEAD) {  // the scan reaches rank 512 (tools/sampler.h:106-116)
+            int nh = 0;
+            while (nh < nB && comp_of(key_of(sv[nh]), sid[nh]) >= low) ++nh;
+            if (nh < selB.k) {
+              const float l512 = value_of(comp_key(low));
+              if (!r.greedy && nh > 0 && __fdiv_rn(__fsub_rn(sv[0], l512), r.prm.temperature) > 20.0f) {  // :111
+                nc = nh;
+                flags |= ARCS_FLAG_TAIL_SKIPPED;
+              } else {
+                flags |= ARCS_FLAG_TAIL_USED;
+              }
+            }
+          }
+          sh[S_NCAND] = nc;
+          sh[S_FLAGS] = flags;
+        }
+        group_sync();
+        nc = sh[S_NCAND];
+      } else {
+        if (gt == 0) {
+          if (bans)  // tools/sampler.h:54-55
+            while (nc > 1 && sv[nc - 1] <= ARCS_BANNED) --nc;
+          sh[S_NCAND] = nc;
+        }
+        group_sync();
+        nc = sh[S_NCAND];
+      }
+      {  // equal logits among the candidates kept: the reference's order there is not defined
+        bool tie = false;
+        for (int i = gt; i + 1 < nc; i += kGroup) tie = tie || sv[i] == sv[i + 1];
+        if (tie) atomicOr(&sh[S_FLAGS], ARCS_FLAG_TIE_TOPK);
+      }
+      const bool draw = (!r.greedy && nc > 1) || (!MASKED && !r.greedy && nc == 1);
+      if (draw) {
+        const float mx = sv[0];
+        for (int i = gt; i < nc; i += kGroup) {
+          const float x = __fdiv_rn(__fsub_rn(sv[i], mx), r.prm.temperature);  // :60 float arithmetic
+          spr[i] = (double)(float)exp((double)x);                              // float exp, widened
+        }
+        group_sync();
+        if (gt == 0) {
+          double z = 0.0;
+          for (int i = 0; i < nc; ++i) z = __dadd_rn(z, spr[i]);  // :58-60 in candidate order
+          spr[ARCS_KCAP] = z;
+        }
+        group_sync();
+        const double z = spr[ARCS_KCAP];
+        for (int i = gt; i < nc; i += kGroup) spr[i] = __ddiv_rn(spr[i], z);  // :64, the same quotients in any order
+      }
+      group_sync();
+      if (gt == 0) {
+        int token = nc > 0 ? sid[0] : -1, n = nc > 0 ? 1 : 0;
+        if (draw) {
+          n = nc;
+          double cum = 0.0;
+          const double mp = __dmul_rn((double)r.prm.min_p, spr[0]);
+          for (int i = 0; i < nc; ++i) {
+            if (r.prm.min_p > 0.0f && spr[i] < mp) { n = max(1, i); break; }        // :65
+            cum = __dadd_rn(cum, spr[i]);
+            if (cum >= (double)r.prm.top_p) { n = i + 1; break; }                   // :67
+          }
+          double tot = 0.0;
+          for (int i = 0; i < n; ++i) tot = __dadd_rn(tot, spr[i]);
+          double rr = __dmul_rn(a.u[b], tot);                                       // :71-72
+          int pick = n - 1;
+          for (int i = 0; i < n; ++i) {
+            rr = __dsub_rn(rr, spr[i]);
+            if (rr <= 0.0) { pick = i; break; }
+          }
+          token = sid[pick];
+        }
+        if (r.k_bad || !r.lists_ok) token = -1;
+        a.token[b] = token;
+        if (a.n_cand) a.n_cand[b] = nc;
+        if (a.n_kept) a.n_kept[b] = n;
+      }
+      group_sync();
+      if (gt == 0 && a.flags) a.flags[b] = sh[S_FLAGS];
+      for (int i = gt; i < a.cand_stride && (a.cand_id || a.cand_val || a.cand_pr); i += kGroup) {
+        const size_t o = (size_t)b * a.cand_stride + i;
+        const bool in = i < nc;
+        if (a.cand_id) a.cand_id[o] = in ? sid[i] : -1;
+        if (a.cand_val) a.cand_val[o] = in ? sv[i] : 0.0f;
+        if (a.cand_pr) a.cand_pr[o] = in ? (draw ? (float)spr[i] : (i == 0 ? 1.0f : 0.0f)) : 0.0f;
+      }
+      group_sync();
+      return true;
+    };
+
+    if (my_n > 0) prepare(0);
+    for (int j = 0; j < my_n; ++j) {
+      RT(0);
+      if (j + 1 < my_n) prepare(j + 1);
+      RT(1);
+      if (!finish(j)) break;
+      RT(2);
     }
-    if (k_bad || !lists_ok) token = -1;
-    a.token[b] = token;
-    if (a.n_cand) a.n_cand[b] = nc;
-    if (a.n_kept) a.n_kept[b] = n;
-    sh[S_NKEPT] = n;
-  }
-  __syncthreads();
-  if (tid == 0 && a.flags) a.flags[b] = sh[S_FLAGS];
-  for (int i = tid; i < a.cand_stride && (a.cand_id || a.cand_val || a.cand_pr); i += kThreads) {
-    const size_t o = (size_t)b * a.cand_stride + i;
-    const bool in = i < nc;
-    if (a.cand_id) a.cand_id[o] = in ? sid[i] : -1;
-    if (a.cand_val) a.cand_val[o] = in ? sv[i] : 0.0f;
-    if (a.cand_pr) a.cand_pr[o] = in ? (draw ? (float)spr[i] : (i == 0 ? 1.0f : 0.0f)) : 0.0f;
+    RT_FLUSH(12, gt == 0);
   }
 }
 
 static size_t sample_smem_bytes(bool masked, int hash_slots) {
-  size_t n = (size_t)kStages * kTileBytes + kStages * 8 + 512 * 4 + (size_t)kTmpCap * 8 + 8 * 4 + 24 * 4;
-  n += (size_t)kCapB * 8;
-  if (masked) n += (size_t)kCapA * 8;
-  n += (size_t)hash_slots * 8;
-  n += (size_t)(kTileBytes / 16) * 2;
+  size_t n = (size_t)kRing * kSTile + (size_t)kQueue * 8 + 2 * kRing * 8 + L_END * 8 + (ARCS_KCAP + 1) * 8 +
+             (size_t)kQueue * 4 + (512 + 256 + 1024) * 4 + (size_t)kTmpCap * 16 + 8 * 4 + S_END * 4 + ARCS_KCAP * 8;
+  n += (size_t)2 * kCapB * 8;
+  if (masked) n += (size_t)2 * kCapA * 8;
+  n += (size_t)2 * hash_slots * 8;
   return n + 128;
 }
 
 }  // namespace arcs
 
 using namespace arcs;
+
+#ifdef ARCS_ROLE_TIMING
+extern "C" int arcs_debug_roles(unsigned long long* out32) {
+  unsigned long long z[32] = {0};
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(out32, g_role, sizeof(z));
+  cudaMemcpyToSymbol(g_role, z, sizeof(z));
+  return 0;
+}
+#endif
 
 extern "C" size_t arcs_sample_workspace_bytes(int32_t B, int32_t V, int32_t masked) {
   if (B <= 0 || V <= 0) return 0;
@@ -610,7 +1141,7 @@ extern "C" int arcs_sample_batch(const arcs_sample_args* g, void* stream) {
   a.max_bias = g->bias_off ? g->max_bias : 0;
   int slots = 32;
   while (slots < 2 * (a.max_hist + a.max_bias)) slots <<= 1;
-  if (slots < kThreads) slots = kThreads;
+  if (slots < kGroup) slots = kGroup;
   a.hash_slots = slots;
   a.hash_shift = 32;
   for (int s = slots; s > 1; s >>= 1) --a.hash_shift;
@@ -631,12 +1162,13 @@ extern "C" int arcs_sample_batch(const arcs_sample_args* g, void* stream) {
   const size_t smem = sample_smem_bytes(masked, slots);
   if (smem > 227 * 1024) return set_error(ARCS_ERR_LIST, "sample_batch: history / bias lists too long for the on-chip table");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const dim3 grid((unsigned)a.nseg * (unsigned)a.B);
+  const int items = a.nseg * a.B;
+  const dim3 grid((unsigned)(items < kSmCount ? items : kSmCount));
 #define ARCS_LAUNCH(T, M)                                                                                \
   do {                                                                                                   \
     cudaError_t e = cudaFuncSetAttribute(sample_kernel<T, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     if (e != cudaSuccess) return set_error(ARCS_ERR_CUDA, cudaGetErrorString(e));                        \
-    sample_kernel<T, M><<<grid, kThreads, smem, st>>>(a);                                                \
+    sample_kernel<T, M><<<grid, kThreadsP, smem, st>>>(a);                                                \
   } while (0)
   if (g->dtype == ARCS_F32) {
     if (masked) ARCS_LAUNCH(float, true);
