@@ -46,6 +46,10 @@ template <> struct Elem<float> {
   static __device__ __forceinline__ float chunk_max(const uint4& q) {
     return fmaxf(fmaxf(__uint_as_float(q.x), __uint_as_float(q.y)), fmaxf(__uint_as_float(q.z), __uint_as_float(q.w)));
   }
+  // chunk-level threshold test: `thr` is made once from a float threshold by make_thr
+  typedef float Thr;
+  static __device__ __forceinline__ Thr make_thr(float t) { return t; }
+  static __device__ __forceinline__ bool chunk_reaches(const uint4& q, Thr t) { return chunk_max(q) >= t; }
 };
 template <> struct Elem<__nv_bfloat16> {
   static constexpr int kPerChunk = 8;
@@ -66,6 +70,17 @@ template <> struct Elem<__nv_bfloat16> {
     __nv_bfloat162 d = *reinterpret_cast<const __nv_bfloat162*>(&q.w);
     const __nv_bfloat162 m = __hmax2(__hmax2(a, b), __hmax2(c, d));  // NaN-ignoring packed max
     return fmaxf(__low2float(m), __high2float(m));
+  }
+  // chunk-level threshold test on packed pairs: the threshold is rounded DOWN to bf16, so the
+  // test can only err on the side of listing a chunk
+  typedef __nv_bfloat162 Thr;
+  static __device__ __forceinline__ Thr make_thr(float t) { return __bfloat162bfloat162(__float2bfloat16_rd(t)); }
+  static __device__ __forceinline__ bool chunk_reaches(const uint4& q, Thr t) {
+    __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&q.x);
+    __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&q.y);
+    __nv_bfloat162 c = *reinterpret_cast<const __nv_bfloat162*>(&q.z);
+    __nv_bfloat162 d = *reinterpret_cast<const __nv_bfloat162*>(&q.w);
+    return __hge2_mask(__hmax2(__hmax2(a, b), __hmax2(c, d)), t) != 0u;
   }
 };
 
@@ -108,9 +123,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   for (uint32_t it = 0; it < kWaitLimit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (it > 1024) __nanosleep(64);
+    if (it > 1) __nanosleep(it > 64 ? 256 : 64);
   }
   return false;
+}
+// The same wait for a whole warp: one lane polls (32 polling lanes would flood the shared-memory
+// pipeline the other warps need), then every lane observes the completed phase once.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity);
+  ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
+  if (ok) mbar_try_wait(bar, parity);
+  return ok != 0;
 }
 // global -> shared bulk copy of `bytes` (multiple of 16; both addresses 16-byte aligned),
 // completion counted on `bar`. No multicast: the destination is this CTA's own shared memory.
@@ -119,6 +143,37 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                    smem_addr(dst)),
                "l"(src), "r"(bytes), "r"(smem_addr(bar))
                : "memory");
+}
+
+
+// ---------------------------------------------------------------- explicit shared-memory accesses
+// Pointers that travel through structs or out-of-line functions lose their address space and
+// compile to generic accesses; these helpers keep atomics and polled words on the shared path.
+__device__ __forceinline__ uint32_t sm_atomic_add(void* p, uint32_t v) {
+  uint32_t old;
+  asm volatile("atom.shared.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(smem_addr(p)), "r"(v) : "memory");
+  return old;
+}
+__device__ __forceinline__ void sm_red_add(void* p, uint32_t v) {
+  asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(smem_addr(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t sm_ld_volatile(const void* p) {
+  uint32_t v;
+  asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_addr(p)) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint32_t sm_ld(const void* p) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_addr(p)));
+  return v;
+}
+__device__ __forceinline__ unsigned long long sm_ld_volatile64(const void* p) {
+  unsigned long long v;
+  asm volatile("ld.volatile.shared.u64 %0, [%1];" : "=l"(v) : "r"(smem_addr(p)) : "memory");
+  return v;
+}
+__device__ __forceinline__ void sm_st_volatile64(void* p, unsigned long long v) {
+  asm volatile("st.volatile.shared.u64 [%0], %1;" ::"r"(smem_addr(p)), "l"(v) : "memory");
 }
 
 __device__ __forceinline__ uint4 lds128(const void* p) { return *reinterpret_cast<const uint4*>(p); }

@@ -80,10 +80,16 @@ __host__ __device__ inline int32_t seg_block_bytes(bool masked) {
 __device__ unsigned long long g_role[32];
 #define RT_DECL long long rt_last = clock64(); unsigned long long rt0 = 0, rt1 = 0, rt2 = 0, rt3 = 0
 #define RT(i) do { const long long n_ = clock64(); const unsigned long long d_ = (unsigned long long)(n_ - rt_last); rt_last = n_; if (i == 0) rt0 += d_; else if (i == 1) rt1 += d_; else if (i == 2) rt2 += d_; else rt3 += d_; } while (0)
+#define RT_COUNT(i, n) do { if (blockIdx.x == 0 && tid == 0) atomicAdd(&g_role[i], (unsigned long long)(n)); } while (0)
+#define XE_T(v) const long long v = clock64()
+#define XE_ADD(i, d) do { if (blockIdx.x == 0 && threadIdx.x == 0) atomicAdd(&g_role[i], (unsigned long long)(d)); } while (0)
 #define RT_FLUSH(base, cond) do { if (blockIdx.x == 0 && (cond)) { atomicAdd(&g_role[base], rt0); atomicAdd(&g_role[base + 1], rt1); atomicAdd(&g_role[base + 2], rt2); atomicAdd(&g_role[base + 3], rt3); } } while (0)
 #else
 #define RT_DECL
 #define RT(i)
+#define RT_COUNT(i, n)
+#define XE_T(v)
+#define XE_ADD(i, d)
 #define RT_FLUSH(base, cond)
 #endif
 
@@ -147,8 +153,7 @@ struct ScanCtx {
   uint32_t* histA;
   uint32_t baseB, baseA;
   int* sh;                 // shared scalars (queue head / tail, abort flag)
-  uint2* q_ent;
-  uint32_t* q_seq;
+  unsigned long long* q_ent;  // queue slots: 0 = empty, else key | (id, flags) << 32
   int32_t* status;
   int32_t col0, id_base;   // global id of the tile's first element
   uint64_t tcB, tcA;       // thresholds the chunk was listed against
@@ -157,7 +162,7 @@ struct ScanCtx {
 __device__ __forceinline__ bool table_has(const uint32_t* hk, int32_t slots, int32_t shift, int32_t c) {
   uint32_t h = hash_of(c, shift);
   for (int probe = 0; probe < slots; ++probe) {
-    const uint32_t kx = hk[h];
+    const uint32_t kx = sm_ld(&hk[h]);
     if (kx == kEmpty) return false;
     if (kx == (uint32_t)c) return true;
     h = (h + 1) & (uint32_t)(slots - 1);
@@ -166,20 +171,19 @@ __device__ __forceinline__ bool table_has(const uint32_t* hk, int32_t slots, int
 }
 
 // append one entry to the scanner -> examiner queue (the caller holds reservation e)
-__device__ __forceinline__ void queue_write(int* sh, uint2* q_ent, uint32_t* q_seq, int32_t* status, uint32_t e,
+__device__ __forceinline__ void queue_write(int* sh, unsigned long long* q_ent, int32_t* status, uint32_t e,
                                             uint32_t key, uint32_t idp) {
-  volatile int* vsh = sh;
   uint32_t spins = 0;  // bounded wait for room
-  while ((int32_t)(e - (uint32_t)vsh[S_QHEAD]) >= kQueue && !vsh[S_ABORT]) {
+  while ((int32_t)(e - sm_ld_volatile(&sh[S_QHEAD])) >= kQueue && !sm_ld_volatile(&sh[S_ABORT])) {
     if (++spins > kWaitLimit) {
-      vsh[S_ABORT] = 1;
+      *reinterpret_cast<volatile int*>(&sh[S_ABORT]) = 1;
       raise_status(status, ARCS_ERR_TIMEOUT);
     }
     __nanosleep(32);
   }
-  q_ent[e % kQueue] = make_uint2(key, idp);
-  __threadfence_block();
-  *reinterpret_cast<volatile uint32_t*>(&q_seq[e % kQueue]) = e + 1u;
+  // one 64-bit store publishes the entry: a slot is zero until written and zeroed again by the
+  // examiner before it frees it (an entry is never zero: data has a non-zero key, a marker a non-zero id)
+  sm_st_volatile64(&q_ent[e % kQueue], (unsigned long long)key | ((unsigned long long)idp << 32));
 }
 
 // The chunks of one warp-wide load whose maximum reached the threshold (bits of `bal`, chunk
@@ -188,17 +192,25 @@ template <typename T, bool MASKED>
 __device__ __noinline__ void scan_examine(const ScanCtx& c, uint4 q, int cbase, unsigned bal) {
   constexpr int E = Elem<T>::kPerChunk;
   const int lane = threadIdx.x & 31;
+#ifdef ARCS_X_EMPTY
+  return;
+#endif
   while (bal) {
     const int jj = lane / E, el = lane % E;
-    const unsigned src = __fns(bal, 0, jj + 1);
-    const bool valid = src < 32u;
-    const int sl = valid ? (int)src : 0;
+    unsigned rest = bal;  // lane group jj takes the jj-th listed chunk
+#pragma unroll
+    for (int i = 0; i < 32 / E - 1; ++i)
+      if (i < jj) rest &= rest - 1u;
+    const bool valid = rest != 0u;
+    const int sl = valid ? __ffs(rest) - 1 : 0;
+    XE_T(t0_);
     const uint32_t w0 = __shfl_sync(0xFFFFFFFFu, q.x, sl), w1 = __shfl_sync(0xFFFFFFFFu, q.y, sl);
     const uint32_t w2 = __shfl_sync(0xFFFFFFFFu, q.z, sl), w3 = __shfl_sync(0xFFFFFFFFu, q.w, sl);
     const float v = elem_of_words<T>(w0, w1, w2, w3, el);
     const int32_t gid = c.col0 + (cbase + sl) * E + el;
     const uint32_t ky = key_of(v);
     const uint64_t cm = comp_of(ky, gid);
+    XE_T(t1_);
     // eligible for the selection proper (B) / for the constrained head ranking (A)
     bool okB = valid && ky != 0u && cm > c.tcB;
     bool okA = MASKED && valid && ky != 0u && cm > c.tcA;
@@ -207,19 +219,30 @@ __device__ __noinline__ void scan_examine(const ScanCtx& c, uint4 q, int cbase, 
     // tokens the table replaces are taken from it when the item is finished, not from the stream
     if ((okB || okA) && c.touched && table_has(c.hk, c.hash_slots, c.hash_shift, gid - c.id_base)) okB = okA = false;
     // count the survivors by the upper 16 bits of their keys: the examiner reads thresholds off these counts
-    if (okB) atomicAdd(&c.histB[coarse_bin(ky, c.baseB)], 1u);
-    if (okA) atomicAdd(&c.histA[coarse_bin(ky, c.baseA)], 1u);
+#ifdef ARCS_X_NOPUSH
+    okB = okA = false;
+#endif
+    if (okB) sm_red_add(&c.histB[coarse_bin(ky, c.baseB)], 1u);
+    if (okA) sm_red_add(&c.histA[coarse_bin(ky, c.baseA)], 1u);
+    XE_T(t2_);
     const bool pass = okB || okA;
     const unsigned pb = __ballot_sync(0xFFFFFFFFu, pass);
     if (pb) {
       const int leader = __ffs(pb) - 1;
       uint32_t base = 0;
-      if (lane == leader) base = atomicAdd(reinterpret_cast<unsigned int*>(&c.sh[S_QTAIL]), (unsigned)__popc(pb));
+      if (lane == leader) base = sm_atomic_add(&c.sh[S_QTAIL], (unsigned)__popc(pb));
       base = __shfl_sync(0xFFFFFFFFu, base, leader);
+      XE_T(t3_);
+      XE_ADD(22, t3_ - t2_);
       if (pass)
-        queue_write(c.sh, c.q_ent, c.q_seq, c.status, base + __popc(pb & ((1u << lane) - 1u)), ky,
+        queue_write(c.sh, c.q_ent, c.status, base + __popc(pb & ((1u << lane) - 1u)), ky,
                     (uint32_t)gid | ((uint32_t)okB << 30) | ((uint32_t)c.par << 31));
     }
+    XE_T(t4_);
+    XE_ADD(20, t1_ - t0_);
+    XE_ADD(21, t2_ - t1_);
+    XE_ADD(23, t4_ - t2_);
+    XE_ADD(24, 1);
     const int done = min(__popc(bal), 32 / E);
     for (int i = 0; i < done; ++i) bal &= bal - 1u;
   }
@@ -230,13 +253,12 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
   extern __shared__ __align__(128) char smem[];
   // ---- carve shared memory (ordered by alignment)
   char* ring = smem;                                                          // kRing * kSTile
-  uint2* q_ent = reinterpret_cast<uint2*>(ring + (size_t)kRing * kSTile);  // [kQueue] (key, id | parity << 31)
+  unsigned long long* q_ent = reinterpret_cast<unsigned long long*>(ring + (size_t)kRing * kSTile);  // [kQueue]
   uint64_t* full = reinterpret_cast<uint64_t*>(q_ent + kQueue);               // [kRing] tile has landed
   uint64_t* empty = full + kRing;                                             // [kRing] tile has been scanned
   unsigned long long* s64 = reinterpret_cast<unsigned long long*>(empty + kRing);  // [L_END]
   double* spr = reinterpret_cast<double*>(s64 + L_END);                       // [ARCS_KCAP + 1]
-  uint32_t* q_seq = reinterpret_cast<uint32_t*>(spr + ARCS_KCAP + 1);         // [kQueue] entry number + 1 once written
-  uint32_t* hist = q_seq + kQueue;                                            // [512] finishers' radix histograms
+  uint32_t* hist = reinterpret_cast<uint32_t*>(spr + ARCS_KCAP + 1);                                                     // [512] finishers' radix histograms
   uint32_t* xhist = hist + 512;                                               // [256] examiner's radix histogram
   uint32_t* xh = xhist + 256;                                                 // [2 parities][B, A][256] coarse histograms
   uint32_t* tk = xh + 4 * 256;                                                 // [kTmpCap] finishers' scratch
@@ -271,7 +293,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
     for (int i = 0; i < S_END; ++i) sh[i] = 0;
     for (int i = 0; i < L_END; ++i) s64[i] = 0ull;
   }
-  for (int i = tid; i < kQueue; i += kThreadsP) q_seq[i] = 0u;
+  for (int i = tid; i < kQueue; i += kThreadsP) q_ent[i] = 0ull;
   for (int i = tid; i < 4 * 256; i += kThreadsP) xh[i] = 0u;
   __syncthreads();  // the only CTA-wide barrier
 
@@ -329,12 +351,15 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
       const Item<T> it = item_of<T>(a, (int)blockIdx.x + j * (int)gridDim.x);
       const int T_ = s_tiles(it.p);
       RT(0);
-      {  // the item's table and first threshold must be ready
-        uint32_t spins = 0;
-        while (vsh[S_PREPARED] <= j && !vsh[S_ABORT]) {
-          if (++spins > kWaitLimit) abort_now();
-          __nanosleep(64);
+      {  // the item's table and first threshold must be ready (one lane polls)
+        if (lane == 0) {
+          uint32_t spins = 0;
+          while (vsh[S_PREPARED] <= j && !vsh[S_ABORT]) {
+            if (++spins > kWaitLimit) abort_now();
+            __nanosleep(64);
+          }
         }
+        __syncwarp();
         __threadfence_block();
       }
       RT(1);
@@ -355,7 +380,6 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
       ctx.baseA = (uint32_t)sh[S_BASE_A + par];
       ctx.sh = sh;
       ctx.q_ent = q_ent;
-      ctx.q_seq = q_seq;
       ctx.status = a.status;
       ctx.id_base = a.id_base;
       const char* tile = ring + (size_t)warp * kSTile;
@@ -363,7 +387,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
         const uint32_t g = G0 + (uint32_t)t;
         if (vsh[S_ABORT]) break;
         RT(0);
-        if (!mbar_wait(&full[warp], (g / kRing) & 1u)) {
+        if (!mbar_wait_warp(&full[warp], (g / kRing) & 1u)) {
           abort_now();
           break;
         }
@@ -372,15 +396,16 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
         const int32_t col0 = it.p.body_first + t * (kSTile / (int)sizeof(T)) + a.id_base;  // global id of the tile's first element
         // thresholds are re-read for every group of chunks: the examiner raises them all the time
         uint64_t tcB = 0, tcA = 0;
-        float tfB = 0.0f, tfA = 0.0f;
+        typename Elem<T>::Thr thB, thA;
         auto refresh = [&]() {
           tcB = v64[L_TAU_B + par];
           tcA = MASKED ? v64[L_TAU_A + par] : 0xFFFFFFFFFFFFFFFFull;
-          // chunk-level test in float: inclusive on the threshold's value (ids are settled per element)
+          // chunk-level test on values: inclusive on the threshold's value (ids are settled per element)
           const uint32_t kB32 = (uint32_t)(tcB >> 32), kA32 = (uint32_t)(tcA >> 32);
-          tfB = value_of(kB32 < 0x007FFFFFu ? 0x007FFFFFu : kB32);
-          tfA = MASKED ? value_of(kA32 < 0x007FFFFFu ? 0x007FFFFFu : kA32) : INFINITY;
+          thB = Elem<T>::make_thr(value_of(kB32 < 0x007FFFFFu ? 0x007FFFFFu : kB32));
+          thA = Elem<T>::make_thr(MASKED ? value_of(kA32 < 0x007FFFFFu ? 0x007FFFFFu : kA32) : INFINITY);
         };
+        const bool whole = nchunk == kSTile / 16;  // only an item's last tile can be short
         ctx.col0 = col0;
 #ifndef ARCS_X_NOSCAN
         for (int c0 = 0; c0 < nchunk; c0 += 4 * 32) {
@@ -388,37 +413,38 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
           bool h[4];
           refresh();
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int ci = c0 + u * 32 + lane;
-            q[u] = ci < nchunk ? lds128(tile + ci * 16) : make_uint4(0, 0, 0, 0);
-          }
+          for (int u = 0; u < 4; ++u) q[u] = lds128(tile + (c0 + u * 32 + lane) * 16);  // (inside the slot even past a short tile's end)
 #pragma unroll
           for (int u = 0; u < 4; ++u) {
             const int ci = c0 + u * 32 + lane;
-            const float m = Elem<T>::chunk_max(q[u]);
-            h[u] = ci < nchunk && m >= tfB;
+            h[u] = Elem<T>::chunk_reaches(q[u], thB);
             if (MASKED) {
-              bool hb = h[u];
+              bool hb = h[u] && ci < nchunk;
               if (hb) {
                 const int32_t gid = col0 + ci * E;
                 uint32_t bits = __ldg(&mrow[gid >> 5]) >> (gid & 31);
                 if ((gid & 31) + E > 32) bits |= __ldg(&mrow[(gid >> 5) + 1]) << (32 - (gid & 31));
                 hb = (bits & ((1u << E) - 1u)) != 0u;
               }
-              h[u] = hb || (ci < nchunk && m >= tfA);
+              h[u] = hb || Elem<T>::chunk_reaches(q[u], thA);
             }
+            if (!whole) h[u] = h[u] && ci < nchunk;
 #ifdef ARCS_X_NOHOT
             h[u] = h[u] && a.V < 0;  // never true, but the test above is still evaluated
 #endif
           }
           if (__any_sync(0xFFFFFFFFu, h[0] || h[1] || h[2] || h[3])) {
+            RT(0);
+            RT_COUNT(16, 1);
             ctx.tcB = tcB;
             ctx.tcA = tcA;
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
               const unsigned bal = __ballot_sync(0xFFFFFFFFu, h[u]);
+              RT_COUNT(17, __popc(bal));
               if (bal) scan_examine<T, MASKED>(ctx, q[u], c0 + u * 32, bal);
             }
+            RT(3);
           }
         }
 #endif
@@ -429,7 +455,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
       __syncwarp();
       if (lane == 0) {  // this warp has queued everything it found in the item
         const uint32_t e = atomicAdd(reinterpret_cast<unsigned int*>(&sh[S_QTAIL]), 1u);
-        queue_write(sh, q_ent, q_seq, a.status, e, 0u, kMarker | ((uint32_t)par << 31));
+        queue_write(sh, q_ent, a.status, e, 0u, kMarker | ((uint32_t)par << 31));
       }
       G0 += (uint32_t)T_;
     }
@@ -475,7 +501,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
         __syncwarp();
       }
       cnt = out;
-      if (cnt > full - kStep) cnt = sel_prune_warp(sel, cnt, sel.k, xhist, xtk, xti);
+      if (full > 0 && cnt > full - kStep) cnt = sel_prune_warp(sel, cnt, sel.k, xhist, xtk, xti);
     };
     // threshold from the scanners' counts
     auto raise = [&](const Sel& sel, const uint32_t* hst, uint32_t base) {
@@ -497,12 +523,12 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
           abort_now();
           break;
         }
-        __nanosleep(32);
+        __nanosleep(200);
         continue;
       }
       if (avail < kStep && polls < 4) {  // let a fuller batch build up
         ++polls;
-        __nanosleep(32);
+        __nanosleep(200);
         continue;
       }
       idle = 0;
@@ -513,18 +539,15 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
 #pragma unroll
       for (int u = 0; u < kStep / 32; ++u) {
         const uint32_t e = head + (uint32_t)(u * 32 + lane);
+        unsigned long long w = 0ull;
         if (u * 32 + lane < nb) {
-          uint32_t spins = 0;  // the entry is reserved; its writer publishes it right after
-          while (*reinterpret_cast<volatile uint32_t*>(&q_seq[e % kQueue]) != e + 1u && !vsh[S_ABORT])
+          volatile unsigned long long* slot = &q_ent[e % kQueue];
+          uint32_t spins = 0;  // the entry is reserved; its writer stores it right after
+          while ((w = *slot) == 0ull && !vsh[S_ABORT])
             if (++spins > kWaitLimit) abort_now();
+          *slot = 0ull;  // empty again before the slot is freed below
         }
-      }
-      __syncwarp();
-      __threadfence_block();
-#pragma unroll
-      for (int u = 0; u < kStep / 32; ++u) {
-        const uint32_t e = head + (uint32_t)(u * 32 + lane);
-        ent[u] = u * 32 + lane < nb ? q_ent[e % kQueue] : make_uint2(0u, 0u);
+        ent[u] = make_uint2((uint32_t)w, (uint32_t)(w >> 32));
       }
       __syncwarp();
       __threadfence_block();
@@ -583,6 +606,15 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
         marks[par] += nmark;
         if (marks[par] == kScanW) {  // every scanner has closed the item: hand its buffers to the finishers
           marks[par] = 0;
+          if (loaded[par]) {  // leave the finishers only what the last threshold has not overtaken
+            const Sel sBk{sB.key, sB.id, sB.cnt, sB.tau, kk[par], 0, kCapB};
+            raise(sBk, xh + (2 * par) * 256, baseB[par]);
+            shrink(sBk, cB[par], 0);
+            if (MASKED) {
+              raise(sA, xh + (2 * par + 1) * 256, baseA[par]);
+              shrink(sA, cA[par], 0);
+            }
+          }
           __syncwarp();
           if (lane == 0) {
             sh[S_CNT_B + par] = cB[par];
@@ -711,20 +743,12 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
           m = fmaxf(m, Elem<T>::chunk_max(ldg128_stream(it.p.body + (size_t)ci * 16)));
           any = true;
         }
-        const uint32_t my = any ? key_of(m) : 0u;
-        tk[gt] = my;
-        if (gt == 0) s64[L_PRUNE_MIN] = 0ull;  // hand-over word of the rank search below
+        tk[gt] = any ? key_of(m) : 0u;
         group_sync();
         if (kth <= min(nchunk, kGroup)) {
-          int gtc = 0, gec = 0;
-          for (int x = 0; x < kGroup; ++x) {
-            const uint32_t o = tk[x];
-            gtc += o > my;
-            gec += o >= my;
-          }
-          if (gtc < kth && kth <= gec && my != 0u) s64[L_PRUNE_MIN] = (unsigned long long)my << 32;  // keeps ties with it
+          const uint32_t kk0 = group_kth_key(tk, kth, ps, gt);
+          tau0B = (unsigned long long)kk0 << 32;  // keeps ties with it
         }
-        group_sync();
       }
       if (MASKED) {
         const Sel sA{akey + par * kCapA, aid + par * kCapA, &sh[S_CNT_A + par], &s64[L_TAU_A + par], ARCS_HEAD, 1024, kCapA};
@@ -744,9 +768,6 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
         }
       }
       if (gt == 0) {
-        if (!MASKED) {
-          tau0B = s64[L_PRUNE_MIN];
-        }
         s64[L_TAU_B + par] = tau0B;
         s64[L_TAU_A + par] = tau0A;
         sh[S_CNT_B + par] = 0;
@@ -774,7 +795,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
         uint32_t spins = 0;
         while (vsh[S_STREAMED] <= j && !vsh[S_ABORT]) {
           if (++spins > kWaitLimit) abort_now();
-          __nanosleep(64);
+          __nanosleep(256);
         }
         bad = vsh[S_ABORT] != 0;
         __threadfence_block();
@@ -1073,7 +1094,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
 
 static size_t sample_smem_bytes(bool masked, int hash_slots) {
   size_t n = (size_t)kRing * kSTile + (size_t)kQueue * 8 + 2 * kRing * 8 + L_END * 8 + (ARCS_KCAP + 1) * 8 +
-             (size_t)kQueue * 4 + (512 + 256 + 1024) * 4 + (size_t)kTmpCap * 16 + 8 * 4 + S_END * 4 + ARCS_KCAP * 8;
+             (512 + 256 + 1024) * 4 + (size_t)kTmpCap * 16 + 8 * 4 + S_END * 4 + ARCS_KCAP * 8;
   n += (size_t)2 * kCapB * 8;
   if (masked) n += (size_t)2 * kCapA * 8;
   n += (size_t)2 * hash_slots * 8;

@@ -170,9 +170,40 @@ __device__ __noinline__ void sel_prune(const Sel& s, int k, const PruneScratch& 
   }
   if (gt == 0) {
     *s.cnt = m;
-    *s.tau = *ps.m64;
+    *s.tau = *ps.m64 - 1ull;  // exclusive: the smallest kept composite itself still passes
   }
   group_sync();
+}
+
+
+// The kth largest (1-based) of the kGroup keys in keys[], found by the whole group with a
+// 4-pass radix select on the 32-bit keys. Every thread returns the same value.
+__device__ __noinline__ uint32_t group_kth_key(const uint32_t* keys, int kth, const PruneScratch& ps, int gt) {
+  const uint32_t my = keys[gt];
+  uint32_t prefix = 0, mask = 0;
+  int krem = kth;
+  for (int pass = 0; pass < 4; ++pass) {
+    const int shift = 24 - 8 * pass;
+    ps.hist[gt] = 0;
+    group_sync();
+    if ((my & mask) == prefix) atomicAdd(&ps.hist[(my >> shift) & 255u], 1u);
+    group_sync();
+    if (gt < 32) {
+      int d, kr;
+      bool ex;
+      find_bin(ps.hist, krem, d, kr, ex);
+      if (gt == 0) {
+        ps.misc[0] = d;
+        ps.misc[1] = kr;
+      }
+    }
+    group_sync();
+    prefix |= (uint32_t)ps.misc[0] << shift;
+    mask |= 0xFFu << shift;
+    krem = ps.misc[1];
+  }
+  group_sync();
+  return prefix;
 }
 
 // The same selection run by ONE warp on a buffer only that warp touches (the examiner warp
@@ -235,7 +266,7 @@ __device__ __noinline__ int sel_prune_warp(const Sel& s, int n, int k, uint32_t*
     s.key[i] = tk[i];
     s.id[i] = ti[i];
   }
-  if (lane == 0) *reinterpret_cast<volatile unsigned long long*>(s.tau) = cmin;
+  if (lane == 0) *reinterpret_cast<volatile unsigned long long*>(s.tau) = cmin - 1ull;  // exclusive threshold
   __syncwarp();
   return out;
 }
