@@ -123,7 +123,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   for (uint32_t it = 0; it < kWaitLimit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (it > 1) __nanosleep(it > 64 ? 256 : 64);
+    if (it > 16) __nanosleep(it > 256 ? 256 : 32);  // (try_wait itself suspends the thread for a while)
   }
   return false;
 }

@@ -24,15 +24,22 @@ namespace arcs {
 constexpr int kScanW = 16;                                 // scanner warps
 constexpr int kExamWarp = kScanW;                          // examiner warp
 constexpr int kProdWarp = kScanW + 1;                      // producer warp (lane 0 works)
-constexpr int kFinWarp0 = kScanW + 2;                      // first finisher warp
-constexpr int kThreadsP = (kFinWarp0 + kGroup / 32) * 32;  // 832 threads
-constexpr int kRing = kScanW;                              // tiles in the ring: scanner w owns slot w
+constexpr int kTauWarp = kScanW + 2;                       // threshold warp
+constexpr int kFinWarp0 = kScanW + 3;                      // first helper warp (preparing group, then finishing group)
+constexpr int kThreadsP = (kFinWarp0 + 2 * kGroup / 32) * 32;  // 864 threads
+#ifndef ARCS_TAU_SLEEP
+#define ARCS_TAU_SLEEP 200
+#endif
+constexpr int kTauSleepNs = ARCS_TAU_SLEEP;                // pause between two threshold updates
+constexpr int kSortCap = 512;                              // most buffer entries ranked by counting
+constexpr int kRing = kScanW;                              // tiles in the ring (a multiple of kScanW: scanner w owns slots w, w + kScanW, ...)
 constexpr int kSTile = 8192;                               // bytes per tile (512 chunks: 16 per lane)
-constexpr int kQueue = 1024;                               // queued elements between scanners and examiner
+constexpr int kStash = 16;                                 // chunks a scanner sets aside per flush
+constexpr int kQueue = 512;                                // queued elements between scanners and examiner
 constexpr uint32_t kIdMask = 0x3FFFFFFFu;                  // queue entry word y: id | eligible-for-B << 30 | parity << 31
 constexpr uint32_t kMarker = kIdMask;                      // id field of a scanner's end-of-item entry
 constexpr int kCapB = 1024;   // candidate buffer: prune trigger (<= 512) + one round of pushes (<= 256)
-constexpr int kCapA = 1280;   // constrained head select (k = 512, trigger 1024)
+constexpr int kCapA = 1152;   // constrained head select (k = 512): fill limit 1024 + one step / round of 128
 constexpr int kBootBytes = 8192;  // prefix of an item read ahead to seed its threshold
 constexpr uint32_t kEmpty = 0xFFFFFFFFu;
 // per touched token: occurrences in the history (low 20 bits) and what applies to it
@@ -138,14 +145,15 @@ __device__ __forceinline__ float elem_of_words<__nv_bfloat16>(uint32_t w0, uint3
 }
 
 // indices into the shared scalar arrays
-enum { S_ABORT = 0, S_QTAIL, S_QHEAD, S_PREPARED, S_STREAMED, S_LAST, S_FLAGS, S_NCAND, S_PICK,
-       S_CNT_B /* [2] */ = 10, S_CNT_A = 12, S_K = 14, S_TRIG = 16, S_TOUCHED = 18, S_BANS = 20, S_BASE_B = 22, S_BASE_A = 24,
-       S_END = 28 };
-enum { L_TAU_B = 0 /* [2] */, L_TAU_A = 2, L_PRUNE_MIN = 4, L_TOP, L_LOW, L_MROW /* [2] */ = 8, L_END = 12 };
+enum { S_ABORT = 0, S_QTAIL, S_QHEAD, S_PREPARED, S_STREAMED, S_LAST, S_FLAGS, S_NCAND, S_PICK, S_FINISHED, S_TAUACK,
+       S_CNT_B /* [2] */ = 12, S_CNT_A /* [2] */ = 14,
+       S_K /* [3] */ = 16, S_TOUCHED = 19, S_BANS = 22, S_BASE_B = 25, S_BASE_A = 28, S_END = 32 };
+enum { L_TAU_B = 0 /* [3] */, L_TAU_A = 3, L_PRUNE_MIN = 6, L_TOP, L_LOW, L_PMIN_P, L_MROW /* [3] */ = 10, L_END = 14 };
 
 // ---- the scanners' rare path, kept out of line so that the streaming loop stays small
 struct ScanCtx {
   const uint32_t* hk;      // the item's table of replaced tokens (columns)
+  const uint32_t* bloom;   // 8192-bit filter over the same columns: most lookups end here
   int32_t hash_slots, hash_shift;
   int32_t touched, bans, par;
   const uint32_t* mrow;
@@ -155,9 +163,11 @@ struct ScanCtx {
   int* sh;                 // shared scalars (queue head / tail, abort flag)
   unsigned long long* q_ent;  // queue slots: 0 = empty, else key | (id, flags) << 32
   int32_t* status;
-  int32_t col0, id_base;   // global id of the tile's first element
+  int32_t id_base;         // global id of column 0
   uint64_t tcB, tcA;       // thresholds the chunk was listed against
 };
+
+__device__ __forceinline__ uint32_t bloom_bit(int32_t c) { return ((uint32_t)c * 0x9E3779B1u) >> 19; }  // 13 bits
 
 __device__ __forceinline__ bool table_has(const uint32_t* hk, int32_t slots, int32_t shift, int32_t c) {
   uint32_t h = hash_of(c, shift);
@@ -186,45 +196,46 @@ __device__ __forceinline__ void queue_write(int* sh, unsigned long long* q_ent, 
   sm_st_volatile64(&q_ent[e % kQueue], (unsigned long long)key | ((unsigned long long)idp << 32));
 }
 
-// The chunks of one warp-wide load whose maximum reached the threshold (bits of `bal`, chunk
-// cbase + lane held in q) are examined one element per lane, up to 32/E chunks per pass.
+// The chunks a scanner warp has set aside (data in sq[], chunk number inside the tile in sc[])
+// are examined one element per lane, 32/E chunks per pass. Runs after the warp has released
+// the tile's ring slot, so the time spent here never holds up the copy engine.
 template <typename T, bool MASKED>
-__device__ __noinline__ void scan_examine(const ScanCtx& c, uint4 q, int cbase, unsigned bal) {
+__device__ __noinline__ void scan_examine(const ScanCtx& c, const uint4* sq, const int32_t* sc, int n) {
   constexpr int E = Elem<T>::kPerChunk;
   const int lane = threadIdx.x & 31;
 #ifdef ARCS_X_EMPTY
   return;
 #endif
-  while (bal) {
-    const int jj = lane / E, el = lane % E;
-    unsigned rest = bal;  // lane group jj takes the jj-th listed chunk
-#pragma unroll
-    for (int i = 0; i < 32 / E - 1; ++i)
-      if (i < jj) rest &= rest - 1u;
-    const bool valid = rest != 0u;
-    const int sl = valid ? __ffs(rest) - 1 : 0;
-    XE_T(t0_);
-    const uint32_t w0 = __shfl_sync(0xFFFFFFFFu, q.x, sl), w1 = __shfl_sync(0xFFFFFFFFu, q.y, sl);
-    const uint32_t w2 = __shfl_sync(0xFFFFFFFFu, q.z, sl), w3 = __shfl_sync(0xFFFFFFFFu, q.w, sl);
-    const float v = elem_of_words<T>(w0, w1, w2, w3, el);
-    const int32_t gid = c.col0 + (cbase + sl) * E + el;
+  for (int i0 = 0; i0 < n; i0 += 32 / E) {
+    const int idx = i0 + lane / E, el = lane % E;
+    const bool valid = idx < n;
+    float v = 0.0f;
+    int32_t gid = 0;
+    if (valid) {
+      v = Elem<T>::from_smem(reinterpret_cast<const char*>(&sq[idx]) + el * (int)sizeof(T));
+      gid = (int32_t)sm_ld(&sc[idx]) + el;
+    }
     const uint32_t ky = key_of(v);
     const uint64_t cm = comp_of(ky, gid);
-    XE_T(t1_);
     // eligible for the selection proper (B) / for the constrained head ranking (A)
     bool okB = valid && ky != 0u && cm > c.tcB;
     bool okA = MASKED && valid && ky != 0u && cm > c.tcA;
     if (MASKED && okB)
       okB = ((__ldg(&c.mrow[gid >> 5]) >> (gid & 31)) & 1u) && !(c.bans && v + 0.0f <= ARCS_BANNED);  // tools/sampler.h:118-119
     // tokens the table replaces are taken from it when the item is finished, not from the stream
-    if ((okB || okA) && c.touched && table_has(c.hk, c.hash_slots, c.hash_shift, gid - c.id_base)) okB = okA = false;
-    // count the survivors by the upper 16 bits of their keys: the examiner reads thresholds off these counts
+#ifndef ARCS_X_NOTABLE
+    if ((okB || okA) && c.touched) {
+      const int32_t col = gid - c.id_base;
+      const uint32_t bb = bloom_bit(col);
+      if (((sm_ld(&c.bloom[bb >> 5]) >> (bb & 31)) & 1u) && table_has(c.hk, c.hash_slots, c.hash_shift, col)) okB = okA = false;
+    }
+#endif
 #ifdef ARCS_X_NOPUSH
     okB = okA = false;
 #endif
+    // count the survivors by the upper 16 bits of their keys: the examiner reads thresholds off these counts
     if (okB) sm_red_add(&c.histB[coarse_bin(ky, c.baseB)], 1u);
     if (okA) sm_red_add(&c.histA[coarse_bin(ky, c.baseA)], 1u);
-    XE_T(t2_);
     const bool pass = okB || okA;
     const unsigned pb = __ballot_sync(0xFFFFFFFFu, pass);
     if (pb) {
@@ -232,19 +243,10 @@ __device__ __noinline__ void scan_examine(const ScanCtx& c, uint4 q, int cbase, 
       uint32_t base = 0;
       if (lane == leader) base = sm_atomic_add(&c.sh[S_QTAIL], (unsigned)__popc(pb));
       base = __shfl_sync(0xFFFFFFFFu, base, leader);
-      XE_T(t3_);
-      XE_ADD(22, t3_ - t2_);
       if (pass)
         queue_write(c.sh, c.q_ent, c.status, base + __popc(pb & ((1u << lane) - 1u)), ky,
                     (uint32_t)gid | ((uint32_t)okB << 30) | ((uint32_t)c.par << 31));
     }
-    XE_T(t4_);
-    XE_ADD(20, t1_ - t0_);
-    XE_ADD(21, t2_ - t1_);
-    XE_ADD(23, t4_ - t2_);
-    XE_ADD(24, 1);
-    const int done = min(__popc(bal), 32 / E);
-    for (int i = 0; i < done; ++i) bal &= bal - 1u;
   }
 }
 
@@ -254,27 +256,34 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
   // ---- carve shared memory (ordered by alignment)
   char* ring = smem;                                                          // kRing * kSTile
   unsigned long long* q_ent = reinterpret_cast<unsigned long long*>(ring + (size_t)kRing * kSTile);  // [kQueue]
-  uint64_t* full = reinterpret_cast<uint64_t*>(q_ent + kQueue);               // [kRing] tile has landed
+  uint4* stash_q = reinterpret_cast<uint4*>(q_ent + kQueue);                   // [kScanW][kStash] chunks set aside by the scanners
+  uint64_t* full = reinterpret_cast<uint64_t*>(stash_q + kScanW * kStash);     // [kRing] tile has landed
   uint64_t* empty = full + kRing;                                             // [kRing] tile has been scanned
   unsigned long long* s64 = reinterpret_cast<unsigned long long*>(empty + kRing);  // [L_END]
   double* spr = reinterpret_cast<double*>(s64 + L_END);                       // [ARCS_KCAP + 1]
-  uint32_t* hist = reinterpret_cast<uint32_t*>(spr + ARCS_KCAP + 1);                                                     // [512] finishers' radix histograms
+  int32_t* stash_c = reinterpret_cast<int32_t*>(spr + ARCS_KCAP + 1);         // [kScanW][kStash]
+  uint32_t* hist = reinterpret_cast<uint32_t*>(stash_c + kScanW * kStash);                                               // [512] finishers' radix histograms
   uint32_t* xhist = hist + 512;                                               // [256] examiner's radix histogram
-  uint32_t* xh = xhist + 256;                                                 // [2 parities][B, A][256] coarse histograms
-  uint32_t* tk = xh + 4 * 256;                                                 // [kTmpCap] finishers' scratch
+  uint32_t* xh = xhist + 256;                                                 // [3 sets][B, A][256] coarse histograms
+  uint32_t* tk = xh + 6 * 256;                                                 // [kTmpCap] finishers' scratch
   int32_t* ti = reinterpret_cast<int32_t*>(tk + kTmpCap);
   uint32_t* xtk = reinterpret_cast<uint32_t*>(ti + kTmpCap);                  // [kTmpCap] examiner's scratch
   int32_t* xti = reinterpret_cast<int32_t*>(xtk + kTmpCap);
   int* misc = reinterpret_cast<int*>(xti + kTmpCap);                          // [8]
-  int* sh = misc + 8;                                                         // [S_END]
+  uint32_t* phist = reinterpret_cast<uint32_t*>(misc + 8);                    // preparing group's scratch: [512]
+  uint32_t* ptk = phist + 512;                                                // [kTmpCap]
+  int32_t* pti = reinterpret_cast<int32_t*>(ptk + kTmpCap);                   // [kTmpCap]
+  int* pmisc = reinterpret_cast<int*>(pti + kTmpCap);                         // [8]
+  int* sh = pmisc + 8;                                                        // [S_END]
   float* sv = reinterpret_cast<float*>(sh + S_END);                           // [ARCS_KCAP] sorted candidates
   int32_t* sid = reinterpret_cast<int32_t*>(sv + ARCS_KCAP);
   uint32_t* bkey = reinterpret_cast<uint32_t*>(sid + ARCS_KCAP);              // [2][kCapB]
   int32_t* bid = reinterpret_cast<int32_t*>(bkey + 2 * kCapB);
   uint32_t* akey = reinterpret_cast<uint32_t*>(bid + 2 * kCapB);              // [2][kCapA] when MASKED
   int32_t* aid = reinterpret_cast<int32_t*>(akey + (MASKED ? 2 * kCapA : 0));
-  uint32_t* hkey = reinterpret_cast<uint32_t*>(aid + (MASKED ? 2 * kCapA : 0));  // [2][hash_slots] token columns
-  uint32_t* hinfo = hkey + 2 * a.hash_slots;                                  // [2][hash_slots]
+  uint32_t* hkey = reinterpret_cast<uint32_t*>(aid + (MASKED ? 2 * kCapA : 0));  // [3][hash_slots] token columns
+  uint32_t* hinfo = hkey + 3 * a.hash_slots;                                  // [3][hash_slots]
+  uint32_t* bloom = hinfo + 3 * a.hash_slots;                                 // [3][256] filter bits over the table's columns
   volatile int* vsh = sh;
   volatile unsigned long long* v64 = s64;
 
@@ -294,15 +303,15 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
     for (int i = 0; i < L_END; ++i) s64[i] = 0ull;
   }
   for (int i = tid; i < kQueue; i += kThreadsP) q_ent[i] = 0ull;
-  for (int i = tid; i < 4 * 256; i += kThreadsP) xh[i] = 0u;
+  for (int i = tid; i < 6 * 256; i += kThreadsP) xh[i] = 0u;
   __syncthreads();  // the only CTA-wide barrier
 
   auto abort_now = [&]() {
     vsh[S_ABORT] = 1;
     raise_status(a.status, ARCS_ERR_TIMEOUT);
   };
-  auto is_touched = [&](int par, int32_t c) -> bool {
-    const uint32_t* hk = hkey + par * a.hash_slots;
+  auto is_touched = [&](int st, int32_t c) -> bool {
+    const uint32_t* hk = hkey + st * a.hash_slots;
     uint32_t h = hash_of(c, a.hash_shift);
     for (int probe = 0; probe < a.hash_slots; ++probe) {
       const uint32_t kx = hk[h];
@@ -347,14 +356,15 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
     uint32_t G0 = 0;  // running number of the item's first tile
     RT_DECL;
     for (int j = 0; j < my_n; ++j) {
-      const int par = j & 1;
+      const int par = j & 1, st = j % 3;  // candidate buffers alternate; tables / thresholds / counts rotate over three sets
       const Item<T> it = item_of<T>(a, (int)blockIdx.x + j * (int)gridDim.x);
       const int T_ = s_tiles(it.p);
       RT(0);
       {  // the item's table and first threshold must be ready (one lane polls)
         if (lane == 0) {
           uint32_t spins = 0;
-          while (vsh[S_PREPARED] <= j && !vsh[S_ABORT]) {
+          // ... and the item two back, which used the same candidate buffers, must be finished
+          while ((vsh[S_PREPARED] <= j || vsh[S_FINISHED] < j - 1) && !vsh[S_ABORT]) {
             if (++spins > kWaitLimit) abort_now();
             __nanosleep(64);
           }
@@ -364,30 +374,35 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
       }
       RT(1);
       if (vsh[S_ABORT]) break;
-      const uint32_t* mrow = MASKED ? reinterpret_cast<const uint32_t*>(s64[L_MROW + par]) : nullptr;
-      const bool touched = sh[S_TOUCHED + par] != 0, bans = MASKED && sh[S_BANS + par] != 0;
+      const uint32_t* mrow = MASKED ? reinterpret_cast<const uint32_t*>(s64[L_MROW + st]) : nullptr;
+      const bool touched = sh[S_TOUCHED + st] != 0, bans = MASKED && sh[S_BANS + st] != 0;
+      uint4* stq = stash_q + warp * kStash;      // chunks this warp has set aside
+      int32_t* stc = stash_c + warp * kStash;
+      int nst = 0;
       ScanCtx ctx;
-      ctx.hk = hkey + par * a.hash_slots;
+      ctx.hk = hkey + st * a.hash_slots;
+      ctx.bloom = bloom + st * 256;
       ctx.hash_slots = a.hash_slots;
       ctx.hash_shift = a.hash_shift;
       ctx.touched = touched;
       ctx.bans = bans;
       ctx.par = par;
       ctx.mrow = mrow;
-      ctx.histB = xh + (2 * par) * 256;
-      ctx.histA = xh + (2 * par + 1) * 256;
-      ctx.baseB = (uint32_t)sh[S_BASE_B + par];
-      ctx.baseA = (uint32_t)sh[S_BASE_A + par];
+      ctx.histB = xh + (2 * st) * 256;
+      ctx.histA = xh + (2 * st + 1) * 256;
+      ctx.baseB = (uint32_t)sh[S_BASE_B + st];
+      ctx.baseA = (uint32_t)sh[S_BASE_A + st];
       ctx.sh = sh;
       ctx.q_ent = q_ent;
       ctx.status = a.status;
       ctx.id_base = a.id_base;
-      const char* tile = ring + (size_t)warp * kSTile;
-      for (int t = (int)(((uint32_t)warp - G0) % kRing); t < T_; t += kRing) {
+      for (int t = (int)(((uint32_t)warp - G0) % kScanW); t < T_; t += kScanW) {
         const uint32_t g = G0 + (uint32_t)t;
+        const int slot = (int)(g % kRing);
+        const char* tile = ring + (size_t)slot * kSTile;
         if (vsh[S_ABORT]) break;
         RT(0);
-        if (!mbar_wait_warp(&full[warp], (g / kRing) & 1u)) {
+        if (!mbar_wait_warp(&full[slot], (g / kRing) & 1u)) {
           abort_now();
           break;
         }
@@ -398,15 +413,14 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
         uint64_t tcB = 0, tcA = 0;
         typename Elem<T>::Thr thB, thA;
         auto refresh = [&]() {
-          tcB = v64[L_TAU_B + par];
-          tcA = MASKED ? v64[L_TAU_A + par] : 0xFFFFFFFFFFFFFFFFull;
+          tcB = v64[L_TAU_B + st];
+          tcA = MASKED ? v64[L_TAU_A + st] : 0xFFFFFFFFFFFFFFFFull;
           // chunk-level test on values: inclusive on the threshold's value (ids are settled per element)
           const uint32_t kB32 = (uint32_t)(tcB >> 32), kA32 = (uint32_t)(tcA >> 32);
           thB = Elem<T>::make_thr(value_of(kB32 < 0x007FFFFFu ? 0x007FFFFFu : kB32));
           thA = Elem<T>::make_thr(MASKED ? value_of(kA32 < 0x007FFFFFu ? 0x007FFFFFu : kA32) : INFINITY);
         };
         const bool whole = nchunk == kSTile / 16;  // only an item's last tile can be short
-        ctx.col0 = col0;
 #ifndef ARCS_X_NOSCAN
         for (int c0 = 0; c0 < nchunk; c0 += 4 * 32) {
           uint4 q[4];
@@ -433,25 +447,53 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
             h[u] = h[u] && a.V < 0;  // never true, but the test above is still evaluated
 #endif
           }
-          if (__any_sync(0xFFFFFFFFu, h[0] || h[1] || h[2] || h[3])) {
-            RT(0);
-            RT_COUNT(16, 1);
-            ctx.tcB = tcB;
-            ctx.tcA = tcA;
+          if (__any_sync(0xFFFFFFFFu, h[0] || h[1] || h[2] || h[3])) {  // set the listed chunks aside
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              const unsigned bal = __ballot_sync(0xFFFFFFFFu, h[u]);
-              RT_COUNT(17, __popc(bal));
-              if (bal) scan_examine<T, MASKED>(ctx, q[u], c0 + u * 32, bal);
+              const unsigned all = __ballot_sync(0xFFFFFFFFu, h[u]);
+              if (all == 0u) continue;
+#pragma unroll
+              for (int half = 0; half < 2; ++half) {  // (half a warp at a time: never more than the stash holds)
+                const unsigned bal = all & (half ? 0xFFFF0000u : 0x0000FFFFu);
+                if (bal == 0u) continue;
+                if (nst + __popc(bal) > kStash) {  // rare: make room first
+                  ctx.tcB = tcB;
+                  ctx.tcA = tcA;
+                  __syncwarp();
+                  scan_examine<T, MASKED>(ctx, stq, stc, nst);
+                  nst = 0;
+                  __syncwarp();
+                }
+                if (h[u] && ((bal >> lane) & 1u)) {
+                  const int pos = nst + __popc(bal & ((1u << lane) - 1u));
+                  stq[pos] = q[u];
+                  stc[pos] = col0 + (c0 + u * 32 + lane) * E;  // global id of the chunk's first element
+                }
+                nst += __popc(bal);
+              }
             }
-            RT(3);
           }
         }
 #endif
         __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[warp]);
+        if (lane == 0) mbar_arrive(&empty[slot]);  // the slot can be refilled while the chunks set aside are examined
+        if (nst >= kStash / 2) {  // examine in batches: full passes, and against a fresher threshold
+          refresh();
+          ctx.tcB = tcB;
+          ctx.tcA = tcA;
+          scan_examine<T, MASKED>(ctx, stq, stc, nst);
+          nst = 0;
+          __syncwarp();
+        }
       }
       if (vsh[S_ABORT]) break;
+      if (nst > 0) {  // what is still set aside
+        ctx.tcB = v64[L_TAU_B + st];
+        ctx.tcA = MASKED ? v64[L_TAU_A + st] : 0xFFFFFFFFFFFFFFFFull;
+        __syncwarp();
+        scan_examine<T, MASKED>(ctx, stq, stc, nst);
+        nst = 0;
+      }
       __syncwarp();
       if (lane == 0) {  // this warp has queued everything it found in the item
         const uint32_t e = atomicAdd(reinterpret_cast<unsigned int*>(&sh[S_QTAIL]), 1u);
@@ -461,6 +503,35 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
     }
     RT(0);
     RT_FLUSH(4, tid == 0);
+  } else if (warp == kTauWarp) {
+    // =================================================================== threshold warp
+    // Keeps reading new thresholds off the coarse histograms of the items that are streaming:
+    // the lower edge of the bin holding the k-th best survivor counted so far. It acknowledges
+    // every hand-over, so that an item's state is recycled only after this warp is done with it.
+    for (;;) {
+      if (vsh[S_ABORT]) break;
+      const int done = vsh[S_STREAMED];
+      if (done >= my_n) break;
+      const int pz = min(vsh[S_PREPARED], done + 2);
+      __threadfence_block();
+      for (int j = done; j < pz; ++j) {
+        const int st = j % 3;
+        int d, kr;
+        bool ex;
+        find_bin(xh + (2 * st) * 256, sh[S_K + st], d, kr, ex);
+        if (d > 0 && lane == 0)
+          atomicMax(&s64[L_TAU_B + st], (unsigned long long)(((uint32_t)sh[S_BASE_B + st] + (uint32_t)d) << 16) << 32);
+        if (MASKED) {
+          find_bin(xh + (2 * st + 1) * 256, ARCS_HEAD, d, kr, ex);
+          if (d > 0 && lane == 0)
+            atomicMax(&s64[L_TAU_A + st], (unsigned long long)(((uint32_t)sh[S_BASE_A + st] + (uint32_t)d) << 16) << 32);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) vsh[S_TAUACK] = done;  // no threshold of an item before `done` will be written from here on
+      __nanosleep(kTauSleepNs);
+    }
+    if (lane == 0) vsh[S_TAUACK] = my_n;
   } else if (warp == kExamWarp) {
     // =================================================================== examiner
     // Owns the candidate buffers while an item streams: moves the queued survivors into them,
@@ -470,7 +541,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
     // when a buffer still overflows, i.e. when one bin holds very many equal or close keys.
     uint32_t head = 0, idle = 0, polls = 0;
     int cB[2] = {0, 0}, cA[2] = {0, 0}, marks[2] = {0, 0}, streamed = 0;
-    int kk[2] = {0, 0};
+    int kk[2] = {0, 0}, itm[2] = {0, 1};  // itm: the item each parity is on
     uint32_t baseB[2] = {0, 0}, baseA[2] = {0, 0};
     bool loaded[2] = {false, false};
     constexpr int kStep = 128;     // queue entries taken per step, four per lane
@@ -510,8 +581,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
       find_bin(hst, sel.k, d, kr, ex);
       if (d <= 0) return;
       const unsigned long long tc = (unsigned long long)((base + (uint32_t)d) << 16) << 32;  // comp > tc <=> key >= edge of bin d
-      if (lane == 0 && tc > *reinterpret_cast<volatile unsigned long long*>(sel.tau))
-        *reinterpret_cast<volatile unsigned long long*>(sel.tau) = tc;
+      if (lane == 0) atomicMax(sel.tau, tc);
       __syncwarp();
     };
     while (streamed < my_n) {
@@ -555,8 +625,9 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
       if (lane == 0) vsh[S_QHEAD] = (int)head;
 #pragma unroll
       for (int par = 0; par < 2; ++par) {
-        const Sel sB{bkey + par * kCapB, bid + par * kCapB, &sh[S_CNT_B + par], &s64[L_TAU_B + par], kk[par], 0, kCapB};
-        const Sel sA{akey + par * kCapA, aid + par * kCapA, &sh[S_CNT_A + par], &s64[L_TAU_A + par], ARCS_HEAD, 0, kCapA};
+        const int st = itm[par] % 3;
+        const Sel sB{bkey + par * kCapB, bid + par * kCapB, &sh[S_CNT_B + par], &s64[L_TAU_B + st], kk[par], 0, kCapB};
+        const Sel sA{akey + par * kCapA, aid + par * kCapA, &sh[S_CNT_A + par], &s64[L_TAU_A + st], ARCS_HEAD, 0, kCapA};
         bool seen = false;
         int nmark = 0;
 #pragma unroll
@@ -569,13 +640,13 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
           if (!__any_sync(0xFFFFFFFFu, mine)) continue;
           if (!loaded[par]) {  // first entry of a new item: its settings were published before it could be queued
             loaded[par] = true;
-            kk[par] = sh[S_K + par];
-            baseB[par] = (uint32_t)sh[S_BASE_B + par];
-            baseA[par] = (uint32_t)sh[S_BASE_A + par];
+            kk[par] = sh[S_K + st];
+            baseB[par] = (uint32_t)sh[S_BASE_B + st];
+            baseA[par] = (uint32_t)sh[S_BASE_A + st];
           }
           seen = true;
           const uint64_t cm = comp_of(ent[u].x, (int32_t)gid);
-          const bool okB = mine && ((ent[u].y >> 30) & 1u) && cm > v64[L_TAU_B + par];
+          const bool okB = mine && ((ent[u].y >> 30) & 1u) && cm > v64[L_TAU_B + st];
           const unsigned bb = __ballot_sync(0xFFFFFFFFu, okB);
           if (okB) {
             const int pos = cB[par] + __popc(bb & ((1u << lane) - 1u));
@@ -584,7 +655,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
           }
           cB[par] += __popc(bb);
           if (MASKED) {
-            const bool okA = mine && cm > v64[L_TAU_A + par];
+            const bool okA = mine && cm > v64[L_TAU_A + st];
             const unsigned ba = __ballot_sync(0xFFFFFFFFu, okA);
             if (okA) {
               const int pos = cA[par] + __popc(ba & ((1u << lane) - 1u));
@@ -594,24 +665,20 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
             cA[par] += __popc(ba);
           }
         }
-        if (seen) {
+        if (seen) {  // (the threshold warp raises the thresholds meanwhile)
           const Sel sBk{sB.key, sB.id, sB.cnt, sB.tau, kk[par], 0, kCapB};
-          raise(sBk, xh + (2 * par) * 256, baseB[par]);
           if (cB[par] > kFullB - kStep) shrink(sBk, cB[par], kFullB);
-          if (MASKED) {
-            raise(sA, xh + (2 * par + 1) * 256, baseA[par]);
-            if (cA[par] > kFullA - kStep) shrink(sA, cA[par], kFullA);
-          }
+          if (MASKED && cA[par] > kFullA - kStep) shrink(sA, cA[par], kFullA);
         }
         marks[par] += nmark;
         if (marks[par] == kScanW) {  // every scanner has closed the item: hand its buffers to the finishers
           marks[par] = 0;
           if (loaded[par]) {  // leave the finishers only what the last threshold has not overtaken
             const Sel sBk{sB.key, sB.id, sB.cnt, sB.tau, kk[par], 0, kCapB};
-            raise(sBk, xh + (2 * par) * 256, baseB[par]);
+            raise(sBk, xh + (2 * st) * 256, baseB[par]);
             shrink(sBk, cB[par], 0);
             if (MASKED) {
-              raise(sA, xh + (2 * par + 1) * 256, baseA[par]);
+              raise(sA, xh + (2 * st + 1) * 256, baseA[par]);
               shrink(sA, cA[par], 0);
             }
           }
@@ -624,8 +691,9 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
           }
           cB[par] = cA[par] = 0;
           loaded[par] = false;
+          itm[par] += 2;
 #pragma unroll
-          for (int x = 0; x < 16; ++x) xh[(2 * par) * 256 + x * 32 + lane] = 0;  // both histograms of this parity
+          for (int x = 0; x < 16; ++x) xh[(2 * st) * 256 + x * 32 + lane] = 0;  // both histograms of the item's set
           ++streamed;
         }
       }
@@ -640,9 +708,10 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
     RT_FLUSH(8, lane == 0);
   } else {
     // =================================================================== finishers
-    const int gt = tid - kFinWarp0 * 32;
+    const int gt = (tid - kFinWarp0 * 32) % kGroup;  // index inside the preparing (first) or finishing (second) group
     RT_DECL;
-    const PruneScratch ps{hist, tk, ti, misc, &s64[L_PRUNE_MIN]};
+    const PruneScratch psF{hist, tk, ti, misc, &s64[L_PRUNE_MIN]};
+    const PruneScratch psP{phist, ptk, pti, pmisc, &s64[L_PMIN_P]};
 
     struct RowCfg {
       arcs_row_params prm;
@@ -674,12 +743,27 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
     // ---- prepare item j: table of the tokens the stream must not supply (every id of the
     // history a penalty applies to, every id of the bias list: tools/sampler.h:154-174) and a
     // first threshold from a short prefix of the item, read ahead of the ring.
-    auto prepare = [&](int j) {
-      const int par = j & 1;
+    auto prepare = [&](int j) -> bool {
+      const int par = j & 1, st = j % 3;
+      RT(0);
+      {  // the item three back used the same set of state: it must be finished and acknowledged
+        bool bad = false;
+        if (gt == 0) {
+          uint32_t spins = 0;
+          while ((vsh[S_FINISHED] < j - 2 || vsh[S_TAUACK] < j - 2) && !vsh[S_ABORT]) {
+            if (++spins > kWaitLimit) abort_now();
+            __nanosleep(256);
+          }
+          bad = vsh[S_ABORT] != 0;
+          __threadfence_block();
+        }
+        if (group_sync_or<1>(bad)) return false;
+      }
+      RT(1);
       const Item<T> it = item_of<T>(a, (int)blockIdx.x + j * (int)gridDim.x);
       const RowCfg r = row_cfg(it.b);
-      uint32_t* hk = hkey + par * a.hash_slots;
-      uint32_t* hi_ = hinfo + par * a.hash_slots;
+      uint32_t* hk = hkey + st * a.hash_slots;
+      uint32_t* hi_ = hinfo + st * a.hash_slots;
       bool bans = false;  // Sampler::bans_: any bias entry <= -100, in range or not (tools/sampler.h:34)
       if (gt == 0) {
         if (r.k_bad) raise_status(a.status, ARCS_ERR_TOPK);
@@ -691,7 +775,8 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
           hk[i] = kEmpty;
           hi_[i] = 0;
         }
-        group_sync();
+        for (int i = gt; i < 256; i += kGroup) bloom[st * 256 + i] = 0u;
+        group_sync<1>();
         auto insert = [&](int32_t t) -> int {  // global id -> slot, -1 when it is not this segment's
           if (t < 0 || t >= Vg) return -1;
           const int32_t c = t - a.id_base;
@@ -699,11 +784,13 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
           uint32_t h = hash_of(c, a.hash_shift);
           for (int probe = 0; probe < a.hash_slots; ++probe) {
             const uint32_t old = atomicCAS(&hk[h], kEmpty, (uint32_t)c);
+            if (old == kEmpty) atomicOr(&bloom[st * 256 + (bloom_bit(c) >> 5)], 1u << (bloom_bit(c) & 31));
             if (old == kEmpty || old == (uint32_t)c) return (int)h;
             h = (h + 1) & (uint32_t)(a.hash_slots - 1);
           }
           return -1;
         };
+#ifndef ARCS_X_NOBUILD
         if (r.pen_on) {
           const int32_t nwin = r.prm.repeat_last_n < 0 ? r.H : min(r.H, r.prm.repeat_last_n);  // tools/sampler.h:163
           for (int i = gt; i < r.H; i += kGroup) {
@@ -712,6 +799,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
             if (s >= 0 && i >= r.H - nwin) atomicOr(&hi_[s], kInfoWindow);
           }
         }
+#endif
         for (int i = gt; i < r.NB; i += kGroup) {
           const float bv = a.bias_vals[r.q0 + i];
           bans = bans || bv <= -100.0f;
@@ -719,7 +807,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
           if (s >= 0) atomicOr(&hi_[s], bv > -100.0f ? kInfoBias : kInfoBan);
         }
       }
-      bans = group_sync_or(bans);
+      bans = group_sync_or<1>(bans);
       // first threshold: the k-th largest of 256 (or, constrained, 1024) maxima over disjoint
       // pieces of the prefix is a lower bound of the k-th best element. Tokens of the prefix that
       // the table replaces may own a maximum without counting, so that many more are skipped.
@@ -732,26 +820,32 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
           extra += ck != kEmpty && (int32_t)ck >= c_lo && (int32_t)ck < c_hi;
         }
         if (extra) atomicAdd(&sh[S_PICK], extra);
-        group_sync();
+        group_sync<1>();
       }
       const int kth = (MASKED ? ARCS_HEAD : r.kB) + sh[S_PICK];
       unsigned long long tau0B = 0ull, tau0A = 0ull;
       if (!MASKED) {
-        float m = -INFINITY;
-        bool any = false;
-        for (int ci = gt; ci < nchunk; ci += kGroup) {
-          m = fmaxf(m, Elem<T>::chunk_max(ldg128_stream(it.p.body + (size_t)ci * 16)));
-          any = true;
+        // two maxima per thread, each over every other one of the thread's chunks of the prefix
+        float m0 = -INFINITY, m1 = -INFINITY;
+        bool any0 = false, any1 = false;
+        for (int ci = gt; ci < nchunk; ci += 2 * kGroup) {
+          m0 = fmaxf(m0, Elem<T>::chunk_max(ldg128_stream(it.p.body + (size_t)ci * 16)));
+          any0 = true;
+          if (ci + kGroup < nchunk) {
+            m1 = fmaxf(m1, Elem<T>::chunk_max(ldg128_stream(it.p.body + (size_t)(ci + kGroup) * 16)));
+            any1 = true;
+          }
         }
-        tk[gt] = any ? key_of(m) : 0u;
-        group_sync();
-        if (kth <= min(nchunk, kGroup)) {
-          const uint32_t kk0 = group_kth_key(tk, kth, ps, gt);
+        ptk[gt] = any0 ? key_of(m0) : 0u;
+        ptk[kGroup + gt] = any1 ? key_of(m1) : 0u;
+        group_sync<1>();
+        if (kth <= min(nchunk, 2 * kGroup)) {
+          const uint32_t kk0 = group_kth_key<1>(ptk, kth, psP, gt);
           tau0B = (unsigned long long)kk0 << 32;  // keeps ties with it
         }
       }
       if (MASKED) {
-        const Sel sA{akey + par * kCapA, aid + par * kCapA, &sh[S_CNT_A + par], &s64[L_TAU_A + par], ARCS_HEAD, 1024, kCapA};
+        const Sel sA{akey + par * kCapA, aid + par * kCapA, &sh[S_CNT_A + par], &s64[L_TAU_A + st], ARCS_HEAD, 1024, kCapA};
         if (kth <= nchunk && nchunk <= kCapA) {
           for (int ci = gt; ci < nchunk; ci += kGroup) {
             sA.key[ci] = key_of(Elem<T>::chunk_max(ldg128_stream(it.p.body + (size_t)ci * 16)));
@@ -761,35 +855,35 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
             *sA.cnt = nchunk;
             *sA.tau = 0ull;
           }
-          group_sync();
-          sel_prune(sA, kth, ps, gt);
+          group_sync<1>();
+          sel_prune<1>(sA, kth, psP, gt);
           tau0A = (*sA.tau >> 32) << 32;
-          group_sync();
+          group_sync<1>();
         }
       }
       if (gt == 0) {
-        s64[L_TAU_B + par] = tau0B;
-        s64[L_TAU_A + par] = tau0A;
-        sh[S_CNT_B + par] = 0;
-        sh[S_CNT_A + par] = 0;
-        sh[S_K + par] = r.kB;
-        sh[S_TRIG + par] = min(512, max(2 * r.kB, r.kB + 128));
-        sh[S_TOUCHED + par] = r.touched_on;
-        sh[S_BANS + par] = bans;
-        sh[S_BASE_B + par] = (int)(tau0B >> 48);
-        sh[S_BASE_A + par] = (int)(tau0A >> 48);
+        s64[L_TAU_B + st] = tau0B;
+        s64[L_TAU_A + st] = tau0A;
+        sh[S_K + st] = r.kB;
+        sh[S_TOUCHED + st] = r.touched_on;
+        sh[S_BANS + st] = bans;
+        sh[S_BASE_B + st] = (int)(tau0B >> 48);
+        sh[S_BASE_A + st] = (int)(tau0A >> 48);
         if (MASKED)
-          s64[L_MROW + par] = reinterpret_cast<unsigned long long>(a.mask + (size_t)(a.mask_row ? a.mask_row[it.b] : it.b) * a.mask_stride);
+          s64[L_MROW + st] = reinterpret_cast<unsigned long long>(a.mask + (size_t)(a.mask_row ? a.mask_row[it.b] : it.b) * a.mask_stride);
         __threadfence_block();
         vsh[S_PREPARED] = j + 1;
       }
-      group_sync();
+      group_sync<1>();
+      RT(2);
+      return true;
     };
 
     // ---- finish item j once the examiner has handed its buffers over. Returns false when the
     // kernel is being abandoned (uniform over the group).
     auto finish = [&](int j) -> bool {
-      const int par = j & 1;
+      const int par = j & 1, st = j % 3;
+      RT(0);
       bool bad = false;
       if (gt == 0) {
         uint32_t spins = 0;
@@ -800,20 +894,20 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
         bad = vsh[S_ABORT] != 0;
         __threadfence_block();
       }
-      if (group_sync_or(bad)) return false;
+      if (group_sync_or<2>(bad)) return false;
       RT(3);
       const Item<T> it = item_of<T>(a, (int)blockIdx.x + j * (int)gridDim.x);
       const RowCfg r = row_cfg(it.b);
       const int b = it.b;
       const T* row = it.row;
       const SegPlan& p = it.p;
-      const uint32_t* hk = hkey + par * a.hash_slots;
-      const uint32_t* hi_ = hinfo + par * a.hash_slots;
-      bool bans = sh[S_BANS + par] != 0;
-      const uint32_t* mrow = MASKED ? reinterpret_cast<const uint32_t*>(s64[L_MROW + par]) : nullptr;
-      const Sel selB{bkey + par * kCapB, bid + par * kCapB, &sh[S_CNT_B + par], &s64[L_TAU_B + par], r.kB,
+      const uint32_t* hk = hkey + st * a.hash_slots;
+      const uint32_t* hi_ = hinfo + st * a.hash_slots;
+      bool bans = sh[S_BANS + st] != 0;
+      const uint32_t* mrow = MASKED ? reinterpret_cast<const uint32_t*>(s64[L_MROW + st]) : nullptr;
+      const Sel selB{bkey + par * kCapB, bid + par * kCapB, &sh[S_CNT_B + par], &s64[L_TAU_B + st], r.kB,
                      min(512, max(2 * r.kB, r.kB + 128)), kCapB};
-      const Sel selA{akey + par * kCapA, aid + par * kCapA, &sh[S_CNT_A + par], &s64[L_TAU_A + par], ARCS_HEAD, 1024, kCapA};
+      const Sel selA{akey + par * kCapA, aid + par * kCapA, &sh[S_CNT_A + par], &s64[L_TAU_A + st], ARCS_HEAD, 1024, kCapA};
 
       bool hot = false;
       // one more element for the selections (all lanes of every finisher warp call it together);
@@ -823,7 +917,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
         const uint64_t cm = comp_of(ky, c + a.id_base);
         bool okB = valid && ky != 0u && cm > *selB.tau;
         bool okA = MASKED && valid && ky != 0u && cm > *selA.tau;
-        if ((okB || okA) && r.touched_on && !from_table && is_touched(par, c)) okB = okA = false;
+        if ((okB || okA) && r.touched_on && !from_table && is_touched(st, c)) okB = okA = false;
         if (MASKED && okB) {
           const int32_t g = c + a.id_base;
           okB = ((__ldg(&mrow[g >> 5]) >> (g & 31)) & 1u) && !(bans && v + 0.0f <= ARCS_BANNED);  // tools/sampler.h:118-119
@@ -834,9 +928,9 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
       // called by the whole group after a barrier behind which nobody pushes
       auto maybe_prune = [&]() {
         const bool pb = *selB.cnt > selB.trig, pa = MASKED && *selA.cnt > selA.trig;
-        group_sync();
-        if (pb) sel_prune(selB, selB.k, ps, gt);
-        if (pa) sel_prune(selA, selA.k, ps, gt);
+        group_sync<2>();
+        if (pb) sel_prune<2>(selB, selB.k, psF, gt);
+        if (pa) sel_prune<2>(selA, selA.k, psF, gt);
       };
 
       // the scalar elements before the first and after the last 16-byte boundary
@@ -847,41 +941,56 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
         consider(tv, tv ? Elem<T>::load(row + p.tail_first + gt) : 0.0f, p.tail_first + gt, false);
       }
       // touched tokens: exact fp32 arithmetic of Sampler::adjusted, one token per thread
+#ifdef ARCS_X_NOTOUCH
+      if (false) {
+#else
       if (r.touched_on) {
-        for (int s0 = 0; s0 < a.hash_slots; s0 += kGroup) {
-          group_sync();
-          maybe_prune();
-          hot = false;
-          const int s = s0 + gt;
-          const uint32_t ck = hk[s];
-          const bool valid = ck != kEmpty;
-          float v = 0.0f;
-          if (valid) {
-            const uint32_t info = hi_[s];
-            const uint32_t cnt = info & kInfoCount;
-            v = Elem<T>::load(row + (int32_t)ck);
-            if (info & kInfoBias) {  // :154-155 in list order, duplicates add again
-              const int32_t g = (int32_t)ck + a.id_base;
-              for (int i = 0; i < r.NB; ++i)
-                if (a.bias_ids[r.q0 + i] == g && a.bias_vals[r.q0 + i] > -100.0f) v = __fadd_rn(v, a.bias_vals[r.q0 + i]);
-            }
-            if (r.pen_on && cnt > 0) {
-              if (r.fp_on) v = __fsub_rn(v, __fmul_rn(r.prm.frequency_penalty, (float)cnt));             // :160
-              if (r.rp_on && (info & kInfoWindow))
-                v = v > 0.0f ? __fdiv_rn(v, r.prm.repeat_penalty) : __fmul_rn(v, r.prm.repeat_penalty);   // :166
-              if (r.pp_on) v = __fsub_rn(v, r.prm.presence_penalty);                                      // :171
-            }
-            if (info & kInfoBan) v = ARCS_BANNED;                                                         // :174
+#endif
+        constexpr int R = MASKED ? 1 : 4;  // table slots per thread per batch: their logits are fetched together
+        for (int s0 = 0; s0 < a.hash_slots; s0 += R * kGroup) {
+          uint32_t ck[R], info[R];
+          float raw[R];
+#pragma unroll
+          for (int x = 0; x < R; ++x) {
+            const int s = s0 + x * kGroup + gt;
+            ck[x] = s < a.hash_slots ? hk[s] : kEmpty;
+            info[x] = ck[x] != kEmpty ? hi_[s] : 0u;
+            raw[x] = ck[x] != kEmpty ? Elem<T>::load(row + (int32_t)ck[x]) : 0.0f;
           }
-          consider(valid, v, (int32_t)ck, true);
+#pragma unroll
+          for (int x = 0; x < R; ++x) {
+            const bool valid = ck[x] != kEmpty;
+            float v = raw[x];
+            if (valid) {
+              const uint32_t cnt = info[x] & kInfoCount;
+              if (info[x] & kInfoBias) {  // :154-155 in list order, duplicates add again
+                const int32_t g = (int32_t)ck[x] + a.id_base;
+                for (int i = 0; i < r.NB; ++i)
+                  if (a.bias_ids[r.q0 + i] == g && a.bias_vals[r.q0 + i] > -100.0f) v = __fadd_rn(v, a.bias_vals[r.q0 + i]);
+              }
+              if (r.pen_on && cnt > 0) {
+                if (r.fp_on) v = __fsub_rn(v, __fmul_rn(r.prm.frequency_penalty, (float)cnt));             // :160
+                if (r.rp_on && (info[x] & kInfoWindow))
+                  v = v > 0.0f ? __fdiv_rn(v, r.prm.repeat_penalty) : __fmul_rn(v, r.prm.repeat_penalty);   // :166
+                if (r.pp_on) v = __fsub_rn(v, r.prm.presence_penalty);                                      // :171
+              }
+              if (info[x] & kInfoBan) v = ARCS_BANNED;                                                      // :174
+            }
+            consider(valid, v, (int32_t)ck[x], true);
+          }
+          // at most R * kGroup pushes on top of a buffer at or below its trigger: inside its capacity
+          if (group_sync_or<2>(hot)) {
+            maybe_prune();
+            hot = false;
+          }
         }
       }
-      group_sync();
-      if (MASKED) sel_prune(selA, selA.k, ps, gt);
+      group_sync<2>();
+      if (MASKED) sel_prune<2>(selA, selA.k, psF, gt);
 
       // rows cut into segments: publish this segment's survivors; the CTA that arrives last merges
       if (a.nseg > 1) {
-        sel_prune(selB, selB.k, ps, gt);
+        sel_prune<2>(selB, selB.k, psF, gt);
         char* blk = a.ws_seg + ((size_t)b * a.nseg + it.seg) * a.seg_block;
         int32_t* hdr = reinterpret_cast<int32_t*>(blk);
         uint32_t* wk = reinterpret_cast<uint32_t*>(blk + 16);
@@ -905,15 +1014,21 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
           hdr[2] = bans;
         }
         __threadfence();
-        group_sync();
+        group_sync<2>();
         if (gt == 0) {
           const unsigned int old = atomicAdd(&a.ws_arrive[b], 1u);
           sh[S_LAST] = old == (unsigned int)a.nseg - 1u;
           if (sh[S_LAST]) a.ws_arrive[b] = 0u;  // ready for the next launch
         }
-        group_sync();
+        group_sync<2>();
         if (!sh[S_LAST]) {
-          group_sync();
+          group_sync<2>();
+          if (gt == 0) {
+            sh[S_CNT_B + par] = 0;
+            sh[S_CNT_A + par] = 0;
+            __threadfence_block();
+            vsh[S_FINISHED] = j + 1;
+          }
           return true;
         }
         __threadfence();
@@ -931,9 +1046,9 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
           const int32_t* gi = reinterpret_cast<const int32_t*>(gk + ARCS_KCAP);
           const int gnb = __ldcg(&gh[0]), gna = __ldcg(&gh[1]);
           bans = bans || __ldcg(&gh[2]) != 0;
-          const int rounds = MASKED ? (ARCS_HEAD + kGroup - 1) / kGroup : 1;
+          const int rounds = ((MASKED ? ARCS_HEAD : ARCS_KCAP) + kGroup - 1) / kGroup;
           for (int rr = 0; rr < rounds; ++rr) {
-            group_sync();
+            group_sync<2>();
             maybe_prune();
             hot = false;
             const int i = rr * kGroup + gt;
@@ -951,15 +1066,15 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
             }
           }
         }
-        group_sync();
-        if (MASKED) sel_prune(selA, selA.k, ps, gt);
+        group_sync<2>();
+        if (MASKED) sel_prune<2>(selA, selA.k, psF, gt);
       }
 
       // ---- candidates best first. Up to 512 entries are ranked by counting, which selects the k
       // best and sorts them in one step; a longer buffer is cut by the radix select first.
-      if (*selB.cnt > 2 * kGroup) sel_prune(selB, selB.k, ps, gt);
-      group_sync();
-      const int nbuf = min(*selB.cnt, 2 * kGroup);
+      if (*selB.cnt > kSortCap) sel_prune<2>(selB, selB.k, psF, gt);
+      group_sync<2>();
+      const int nbuf = min(*selB.cnt, kSortCap);
       const int nB = min(nbuf, selB.k);
       for (int i = gt; i < nbuf; i += kGroup) {
         const uint32_t ky = selB.key[i];
@@ -977,7 +1092,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
         s64[L_LOW] = 0xFFFFFFFFFFFFFFFFull;   // smallest composite of the head
         sh[S_FLAGS] = 0;
       }
-      group_sync();
+      group_sync<2>();
       // ---- tools/sampler.h:54-77 (or :105-143)
       int flags = 0, nc = nB;
       if (MASKED) {
@@ -987,7 +1102,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
           if (!(bans && value_of(selA.key[i]) <= ARCS_BANNED)) atomicMax(&s64[L_TOP], (unsigned long long)c);
           atomicMin(&s64[L_LOW], (unsigned long long)c);
         }
-        group_sync();
+        group_sync<2>();
         if (gt == 0) {
           const uint64_t top = s64[L_TOP], low = s64[L_LOW];
           if (top != 0ull && (nB == 0 || comp_of(key_of(sv[0]), sid[0]) != top)) flags |= ARCS_FLAG_FIRST_REFUSED;
@@ -1007,7 +1122,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
           sh[S_NCAND] = nc;
           sh[S_FLAGS] = flags;
         }
-        group_sync();
+        group_sync<2>();
         nc = sh[S_NCAND];
       } else {
         if (gt == 0) {
@@ -1015,7 +1130,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
             while (nc > 1 && sv[nc - 1] <= ARCS_BANNED) --nc;
           sh[S_NCAND] = nc;
         }
-        group_sync();
+        group_sync<2>();
         nc = sh[S_NCAND];
       }
       {  // equal logits among the candidates kept: the reference's order there is not defined
@@ -1030,17 +1145,17 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
           const float x = __fdiv_rn(__fsub_rn(sv[i], mx), r.prm.temperature);  // :60 float arithmetic
           spr[i] = (double)(float)exp((double)x);                              // float exp, widened
         }
-        group_sync();
+        group_sync<2>();
         if (gt == 0) {
           double z = 0.0;
           for (int i = 0; i < nc; ++i) z = __dadd_rn(z, spr[i]);  // :58-60 in candidate order
           spr[ARCS_KCAP] = z;
         }
-        group_sync();
+        group_sync<2>();
         const double z = spr[ARCS_KCAP];
         for (int i = gt; i < nc; i += kGroup) spr[i] = __ddiv_rn(spr[i], z);  // :64, the same quotients in any order
       }
-      group_sync();
+      group_sync<2>();
       if (gt == 0) {
         int token = nc > 0 ? sid[0] : -1, n = nc > 0 ? 1 : 0;
         if (draw) {
@@ -1067,7 +1182,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
         if (a.n_cand) a.n_cand[b] = nc;
         if (a.n_kept) a.n_kept[b] = n;
       }
-      group_sync();
+      group_sync<2>();
       if (gt == 0 && a.flags) a.flags[b] = sh[S_FLAGS];
       for (int i = gt; i < a.cand_stride && (a.cand_id || a.cand_val || a.cand_pr); i += kGroup) {
         const size_t o = (size_t)b * a.cand_stride + i;
@@ -1076,28 +1191,34 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
         if (a.cand_val) a.cand_val[o] = in ? sv[i] : 0.0f;
         if (a.cand_pr) a.cand_pr[o] = in ? (draw ? (float)spr[i] : (i == 0 ? 1.0f : 0.0f)) : 0.0f;
       }
-      group_sync();
+      group_sync<2>();
+      if (gt == 0) {
+        sh[S_CNT_B + par] = 0;  // the buffers are free for the item after next
+        sh[S_CNT_A + par] = 0;
+        __threadfence_block();
+        vsh[S_FINISHED] = j + 1;
+      }
+      RT(2);
       return true;
     };
 
-    if (my_n > 0) prepare(0);
-    for (int j = 0; j < my_n; ++j) {
-      RT(0);
-      if (j + 1 < my_n) prepare(j + 1);
-      RT(1);
-      if (!finish(j)) break;
-      RT(2);
+    if (warp < kFinWarp0 + kGroup / 32) {
+      for (int j = 0; j < my_n; ++j)
+        if (!prepare(j)) break;
+    } else {
+      for (int j = 0; j < my_n; ++j)
+        if (!finish(j)) break;
     }
-    RT_FLUSH(12, gt == 0);
+    RT_FLUSH(warp < kFinWarp0 + kGroup / 32 ? 12 : 20, gt == 0);
   }
 }
 
 static size_t sample_smem_bytes(bool masked, int hash_slots) {
-  size_t n = (size_t)kRing * kSTile + (size_t)kQueue * 8 + 2 * kRing * 8 + L_END * 8 + (ARCS_KCAP + 1) * 8 +
-             (512 + 256 + 1024) * 4 + (size_t)kTmpCap * 16 + 8 * 4 + S_END * 4 + ARCS_KCAP * 8;
+  size_t n = (size_t)kRing * kSTile + (size_t)kQueue * 8 + (size_t)kScanW * kStash * 20 + 2 * kRing * 8 + L_END * 8 + (ARCS_KCAP + 1) * 8 +
+             (512 + 256 + 1536) * 4 + (size_t)kTmpCap * 16 + 8 * 4 + S_END * 4 + ARCS_KCAP * 8 + 512 * 4 + (size_t)kTmpCap * 8 + 8 * 4;
   n += (size_t)2 * kCapB * 8;
   if (masked) n += (size_t)2 * kCapA * 8;
-  n += (size_t)2 * hash_slots * 8;
+  n += (size_t)3 * hash_slots * 8 + 3 * 256 * 4;
   return n + 128;
 }
 

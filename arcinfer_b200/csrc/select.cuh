@@ -1,6 +1,6 @@
 // Exact top-k selection in shared memory over 64-bit (key, ~id) composites: a candidate
 // buffer with a rising threshold, pruned by an 8-bit radix select. Two forms: one run by a
-// single warp on a buffer only that warp touches, one run by a 256-thread group that
+// single warp on a buffer only that warp touches, one run by a helper group of warps that
 // synchronises on a named barrier (the other warps of the CTA keep streaming meanwhile).
 #pragma once
 #include "common.cuh"
@@ -8,10 +8,12 @@
 namespace arcs {
 
 constexpr int kTmpCap = ARCS_HEAD;  // most entries a prune keeps (the constrained head select keeps 512)
-constexpr int kGroup = 256;         // threads of the finishing group
-constexpr int kGroupBar = 1;        // its named barrier
+constexpr int kGroup = 128;         // threads of each helper group (one prepares items, one finishes them)
 
-__device__ __forceinline__ void group_sync() { asm volatile("bar.sync %0, %1;" ::"n"(kGroupBar), "n"(kGroup) : "memory"); }
+// named-barrier synchronisation of one helper group (BAR: barrier number, kGroup threads)
+template <int BAR>
+__device__ __forceinline__ void group_sync() { asm volatile("bar.sync %0, %1;" ::"n"(BAR), "n"(kGroup) : "memory"); }
+template <int BAR>
 __device__ __forceinline__ bool group_sync_or(bool pred) {
   uint32_t r;
   asm volatile(
@@ -20,7 +22,7 @@ __device__ __forceinline__ bool group_sync_or(bool pred) {
       "bar.red.or.pred p, %2, %3, q;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(r)
-      : "r"((uint32_t)pred), "n"(kGroupBar), "n"(kGroup)
+      : "r"((uint32_t)pred), "n"(BAR), "n"(kGroup)
       : "memory");
   return r != 0;
 }
@@ -111,16 +113,16 @@ __device__ __forceinline__ void find_bin(const uint32_t* h, int krem, int& digit
 // finishing group (gt = thread index inside the group) with the buffer quiescent. Radix
 // select, most significant byte first, over the composite (key << 32 | ~id): composites are
 // unique, so the k-th is found exactly, ties included.
+template <int BAR>
 __device__ __noinline__ void sel_prune(const Sel& s, int k, const PruneScratch& ps, int gt) {
   const int n = min(*s.cnt, s.cap);
   if (n <= k) return;
-  ps.hist[gt] = 0;
-  ps.hist[256 + gt] = 0;
+  for (int i = gt; i < 512; i += kGroup) ps.hist[i] = 0;
   if (gt == 0) {
     ps.misc[3] = 0;
     *ps.m64 = 0xFFFFFFFFFFFFFFFFull;
   }
-  group_sync();
+  group_sync<BAR>();
   uint64_t prefix = 0, mask = 0;
   int krem = k;
   for (int pass = 0; pass < 8; ++pass) {
@@ -130,8 +132,8 @@ __device__ __noinline__ void sel_prune(const Sel& s, int k, const PruneScratch& 
       const uint64_t c = comp_of(s.key[i], s.id[i]);
       if ((c & mask) == prefix) atomicAdd(&h[(uint32_t)(c >> shift) & 255u], 1u);
     }
-    ps.hist[((pass + 1) & 1) * 256 + gt] = 0;
-    group_sync();
+    for (int i = gt; i < 256; i += kGroup) ps.hist[((pass + 1) & 1) * 256 + i] = 0;
+    group_sync<BAR>();
     if (gt < 32) {
       int d, kr;
       bool ex;
@@ -142,7 +144,7 @@ __device__ __noinline__ void sel_prune(const Sel& s, int k, const PruneScratch& 
         ps.misc[2] = ex;
       }
     }
-    group_sync();
+    group_sync<BAR>();
     const int d = ps.misc[0];
     krem = ps.misc[1];
     const bool exact = ps.misc[2] != 0;
@@ -162,7 +164,7 @@ __device__ __noinline__ void sel_prune(const Sel& s, int k, const PruneScratch& 
       atomicMin(ps.m64, (unsigned long long)c);
     }
   }
-  group_sync();
+  group_sync<BAR>();
   const int m = min(ps.misc[3], kTmpCap);
   for (int i = gt; i < m; i += kGroup) {
     s.key[i] = ps.tk[i];
@@ -172,22 +174,24 @@ __device__ __noinline__ void sel_prune(const Sel& s, int k, const PruneScratch& 
     *s.cnt = m;
     *s.tau = *ps.m64 - 1ull;  // exclusive: the smallest kept composite itself still passes
   }
-  group_sync();
+  group_sync<BAR>();
 }
 
 
-// The kth largest (1-based) of the kGroup keys in keys[], found by the whole group with a
+// The kth largest (1-based) of the 2 * kGroup keys in keys[], found by the whole group with a
 // 4-pass radix select on the 32-bit keys. Every thread returns the same value.
+template <int BAR>
 __device__ __noinline__ uint32_t group_kth_key(const uint32_t* keys, int kth, const PruneScratch& ps, int gt) {
-  const uint32_t my = keys[gt];
+  const uint32_t my0 = keys[gt], my1 = keys[kGroup + gt];
   uint32_t prefix = 0, mask = 0;
   int krem = kth;
   for (int pass = 0; pass < 4; ++pass) {
     const int shift = 24 - 8 * pass;
-    ps.hist[gt] = 0;
-    group_sync();
-    if ((my & mask) == prefix) atomicAdd(&ps.hist[(my >> shift) & 255u], 1u);
-    group_sync();
+    for (int i = gt; i < 256; i += kGroup) ps.hist[i] = 0;
+    group_sync<BAR>();
+    if ((my0 & mask) == prefix) atomicAdd(&ps.hist[(my0 >> shift) & 255u], 1u);
+    if ((my1 & mask) == prefix) atomicAdd(&ps.hist[(my1 >> shift) & 255u], 1u);
+    group_sync<BAR>();
     if (gt < 32) {
       int d, kr;
       bool ex;
@@ -197,12 +201,12 @@ __device__ __noinline__ uint32_t group_kth_key(const uint32_t* keys, int kth, co
         ps.misc[1] = kr;
       }
     }
-    group_sync();
+    group_sync<BAR>();
     prefix |= (uint32_t)ps.misc[0] << shift;
     mask |= 0xFFu << shift;
     krem = ps.misc[1];
   }
-  group_sync();
+  group_sync<BAR>();
   return prefix;
 }
 
@@ -266,7 +270,7 @@ __device__ __noinline__ int sel_prune_warp(const Sel& s, int n, int k, uint32_t*
     s.key[i] = tk[i];
     s.id[i] = ti[i];
   }
-  if (lane == 0) *reinterpret_cast<volatile unsigned long long*>(s.tau) = cmin - 1ull;  // exclusive threshold
+  if (lane == 0) atomicMax(s.tau, cmin - 1ull);  // exclusive threshold; never lowered (another warp raises it too)
   __syncwarp();
   return out;
 }
