@@ -79,6 +79,9 @@ lib.arcs_argmax_workspace_bytes.restype = C.c_size_t
 lib.arcs_argmax_workspace_bytes.argtypes = [C.c_int32, C.c_int32]
 lib.arcs_argmax_batch.restype = C.c_int
 lib.arcs_argmax_batch.argtypes = [C.POINTER(ArgmaxArgs), C.c_void_p]
+lib.arcs_argmax_batch_static.restype = C.c_int
+lib.arcs_argmax_batch_static.argtypes = [C.POINTER(ArgmaxArgs), C.c_void_p]
+lib.arcs_argmax_static_scratch_bytes.restype = C.c_size_t
 lib.arcs_dfa_mask.restype = C.c_int
 lib.arcs_dfa_mask.argtypes = [
     C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
@@ -184,7 +187,7 @@ def sample_batch(logits, params, u, hist_off=None, hist_ids=None, bias_off=None,
     return out
 
 
-def argmax_batch(logits, V=None, want_lse=False, row_off=None, draft=None, draft_off=None, status=None):
+def argmax_batch(logits, V=None, want_lse=False, row_off=None, draft=None, draft_off=None, status=None, static_scratch=False):
     """arcs_argmax_batch: first maximum per row, optional (max, sumexp), optional greedy
     acceptance for rows grouped into slots (row_off / draft / draft_off int32 device tensors)."""
     assert logits.is_cuda and logits.dim() == 2 and logits.stride(1) == 1
@@ -201,13 +204,17 @@ def argmax_batch(logits, V=None, want_lse=False, row_off=None, draft=None, draft
     if status is None:
         status = torch.zeros(1, dtype=torch.int32, device=dev)
     out["status"] = status
-    ws = _workspace("argmax", dev, lib.arcs_argmax_workspace_bytes(R, V))
+    ws = None if static_scratch else _workspace("argmax", dev, lib.arcs_argmax_workspace_bytes(R, V))
     a = ArgmaxArgs()
     a.logits, a.dtype, a.R, a.V, a.row_stride = logits.data_ptr(), _dtype_code(logits), R, V, logits.stride(0)
     a.argmax, a.max_sumexp = out["argmax"].data_ptr(), _ptr(out.get("max_sumexp"))
     a.slots, a.row_off, a.draft, a.draft_off = slots, _ptr(row_off), _ptr(draft), _ptr(draft_off)
     a.accepted, a.next = _ptr(out.get("accepted")), _ptr(out.get("next"))
-    a.workspace, a.workspace_bytes, a.status = ws.data_ptr(), ws.numel(), status.data_ptr()
+    a.status = status.data_ptr()
+    if static_scratch:  # the entry point that allocates nothing: scratch is a fixed array inside the library
+        _check(lib.arcs_argmax_batch_static(C.byref(a), _stream(dev)), "arcs_argmax_batch_static")
+        return out
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
     _check(lib.arcs_argmax_batch(C.byref(a), _stream(dev)), "arcs_argmax_batch")
     return out
 

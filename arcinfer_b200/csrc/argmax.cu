@@ -2,6 +2,8 @@
 // draft-acceptance count per slot. One launch: every CTA streams one segment of one row, folds
 // its (value, id) into a 64-bit atomic max per row, and the CTA that finishes last decodes the
 // rows and walks the slots.
+#include <atomic>
+
 #include "plan.h"
 #include "stream.cuh"
 
@@ -243,4 +245,53 @@ extern "C" int arcs_argmax_batch(const arcs_argmax_args* g, void* stream) {
   }
 #undef ARCS_LAUNCH
   return check_launch("argmax_batch");
+}
+
+// ---------------------------------------------------------------------------------------------
+// arcs_argmax_batch_static: the same launch with its scratch in a fixed device array.
+// ---------------------------------------------------------------------------------------------
+// Some callers of this library must not allocate device memory: a serving loop that has handed
+// the whole of HBM to its own pool (weights, KV cache) and runs with the allocator closed, or
+// code running where an allocation would synchronise the device (between the kernels of a
+// latency-critical step). For them the scratch lives here, once per GPU that loads the library,
+// until the process exits.
+constexpr size_t kStaticScratchBytes = 1u << 20;  // 1 MiB: e.g. 1024 rows x 64 segments
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+namespace {
+constexpr int kMaxDevices = 64;
+void* g_static_ptr[kMaxDevices];           // device address of g_static_scratch, per device
+std::atomic<int> g_static_ready[kMaxDevices];
+}  // namespace
+
+extern "C" size_t arcs_argmax_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+extern "C" int arcs_argmax_batch_static(const arcs_argmax_args* g, void* stream) {
+  if (!g || g->R <= 0 || g->V <= 0) return set_error(ARCS_ERR_ARG, "argmax_batch_static: bad argument");
+  const size_t need = arcs_argmax_workspace_bytes(g->R, g->V);
+  if (need > kStaticScratchBytes) {
+    snprintf(error_buffer(), 256, "argmax_batch_static: %d rows x %d columns need %zu bytes of scratch, the fixed array holds %zu",
+             g->R, g->V, need, kStaticScratchBytes);
+    return ARCS_ERR_WORKSPACE;
+  }
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return set_error(ARCS_ERR_CUDA, cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return set_error(ARCS_ERR_ARG, "argmax_batch_static: device index out of range");
+  if (!g_static_ready[dev].load(std::memory_order_acquire)) {
+    // Set-up, once per device, with that device current: in host code the array's name is only a
+    // handle; the address a kernel can use comes from the runtime. The array is cleared here
+    // because the kernels rely on finding (and leaving) their counters at zero.
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_scratch);
+    if (e != cudaSuccess || !p) return set_error(ARCS_ERR_CUDA, e != cudaSuccess ? cudaGetErrorString(e) : "no address for the scratch array");
+    e = cudaMemsetAsync(p, 0, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return set_error(ARCS_ERR_CUDA, cudaGetErrorString(e));
+    g_static_ptr[dev] = p;
+    g_static_ready[dev].store(1, std::memory_order_release);
+  }
+  arcs_argmax_args a = *g;
+  a.workspace = g_static_ptr[dev];
+  a.workspace_bytes = kStaticScratchBytes;
+  return arcs_argmax_batch(&a, stream);
 }

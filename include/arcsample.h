@@ -129,6 +129,21 @@ typedef struct {
 size_t arcs_argmax_workspace_bytes(int32_t R, int32_t V);
 int arcs_argmax_batch(const arcs_argmax_args* args, void* stream);
 
+/* Variant of arcs_argmax_batch for callers that cannot allocate device memory (no counterpart in
+ * the reference, whose sampler runs on the host). A host that has given all of HBM to its own
+ * pool, or that must not call the allocator between the kernels of a step because the call may
+ * synchronise the device, cannot supply the workspace the plain entry point wants. Here the
+ * scratch is a fixed array inside the library: arcs_argmax_static_scratch_bytes() bytes (1 MiB)
+ * on every GPU that loads the library, held until the process exits. `workspace` and
+ * `workspace_bytes` of the argument block are ignored; inputs and outputs are still the
+ * caller's. Shapes whose scratch (arcs_argmax_workspace_bytes) exceeds the array are refused with
+ * ARCS_ERR_WORKSPACE. The first call on a device looks the array's device address up and clears
+ * it on the given stream: make that call before capturing a stream. All calls on a device share
+ * the array: two calls that overlap on the GPU (different streams) race; calls on one stream are
+ * safe, each leaves the array clean for the next. No allocation is made by this call. */
+size_t arcs_argmax_static_scratch_bytes(void);
+int arcs_argmax_batch_static(const arcs_argmax_args* args, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * dfa_mask: allowed(t) for every token of a vocabulary under a byte automaton, packed.
  * Replaces the per-candidate predicate calls of tools/server_chat.h:539-557
