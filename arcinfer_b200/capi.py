@@ -175,7 +175,7 @@ def sample_batch(logits, params, u, hist_off=None, hist_ids=None, bias_off=None,
     a.bias_off, a.bias_ids, a.bias_vals = _ptr(bias_off), _ptr(bias_ids), _ptr(bias_vals)
     a.u = u.data_ptr()
     a.mask, a.mask_row = _ptr(mask), _ptr(mask_row)
-    a.mask_stride = mask.stride(0) if masked else 0
+    a.mask_stride = (mask.stride(0) if mask.shape[0] > 1 else mask.shape[1]) if masked else 0
     a.max_hist, a.max_bias, a.id_base, a.v_global = max_hist, max_bias, id_base, v_global
     a.token, a.n_cand, a.n_kept, a.flags = (out[k].data_ptr() for k in ("token", "n_cand", "n_kept", "flags"))
     if want_cands:
@@ -324,7 +324,8 @@ class SamplePlan:
         a.logits, a.dtype, a.B, a.V, a.row_stride = logits.data_ptr(), _dtype_code(logits), B, V, logits.stride(0)
         a.params, a.u = params.data_ptr(), u.data_ptr()
         a.hist_off, a.hist_ids, a.max_hist = _ptr(hist_off), _ptr(hist_ids), max_hist
-        a.mask, a.mask_row, a.mask_stride = _ptr(mask), _ptr(mask_row), (mask.stride(0) if masked else 0)
+        a.mask, a.mask_row = _ptr(mask), _ptr(mask_row)
+        a.mask_stride = (mask.stride(0) if mask.shape[0] > 1 else mask.shape[1]) if masked else 0
         a.id_base, a.v_global = id_base, v_global
         a.token, a.n_cand, a.n_kept, a.flags = (self.out[k].data_ptr() for k in ("token", "n_cand", "n_kept", "flags"))
         if want_cands:

@@ -164,6 +164,8 @@ __global__ void __launch_bounds__(kThreads) argmax_kernel(const ArgmaxDev a) {
       for (int g = 0; g < a.nseg; ++g) {
         const float2 pr = __ldcg(&a.ws_part[(size_t)i * a.nseg + g]);
         lse_merge(m, s, pr.x, pr.y);
+        // leave zeros behind: a later launch of another shape may keep a row's maximum here
+        a.ws_part[(size_t)i * a.nseg + g] = make_float2(0.0f, 0.0f);
       }
       a.max_sumexp[2 * i] = m;
       a.max_sumexp[2 * i + 1] = s;

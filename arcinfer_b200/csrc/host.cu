@@ -25,6 +25,7 @@ struct arcs_host_ctx {
   int32_t *argmax = nullptr, *row_off = nullptr, *draft = nullptr, *draft_off = nullptr, *accepted = nullptr, *next = nullptr;
   float* max_sumexp = nullptr;
   void* ws[2] = {nullptr, nullptr};
+  void* ws_argmax = nullptr;  // (the two kernels lay their scratch out differently: kept apart)
   size_t ws_bytes = 0;
   int32_t* status = nullptr;
   int32_t last_status = 0;
@@ -48,7 +49,7 @@ extern "C" void arcs_host_destroy(arcs_host_ctx* c) {
                   (void*)c->bias_ids, (void*)c->bias_vals, (void*)c->u, (void*)c->mask, (void*)c->mask_row,
                   (void*)c->token, (void*)c->n_cand, (void*)c->n_kept, (void*)c->flags, (void*)c->cand_id,
                   (void*)c->cand_val, (void*)c->cand_pr, (void*)c->argmax, (void*)c->row_off, (void*)c->draft,
-                  (void*)c->draft_off, (void*)c->accepted, (void*)c->next, (void*)c->max_sumexp, c->ws[0], c->ws[1],
+                  (void*)c->draft_off, (void*)c->accepted, (void*)c->next, (void*)c->max_sumexp, c->ws[0], c->ws[1], c->ws_argmax,
                   (void*)c->status})
     if (p) cudaFree(p);
   if (c->small_ready) cudaEventDestroy(c->small_ready);
@@ -76,7 +77,7 @@ extern "C" int arcs_host_create(arcs_host_ctx** out, int32_t device, int32_t max
   const size_t B = (size_t)max_B;
   // Upper bound of the scratch any chunk of <= max_B rows can ask for: rows * segments never
   // exceeds 4 CTAs per SM plus one segment per row (plan_segments), each with a masked block.
-  const size_t wsb = 4096 + (size_t)max_B * 16 + ((size_t)kSmCount * 4 + (size_t)max_B) * (16 + ARCS_KCAP * 8 + ARCS_HEAD * 8 + 8);
+  const size_t wsb = 4096 + ((size_t)1 << 18) + (size_t)max_B * 16 + ((size_t)kSmCount * 4 + (size_t)max_B) * (16 + ARCS_KCAP * 8 + ARCS_HEAD * 8 + 8);
   c->ws_bytes = wsb;
   cudaError_t e = cudaSuccess;
   auto ok = [&](cudaError_t r) { if (e == cudaSuccess) e = r; };
@@ -111,6 +112,8 @@ extern "C" int arcs_host_create(arcs_host_ctx** out, int32_t device, int32_t max
     ok(cudaMalloc(&c->ws[i], wsb));
     if (e == cudaSuccess) ok(cudaMemset(c->ws[i], 0, wsb));
   }
+  ok(cudaMalloc(&c->ws_argmax, wsb));
+  if (e == cudaSuccess) ok(cudaMemset(c->ws_argmax, 0, wsb));
   ok(dalloc(&c->status, 1));
   if (e == cudaSuccess) ok(cudaMemset(c->status, 0, sizeof(int32_t)));
   if (e == cudaSuccess) ok(cudaDeviceSynchronize());
@@ -140,6 +143,7 @@ static int finish(arcs_host_ctx* c) {
   if (c->last_status != 0) {  // leave the scratch clean for the next call
     CU(cudaMemset(c->ws[0], 0, c->ws_bytes));
     CU(cudaMemset(c->ws[1], 0, c->ws_bytes));
+    CU(cudaMemset(c->ws_argmax, 0, c->ws_bytes));
     CU(cudaMemset(c->status, 0, sizeof(int32_t)));
     return set_error(c->last_status, "device status set by the kernels");
   }
@@ -277,7 +281,7 @@ extern "C" int arcs_argmax_batch_host(arcs_host_ctx* c, const arcs_argmax_args* 
   d.draft_off = c->draft_off;
   d.accepted = c->accepted;
   d.next = c->next;
-  d.workspace = c->ws[0];
+  d.workspace = c->ws_argmax;
   d.workspace_bytes = c->ws_bytes;
   d.status = c->status;
   const int rc = arcs_argmax_batch(&d, st);

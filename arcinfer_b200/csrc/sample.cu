@@ -744,7 +744,7 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
     // history a penalty applies to, every id of the bias list: tools/sampler.h:154-174) and a
     // first threshold from a short prefix of the item, read ahead of the ring.
     auto prepare = [&](int j) -> bool {
-      const int par = j & 1, st = j % 3;
+      const int st = j % 3;
       RT(0);
       {  // the item three back used the same set of state: it must be finished and acknowledged
         bool bad = false;
@@ -840,25 +840,20 @@ __global__ void __launch_bounds__(kThreadsP, 1) sample_kernel(const SampleDev a)
         ptk[kGroup + gt] = any1 ? key_of(m1) : 0u;
         group_sync<1>();
         if (kth <= min(nchunk, 2 * kGroup)) {
-          const uint32_t kk0 = group_kth_key<1>(ptk, kth, psP, gt);
+          const uint32_t kk0 = group_kth_key<1>(ptk, 2 * kGroup, kth, psP, gt);
           tau0B = (unsigned long long)kk0 << 32;  // keeps ties with it
         }
       }
       if (MASKED) {
-        const Sel sA{akey + par * kCapA, aid + par * kCapA, &sh[S_CNT_A + par], &s64[L_TAU_A + st], ARCS_HEAD, 1024, kCapA};
-        if (kth <= nchunk && nchunk <= kCapA) {
-          for (int ci = gt; ci < nchunk; ci += kGroup) {
-            sA.key[ci] = key_of(Elem<T>::chunk_max(ldg128_stream(it.p.body + (size_t)ci * 16)));
-            sA.id[ci] = ci;
-          }
-          if (gt == 0) {
-            *sA.cnt = nchunk;
-            *sA.tau = 0ull;
-          }
+        // constrained rows rank the whole vocabulary's best 512: k-th largest of up to 1024 chunk
+        // maxima of the prefix (kept in this group's own scratch: the candidate buffers may still
+        // belong to the item two back)
+        constexpr int kKeys = 2 * kTmpCap;  // ptk and pti lie back to back
+        if (kth <= nchunk && nchunk <= kKeys) {
+          for (int ci = gt; ci < kKeys; ci += kGroup)
+            ptk[ci] = ci < nchunk ? key_of(Elem<T>::chunk_max(ldg128_stream(it.p.body + (size_t)ci * 16))) : 0u;
           group_sync<1>();
-          sel_prune<1>(sA, kth, psP, gt);
-          tau0A = (*sA.tau >> 32) << 32;
-          group_sync<1>();
+          tau0A = (unsigned long long)group_kth_key<1>(ptk, kKeys, kth, psP, gt) << 32;  // keeps ties with it
         }
       }
       if (gt == 0) {
@@ -1236,11 +1231,18 @@ extern "C" int arcs_debug_roles(unsigned long long* out32) {
 }
 #endif
 
+// Workspace layout: [0, 256) reserved; then kMaxRows arrival counters (a fixed zone, so that no
+// launch of another shape ever leaves list data where a later launch keeps a counter: counters are
+// the only words that must be zero between launches, and every launch leaves them zero); then the
+// per-segment survivor lists, which need no initialisation.
+constexpr int kMaxRows = 65536;
+constexpr size_t kSegZone = 256 + (size_t)kMaxRows * 4;
+
 extern "C" size_t arcs_sample_workspace_bytes(int32_t B, int32_t V, int32_t masked) {
   if (B <= 0 || V <= 0) return 0;
   int nseg, seg_len;
   plan_segments(B, V, &nseg, &seg_len);
-  return 256 + (size_t)B * 4 + 256 + (nseg > 1 ? (size_t)B * nseg * seg_block_bytes(masked != 0) : 0);
+  return kSegZone + (nseg > 1 ? (size_t)B * nseg * seg_block_bytes(masked != 0) : 0);
 }
 
 extern "C" int arcs_sample_batch(const arcs_sample_args* g, void* stream) {
@@ -1252,6 +1254,7 @@ extern "C" int arcs_sample_batch(const arcs_sample_args* g, void* stream) {
     return set_error(ARCS_ERR_ARG, "sample_batch: list offsets without the list");
   if (g->max_hist < 0 || g->max_bias < 0 || g->max_hist > (1 << 19) || g->max_bias > (1 << 16))
     return set_error(ARCS_ERR_ARG, "sample_batch: max_hist / max_bias out of range");
+  if (g->B > kMaxRows) return set_error(ARCS_ERR_ARG, "sample_batch: more than 65536 rows in one call");
   const bool masked = g->mask != nullptr;
   if (masked && g->mask_stride < (g->V + 31) / 32) return set_error(ARCS_ERR_ARG, "sample_batch: mask_stride too small");
   if (masked && (g->id_base != 0 || (g->v_global != 0 && g->v_global != g->V)))
@@ -1297,7 +1300,7 @@ extern "C" int arcs_sample_batch(const arcs_sample_args* g, void* stream) {
   a.cand_stride = g->cand_stride;
   char* ws = static_cast<char*>(g->workspace);
   a.ws_arrive = reinterpret_cast<unsigned int*>(ws + 256);
-  a.ws_seg = ws + 256 + (((size_t)g->B * 4 + 255) / 256) * 256;
+  a.ws_seg = ws + kSegZone;
   a.seg_block = seg_block_bytes(masked);
   a.status = g->status;
 

@@ -178,19 +178,21 @@ __device__ __noinline__ void sel_prune(const Sel& s, int k, const PruneScratch& 
 }
 
 
-// The kth largest (1-based) of the 2 * kGroup keys in keys[], found by the whole group with a
-// 4-pass radix select on the 32-bit keys. Every thread returns the same value.
+// The kth largest (1-based) of the n keys in keys[] (n a multiple of kGroup, at most 8 * kGroup),
+// found by the whole group with a 4-pass radix select on the 32-bit keys. Every thread returns
+// the same value.
 template <int BAR>
-__device__ __noinline__ uint32_t group_kth_key(const uint32_t* keys, int kth, const PruneScratch& ps, int gt) {
-  const uint32_t my0 = keys[gt], my1 = keys[kGroup + gt];
+__device__ __noinline__ uint32_t group_kth_key(const uint32_t* keys, int n, int kth, const PruneScratch& ps, int gt) {
   uint32_t prefix = 0, mask = 0;
   int krem = kth;
   for (int pass = 0; pass < 4; ++pass) {
     const int shift = 24 - 8 * pass;
     for (int i = gt; i < 256; i += kGroup) ps.hist[i] = 0;
     group_sync<BAR>();
-    if ((my0 & mask) == prefix) atomicAdd(&ps.hist[(my0 >> shift) & 255u], 1u);
-    if ((my1 & mask) == prefix) atomicAdd(&ps.hist[(my1 >> shift) & 255u], 1u);
+    for (int i = gt; i < n; i += kGroup) {
+      const uint32_t my = keys[i];
+      if ((my & mask) == prefix) atomicAdd(&ps.hist[(my >> shift) & 255u], 1u);
+    }
     group_sync<BAR>();
     if (gt < 32) {
       int d, kr;
