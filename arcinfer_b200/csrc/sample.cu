@@ -196,9 +196,11 @@ __device__ __forceinline__ void queue_write(int* sh, unsigned long long* q_ent, 
   sm_st_volatile64(&q_ent[e % kQueue], (unsigned long long)key | ((unsigned long long)idp << 32));
 }
 
-// The chunks a scanner warp has set aside (data in sq[], chunk number inside the tile in sc[])
-// are examined one element per lane, 32/E chunks per pass. Runs after the warp has released
-// the tile's ring slot, so the time spent here never holds up the copy engine.
+// The chunks a scanner warp has set aside (data in sq[], global id of each chunk's first element
+// in sc[]) are examined one chunk per lane: a float compare finds the (usually single) element
+// that reaches the threshold, then those elements go through the exact test together. Runs
+// after the warp has released the tile's ring slot, so the time spent here never holds up the
+// copy engine.
 template <typename T, bool MASKED>
 __device__ __noinline__ void scan_examine(const ScanCtx& c, const uint4* sq, const int32_t* sc, int n) {
   constexpr int E = Elem<T>::kPerChunk;
@@ -206,15 +208,26 @@ __device__ __noinline__ void scan_examine(const ScanCtx& c, const uint4* sq, con
 #ifdef ARCS_X_EMPTY
   return;
 #endif
-  for (int i0 = 0; i0 < n; i0 += 32 / E) {
-    const int idx = i0 + lane / E, el = lane % E;
-    const bool valid = idx < n;
-    float v = 0.0f;
-    int32_t gid = 0;
-    if (valid) {
-      v = Elem<T>::from_smem(reinterpret_cast<const char*>(&sq[idx]) + el * (int)sizeof(T));
-      gid = (int32_t)sm_ld(&sc[idx]) + el;
-    }
+  // threshold values (inclusive): the exact comparison on (key, id) follows per element
+  const uint32_t kB32 = (uint32_t)(c.tcB >> 32), kA32 = (uint32_t)(c.tcA >> 32);
+  const float tfB = value_of(kB32 < 0x007FFFFFu ? 0x007FFFFFu : kB32);
+  const float tfA = MASKED ? value_of(kA32 < 0x007FFFFFu ? 0x007FFFFFu : kA32) : INFINITY;
+  const float tf = fminf(tfB, tfA);
+  uint4 q = make_uint4(0, 0, 0, 0);
+  int32_t g0 = 0;
+  uint32_t bits = 0;  // elements of this lane's chunk still to be examined
+  if (lane < n) {
+    q = lds128(&sq[lane]);
+    g0 = (int32_t)sm_ld(&sc[lane]);
+#pragma unroll
+    for (int e = 0; e < E; ++e) bits |= (Elem<T>::get(q, e) >= tf ? 1u : 0u) << e;
+  }
+  while (__any_sync(0xFFFFFFFFu, bits != 0u)) {
+    const bool valid = bits != 0u;
+    const int el = valid ? __ffs(bits) - 1 : 0;
+    bits &= bits - 1u;
+    const float v = elem_of_words<T>(q.x, q.y, q.z, q.w, el);
+    const int32_t gid = g0 + el;
     const uint32_t ky = key_of(v);
     const uint64_t cm = comp_of(ky, gid);
     // eligible for the selection proper (B) / for the constrained head ranking (A)
@@ -233,7 +246,7 @@ __device__ __noinline__ void scan_examine(const ScanCtx& c, const uint4* sq, con
 #ifdef ARCS_X_NOPUSH
     okB = okA = false;
 #endif
-    // count the survivors by the upper 16 bits of their keys: the examiner reads thresholds off these counts
+    // count the survivors by the upper 16 bits of their keys: the threshold warp reads thresholds off these counts
     if (okB) sm_red_add(&c.histB[coarse_bin(ky, c.baseB)], 1u);
     if (okA) sm_red_add(&c.histA[coarse_bin(ky, c.baseA)], 1u);
     const bool pass = okB || okA;
