@@ -72,7 +72,7 @@ class ArgmaxArgs(C.Structure):
 lib.arcs_last_error.restype = C.c_char_p
 lib.arcs_version.restype = C.c_int
 lib.arcs_sample_workspace_bytes.restype = C.c_size_t
-lib.arcs_sample_workspace_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int32]
+lib.arcs_sample_workspace_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32]
 lib.arcs_sample_batch.restype = C.c_int
 lib.arcs_sample_batch.argtypes = [C.POINTER(SampleArgs), C.c_void_p]
 lib.arcs_argmax_workspace_bytes.restype = C.c_size_t
@@ -166,7 +166,8 @@ def sample_batch(logits, params, u, hist_off=None, hist_ids=None, bias_off=None,
         status = torch.zeros(1, dtype=torch.int32, device=dev)
     out["status"] = status
     masked = mask is not None
-    nbytes = lib.arcs_sample_workspace_bytes(B, V, int(masked))
+    max_list = (max_hist if hist_off is not None else 0) + (max_bias if bias_off is not None else 0)
+    nbytes = lib.arcs_sample_workspace_bytes(B, V, int(masked), max_list)
     ws = _workspace("sample", dev, nbytes)
     a = SampleArgs()
     a.logits, a.dtype, a.B, a.V, a.row_stride = logits.data_ptr(), _dtype_code(logits), B, V, logits.stride(0)
@@ -319,7 +320,8 @@ class SamplePlan:
         self.out = {k: torch.empty(B, dtype=torch.int32, device=dev) for k in ("token", "n_cand", "n_kept", "flags")}
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
         masked = mask is not None
-        self.ws = _workspace("sample", dev, lib.arcs_sample_workspace_bytes(B, V, int(masked)))
+        max_list = max_hist if hist_off is not None else 0
+        self.ws = _workspace("sample", dev, lib.arcs_sample_workspace_bytes(B, V, int(masked), max_list))
         a = SampleArgs()
         a.logits, a.dtype, a.B, a.V, a.row_stride = logits.data_ptr(), _dtype_code(logits), B, V, logits.stride(0)
         a.params, a.u = params.data_ptr(), u.data_ptr()

@@ -24,9 +24,10 @@ struct arcs_host_ctx {
   float *cand_val = nullptr, *cand_pr = nullptr;
   int32_t *argmax = nullptr, *row_off = nullptr, *draft = nullptr, *draft_off = nullptr, *accepted = nullptr, *next = nullptr;
   float* max_sumexp = nullptr;
-  void* ws[2] = {nullptr, nullptr};
-  void* ws_argmax = nullptr;  // (the two kernels lay their scratch out differently: kept apart)
-  size_t ws_bytes = 0;
+  void* ws[2] = {nullptr, nullptr};  // sample_batch scratch, one per stream, grown on demand
+  size_t ws_sample_bytes = 0;
+  void* ws_argmax = nullptr;
+  size_t ws_bytes = 0;               // argmax scratch
   int32_t* status = nullptr;
   int32_t last_status = 0;
 };
@@ -108,10 +109,6 @@ extern "C" int arcs_host_create(arcs_host_ctx** out, int32_t device, int32_t max
   ok(dalloc(&c->accepted, B));
   ok(dalloc(&c->next, B));
   ok(dalloc(&c->max_sumexp, B * 2));
-  for (int i = 0; i < 2; ++i) {
-    ok(cudaMalloc(&c->ws[i], wsb));
-    if (e == cudaSuccess) ok(cudaMemset(c->ws[i], 0, wsb));
-  }
   ok(cudaMalloc(&c->ws_argmax, wsb));
   if (e == cudaSuccess) ok(cudaMemset(c->ws_argmax, 0, wsb));
   ok(dalloc(&c->status, 1));
@@ -141,8 +138,6 @@ static int finish(arcs_host_ctx* c) {
   CU(cudaStreamSynchronize(c->st[1]));
   CU(cudaStreamSynchronize(c->st[0]));
   if (c->last_status != 0) {  // leave the scratch clean for the next call
-    CU(cudaMemset(c->ws[0], 0, c->ws_bytes));
-    CU(cudaMemset(c->ws[1], 0, c->ws_bytes));
     CU(cudaMemset(c->ws_argmax, 0, c->ws_bytes));
     CU(cudaMemset(c->status, 0, sizeof(int32_t)));
     return set_error(c->last_status, "device status set by the kernels");
@@ -190,6 +185,19 @@ extern "C" int arcs_sample_batch_host(arcs_host_ctx* c, const arcs_sample_args* 
   CU(cudaStreamWaitEvent(c->st[1], c->small_ready, 0));
 
   const int32_t R = chunk_rows(c, B, V);
+  {  // the kernels' scratch depends on the chunk shape and the longest list: grow it when needed
+    const size_t need = arcs_sample_workspace_bytes(R, V, masked, (h->hist_off ? h->max_hist : 0) + (h->bias_off ? h->max_bias : 0));
+    if (need > c->ws_sample_bytes) {
+      CU(cudaStreamSynchronize(c->st[1]));
+      for (int i = 0; i < 2; ++i) {
+        if (c->ws[i]) CU(cudaFree(c->ws[i]));
+        c->ws[i] = nullptr;
+      }
+      c->ws_sample_bytes = 0;
+      for (int i = 0; i < 2; ++i) CU(cudaMalloc(&c->ws[i], need));
+      c->ws_sample_bytes = need;
+    }
+  }
   const bool cands = h->cand_id || h->cand_val || h->cand_pr;
   int k = 0;
   for (int32_t r0 = 0; r0 < B; r0 += R, ++k) {
@@ -225,7 +233,7 @@ extern "C" int arcs_sample_batch_host(arcs_host_ctx* c, const arcs_sample_args* 
     d.cand_pr = cands ? c->cand_pr + (size_t)r0 * ARCS_KCAP : nullptr;
     d.cand_stride = ARCS_KCAP;
     d.workspace = c->ws[k & 1];
-    d.workspace_bytes = c->ws_bytes;
+    d.workspace_bytes = c->ws_sample_bytes;
     d.status = c->status;
     const int rc = arcs_sample_batch(&d, st);
     if (rc != ARCS_OK) {

@@ -93,12 +93,13 @@ typedef struct {
   float* cand_pr;            /* [B][cand_stride] optional: their probabilities pr[i]/z */
   int32_t cand_stride;       /* >= ARCS_KCAP when any cand_* is given */
   /* scratch */
-  void* workspace;           /* arcs_sample_workspace_bytes() bytes, zeroed once before first use */
+  void* workspace;           /* arcs_sample_workspace_bytes() bytes, 16-byte aligned; needs no initialisation */
   size_t workspace_bytes;
   int32_t* status;           /* optional device word: 0 or an arcs_status set by the kernels */
 } arcs_sample_args;
 
-size_t arcs_sample_workspace_bytes(int32_t B, int32_t V, int32_t masked);
+/* max_list: max_hist + max_bias of the call (0 without lists) */
+size_t arcs_sample_workspace_bytes(int32_t B, int32_t V, int32_t masked, int32_t max_list);
 int arcs_sample_batch(const arcs_sample_args* args, void* stream);
 
 /* ------------------------------------------------------------------------------------------

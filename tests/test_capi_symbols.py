@@ -27,8 +27,9 @@ def test_argument_checks_need_no_device():
     assert b"bad argument" in ab.lib.arcs_last_error()
     g = ab.capi.ArgmaxArgs()
     assert ab.lib.arcs_argmax_batch(C.byref(g), None) == 1
-    assert ab.lib.arcs_sample_workspace_bytes(1024, 262144, 0) >= 1024 * 4
-    assert ab.lib.arcs_sample_workspace_bytes(8, 262144, 1) > ab.lib.arcs_sample_workspace_bytes(8, 262144, 0)
+    assert ab.lib.arcs_sample_workspace_bytes(1024, 262144, 0, 0) >= 1024 * 4
+    assert ab.lib.arcs_sample_workspace_bytes(8, 262144, 1, 0) > ab.lib.arcs_sample_workspace_bytes(8, 262144, 0, 0)
+    assert ab.lib.arcs_sample_workspace_bytes(8, 262144, 0, 512) > ab.lib.arcs_sample_workspace_bytes(8, 262144, 0, 0)
 
 
 def test_struct_layout_matches_header():
