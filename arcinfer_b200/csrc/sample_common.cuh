@@ -23,7 +23,6 @@ constexpr int kBootBytes = 8192;  // prefix of an item read ahead to seed its th
 constexpr uint32_t kEmpty = 0xFFFFFFFFu;
 // per touched token: occurrences in the history (low 20 bits) and what applies to it
 constexpr uint32_t kInfoCount = 0xFFFFFu, kInfoWindow = 1u << 31, kInfoBias = 1u << 30, kInfoBan = 1u << 29;
-constexpr int kBloomWords = 256;  // 8192-bit filter over the table's columns
 constexpr int kMaxScalars = 16;   // elements of an item outside its 16-byte aligned body (fewer than 8 at either end)
 
 struct SampleDev {
@@ -57,7 +56,7 @@ struct SampleDev {
 };
 
 // ---- one item's block of the workspace
-// [ItemHdr][filter kBloomWords words][table columns hash_slots words]   <- copied to shared memory by the stream kernel
+// [ItemHdr][table columns hash_slots words]   <- copied to shared memory by the stream kernel
 // [entries the prepare kernel supplies: hash_slots + kMaxScalars]        (key | word y << 32)
 // [survivors of the stream, selection proper: kCapB][constrained head ranking: kCapA when masked]
 struct ItemHdr {
@@ -67,17 +66,16 @@ struct ItemHdr {
   int32_t baseB, baseA;             // upper 16 key bits the coarse histograms start at
   int32_t n_pre;                    // entries supplied by the prepare kernel
   int32_t n_candB, n_candA;         // survivors written by the stream kernel
-  int32_t pad[4];
+  unsigned long long tauB, tauA;    // last thresholds of the stream: at least K (512) eligible elements of the item lie above
 };
 static_assert(sizeof(ItemHdr) == 64, "ItemHdr is copied as 64 bytes");
 
-__host__ __device__ inline int32_t item_tab_bytes(int hash_slots) { return (int32_t)sizeof(ItemHdr) + kBloomWords * 4 + hash_slots * 4; }
+__host__ __device__ inline int32_t item_tab_bytes(int hash_slots) { return (int32_t)sizeof(ItemHdr) + hash_slots * 4; }
 __host__ __device__ inline int64_t item_block_bytes(bool masked, int hash_slots) {
   return (int64_t)item_tab_bytes(hash_slots) + (int64_t)(hash_slots + kMaxScalars) * 8 + (int64_t)kCapB * 8 + (masked ? (int64_t)kCapA * 8 : 0);
 }
 struct ItemWs {
   ItemHdr* hdr;
-  uint32_t* bloom;
   uint32_t* hkey;
   unsigned long long* pre;
   unsigned long long* candB;
@@ -87,16 +85,23 @@ __device__ __forceinline__ ItemWs item_ws(const SampleDev& a, int item) {
   char* p = a.ws_items + (size_t)item * a.item_block;
   ItemWs w;
   w.hdr = reinterpret_cast<ItemHdr*>(p);
-  w.bloom = reinterpret_cast<uint32_t*>(p + sizeof(ItemHdr));
-  w.hkey = w.bloom + kBloomWords;
+  w.hkey = reinterpret_cast<uint32_t*>(p + sizeof(ItemHdr));
   w.pre = reinterpret_cast<unsigned long long*>(w.hkey + a.hash_slots);
   w.candB = w.pre + a.hash_slots + kMaxScalars;
   w.candA = w.candB + kCapB;
   return w;
 }
 
+#ifdef ARCS_TRACE
+__device__ long long g_trace[64];
+#define TR(i) do { if (blockIdx.x == 300 && threadIdx.x == 0) g_trace[i] = clock64(); } while (0)
+__device__ long long g_trace2[8 * 16];
+#define TS(ev, j) do { if (blockIdx.x == 0 && (j) < 16) g_trace2[(ev) * 16 + (j)] = clock64(); } while (0)
+#else
+#define TR(i)
+#define TS(ev, j)
+#endif
 __device__ __forceinline__ uint32_t hash_of(int32_t id, int shift) { return ((uint32_t)id * 2654435761u) >> shift; }
-__device__ __forceinline__ uint32_t bloom_bit(int32_t c) { return ((uint32_t)c * 0x9E3779B1u) >> 19; }  // 13 bits
 
 // what every kernel derives from an item number
 template <typename T>

@@ -11,8 +11,30 @@
 
 namespace arcs {
 
+constexpr int kBootKeys = 1024;  // most maxima the first threshold is read off (constrained rows; 256 otherwise)
+
 static size_t prep_smem_bytes(int hash_slots) {
-  return (size_t)hash_slots * 8 + kBloomWords * 4 + 512 * 4 + (size_t)kTmpCap * 8 + 16 * 4 + 16;
+  return (size_t)hash_slots * 8 + (size_t)kBootKeys * 4 + 16 * 4 + 16;
+}
+
+// A lower bound of the kth largest (1-based) of n keys (n a multiple of 128), found by ONE warp
+// with a bit-by-bit search on the keys' upper 16 bits (bf16 resolution; exact for bf16 data):
+// the largest t with at least kth keys >= t. No shared-memory atomics, a few hundred instructions.
+__device__ __forceinline__ uint32_t warp_kth16(const uint32_t* keys, int n, int kth) {
+  const int lane = threadIdx.x & 31;
+  const uint4* k4 = reinterpret_cast<const uint4*>(keys);
+  uint32_t t = 0;
+  for (int bit = 15; bit >= 0; --bit) {
+    const uint32_t cand = (t | (1u << bit)) << 16;
+    int c = 0;
+    for (int i = lane; i < n / 4; i += 32) {
+      const uint4 q = k4[i];
+      c += (q.x >= cand) + (q.y >= cand) + (q.z >= cand) + (q.w >= cand);
+    }
+    c = __reduce_add_sync(0xFFFFFFFFu, c);
+    if (c >= kth) t |= 1u << bit;
+  }
+  return t << 16;
 }
 
 template <typename T, bool MASKED>
@@ -21,11 +43,8 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
   unsigned long long* m64 = reinterpret_cast<unsigned long long*>(smem);      // [2]
   uint32_t* hk = reinterpret_cast<uint32_t*>(m64 + 2);                         // [hash_slots] token columns
   uint32_t* hi_ = hk + a.hash_slots;                                           // [hash_slots] what applies to them
-  uint32_t* bloom = hi_ + a.hash_slots;                                        // [kBloomWords]
-  uint32_t* phist = bloom + kBloomWords;                                       // [512]
-  uint32_t* ptk = phist + 512;                                                 // [kTmpCap]
-  int32_t* pti = reinterpret_cast<int32_t*>(ptk + kTmpCap);                    // [kTmpCap]
-  int* pmisc = reinterpret_cast<int*>(pti + kTmpCap);                          // [8] select scratch, [8..] counters
+  uint32_t* ptk = hi_ + a.hash_slots;                                          // [kBootKeys] maxima over pieces of the prefix
+  int* pmisc = reinterpret_cast<int*>(ptk + kBootKeys);                        // [8..] counters
   int* n_pre = pmisc + 8;
   int* n_extra = pmisc + 9;
 
@@ -33,9 +52,13 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
   const int gt = threadIdx.x;
   const int item = blockIdx.x;
   const int32_t Vg = a.v_global > 0 ? a.v_global : a.V;
-  const PruneScratch psP{phist, ptk, pti, pmisc, &m64[0]};
+  TR(0);
   const Item<T> it = item_of<T>(a, item);
   const RowCfg r = row_cfg<MASKED>(a, it.b);
+#ifdef ARCS_TRACE
+  if (r.H > 100000) return;  // (wait for the settings, so that the trace separates the phases)
+#endif
+  TR(1);
   const ItemWs w = item_ws(a, item);
   const uint32_t* mrow = MASKED ? a.mask + (size_t)(a.mask_row ? a.mask_row[it.b] : it.b) * a.mask_stride : nullptr;
 
@@ -61,6 +84,10 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
     }
   }
 
+#ifdef ARCS_TRACE
+  if (m0 == 123.f) return;
+#endif
+  TR(2);
   bool bans = false;  // Sampler::bans_: any bias entry <= -100, in range or not (tools/sampler.h:34)
   for (int i = gt; i < r.NB && r.lists_ok; i += kGroup) bans = bans || a.bias_vals[r.q0 + i] <= -100.0f;
   if (r.touched_on) {
@@ -68,45 +95,76 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
       hk[i] = kEmpty;
       hi_[i] = 0;
     }
-    for (int i = gt; i < kBloomWords; i += kGroup) bloom[i] = 0u;
     __syncthreads();
+    TR(16);
     auto insert = [&](int32_t t) -> int {  // global id -> slot, -1 when it is not this item's
       if (t < 0 || t >= Vg) return -1;
       const int32_t c = t - a.id_base;
       if (c < it.lo || c >= it.hi) return -1;
       uint32_t h = hash_of(c, a.hash_shift);
+#ifdef ARCS_X_NOCAS
+      hk[h] = (uint32_t)c;
+      return (int)h;
+#endif
       for (int probe = 0; probe < a.hash_slots; ++probe) {
         const uint32_t old = atomicCAS(&hk[h], kEmpty, (uint32_t)c);
-        if (old == kEmpty) atomicOr(&bloom[bloom_bit(c) >> 5], 1u << (bloom_bit(c) & 31));
-        if (old == kEmpty || old == (uint32_t)c) return (int)h;
+        if (old == kEmpty) return (int)h;                                      // first occurrence
+        if (old == (uint32_t)c) return (int)h | 0x40000000;                    // seen before
         h = (h + 1) & (uint32_t)(a.hash_slots - 1);
       }
       return -1;
     };
-    if (r.pen_on) {
-      const int32_t nwin = r.prm.repeat_last_n < 0 ? r.H : min(r.H, r.prm.repeat_last_n);  // tools/sampler.h:163
-      for (int i = gt; i < r.H; i += kGroup) {
-        const int s = insert(a.hist_ids[r.h0 + i]);
-        if (s >= 0) atomicAdd(&hi_[s], 1u);
-        if (s >= 0 && i >= r.H - nwin) atomicOr(&hi_[s], kInfoWindow);
-      }
-    }
+    // the bias list goes in first: a slot that carries a bias flag was opened by it, any other by the history
     for (int i = gt; i < r.NB; i += kGroup) {
       const int s = insert(a.bias_ids[r.q0 + i]);
-      if (s >= 0) atomicOr(&hi_[s], a.bias_vals[r.q0 + i] > -100.0f ? kInfoBias : kInfoBan);
+      if (s >= 0) atomicOr(&hi_[s & 0x3FFFFFFF], a.bias_vals[r.q0 + i] > -100.0f ? kInfoBias : kInfoBan);
+    }
+    __syncthreads();
+    if (r.pen_on) {
+      const int32_t nwin = r.prm.repeat_last_n < 0 ? r.H : min(r.H, r.prm.repeat_last_n);  // tools/sampler.h:163
+      constexpr int R = 4;  // ids fetched together: one trip to memory per batch, not per id
+      for (int i0 = 0; i0 < r.H; i0 += R * kGroup) {
+        int32_t t[R];
+#pragma unroll
+        for (int x = 0; x < R; ++x) {
+          const int i = i0 + x * kGroup + gt;
+          t[x] = i < r.H ? __ldg(&a.hist_ids[r.h0 + i]) : -1;
+        }
+#ifdef ARCS_TRACE
+        if (t[0] + t[1] + t[2] + t[3] == -12345) return;
+        TR(17);
+#endif
+#pragma unroll
+        for (int x = 0; x < R; ++x) {
+          const int i = i0 + x * kGroup + gt;
+          // shared-memory atomics are the scarce unit here: one per id, more only for a repeated
+          // id (its count is 1 + the additions) and for a window shorter than the history
+          const int s = insert(t[x]);
+          if (s >= 0 && (s & 0x40000000)) atomicAdd(&hi_[s & 0x3FFFFFFF], 1u);
+          if (s >= 0 && nwin < r.H && i >= r.H - nwin) atomicOr(&hi_[s & 0x3FFFFFFF], kInfoWindow);
+        }
+      }
     }
   }
   bans = __syncthreads_or(bans) != 0;
+  TR(3);
 
-  // one more entry for the finish kernel: v is the final (adjusted) logit of column c
-  auto supply = [&](float v, int32_t c) {
+  // one more entry for the finish kernel (called by whole warps; lanes with `valid` supply):
+  // v is the final (adjusted) logit of column c
+  auto supply = [&](bool valid, float v, int32_t c) {
     const uint32_t ky = key_of(v);
-    if (ky == 0u) return;
+    valid = valid && ky != 0u;
+    const unsigned bal = __ballot_sync(0xFFFFFFFFu, valid);
+    if (bal == 0u) return;
+    const int lane = gt & 31, leader = __ffs(bal) - 1;
+    int base = 0;
+    if (lane == leader) base = atomicAdd(n_pre, __popc(bal));
+    base = __shfl_sync(0xFFFFFFFFu, base, leader);
+    if (!valid) return;
     const int32_t g = c + a.id_base;
     bool okB = true;
     if (MASKED) okB = ((__ldg(&mrow[g >> 5]) >> (g & 31)) & 1u) && !(bans && v + 0.0f <= ARCS_BANNED);  // tools/sampler.h:118-119
-    const int pos = atomicAdd(n_pre, 1);
-    w.pre[pos] = (unsigned long long)ky | ((unsigned long long)((uint32_t)g | (okB ? kOkB : 0u)) << 32);
+    w.pre[base + __popc(bal & ((1u << lane) - 1u))] = (unsigned long long)ky | ((unsigned long long)((uint32_t)g | (okB ? kOkB : 0u)) << 32);
   };
   auto is_touched = [&](int32_t c) -> bool {
     uint32_t h = hash_of(c, a.hash_shift);
@@ -123,7 +181,8 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
   // logits fetched together
   int extra = 0;  // touched tokens inside the prefix: they may own a maximum there without counting
   if (r.touched_on) {
-    constexpr int R = 4;
+    constexpr int R = 8;
+    const bool all_window = (r.prm.repeat_last_n < 0 ? r.H : min(r.H, r.prm.repeat_last_n)) >= r.H;
     const int32_t c_lo = it.p.body_first, c_hi = it.p.body_first + nchunk * E;
     for (int s0 = 0; s0 < a.hash_slots; s0 += R * kGroup) {
       uint32_t ck[R], info[R];
@@ -135,37 +194,45 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
         info[x] = ck[x] != kEmpty ? hi_[s] : 0u;
         raw[x] = ck[x] != kEmpty ? Elem<T>::load(it.row + (int32_t)ck[x]) : 0.0f;
       }
+#ifdef ARCS_TRACE
+      if (raw[0] + raw[1] + raw[2] + raw[3] + raw[4] + raw[5] + raw[6] + raw[7] == -12345.f) return;
+      if (s0 == 0) TR(18);
+#endif
 #pragma unroll
       for (int x = 0; x < R; ++x) {
-        if (ck[x] == kEmpty) continue;
-        extra += (int32_t)ck[x] >= c_lo && (int32_t)ck[x] < c_hi;
+        const bool valid = ck[x] != kEmpty;
         float v = raw[x];
-        const uint32_t cnt = info[x] & kInfoCount;
-        if (info[x] & kInfoBias) {  // :154-155 in list order, duplicates add again
-          const int32_t g = (int32_t)ck[x] + a.id_base;
-          for (int i = 0; i < r.NB; ++i)
-            if (a.bias_ids[r.q0 + i] == g && a.bias_vals[r.q0 + i] > -100.0f) v = __fadd_rn(v, a.bias_vals[r.q0 + i]);
+        if (valid) {
+          extra += (int32_t)ck[x] >= c_lo && (int32_t)ck[x] < c_hi;
+          const uint32_t cnt = (info[x] & kInfoCount) + ((info[x] & (kInfoBias | kInfoBan)) ? 0u : 1u);  // (the id that opened a slot is not added)
+          if (info[x] & kInfoBias) {  // :154-155 in list order, duplicates add again
+            const int32_t g = (int32_t)ck[x] + a.id_base;
+            for (int i = 0; i < r.NB; ++i)
+              if (a.bias_ids[r.q0 + i] == g && a.bias_vals[r.q0 + i] > -100.0f) v = __fadd_rn(v, a.bias_vals[r.q0 + i]);
+          }
+          if (r.pen_on && cnt > 0) {
+            if (r.fp_on) v = __fsub_rn(v, __fmul_rn(r.prm.frequency_penalty, (float)cnt));             // :160
+            if (r.rp_on && (all_window || (info[x] & kInfoWindow)))
+              v = v > 0.0f ? __fdiv_rn(v, r.prm.repeat_penalty) : __fmul_rn(v, r.prm.repeat_penalty);   // :166
+            if (r.pp_on) v = __fsub_rn(v, r.prm.presence_penalty);                                      // :171
+          }
+          if (info[x] & kInfoBan) v = ARCS_BANNED;                                                      // :174
         }
-        if (r.pen_on && cnt > 0) {
-          if (r.fp_on) v = __fsub_rn(v, __fmul_rn(r.prm.frequency_penalty, (float)cnt));             // :160
-          if (r.rp_on && (info[x] & kInfoWindow))
-            v = v > 0.0f ? __fdiv_rn(v, r.prm.repeat_penalty) : __fmul_rn(v, r.prm.repeat_penalty);   // :166
-          if (r.pp_on) v = __fsub_rn(v, r.prm.presence_penalty);                                      // :171
-        }
-        if (info[x] & kInfoBan) v = ARCS_BANNED;                                                      // :174
-        supply(v, (int32_t)ck[x]);
+        supply(valid, v, (int32_t)ck[x]);
       }
     }
+    TR(19);
     if (extra) atomicAdd(n_extra, extra);
   }
+  TR(4);
   // the scalar elements before the first and after the last 16-byte boundary
-  if (gt < it.p.head_n) {
-    const int32_t c = it.lo + gt;
-    if (!(r.touched_on && is_touched(c))) supply(Elem<T>::load(it.row + c), c);
-  }
-  if (gt >= 32 && gt - 32 < it.p.tail_n) {
-    const int32_t c = it.p.tail_first + gt - 32;
-    if (!(r.touched_on && is_touched(c))) supply(Elem<T>::load(it.row + c), c);
+  if (gt < 64) {  // (two whole warps: the first takes the head, the second the tail)
+    const bool head = gt < 32;
+    const int e = gt & 31;
+    bool valid = head ? e < it.p.head_n : e < it.p.tail_n;
+    const int32_t c = head ? it.lo + e : it.p.tail_first + e;
+    if (valid && r.touched_on && is_touched(c)) valid = false;
+    supply(valid, valid ? Elem<T>::load(it.row + c) : 0.0f, c);
   }
   __syncthreads();
 
@@ -178,17 +245,23 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
     ptk[gt] = any0 ? key_of(m0) : 0u;
     ptk[kGroup + gt] = any1 ? key_of(m1) : 0u;
     __syncthreads();
-    if (kth <= min(nchunk, 2 * kGroup)) tau0B = (unsigned long long)group_kth_key<1>(ptk, 2 * kGroup, kth, psP, gt) << 32;  // keeps ties with it
+    if (kth <= min(nchunk, 2 * kGroup)) {
+      if (gt < 32) m64[1] = (unsigned long long)warp_kth16(ptk, 2 * kGroup, kth) << 32;  // keeps ties with it
+      __syncthreads();
+      tau0B = m64[1];
+    }
   } else {
     // constrained rows rank the whole vocabulary's best 512: k-th largest of up to 1024 chunk maxima
-    constexpr int kKeys = 2 * kTmpCap;  // ptk and pti lie back to back
-    if (kth <= nchunk && nchunk <= kKeys) {
-      for (int ci = gt; ci < kKeys; ci += kGroup)
+    if (kth <= nchunk && nchunk <= kBootKeys) {
+      for (int ci = gt; ci < kBootKeys; ci += kGroup)
         ptk[ci] = ci < nchunk ? key_of(Elem<T>::chunk_max(ldg128_stream(it.p.body + (size_t)ci * 16))) : 0u;
       __syncthreads();
-      tau0A = (unsigned long long)group_kth_key<1>(ptk, kKeys, kth, psP, gt) << 32;  // keeps ties with it
+      if (gt < 32) m64[1] = (unsigned long long)warp_kth16(ptk, kBootKeys, kth) << 32;  // keeps ties with it
+      __syncthreads();
+      tau0A = m64[1];
     }
   }
+  TR(5);
   // ---- the item's block
   if (gt == 0) {
     ItemHdr h;
@@ -202,13 +275,14 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
     h.n_pre = *n_pre;
     h.n_candB = 0;
     h.n_candA = 0;
-    h.pad[0] = h.pad[1] = h.pad[2] = h.pad[3] = 0;
+    h.tauB = tau0B;
+    h.tauA = tau0A;
     *w.hdr = h;
   }
   if (r.touched_on) {
-    for (int i = gt; i < kBloomWords; i += kGroup) w.bloom[i] = bloom[i];
     for (int i = gt; i < a.hash_slots; i += kGroup) w.hkey[i] = hk[i];
   }
+  TR(6);
 }
 
 }  // namespace arcs

@@ -21,7 +21,7 @@ namespace arcs {
 
 constexpr int kScanW = 16;                                 // scanner warps
 #ifndef ARCS_SHARE
-#define ARCS_SHARE 4
+#define ARCS_SHARE 2
 #endif
 constexpr int kShare = ARCS_SHARE;                         // scanner warps that split one tile between them
 constexpr int kTeams = kScanW / kShare;
@@ -30,7 +30,7 @@ constexpr int kProdWarp = kScanW + 1;                      // producer warp (its
 constexpr int kTauWarp = kScanW + 2;                       // threshold warp
 constexpr int kThreadsS = (kScanW + 3) * 32;               // 608 threads
 #ifndef ARCS_PROD_LANES
-#define ARCS_PROD_LANES 1
+#define ARCS_PROD_LANES 2
 #endif
 constexpr int kProdLanes = ARCS_PROD_LANES;                // lanes of the producer warp that issue copies
 #ifndef ARCS_TAU_SLEEP
@@ -76,7 +76,6 @@ __device__ __forceinline__ float elem_of_words<__nv_bfloat16>(uint32_t w0, uint3
 // ---- the scanners' rare path, kept out of line so that the streaming loop stays small
 struct ScanCtx {
   const uint32_t* hk;      // the item's table of replaced tokens (columns)
-  const uint32_t* bloom;   // filter over the same columns: most lookups end here
   int32_t hash_slots, hash_shift;
   int32_t touched, bans, par;
   const uint32_t* mrow;
@@ -155,9 +154,7 @@ __device__ __noinline__ void scan_examine(const ScanCtx& c, const uint4* sq, con
       okB = ((__ldg(&c.mrow[gid >> 5]) >> (gid & 31)) & 1u) && !(c.bans && v + 0.0f <= ARCS_BANNED);  // tools/sampler.h:118-119
     // tokens the table replaces are supplied by the prepare kernel, not by the stream
     if ((okB || okA) && c.touched) {
-      const int32_t col = gid - c.id_base;
-      const uint32_t bb = bloom_bit(col);
-      if (((sm_ld(&c.bloom[bb >> 5]) >> (bb & 31)) & 1u) && table_has(c.hk, c.hash_slots, c.hash_shift, col)) okB = okA = false;
+      if (table_has(c.hk, c.hash_slots, c.hash_shift, gid - c.id_base)) okB = okA = false;  // (half the slots are empty: most lookups end at the first)
     }
     // count the survivors by the upper 16 bits of their keys: the threshold warp reads thresholds off these counts
     if (okB) sm_red_add(&c.histB[coarse_bin(ky, c.baseB)], 1u);
@@ -210,7 +207,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
   volatile int* vsh = sh;
   volatile unsigned long long* v64 = s64;
   auto tab_hdr = [&](int st) { return reinterpret_cast<const ItemHdr*>(tabs + (size_t)st * tab_bytes); };
-  auto tab_bloom = [&](int st) { return reinterpret_cast<const uint32_t*>(tabs + (size_t)st * tab_bytes + sizeof(ItemHdr)); };
+  auto tab_keys = [&](int st) { return reinterpret_cast<const uint32_t*>(tabs + (size_t)st * tab_bytes + sizeof(ItemHdr)); };
 
   constexpr int E = Elem<T>::kPerChunk;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -230,6 +227,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
   for (int i = tid; i < kQueue; i += kThreadsS) q_ent[i] = 0ull;
   for (int i = tid; i < 6 * 256; i += kThreadsS) xh[i] = 0u;
   __syncthreads();  // the only CTA-wide barrier
+  if (tid == 0) TS(0, 0);
 
   auto abort_now = [&]() {
     vsh[S_ABORT] = 1;
@@ -299,14 +297,14 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
         __threadfence_block();
       }
       if (vsh[S_ABORT]) break;
+      if (tid == 0) TS(2, j);
       mbar_try_wait(&tab_full[st], (uint32_t)(j / 3) & 1u);  // (complete: every lane observes the copied table through it)
       const ItemHdr* hd = tab_hdr(st);
       uint4* stq = stash_q + warp * kStash;      // chunks this warp has set aside
       int32_t* stc = stash_c + warp * kStash;
       int nst = 0;
       ScanCtx ctx;
-      ctx.hk = tab_bloom(st) + kBloomWords;
-      ctx.bloom = tab_bloom(st);
+      ctx.hk = tab_keys(st);
       ctx.hash_slots = a.hash_slots;
       ctx.hash_shift = a.hash_shift;
       ctx.touched = hd->touched;
@@ -418,6 +416,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
         nst = 0;
       }
       __syncwarp();
+      if (tid == 0) TS(3, j);
       if (lane == 0) {  // this warp has queued everything it found in the item
         const uint32_t e = atomicAdd(reinterpret_cast<unsigned int*>(&sh[S_QTAIL]), 1u);
         queue_write(sh, q_ent, a.status, e, 0u, kMarker | ((uint32_t)par << 31));
@@ -456,6 +455,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
             s64[L_TAU_A + st] = hd->tau0A;
             __threadfence_block();
             vsh[S_PREPARED] = prepped + 1;
+            TS(1, prepped);
           }
           ++prepped;
           idle = 0;
@@ -653,6 +653,8 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
         if (lane == 0) {
           w.hdr->n_candB = x.cB;
           w.hdr->n_candA = MASKED ? x.cA : 0;
+          w.hdr->tauB = *sBk.tau;
+          w.hdr->tauA = *sA.tau;
         }
 #pragma unroll
         for (int i = 0; i < 16; ++i) xh[(2 * st) * 256 + i * 32 + lane] = 0;  // both histograms of the item's set
@@ -660,6 +662,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
         __threadfence_block();
         ++streamed;
         if (lane == 0) vsh[S_STREAMED] = streamed;
+        if (lane == 0) TS(4, x.itm);
         return true;
       };
       const bool done_o = serve(older);
