@@ -22,6 +22,11 @@ extern "C" int arcs_debug_trace(long long* out64) {
   cudaMemcpyFromSymbol(out64, g_trace, sizeof(long long) * 64);
   return 0;
 }
+extern "C" int arcs_debug_clear() {
+  static long long z[128];
+  cudaMemcpyToSymbol(g_trace2, z, sizeof(z));
+  return 0;
+}
 extern "C" int arcs_debug_trace2(long long* out128) {
   cudaDeviceSynchronize();
   cudaMemcpyFromSymbol(out128, g_trace2, sizeof(long long) * 128);
@@ -46,6 +51,8 @@ extern "C" int arcs_sample_batch(const arcs_sample_args* g, void* stream) {
   if (g->max_hist < 0 || g->max_bias < 0 || g->max_hist > (1 << 19) || g->max_bias > (1 << 16))
     return set_error(ARCS_ERR_ARG, "sample_batch: max_hist / max_bias out of range");
   if (g->B > kMaxRows) return set_error(ARCS_ERR_ARG, "sample_batch: more than 65536 rows in one call");
+  if ((int64_t)g->V + g->id_base >= (int64_t)kIdMask || g->v_global >= (int32_t)kIdMask)
+    return set_error(ARCS_ERR_ARG, "sample_batch: token ids must stay below 2^29 - 1");
   const bool masked = g->mask != nullptr;
   if (masked && g->mask_stride < (g->V + 31) / 32) return set_error(ARCS_ERR_ARG, "sample_batch: mask_stride too small");
   if (masked && (g->id_base != 0 || (g->v_global != 0 && g->v_global != g->V)))

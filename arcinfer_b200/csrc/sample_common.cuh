@@ -15,8 +15,8 @@
 
 namespace arcs {
 
-constexpr uint32_t kIdMask = 0x3FFFFFFFu;  // entry word y: id | eligible for the selection proper << 30 | parity << 31
-constexpr uint32_t kOkB = 1u << 30;
+constexpr uint32_t kIdMask = 0x1FFFFFFFu;  // entry word y: id | flagged by the filter << 29 | eligible for the selection proper << 30 | parity << 31
+constexpr uint32_t kTch = 1u << 29, kOkB = 1u << 30;
 constexpr int kCapB = 1024;   // candidate buffer: prune trigger (<= 512) + one round of pushes
 constexpr int kCapA = 1152;   // constrained head select (k = 512): fill limit 1024 + one step / round of 128
 constexpr int kBootBytes = 8192;  // prefix of an item read ahead to seed its threshold
@@ -56,27 +56,41 @@ struct SampleDev {
 };
 
 // ---- one item's block of the workspace
-// [ItemHdr][table columns hash_slots words]   <- copied to shared memory by the stream kernel
-// [entries the prepare kernel supplies: hash_slots + kMaxScalars]        (key | word y << 32)
+// [ItemHdr][filter bloom_words words]                                  <- copied to shared memory by the stream kernel
+// [entries with final values, from the prepare kernel, then hot elements the filter flagged, from
+//  the stream kernel, raw: hash_slots + kMaxScalars]                   (key | word y << 32)
 // [survivors of the stream, selection proper: kCapB][constrained head ranking: kCapA when masked]
 struct ItemHdr {
   unsigned long long tau0B, tau0A;  // first thresholds (exclusive composites)
+  unsigned long long tauB, tauA;    // last thresholds of the stream: at least K (512) eligible elements of the item lie above
   int32_t K;                        // entries the selection proper keeps
-  int32_t touched, bans;            // the table is in use; a bias entry <= -100 exists (tools/sampler.h:34)
+  int32_t touched;                  // kTouchNone / kTouchLight / kTouchTable
+  int32_t bans;                     // a bias entry <= -100 exists (tools/sampler.h:34)
   int32_t baseB, baseA;             // upper 16 key bits the coarse histograms start at
   int32_t n_pre;                    // entries supplied by the prepare kernel
+  int32_t n_tch;                    // flagged hot elements appended by the stream kernel
   int32_t n_candB, n_candA;         // survivors written by the stream kernel
-  unsigned long long tauB, tauA;    // last thresholds of the stream: at least K (512) eligible elements of the item lie above
+  int32_t pad[7];
 };
-static_assert(sizeof(ItemHdr) == 64, "ItemHdr is copied as 64 bytes");
+static_assert(sizeof(ItemHdr) == 96, "ItemHdr is copied as 96 bytes");
+// How an item's penalised / biased tokens reach the finish kernel.
+//  light: penalties can only lower a logit, so a history token matters only if its raw logit is
+//         hot: the stream flags hot elements the filter knows and the finish kernel adjusts them;
+//         the (few) bias tokens are evaluated by the prepare kernel.
+//  table: some penalty can raise a logit, or the bias list is long: the prepare kernel evaluates
+//         every touched token; flagged hot elements that are touched are dropped later.
+constexpr int kTouchNone = 0, kTouchLight = 1, kTouchTable = 2;
+constexpr int kLightBias = 64;  // longest bias list handled without the table
 
-__host__ __device__ inline int32_t item_tab_bytes(int hash_slots) { return (int32_t)sizeof(ItemHdr) + hash_slots * 4; }
+__host__ __device__ inline int32_t bloom_words_of(int hash_slots) { return hash_slots / 4 < 256 ? 256 : hash_slots / 4; }
+__host__ __device__ inline int32_t item_tab_bytes(int hash_slots) { return (int32_t)sizeof(ItemHdr) + bloom_words_of(hash_slots) * 4; }
+__host__ __device__ inline int32_t item_pre_cap(int hash_slots) { return hash_slots + kMaxScalars; }
 __host__ __device__ inline int64_t item_block_bytes(bool masked, int hash_slots) {
-  return (int64_t)item_tab_bytes(hash_slots) + (int64_t)(hash_slots + kMaxScalars) * 8 + (int64_t)kCapB * 8 + (masked ? (int64_t)kCapA * 8 : 0);
+  return (int64_t)item_tab_bytes(hash_slots) + (int64_t)item_pre_cap(hash_slots) * 8 + (int64_t)kCapB * 8 + (masked ? (int64_t)kCapA * 8 : 0);
 }
 struct ItemWs {
   ItemHdr* hdr;
-  uint32_t* hkey;
+  uint32_t* bloom;
   unsigned long long* pre;
   unsigned long long* candB;
   unsigned long long* candA;
@@ -85,12 +99,14 @@ __device__ __forceinline__ ItemWs item_ws(const SampleDev& a, int item) {
   char* p = a.ws_items + (size_t)item * a.item_block;
   ItemWs w;
   w.hdr = reinterpret_cast<ItemHdr*>(p);
-  w.hkey = reinterpret_cast<uint32_t*>(p + sizeof(ItemHdr));
-  w.pre = reinterpret_cast<unsigned long long*>(w.hkey + a.hash_slots);
-  w.candB = w.pre + a.hash_slots + kMaxScalars;
+  w.bloom = reinterpret_cast<uint32_t*>(p + sizeof(ItemHdr));
+  w.pre = reinterpret_cast<unsigned long long*>(w.bloom + bloom_words_of(a.hash_slots));
+  w.candB = w.pre + item_pre_cap(a.hash_slots);
   w.candA = w.candB + kCapB;
   return w;
 }
+// bit of a column in an item's filter (bits: 32 * bloom_words, a power of two)
+__device__ __forceinline__ uint32_t bloom_bit(int32_t c, int bloom_words) { return (((uint32_t)c * 0x9E3779B1u) >> 8) & (uint32_t)(bloom_words * 32 - 1); }
 
 #ifdef ARCS_TRACE
 __device__ long long g_trace[64];
@@ -127,6 +143,7 @@ struct RowCfg {
   arcs_row_params prm;
   int kB;
   bool greedy, k_bad, fp_on, rp_on, pp_on, pen_on, lists_ok, touched_on;
+  int touch;  // kTouchNone / kTouchLight / kTouchTable
   int32_t h0, H, q0, NB;
 };
 template <bool MASKED>
@@ -149,7 +166,23 @@ __device__ __forceinline__ RowCfg row_cfg(const SampleDev& a, int b) {
   r.pen_on = (r.fp_on || r.rp_on || r.pp_on) && r.H > 0;
   r.lists_ok = r.H <= a.max_hist && r.NB <= a.max_bias;
   r.touched_on = (r.pen_on || r.NB > 0) && r.lists_ok;
+  const bool lowering = (!r.rp_on || r.prm.repeat_penalty >= 1.0f) && !(r.prm.frequency_penalty < 0.0f) && !(r.prm.presence_penalty < 0.0f);
+  r.touch = !r.touched_on ? kTouchNone : ((r.pen_on && !lowering) || r.NB > kLightBias) ? kTouchTable : kTouchLight;
   return r;
+}
+
+// tools/sampler.h:160-171 for a token that occurs cnt (> 0) times in the history; in_window: one
+// of the occurrences lies inside the repeat window
+__device__ __forceinline__ float penalise(const RowCfg& r, float v, uint32_t cnt, bool in_window) {
+  if (r.fp_on) v = __fsub_rn(v, __fmul_rn(r.prm.frequency_penalty, (float)cnt));                         // :160
+  if (r.rp_on && in_window) v = v > 0.0f ? __fdiv_rn(v, r.prm.repeat_penalty) : __fmul_rn(v, r.prm.repeat_penalty);  // :166
+  if (r.pp_on) v = __fsub_rn(v, r.prm.presence_penalty);                                                 // :171
+  return v;
+}
+// first history index inside the repeat window (tools/sampler.h:163)
+__device__ __forceinline__ int32_t window_start(const RowCfg& r) {
+  const int32_t nwin = r.prm.repeat_last_n < 0 ? r.H : min(r.H, r.prm.repeat_last_n);
+  return r.H - nwin;
 }
 
 }  // namespace arcs

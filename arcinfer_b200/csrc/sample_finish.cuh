@@ -10,6 +10,7 @@
 
 namespace arcs {
 
+constexpr int kStage = 512;    // flagged entries settled together
 constexpr int kSortCap = 160;  // a longer buffer is cut to the k best by the radix select before it is ranked by counting
 
 template <typename T, bool MASKED>
@@ -26,32 +27,58 @@ __global__ void __launch_bounds__(kGroup) finish_kernel(const SampleDev a) {
   __shared__ float sv[ARCS_KCAP];
   __shared__ int32_t sid[ARCS_KCAP];
   __shared__ int misc[8];
-  __shared__ int sh[8];
+  __shared__ int sh[12];
   __shared__ int seg_n[3][kMaxSeg];
+  __shared__ uint32_t fl_key[kStage];   // hot elements the filter flagged, waiting to be settled
+  __shared__ int32_t fl_id[kStage];     // (global id | kOkB)
+  __shared__ uint32_t fl_cnt[kStage];   // occurrences in the history | in the repeat window << 31 | in the bias list << 30
   enum { L_TAU_B = 0, L_TAU_A, L_PRUNE_MIN, L_TOP, L_LOW };
-  enum { S_CNT_B = 0, S_CNT_A, S_FLAGS, S_NCAND, S_BANS };
+  enum { S_CNT_B = 0, S_CNT_A, S_FLAGS, S_NCAND, S_BANS, S_NFLAG, S_NLIST, S_NLISTA };
 
   const int gt = threadIdx.x;
   const int b = blockIdx.x;
   const int32_t Vg = a.v_global > 0 ? a.v_global : a.V;
   TR(8);
-  const RowCfg r = row_cfg<MASKED>(a, b);
-#ifdef ARCS_TRACE
-  if (r.H > 100000) return;
-#endif
-  TR(9);
-  const PruneScratch psF{hist, tk, ti, misc, &s64[L_PRUNE_MIN]};
-  const Sel selB{bkey, bid, &sh[S_CNT_B], &s64[L_TAU_B], r.kB, kCapB - kGroup, kCapB};  // (pruned only when the buffer is nearly full)
-  const Sel selA{akey, aid, &sh[S_CNT_A], &s64[L_TAU_A], ARCS_HEAD, 1024, kCapA};
   if (gt == 0) {
     sh[S_CNT_B] = 0;
     sh[S_CNT_A] = 0;
     sh[S_FLAGS] = 0;
     sh[S_BANS] = 0;
+    sh[S_NFLAG] = 0;
+    sh[S_NLIST] = 0;
+    sh[S_NLISTA] = 0;
     s64[L_TAU_B] = 0ull;
     s64[L_TAU_A] = 0ull;
   }
   __syncthreads();
+  // what the segments' headers say (fetched together with the row's settings). Nothing at or
+  // below the largest threshold a segment's stream ended on can be among the k best: that
+  // segment alone holds k above it.
+  for (int g = gt; g < a.nseg; g += kGroup) {
+    const ItemHdr* hd = item_ws(a, b * a.nseg + g).hdr;
+    const int n0 = __ldcg(&hd->n_pre) + __ldcg(&hd->n_tch);  // (the stream kernel appends right behind the prepare kernel's entries)
+    const int n1 = __ldcg(&hd->n_candB), n2 = MASKED ? __ldcg(&hd->n_candA) : 0;
+    seg_n[0][g] = n0;
+    seg_n[1][g] = n1;
+    seg_n[2][g] = n2;
+    atomicAdd(&sh[S_NLIST], n0 + n1);
+    if (MASKED) atomicAdd(&sh[S_NLISTA], n0 + n2);
+    if (__ldcg(&hd->bans) != 0) atomicOr(&sh[S_BANS], 1);
+    atomicMax(&s64[L_TAU_B], __ldcg(&hd->tauB));
+    if (MASKED) atomicMax(&s64[L_TAU_A], __ldcg(&hd->tauA));
+  }
+  const RowCfg r = row_cfg<MASKED>(a, b);
+  __syncthreads();
+#ifdef ARCS_TRACE
+  if (r.H > 100000000) return;
+#endif
+  TR(9);
+  const bool bans = sh[S_BANS] != 0;
+  // barriers between the rounds of pushes are needed only when a buffer or the stage could overflow
+  const bool careful = sh[S_NLIST] > kCapB - kGroup || (MASKED && sh[S_NLISTA] > 1024) || sh[S_NLIST] > kStage - kGroup;
+  const PruneScratch psF{hist, tk, ti, misc, &s64[L_PRUNE_MIN]};
+  const Sel selB{bkey, bid, &sh[S_CNT_B], &s64[L_TAU_B], r.kB, kCapB - kGroup, kCapB};  // (pruned only when the buffer is nearly full)
+  const Sel selA{akey, aid, &sh[S_CNT_A], &s64[L_TAU_A], ARCS_HEAD, 1024, kCapA};
 
   bool hot = false;
   // called by the whole group after a barrier behind which nobody pushes
@@ -61,53 +88,124 @@ __global__ void __launch_bounds__(kGroup) finish_kernel(const SampleDev a) {
     if (pb) sel_prune<2>(selB, selB.k, psF, gt);
     if (pa) sel_prune<2>(selA, selA.k, psF, gt);
   };
-  // one list of entries (key | word y << 32) into the selections, a round of kGroup at a time;
-  // the entries of several rounds are fetched together
-  auto take = [&](const unsigned long long* list, int n, bool toB, bool toA) {
+  const uint32_t* mrow = MASKED ? a.mask + (size_t)(a.mask_row ? a.mask_row[b] : b) * a.mask_stride : nullptr;
+  // after a round of pushes: prune when a buffer has grown past its trigger
+  // (at most kGroup pushes on top of a buffer at or below its trigger: inside its capacity)
+  auto after_push = [&]() {
+    if (group_sync_or<2>(hot)) {
+      maybe_prune();
+      hot = false;
+    }
+  };
+  // Settle the staged flagged entries (tools/sampler.h:154-174 for them): one in the bias list
+  // was evaluated by the prepare kernel and is dropped here; one in the history is dropped too
+  // when the prepare kernel evaluated the history (table mode), else penalised here; one the
+  // filter flagged by accident is an ordinary element.
+  auto settle = [&]() {
+    group_sync<2>();
+    const int nF = min(sh[S_NFLAG], kStage);
+    if (nF == 0) return;
+    for (int f = gt; f < nF; f += kGroup) fl_cnt[f] = 0u;
+    group_sync<2>();
+    const int32_t w0 = window_start(r);
+    for (int i = gt; i < r.NB; i += kGroup) {
+      const int32_t t = a.bias_ids[r.q0 + i];
+      for (int f = 0; f < nF; ++f)
+        if ((fl_id[f] & (int32_t)kIdMask) == t) atomicOr(&fl_cnt[f], 1u << 30);
+    }
+    if (r.pen_on) {
+      for (int i = gt; i < r.H; i += kGroup) {
+        const int32_t t = __ldg(&a.hist_ids[r.h0 + i]);
+        for (int f = 0; f < nF; ++f)
+          if ((fl_id[f] & (int32_t)kIdMask) == t) {
+            atomicAdd(&fl_cnt[f], 1u);
+            if (i >= w0) atomicOr(&fl_cnt[f], 1u << 31);
+          }
+      }
+    }
+    group_sync<2>();
+    for (int f0 = 0; f0 < nF; f0 += kGroup) {
+      const int f = f0 + gt;
+      bool p = f < nF;
+      uint32_t ky = 0u;
+      int32_t id = 0;
+      bool okB = false;
+      if (p) {
+        const uint32_t info = fl_cnt[f], cnt = info & 0x3FFFFFFFu;
+        ky = fl_key[f];
+        id = fl_id[f] & (int32_t)kIdMask;
+        okB = (fl_id[f] & (int32_t)kOkB) != 0;
+        if ((info >> 30) & 1u) {
+          p = false;
+        } else if (cnt > 0) {
+          if (r.touch == kTouchTable) {
+            p = false;
+          } else {
+            const float v = penalise(r, value_of(ky), cnt, w0 == 0 || (info >> 31));
+            ky = key_of(v);
+            p = ky != 0u;
+            if (MASKED) okB = ((__ldg(&mrow[id >> 5]) >> (id & 31)) & 1u) && !(bans && v + 0.0f <= ARCS_BANNED);  // tools/sampler.h:118-119
+          }
+        }
+      }
+      const uint64_t cm = comp_of(ky, id);
+      sel_push(selB, p && okB && cm > *selB.tau, ky, id, hot, a.status);
+      if (MASKED) sel_push(selA, p && cm > *selA.tau, ky, id, hot, a.status);
+      after_push();
+    }
+    if (gt == 0) sh[S_NFLAG] = 0;
+    group_sync<2>();
+  };
+  // Two lists of entries (key | word y << 32) into the selections, a round of kGroup at a time:
+  // `first` feeds both selections, `second` only one (the selection proper, or with toA the
+  // constrained head ranking). The entries of several rounds are fetched together; flagged
+  // entries are staged.
+  auto take = [&](const unsigned long long* first, int n1, const unsigned long long* second, int n2, bool toA) {
     constexpr int R = 4;
+    const int n = n1 + n2;
     for (int i0 = 0; i0 < n; i0 += R * kGroup) {
       unsigned long long e[R];
 #pragma unroll
       for (int x = 0; x < R; ++x) {
         const int i = i0 + x * kGroup + gt;
-        e[x] = i < n ? __ldcg(&list[i]) : 0ull;
+        e[x] = i < n1 ? __ldcg(&first[i]) : i < n ? __ldcg(&second[i - n1]) : 0ull;
       }
 #pragma unroll
       for (int x = 0; x < R; ++x) {
         if (i0 + x * kGroup >= n) break;
-        const bool p = i0 + x * kGroup + gt < n;
+        const int i = i0 + x * kGroup + gt;
+        const bool p = i < n, one = i < n1;
         const uint32_t ky = (uint32_t)e[x], y = (uint32_t)(e[x] >> 32);
         const int32_t id = (int32_t)(y & kIdMask);
+        const bool fl = p && (y & kTch);
         const uint64_t cm = comp_of(ky, id);
-        if (toB) sel_push(selB, p && (y & kOkB) && cm > *selB.tau, ky, id, hot, a.status);
-        if (MASKED && toA) sel_push(selA, p && cm > *selA.tau, ky, id, hot, a.status);
-        // at most kGroup pushes on top of a buffer at or below its trigger: inside its capacity
-        if (group_sync_or<2>(hot)) {
-          maybe_prune();
-          hot = false;
+        sel_push(selB, p && !fl && (one || !toA) && (y & kOkB) && cm > *selB.tau, ky, id, hot, a.status);
+        if (MASKED) sel_push(selA, p && !fl && (one || toA) && cm > *selA.tau, ky, id, hot, a.status);
+        const unsigned bf = __ballot_sync(0xFFFFFFFFu, fl);
+        if (bf) {
+          const int lane = gt & 31, leader = __ffs(bf) - 1;
+          int base = 0;
+          if (lane == leader) base = atomicAdd(&sh[S_NFLAG], __popc(bf));
+          base = __shfl_sync(0xFFFFFFFFu, base, leader);
+          if (fl) {
+            const int pos = base + __popc(bf & ((1u << lane) - 1u));  // (inside the stage: it is emptied below before a round could overflow it)
+            fl_key[pos] = ky;
+            fl_id[pos] = (int32_t)(y & (kIdMask | kOkB));
+          }
+        }
+        if (careful) {
+          after_push();
+          if (sh[S_NFLAG] > kStage - kGroup) settle();
         }
       }
     }
   };
-  // what the segments' headers say, fetched together. Nothing at or below the largest threshold a
-  // segment's stream ended on can be among the k best: that segment alone holds k above it.
-  for (int g = gt; g < a.nseg; g += kGroup) {
-    const ItemHdr* hd = item_ws(a, b * a.nseg + g).hdr;
-    seg_n[0][g] = __ldcg(&hd->n_pre);
-    seg_n[1][g] = __ldcg(&hd->n_candB);
-    seg_n[2][g] = MASKED ? __ldcg(&hd->n_candA) : 0;
-    if (__ldcg(&hd->bans) != 0) atomicOr(&sh[S_BANS], 1);
-    atomicMax(&s64[L_TAU_B], __ldcg(&hd->tauB));
-    if (MASKED) atomicMax(&s64[L_TAU_A], __ldcg(&hd->tauA));
-  }
-  __syncthreads();
-  const bool bans = sh[S_BANS] != 0;
   for (int g = 0; g < a.nseg; ++g) {
     const ItemWs w = item_ws(a, b * a.nseg + g);
-    take(w.pre, seg_n[0][g], true, true);
-    take(w.candB, seg_n[1][g], true, false);
-    if (MASKED) take(w.candA, seg_n[2][g], false, true);
+    take(w.pre, seg_n[0][g], w.candB, seg_n[1][g], false);
+    if (MASKED) take(nullptr, 0, w.candA, seg_n[2][g], true);
   }
+  settle();
   group_sync<2>();
   TR(10);
   if (MASKED) sel_prune<2>(selA, selA.k, psF, gt);
@@ -192,6 +290,7 @@ __global__ void __launch_bounds__(kGroup) finish_kernel(const SampleDev a) {
     group_sync<2>();
     if (gt == 0) {
       double z = 0.0;
+#pragma unroll 8
       for (int i = 0; i < nc; ++i) z = __dadd_rn(z, spr[i]);  // :58-60 in candidate order
       spr[ARCS_KCAP] = z;
     }
@@ -208,6 +307,7 @@ __global__ void __launch_bounds__(kGroup) finish_kernel(const SampleDev a) {
     sh[S_NCAND] = nc;  // n: candidates left after the cuts
     if (draw) {
       double c = 0.0;
+#pragma unroll 8
       for (int i = 0; i < nc; ++i) {
         c = __dadd_rn(c, spr[i]);
         cum[i] = c;
@@ -231,11 +331,17 @@ __global__ void __launch_bounds__(kGroup) finish_kernel(const SampleDev a) {
       n = sh[S_NCAND];
       const double tot = cum[n - 1];                                            // the same sum, in the same order, as :70
       double rr = __dmul_rn(a.u[b], tot);                                       // :71-72
-      int pick = n - 1;
-      for (int i = 0; i < n; ++i) {
-        rr = __dsub_rn(rr, spr[i]);
-        if (rr <= 0.0) { pick = i; break; }
+      int pick = -1;
+      for (int i = 0; i < n && pick < 0; i += 4) {  // (four steps of the chain at a time: the loads run ahead of it)
+        const double p0 = spr[i], p1 = i + 1 < n ? spr[i + 1] : 0.0, p2 = i + 2 < n ? spr[i + 2] : 0.0, p3 = i + 3 < n ? spr[i + 3] : 0.0;
+        const double r0 = __dsub_rn(rr, p0), r1 = __dsub_rn(r0, p1), r2 = __dsub_rn(r1, p2), r3 = __dsub_rn(r2, p3);
+        if (r0 <= 0.0) pick = i;
+        else if (i + 1 < n && r1 <= 0.0) pick = i + 1;
+        else if (i + 2 < n && r2 <= 0.0) pick = i + 2;
+        else if (i + 3 < n && r3 <= 0.0) pick = i + 3;
+        rr = r3;
       }
+      if (pick < 0) pick = n - 1;
       token = sid[pick];
     }
     if (r.k_bad || !r.lists_ok) token = -1;

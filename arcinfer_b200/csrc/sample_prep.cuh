@@ -1,11 +1,14 @@
 // prepare_kernel: everything about an item that does not need the pass over its logits.
 //
-// One CTA of kGroup threads per item (a row, or a segment of a row). It builds the table of the
-// tokens the stream must not supply (every id of the history a penalty applies to, every id of
-// the bias list: tools/sampler.h:154-174), evaluates those tokens itself with the exact fp32
-// arithmetic of Sampler::adjusted, adds the few elements outside the item's 16-byte aligned
-// body, and reads a first threshold off a short prefix of the item. Results go to the item's
-// block of the workspace.
+// One CTA of kGroup threads per item (a row, or a segment of a row). It writes to the item's
+// block of the workspace:
+//  - a filter over the columns a penalty or a bias touches (tools/sampler.h:154-174), which the
+//    stream kernel consults for its hot elements;
+//  - entries with final values for the tokens it evaluates itself, with the exact fp32
+//    arithmetic of Sampler::adjusted: the bias tokens, and - when some penalty can raise a
+//    logit, so that a token may matter although its raw logit is not hot - every history token;
+//  - the few elements outside the item's 16-byte aligned body;
+//  - a first threshold read off a short prefix of the item.
 #pragma once
 #include "sample_common.cuh"
 
@@ -14,7 +17,7 @@ namespace arcs {
 constexpr int kBootKeys = 1024;  // most maxima the first threshold is read off (constrained rows; 256 otherwise)
 
 static size_t prep_smem_bytes(int hash_slots) {
-  return (size_t)hash_slots * 8 + (size_t)kBootKeys * 4 + 16 * 4 + 16;
+  return 16 + (size_t)hash_slots * 8 + (size_t)kBootKeys * 4 + 5 * (size_t)bloom_words_of(hash_slots) * 4 + 16 * 4;
 }
 
 // A lower bound of the kth largest (1-based) of n keys (n a multiple of 128), found by ONE warp
@@ -40,23 +43,26 @@ __device__ __forceinline__ uint32_t warp_kth16(const uint32_t* keys, int n, int 
 template <typename T, bool MASKED>
 __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
   extern __shared__ __align__(128) char smem[];
+  const int bw = bloom_words_of(a.hash_slots);
   unsigned long long* m64 = reinterpret_cast<unsigned long long*>(smem);      // [2]
-  uint32_t* hk = reinterpret_cast<uint32_t*>(m64 + 2);                         // [hash_slots] token columns
+  uint32_t* hk = reinterpret_cast<uint32_t*>(m64 + 2);                         // [hash_slots] token columns (table mode)
   uint32_t* hi_ = hk + a.hash_slots;                                           // [hash_slots] what applies to them
   uint32_t* ptk = hi_ + a.hash_slots;                                          // [kBootKeys] maxima over pieces of the prefix
-  int* pmisc = reinterpret_cast<int*>(ptk + kBootKeys);                        // [8..] counters
-  int* n_pre = pmisc + 8;
-  int* n_extra = pmisc + 9;
+  uint32_t* wb = ptk + kBootKeys;                                              // [4][bw] one filter per warp, merged into ...
+  uint32_t* bl = wb + 4 * bw;                                                  // [bw] ... the item's filter
+  int* pmisc = reinterpret_cast<int*>(bl + bw);
+  int* n_pre = pmisc + 0;
+  int* n_extra = pmisc + 1;
 
   constexpr int E = Elem<T>::kPerChunk;
-  const int gt = threadIdx.x;
+  const int gt = threadIdx.x, lane = gt & 31, warp = gt >> 5;
   const int item = blockIdx.x;
   const int32_t Vg = a.v_global > 0 ? a.v_global : a.V;
   TR(0);
   const Item<T> it = item_of<T>(a, item);
   const RowCfg r = row_cfg<MASKED>(a, it.b);
 #ifdef ARCS_TRACE
-  if (r.H > 100000) return;  // (wait for the settings, so that the trace separates the phases)
+  if (r.H > 100000000) return;  // (wait for the settings, so that the trace separates the phases)
 #endif
   TR(1);
   const ItemWs w = item_ws(a, item);
@@ -68,8 +74,9 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
     *n_pre = 0;
     *n_extra = 0;
   }
-  // the prefix is fetched first: its latency hides behind the table work
+  // the prefix is fetched first: its latency hides behind the list work
   const int nchunk = min(it.p.body_bytes, MASKED ? 2 * kBootBytes : kBootBytes) / 16;
+  const int32_t c_lo = it.p.body_first, c_hi = it.p.body_first + nchunk * E;  // columns of the prefix
   float m0 = -INFINITY, m1 = -INFINITY;
   bool any0 = false, any1 = false;
   if (!MASKED) {
@@ -83,29 +90,117 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
       }
     }
   }
-
-#ifdef ARCS_TRACE
-  if (m0 == 123.f) return;
-#endif
   TR(2);
+
   bool bans = false;  // Sampler::bans_: any bias entry <= -100, in range or not (tools/sampler.h:34)
   for (int i = gt; i < r.NB && r.lists_ok; i += kGroup) bans = bans || a.bias_vals[r.q0 + i] <= -100.0f;
-  if (r.touched_on) {
+  bans = __syncthreads_or(bans) != 0;
+
+  // column of a listed id inside this item, -1 when it is not this item's
+  auto col_of = [&](int32_t t) -> int32_t {
+    if (t < 0 || t >= Vg) return -1;
+    const int32_t c = t - a.id_base;
+    return (c < it.lo || c >= it.hi) ? -1 : c;
+  };
+  // one more column for the filter (called by whole warps). Each warp fills its own copy without
+  // atomics: lanes that hit the same word combine their bits and one of them writes.
+  auto bloom_add = [&](bool valid, int32_t c) {
+    const uint32_t bit = bloom_bit(c, bw);
+    const uint32_t word = valid ? (bit >> 5) : (0x80000000u | (uint32_t)lane);
+    const unsigned peers = __match_any_sync(0xFFFFFFFFu, word);
+    const uint32_t comb = __reduce_or_sync(peers, 1u << (bit & 31));
+    if (valid && lane == __ffs(peers) - 1) wb[warp * bw + word] |= comb;
+    __syncwarp();
+  };
+  // one more entry for the finish kernel (called by whole warps; lanes with `valid` supply):
+  // v is the logit of column c, final unless the entry is flagged for the finish kernel to settle
+  auto supply = [&](bool valid, float v, int32_t c, bool flagged) {
+    const uint32_t ky = key_of(v);
+    valid = valid && ky != 0u;
+    const unsigned bal = __ballot_sync(0xFFFFFFFFu, valid);
+    if (bal == 0u) return;
+    const int leader = __ffs(bal) - 1;
+    int base = 0;
+    if (lane == leader) base = atomicAdd(n_pre, __popc(bal));
+    base = __shfl_sync(0xFFFFFFFFu, base, leader);
+    if (!valid) return;
+    const int32_t g = c + a.id_base;
+    bool okB = true;
+    if (MASKED) okB = ((__ldg(&mrow[g >> 5]) >> (g & 31)) & 1u) && !(bans && v + 0.0f <= ARCS_BANNED);  // tools/sampler.h:118-119
+    w.pre[base + __popc(bal & ((1u << lane) - 1u))] =
+        (unsigned long long)ky | ((unsigned long long)((uint32_t)g | (okB ? kOkB : 0u) | (flagged ? kTch : 0u)) << 32);
+  };
+
+  int extra = 0;  // listed columns inside the prefix: they may own a maximum there without counting
+  if (r.touch != kTouchNone) {
+    for (int i = gt; i < 4 * bw; i += kGroup) wb[i] = 0u;
+    __syncthreads();
+  }
+  if (r.touch == kTouchLight) {
+    // ---- the filter over every listed column; the bias tokens evaluated here
+    constexpr int R = 4;  // ids fetched together: one trip to memory per batch, not per id
+    if (r.pen_on) {
+      for (int i0 = 0; i0 < r.H; i0 += R * kGroup) {
+        int32_t t[R];
+#pragma unroll
+        for (int x = 0; x < R; ++x) {
+          const int i = i0 + x * kGroup + gt;
+          t[x] = i < r.H ? __ldg(&a.hist_ids[r.h0 + i]) : -1;
+        }
+#pragma unroll
+        for (int x = 0; x < R; ++x) {
+          const int32_t c = col_of(t[x]);
+          extra += c >= c_lo && c < c_hi;
+          bloom_add(c >= 0, c);
+        }
+      }
+    }
+    if (r.NB > 0) {
+      const int32_t w0 = window_start(r);
+      for (int i0 = 0; i0 < r.NB; i0 += kGroup) {  // (one round: the list is short in this mode)
+        const int i = i0 + gt;
+        const int32_t t = i < r.NB ? a.bias_ids[r.q0 + i] : -1;
+        const int32_t c = col_of(t);
+        bool first = c >= 0;  // evaluated once, at the id's first entry
+        for (int j = 0; j < i && first; ++j) first = a.bias_ids[r.q0 + j] != t;
+        extra += first && c >= c_lo && c < c_hi;
+        bloom_add(first, c);
+        float v = 0.0f;
+        if (first) {
+          v = Elem<T>::load(it.row + c);
+          bool ban = false;
+          for (int j = i; j < r.NB; ++j) {  // :154-155 in list order, duplicates add again
+            if (a.bias_ids[r.q0 + j] != t) continue;
+            const float bv = a.bias_vals[r.q0 + j];
+            if (bv > -100.0f) v = __fadd_rn(v, bv);
+            else ban = true;
+          }
+          if (r.pen_on) {
+            uint32_t cnt = 0;
+            bool in_win = false;
+            for (int h = 0; h < r.H; ++h)
+              if (__ldg(&a.hist_ids[r.h0 + h]) == t) {
+                ++cnt;
+                in_win = in_win || h >= w0;
+              }
+            if (cnt > 0) v = penalise(r, v, cnt, in_win);
+          }
+          if (ban) v = ARCS_BANNED;                                                                    // :174
+        }
+        supply(first, v, c, false);
+      }
+    }
+  } else if (r.touch == kTouchTable) {
+    // ---- every listed token evaluated here: a table of the distinct columns first
     for (int i = gt; i < a.hash_slots; i += kGroup) {
       hk[i] = kEmpty;
       hi_[i] = 0;
     }
     __syncthreads();
-    TR(16);
-    auto insert = [&](int32_t t) -> int {  // global id -> slot, -1 when it is not this item's
-      if (t < 0 || t >= Vg) return -1;
-      const int32_t c = t - a.id_base;
-      if (c < it.lo || c >= it.hi) return -1;
+    auto insert = [&](int32_t t) -> int {  // global id -> slot (| 0x40000000 when it was there), -1 when it is not this item's
+      const int32_t c = col_of(t);
+      if (c < 0) return -1;
       uint32_t h = hash_of(c, a.hash_shift);
-#ifdef ARCS_X_NOCAS
-      hk[h] = (uint32_t)c;
-      return (int)h;
-#endif
       for (int probe = 0; probe < a.hash_slots; ++probe) {
         const uint32_t old = atomicCAS(&hk[h], kEmpty, (uint32_t)c);
         if (old == kEmpty) return (int)h;                                      // first occurrence
@@ -120,70 +215,18 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
       if (s >= 0) atomicOr(&hi_[s & 0x3FFFFFFF], a.bias_vals[r.q0 + i] > -100.0f ? kInfoBias : kInfoBan);
     }
     __syncthreads();
+    const int32_t w0 = window_start(r);
     if (r.pen_on) {
-      const int32_t nwin = r.prm.repeat_last_n < 0 ? r.H : min(r.H, r.prm.repeat_last_n);  // tools/sampler.h:163
-      constexpr int R = 4;  // ids fetched together: one trip to memory per batch, not per id
-      for (int i0 = 0; i0 < r.H; i0 += R * kGroup) {
-        int32_t t[R];
-#pragma unroll
-        for (int x = 0; x < R; ++x) {
-          const int i = i0 + x * kGroup + gt;
-          t[x] = i < r.H ? __ldg(&a.hist_ids[r.h0 + i]) : -1;
-        }
-#ifdef ARCS_TRACE
-        if (t[0] + t[1] + t[2] + t[3] == -12345) return;
-        TR(17);
-#endif
-#pragma unroll
-        for (int x = 0; x < R; ++x) {
-          const int i = i0 + x * kGroup + gt;
-          // shared-memory atomics are the scarce unit here: one per id, more only for a repeated
-          // id (its count is 1 + the additions) and for a window shorter than the history
-          const int s = insert(t[x]);
-          if (s >= 0 && (s & 0x40000000)) atomicAdd(&hi_[s & 0x3FFFFFFF], 1u);
-          if (s >= 0 && nwin < r.H && i >= r.H - nwin) atomicOr(&hi_[s & 0x3FFFFFFF], kInfoWindow);
-        }
+      for (int i = gt; i < r.H; i += kGroup) {
+        // one atomic per id, more only for a repeated id (its count is 1 + the additions) and
+        // for a window shorter than the history
+        const int s = insert(a.hist_ids[r.h0 + i]);
+        if (s >= 0 && (s & 0x40000000)) atomicAdd(&hi_[s & 0x3FFFFFFF], 1u);
+        if (s >= 0 && w0 > 0 && i >= w0) atomicOr(&hi_[s & 0x3FFFFFFF], kInfoWindow);
       }
     }
-  }
-  bans = __syncthreads_or(bans) != 0;
-  TR(3);
-
-  // one more entry for the finish kernel (called by whole warps; lanes with `valid` supply):
-  // v is the final (adjusted) logit of column c
-  auto supply = [&](bool valid, float v, int32_t c) {
-    const uint32_t ky = key_of(v);
-    valid = valid && ky != 0u;
-    const unsigned bal = __ballot_sync(0xFFFFFFFFu, valid);
-    if (bal == 0u) return;
-    const int lane = gt & 31, leader = __ffs(bal) - 1;
-    int base = 0;
-    if (lane == leader) base = atomicAdd(n_pre, __popc(bal));
-    base = __shfl_sync(0xFFFFFFFFu, base, leader);
-    if (!valid) return;
-    const int32_t g = c + a.id_base;
-    bool okB = true;
-    if (MASKED) okB = ((__ldg(&mrow[g >> 5]) >> (g & 31)) & 1u) && !(bans && v + 0.0f <= ARCS_BANNED);  // tools/sampler.h:118-119
-    w.pre[base + __popc(bal & ((1u << lane) - 1u))] = (unsigned long long)ky | ((unsigned long long)((uint32_t)g | (okB ? kOkB : 0u)) << 32);
-  };
-  auto is_touched = [&](int32_t c) -> bool {
-    uint32_t h = hash_of(c, a.hash_shift);
-    for (int probe = 0; probe < a.hash_slots; ++probe) {
-      const uint32_t kx = hk[h];
-      if (kx == kEmpty) return false;
-      if (kx == (uint32_t)c) return true;
-      h = (h + 1) & (uint32_t)(a.hash_slots - 1);
-    }
-    return false;
-  };
-
-  // touched tokens: exact fp32 arithmetic of Sampler::adjusted, a few tokens per thread, their
-  // logits fetched together
-  int extra = 0;  // touched tokens inside the prefix: they may own a maximum there without counting
-  if (r.touched_on) {
-    constexpr int R = 8;
-    const bool all_window = (r.prm.repeat_last_n < 0 ? r.H : min(r.H, r.prm.repeat_last_n)) >= r.H;
-    const int32_t c_lo = it.p.body_first, c_hi = it.p.body_first + nchunk * E;
+    __syncthreads();
+    constexpr int R = 4;  // table slots per thread per batch: their logits are fetched together
     for (int s0 = 0; s0 < a.hash_slots; s0 += R * kGroup) {
       uint32_t ck[R], info[R];
       float raw[R];
@@ -194,10 +237,6 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
         info[x] = ck[x] != kEmpty ? hi_[s] : 0u;
         raw[x] = ck[x] != kEmpty ? Elem<T>::load(it.row + (int32_t)ck[x]) : 0.0f;
       }
-#ifdef ARCS_TRACE
-      if (raw[0] + raw[1] + raw[2] + raw[3] + raw[4] + raw[5] + raw[6] + raw[7] == -12345.f) return;
-      if (s0 == 0) TR(18);
-#endif
 #pragma unroll
       for (int x = 0; x < R; ++x) {
         const bool valid = ck[x] != kEmpty;
@@ -210,34 +249,44 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
             for (int i = 0; i < r.NB; ++i)
               if (a.bias_ids[r.q0 + i] == g && a.bias_vals[r.q0 + i] > -100.0f) v = __fadd_rn(v, a.bias_vals[r.q0 + i]);
           }
-          if (r.pen_on && cnt > 0) {
-            if (r.fp_on) v = __fsub_rn(v, __fmul_rn(r.prm.frequency_penalty, (float)cnt));             // :160
-            if (r.rp_on && (all_window || (info[x] & kInfoWindow)))
-              v = v > 0.0f ? __fdiv_rn(v, r.prm.repeat_penalty) : __fmul_rn(v, r.prm.repeat_penalty);   // :166
-            if (r.pp_on) v = __fsub_rn(v, r.prm.presence_penalty);                                      // :171
-          }
+          if (r.pen_on && cnt > 0) v = penalise(r, v, cnt, w0 == 0 || (info[x] & kInfoWindow));
           if (info[x] & kInfoBan) v = ARCS_BANNED;                                                      // :174
         }
-        supply(valid, v, (int32_t)ck[x]);
+        bloom_add(valid, (int32_t)ck[x]);
+        supply(valid, v, (int32_t)ck[x], false);
       }
     }
-    TR(19);
-    if (extra) atomicAdd(n_extra, extra);
   }
-  TR(4);
-  // the scalar elements before the first and after the last 16-byte boundary
+  if (extra) atomicAdd(n_extra, extra);
+  __syncthreads();
+  TR(3);
+  // ---- the item's filter: the warps' copies merged, kept here and written out
+  if (r.touch != kTouchNone) {
+    for (int i = gt; i < bw; i += kGroup) {
+      const uint32_t m = wb[i] | wb[bw + i] | wb[2 * bw + i] | wb[3 * bw + i];
+      bl[i] = m;
+      w.bloom[i] = m;
+    }
+    __syncthreads();
+  }
+  // the scalar elements before the first and after the last 16-byte boundary; one the filter
+  // knows is flagged, like a hot element of the stream, for the finish kernel to settle
   if (gt < 64) {  // (two whole warps: the first takes the head, the second the tail)
     const bool head = gt < 32;
-    const int e = gt & 31;
-    bool valid = head ? e < it.p.head_n : e < it.p.tail_n;
-    const int32_t c = head ? it.lo + e : it.p.tail_first + e;
-    if (valid && r.touched_on && is_touched(c)) valid = false;
-    supply(valid, valid ? Elem<T>::load(it.row + c) : 0.0f, c);
+    const bool valid = head ? lane < it.p.head_n : lane < it.p.tail_n;
+    const int32_t c = head ? it.lo + lane : it.p.tail_first + lane;
+    bool flagged = false;
+    if (valid && r.touch != kTouchNone) {
+      const uint32_t bit = bloom_bit(c, bw);
+      flagged = (bl[bit >> 5] >> (bit & 31)) & 1u;
+    }
+    supply(valid, valid ? Elem<T>::load(it.row + c) : 0.0f, c, flagged);
   }
   __syncthreads();
+  TR(4);
 
   // first threshold: the k-th largest of 256 (or, constrained, 1024) maxima over disjoint pieces
-  // of the prefix is a lower bound of the k-th best element; touched tokens inside the prefix
+  // of the prefix is a lower bound of the k-th best element; listed columns inside the prefix
   // may own a maximum without counting, so that many more are skipped
   const int kth = (MASKED ? ARCS_HEAD : r.kB) + *n_extra;
   unsigned long long tau0B = 0ull, tau0A = 0ull;
@@ -262,25 +311,24 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
     }
   }
   TR(5);
-  // ---- the item's block
+  // ---- the item's header
   if (gt == 0) {
     ItemHdr h;
     h.tau0B = tau0B;
     h.tau0A = tau0A;
+    h.tauB = tau0B;
+    h.tauA = tau0A;
     h.K = r.kB;
-    h.touched = r.touched_on;
+    h.touched = r.touch;
     h.bans = bans;
     h.baseB = (int32_t)(tau0B >> 48);
     h.baseA = (int32_t)(tau0A >> 48);
     h.n_pre = *n_pre;
+    h.n_tch = 0;
     h.n_candB = 0;
     h.n_candA = 0;
-    h.tauB = tau0B;
-    h.tauA = tau0A;
+    for (int i = 0; i < 7; ++i) h.pad[i] = 0;
     *w.hdr = h;
-  }
-  if (r.touched_on) {
-    for (int i = gt; i < a.hash_slots; i += kGroup) w.hkey[i] = hk[i];
   }
   TR(6);
 }

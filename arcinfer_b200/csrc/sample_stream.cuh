@@ -36,6 +36,10 @@ constexpr int kProdLanes = ARCS_PROD_LANES;                // lanes of the produ
 #ifndef ARCS_TAU_SLEEP
 #define ARCS_TAU_SLEEP 200
 #endif
+#ifndef ARCS_EXAM_SLEEP
+#define ARCS_EXAM_SLEEP 200
+#endif
+constexpr int kExamSleepNs = ARCS_EXAM_SLEEP;              // examiner's pause while the queue is short
 constexpr int kTauSleepNs = ARCS_TAU_SLEEP;                // pause between two threshold updates
 #ifndef ARCS_RING
 #define ARCS_RING 16
@@ -75,8 +79,8 @@ __device__ __forceinline__ float elem_of_words<__nv_bfloat16>(uint32_t w0, uint3
 
 // ---- the scanners' rare path, kept out of line so that the streaming loop stays small
 struct ScanCtx {
-  const uint32_t* hk;      // the item's table of replaced tokens (columns)
-  int32_t hash_slots, hash_shift;
+  const uint32_t* bloom;   // the item's filter over the columns a penalty or a bias touches
+  int32_t bw;              // its size in words
   int32_t touched, bans, par;
   const uint32_t* mrow;
   uint32_t* histB;         // coarse histograms of the item
@@ -88,17 +92,6 @@ struct ScanCtx {
   int32_t id_base;         // global id of column 0
   uint64_t tcB, tcA;       // thresholds the chunk was listed against
 };
-
-__device__ __forceinline__ bool table_has(const uint32_t* hk, int32_t slots, int32_t shift, int32_t c) {
-  uint32_t h = hash_of(c, shift);
-  for (int probe = 0; probe < slots; ++probe) {
-    const uint32_t kx = sm_ld(&hk[h]);
-    if (kx == kEmpty) return false;
-    if (kx == (uint32_t)c) return true;
-    h = (h + 1) & (uint32_t)(slots - 1);
-  }
-  return false;
-}
 
 // append one entry to the scanner -> examiner queue (the caller holds reservation e)
 __device__ __forceinline__ void queue_write(int* sh, unsigned long long* q_ent, int32_t* status, uint32_t e,
@@ -152,13 +145,16 @@ __device__ __noinline__ void scan_examine(const ScanCtx& c, const uint4* sq, con
     bool okA = MASKED && valid && ky != 0u && cm > c.tcA;
     if (MASKED && okB)
       okB = ((__ldg(&c.mrow[gid >> 5]) >> (gid & 31)) & 1u) && !(c.bans && v + 0.0f <= ARCS_BANNED);  // tools/sampler.h:118-119
-    // tokens the table replaces are supplied by the prepare kernel, not by the stream
+    // a hot element the filter knows may be a penalised or biased token: it is flagged for the
+    // finish kernel to settle, and counts for no threshold
+    bool tch = false;
     if ((okB || okA) && c.touched) {
-      if (table_has(c.hk, c.hash_slots, c.hash_shift, gid - c.id_base)) okB = okA = false;  // (half the slots are empty: most lookups end at the first)
+      const uint32_t bit = bloom_bit(gid - c.id_base, c.bw);
+      tch = (sm_ld(&c.bloom[bit >> 5]) >> (bit & 31)) & 1u;
     }
     // count the survivors by the upper 16 bits of their keys: the threshold warp reads thresholds off these counts
-    if (okB) sm_red_add(&c.histB[coarse_bin(ky, c.baseB)], 1u);
-    if (okA) sm_red_add(&c.histA[coarse_bin(ky, c.baseA)], 1u);
+    if (okB && !tch) sm_red_add(&c.histB[coarse_bin(ky, c.baseB)], 1u);
+    if (okA && !tch) sm_red_add(&c.histA[coarse_bin(ky, c.baseA)], 1u);
     const bool pass = okB || okA;
     const unsigned pb = __ballot_sync(0xFFFFFFFFu, pass);
     if (pb) {
@@ -168,7 +164,7 @@ __device__ __noinline__ void scan_examine(const ScanCtx& c, const uint4* sq, con
       base = __shfl_sync(0xFFFFFFFFu, base, leader);
       if (pass)
         queue_write(c.sh, c.q_ent, c.status, base + __popc(pb & ((1u << lane) - 1u)), ky,
-                    (uint32_t)gid | ((uint32_t)okB << 30) | ((uint32_t)c.par << 31));
+                    (uint32_t)gid | (tch ? kTch : 0u) | ((uint32_t)okB << 30) | ((uint32_t)c.par << 31));
     }
   }
 }
@@ -207,7 +203,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
   volatile int* vsh = sh;
   volatile unsigned long long* v64 = s64;
   auto tab_hdr = [&](int st) { return reinterpret_cast<const ItemHdr*>(tabs + (size_t)st * tab_bytes); };
-  auto tab_keys = [&](int st) { return reinterpret_cast<const uint32_t*>(tabs + (size_t)st * tab_bytes + sizeof(ItemHdr)); };
+  auto tab_bloom = [&](int st) { return reinterpret_cast<const uint32_t*>(tabs + (size_t)st * tab_bytes + sizeof(ItemHdr)); };
 
   constexpr int E = Elem<T>::kPerChunk;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -304,9 +300,8 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
       int32_t* stc = stash_c + warp * kStash;
       int nst = 0;
       ScanCtx ctx;
-      ctx.hk = tab_keys(st);
-      ctx.hash_slots = a.hash_slots;
-      ctx.hash_shift = a.hash_shift;
+      ctx.bloom = tab_bloom(st);
+      ctx.bw = bloom_words_of(a.hash_slots);
       ctx.touched = hd->touched;
       ctx.bans = MASKED && hd->bans != 0;
       ctx.par = par;
@@ -417,6 +412,9 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
       }
       __syncwarp();
       if (tid == 0) TS(3, j);
+#ifdef ARCS_TRACE
+      if (lane == 0 && blockIdx.x == 0 && j < 16) atomicMax((unsigned long long*)&g_trace2[6 * 16 + j], (unsigned long long)clock64());
+#endif
       if (lane == 0) {  // this warp has queued everything it found in the item
         const uint32_t e = atomicAdd(reinterpret_cast<unsigned int*>(&sh[S_QTAIL]), 1u);
         queue_write(sh, q_ent, a.status, e, 0u, kMarker | ((uint32_t)par << 31));
@@ -501,8 +499,11 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
       int cB, cA, marks, itm, K;
       uint32_t baseB, baseA;
       bool loaded;
+      int nT, roomT;                // flagged entries written to the item's block, and the room left there
+      unsigned long long* listT;
     };
-    XItem older{0, 0, 0, 0, 1, 0u, 0u, false}, newer{0, 0, 0, 1, 1, 0u, 0u, false};
+    auto fresh = [](int itm) { return XItem{0, 0, 0, itm, 1, 0u, 0u, false, 0, 0, nullptr}; };
+    XItem older = fresh(0), newer = fresh(1);
     constexpr int kStep = 128;     // queue entries taken per step, four per lane
     constexpr int kFullB = 512, kFullA = 1024;  // buffer fill at which stale entries are dropped
     // drop what the threshold has overtaken; if the buffer is still too full, select exactly
@@ -550,12 +551,12 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
           abort_now();
           break;
         }
-        __nanosleep(200);
+        __nanosleep(kExamSleepNs);
         continue;
       }
       if (avail < kStep && polls < 4) {  // let a fuller batch build up
         ++polls;
-        __nanosleep(200);
+        __nanosleep(kExamSleepNs);
         continue;
       }
       idle = 0;
@@ -601,6 +602,8 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
           x.K = hd->K;
           x.baseB = (uint32_t)hd->baseB;
           x.baseA = (uint32_t)hd->baseA;
+          x.listT = item_ws(a, (int)blockIdx.x + x.itm * (int)gridDim.x).pre + hd->n_pre;
+          x.roomT = item_pre_cap(a.hash_slots) - hd->n_pre;
           x.loaded = true;
         }
         const Sel sBk{sB.key, sB.id, nullptr, sB.tau, x.K, 0, kCapB};
@@ -611,7 +614,20 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
           const bool mine = valid && gid != kMarker;
           if (!__any_sync(0xFFFFFFFFu, mine)) continue;
           const uint64_t cm = comp_of(ent[u].x, (int32_t)gid);
-          const bool okB = mine && ((ent[u].y >> 30) & 1u) && cm > v64[L_TAU_B + st];
+          const bool tch = mine && (ent[u].y & kTch);
+          if (__any_sync(0xFFFFFFFFu, tch)) {
+            // flagged by the filter: straight to the item's block, raw, unless no threshold lets it matter any more.
+            // (Room: the listed tokens themselves plus the filter's few false alarms among the hot elements.)
+            const bool keep = tch && (cm > v64[L_TAU_B + st] || (MASKED && cm > v64[L_TAU_A + st]));
+            const unsigned bt = __ballot_sync(0xFFFFFFFFu, keep);
+            const int pos = x.nT + __popc(bt & ((1u << lane) - 1u));
+            if (keep) {
+              if (pos < x.roomT) x.listT[pos] = (unsigned long long)ent[u].x | ((unsigned long long)(ent[u].y & ~(1u << 31)) << 32);
+              else raise_status(a.status, ARCS_ERR_LIST);
+            }
+            x.nT = min(x.nT + __popc(bt), x.roomT);
+          }
+          const bool okB = mine && !tch && ((ent[u].y >> 30) & 1u) && cm > v64[L_TAU_B + st];
           const unsigned bb = __ballot_sync(0xFFFFFFFFu, okB);
           if (okB) {
             const int pos = x.cB + __popc(bb & ((1u << lane) - 1u));
@@ -620,7 +636,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
           }
           x.cB += __popc(bb);
           if (MASKED) {
-            const bool okA = mine && cm > v64[L_TAU_A + st];
+            const bool okA = mine && !tch && cm > v64[L_TAU_A + st];
             const unsigned ba = __ballot_sync(0xFFFFFFFFu, okA);
             if (okA) {
               const int pos = x.cA + __popc(ba & ((1u << lane) - 1u));
@@ -635,6 +651,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
         if (MASKED && x.cA > kFullA - kStep) shrink(sA, x.cA, kFullA);
         x.marks += nmark;
         if (x.marks < kScanW) return false;
+        if (lane == 0) TS(5, x.itm);
         // every scanner has closed the item: write out what the last threshold has not overtaken
         raise(sBk, xh + (2 * st) * 256, x.baseB);
         shrink(sBk, x.cB, 0);
@@ -653,6 +670,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
         if (lane == 0) {
           w.hdr->n_candB = x.cB;
           w.hdr->n_candA = MASKED ? x.cA : 0;
+          w.hdr->n_tch = x.nT;
           w.hdr->tauB = *sBk.tau;
           w.hdr->tauA = *sA.tau;
         }
@@ -670,11 +688,11 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
       if (done_o) {
         const int next = newer.itm + 1;
         if (done_n) {
-          older = XItem{0, 0, 0, next, 1, 0u, 0u, false};
-          newer = XItem{0, 0, 0, next + 1, 1, 0u, 0u, false};
+          older = fresh(next);
+          newer = fresh(next + 1);
         } else {
           older = newer;
-          newer = XItem{0, 0, 0, next, 1, 0u, 0u, false};
+          newer = fresh(next);
         }
       }
     }
