@@ -75,6 +75,8 @@ lib.arcs_sample_workspace_bytes.restype = C.c_size_t
 lib.arcs_sample_workspace_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32]
 lib.arcs_sample_batch.restype = C.c_int
 lib.arcs_sample_batch.argtypes = [C.POINTER(SampleArgs), C.c_void_p]
+lib.arcs_sample_batch_timed.restype = C.c_int
+lib.arcs_sample_batch_timed.argtypes = [C.POINTER(SampleArgs), C.c_void_p, C.POINTER(C.c_float)]
 lib.arcs_argmax_workspace_bytes.restype = C.c_size_t
 lib.arcs_argmax_workspace_bytes.argtypes = [C.c_int32, C.c_int32]
 lib.arcs_argmax_batch.restype = C.c_int
@@ -342,3 +344,10 @@ class SamplePlan:
         s = _stream(self.device) if stream is None else stream
         _check(lib.arcs_sample_batch(C.byref(self.args), s), "arcs_sample_batch")
         return self.out
+
+    def launch_timed(self, stream=None):
+        """One call with CUDA events between its kernels: (prepare, stream, finish) milliseconds."""
+        s = _stream(self.device) if stream is None else stream
+        ms = (C.c_float * 3)()
+        _check(lib.arcs_sample_batch_timed(C.byref(self.args), s, ms), "arcs_sample_batch_timed")
+        return tuple(ms)

@@ -161,6 +161,23 @@ __device__ __forceinline__ uint32_t sm_atomic_add(void* p, uint32_t v) {
 __device__ __forceinline__ void sm_red_add(void* p, uint32_t v) {
   asm volatile("red.shared.add.u32 [%0], %1;" ::"r"(smem_addr(p)), "r"(v) : "memory");
 }
+__device__ __forceinline__ void sm_red_or(void* p, uint32_t v) {
+  asm volatile("red.shared.or.b32 [%0], %1;" ::"r"(smem_addr(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void sm_red_min_s32(void* p, int32_t v) {
+  asm volatile("red.shared.min.s32 [%0], %1;" ::"r"(smem_addr(p)), "r"(v) : "memory");
+}
+__device__ __forceinline__ void sm_red_max_u64(void* p, unsigned long long v) {
+  asm volatile("red.shared.max.u64 [%0], %1;" ::"r"(smem_addr(p)), "l"(v) : "memory");
+}
+__device__ __forceinline__ void sm_red_min_u64(void* p, unsigned long long v) {
+  asm volatile("red.shared.min.u64 [%0], %1;" ::"r"(smem_addr(p)), "l"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t sm_atomic_cas(void* p, uint32_t expect, uint32_t v) {
+  uint32_t old;
+  asm volatile("atom.shared.cas.b32 %0, [%1], %2, %3;" : "=r"(old) : "r"(smem_addr(p)), "r"(expect), "r"(v) : "memory");
+  return old;
+}
 __device__ __forceinline__ uint32_t sm_ld_volatile(const void* p) {
   uint32_t v;
   asm volatile("ld.volatile.shared.u32 %0, [%1];" : "=r"(v) : "r"(smem_addr(p)) : "memory");

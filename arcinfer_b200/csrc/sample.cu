@@ -41,7 +41,8 @@ extern "C" size_t arcs_sample_workspace_bytes(int32_t B, int32_t V, int32_t mask
   return (size_t)B * nseg * (size_t)item_block_bytes(masked != 0, table_slots(max_list));
 }
 
-extern "C" int arcs_sample_batch(const arcs_sample_args* g, void* stream) {
+// events[0..3], when given, are recorded before the first launch and after each of the three
+static int sample_launch(const arcs_sample_args* g, void* stream, cudaEvent_t* events) {
   if (int inj = fault_injected()) return inj;
   if (!g || !g->logits || !g->params || !g->u || !g->token || g->B <= 0 || g->V <= 0 || g->row_stride < g->V ||
       (g->dtype != ARCS_F32 && g->dtype != ARCS_BF16))
@@ -112,9 +113,13 @@ extern "C" int arcs_sample_batch(const arcs_sample_args* g, void* stream) {
     if (e == cudaSuccess && smem_p > 48 * 1024)                                                                    \
       e = cudaFuncSetAttribute(prepare_kernel<T, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_p);    \
     if (e != cudaSuccess) return set_error(ARCS_ERR_CUDA, cudaGetErrorString(e));                                  \
+    if (events) cudaEventRecord(events[0], st);                                                                    \
     prepare_kernel<T, M><<<(unsigned)items, kGroup, smem_p, st>>>(a);                                              \
+    if (events) cudaEventRecord(events[1], st);                                                                    \
     stream_kernel<T, M><<<grid_s, kThreadsS, smem_s, st>>>(a);                                                     \
+    if (events) cudaEventRecord(events[2], st);                                                                    \
     finish_kernel<T, M><<<(unsigned)a.B, kGroup, 0, st>>>(a);                                                      \
+    if (events) cudaEventRecord(events[3], st);                                                                    \
   } while (0)
   if (g->dtype == ARCS_F32) {
     if (masked) ARCS_LAUNCH(float, true);
@@ -125,4 +130,19 @@ extern "C" int arcs_sample_batch(const arcs_sample_args* g, void* stream) {
   }
 #undef ARCS_LAUNCH
   return check_launch("sample_batch");
+}
+
+extern "C" int arcs_sample_batch(const arcs_sample_args* g, void* stream) { return sample_launch(g, stream, nullptr); }
+
+extern "C" int arcs_sample_batch_timed(const arcs_sample_args* g, void* stream, float* ms3) {
+  if (!ms3) return set_error(ARCS_ERR_ARG, "sample_batch_timed: no output");
+  cudaEvent_t ev[4];
+  for (auto& e : ev)
+    if (cudaEventCreate(&e) != cudaSuccess) return set_error(ARCS_ERR_CUDA, "sample_batch_timed: cannot create events");
+  int rc = sample_launch(g, stream, ev);
+  if (rc == ARCS_OK && cudaEventSynchronize(ev[3]) != cudaSuccess) rc = set_error(ARCS_ERR_CUDA, "sample_batch_timed: synchronize failed");
+  for (int i = 0; i < 3 && rc == ARCS_OK; ++i)
+    if (cudaEventElapsedTime(&ms3[i], ev[i], ev[i + 1]) != cudaSuccess) rc = set_error(ARCS_ERR_CUDA, "sample_batch_timed: elapsed time failed");
+  for (auto& e : ev) cudaEventDestroy(e);
+  return rc;
 }

@@ -17,8 +17,10 @@ namespace arcs {
 
 constexpr uint32_t kIdMask = 0x1FFFFFFFu;  // entry word y: id | flagged by the filter << 29 | eligible for the selection proper << 30 | parity << 31
 constexpr uint32_t kTch = 1u << 29, kOkB = 1u << 30;
-constexpr int kCapB = 1024;   // candidate buffer: prune trigger (<= 512) + one round of pushes
-constexpr int kCapA = 1152;   // constrained head select (k = 512): fill limit 1024 + one step / round of 128
+constexpr int kCapB = 1024;   // finish kernel's candidate buffer: prune trigger + one round of pushes
+constexpr int kCapA = 1152;   // ... for the constrained head select (k = 512): fill limit 1024 + one round of 128
+constexpr int kListB = 2048;  // survivors of the stream an item's block holds: selection proper (typically k * (1 + ln(V / 4096)))
+constexpr int kListA = 4096;  // ... constrained head ranking
 constexpr int kBootBytes = 8192;  // prefix of an item read ahead to seed its threshold
 constexpr uint32_t kEmpty = 0xFFFFFFFFu;
 // per touched token: occurrences in the history (low 20 bits) and what applies to it
@@ -59,7 +61,7 @@ struct SampleDev {
 // [ItemHdr][filter bloom_words words]                                  <- copied to shared memory by the stream kernel
 // [entries with final values, from the prepare kernel, then hot elements the filter flagged, from
 //  the stream kernel, raw: hash_slots + kMaxScalars]                   (key | word y << 32)
-// [survivors of the stream, selection proper: kCapB][constrained head ranking: kCapA when masked]
+// [survivors of the stream, selection proper: kListB][constrained head ranking: kListA when masked]
 struct ItemHdr {
   unsigned long long tau0B, tau0A;  // first thresholds (exclusive composites)
   unsigned long long tauB, tauA;    // last thresholds of the stream: at least K (512) eligible elements of the item lie above
@@ -82,11 +84,12 @@ static_assert(sizeof(ItemHdr) == 96, "ItemHdr is copied as 96 bytes");
 constexpr int kTouchNone = 0, kTouchLight = 1, kTouchTable = 2;
 constexpr int kLightBias = 64;  // longest bias list handled without the table
 
-__host__ __device__ inline int32_t bloom_words_of(int hash_slots) { return hash_slots / 4 < 256 ? 256 : hash_slots / 4; }
+// filter size: 64 bits per listed id or more, two bits set per id: about one false alarm in a thousand lookups
+__host__ __device__ inline int32_t bloom_words_of(int hash_slots) { return hash_slots < 256 ? 256 : hash_slots; }
 __host__ __device__ inline int32_t item_tab_bytes(int hash_slots) { return (int32_t)sizeof(ItemHdr) + bloom_words_of(hash_slots) * 4; }
 __host__ __device__ inline int32_t item_pre_cap(int hash_slots) { return hash_slots + kMaxScalars; }
 __host__ __device__ inline int64_t item_block_bytes(bool masked, int hash_slots) {
-  return (int64_t)item_tab_bytes(hash_slots) + (int64_t)item_pre_cap(hash_slots) * 8 + (int64_t)kCapB * 8 + (masked ? (int64_t)kCapA * 8 : 0);
+  return (int64_t)item_tab_bytes(hash_slots) + (int64_t)item_pre_cap(hash_slots) * 8 + (int64_t)kListB * 8 + (masked ? (int64_t)kListA * 8 : 0);
 }
 struct ItemWs {
   ItemHdr* hdr;
@@ -102,11 +105,17 @@ __device__ __forceinline__ ItemWs item_ws(const SampleDev& a, int item) {
   w.bloom = reinterpret_cast<uint32_t*>(p + sizeof(ItemHdr));
   w.pre = reinterpret_cast<unsigned long long*>(w.bloom + bloom_words_of(a.hash_slots));
   w.candB = w.pre + item_pre_cap(a.hash_slots);
-  w.candA = w.candB + kCapB;
+  w.candA = w.candB + kListB;
   return w;
 }
-// bit of a column in an item's filter (bits: 32 * bloom_words, a power of two)
-__device__ __forceinline__ uint32_t bloom_bit(int32_t c, int bloom_words) { return (((uint32_t)c * 0x9E3779B1u) >> 8) & (uint32_t)(bloom_words * 32 - 1); }
+// the two bits of a column in an item's filter (bits: 32 * bloom_words, a power of two)
+__device__ __forceinline__ uint32_t bloom_bit1(int32_t c, int bloom_words) { return (((uint32_t)c * 0x9E3779B1u) >> 8) & (uint32_t)(bloom_words * 32 - 1); }
+__device__ __forceinline__ uint32_t bloom_bit2(int32_t c, int bloom_words) { return (((uint32_t)c * 0x85EBCA6Bu) >> 7) & (uint32_t)(bloom_words * 32 - 1); }
+template <typename LOAD>
+__device__ __forceinline__ bool bloom_has(LOAD load, int bloom_words, int32_t c) {
+  const uint32_t b1 = bloom_bit1(c, bloom_words), b2 = bloom_bit2(c, bloom_words);
+  return ((load(b1 >> 5) >> (b1 & 31)) & (load(b2 >> 5) >> (b2 & 31)) & 1u) != 0u;
+}
 
 #ifdef ARCS_TRACE
 __device__ long long g_trace[64];

@@ -28,12 +28,12 @@ __global__ void __launch_bounds__(kGroup) finish_kernel(const SampleDev a) {
   __shared__ int32_t sid[ARCS_KCAP];
   __shared__ int misc[8];
   __shared__ int sh[12];
-  __shared__ int seg_n[3][kMaxSeg];
+  __shared__ int seg_n[4][kMaxSeg];  // per segment: entries of the prepare kernel (+ flagged ones of the stream), survivors B, A, overflowed
   __shared__ uint32_t fl_key[kStage];   // hot elements the filter flagged, waiting to be settled
   __shared__ int32_t fl_id[kStage];     // (global id | kOkB)
   __shared__ uint32_t fl_cnt[kStage];   // occurrences in the history | in the repeat window << 31 | in the bias list << 30
   enum { L_TAU_B = 0, L_TAU_A, L_PRUNE_MIN, L_TOP, L_LOW };
-  enum { S_CNT_B = 0, S_CNT_A, S_FLAGS, S_NCAND, S_BANS, S_NFLAG, S_NLIST, S_NLISTA };
+  enum { S_CNT_B = 0, S_CNT_A, S_FLAGS, S_NCAND, S_BANS, S_NFLAG, S_NLIST, S_NLISTA, S_OVER, S_NPRE };
 
   const int gt = threadIdx.x;
   const int b = blockIdx.x;
@@ -47,6 +47,8 @@ __global__ void __launch_bounds__(kGroup) finish_kernel(const SampleDev a) {
     sh[S_NFLAG] = 0;
     sh[S_NLIST] = 0;
     sh[S_NLISTA] = 0;
+    sh[S_OVER] = 0;
+    sh[S_NPRE] = 0;
     s64[L_TAU_B] = 0ull;
     s64[L_TAU_A] = 0ull;
   }
@@ -56,16 +58,24 @@ __global__ void __launch_bounds__(kGroup) finish_kernel(const SampleDev a) {
   // segment alone holds k above it.
   for (int g = gt; g < a.nseg; g += kGroup) {
     const ItemHdr* hd = item_ws(a, b * a.nseg + g).hdr;
-    const int n0 = __ldcg(&hd->n_pre) + __ldcg(&hd->n_tch);  // (the stream kernel appends right behind the prepare kernel's entries)
-    const int n1 = __ldcg(&hd->n_candB), n2 = MASKED ? __ldcg(&hd->n_candA) : 0;
+    int n0 = __ldcg(&hd->n_pre);
+    const int nt = __ldcg(&hd->n_tch);
+    int n1 = __ldcg(&hd->n_candB), n2 = MASKED ? __ldcg(&hd->n_candA) : 0;
+    // a list of the stream that overflowed was only counted: the segment is read again below
+    const bool over = n1 > kListB || n2 > kListA || nt > item_pre_cap(a.hash_slots) - n0;
+    if (over) n1 = n2 = 0;
+    else n0 += nt;  // (the stream kernel appends right behind the prepare kernel's entries)
     seg_n[0][g] = n0;
     seg_n[1][g] = n1;
     seg_n[2][g] = n2;
-    atomicAdd(&sh[S_NLIST], n0 + n1);
-    if (MASKED) atomicAdd(&sh[S_NLISTA], n0 + n2);
-    if (__ldcg(&hd->bans) != 0) atomicOr(&sh[S_BANS], 1);
-    atomicMax(&s64[L_TAU_B], __ldcg(&hd->tauB));
-    if (MASKED) atomicMax(&s64[L_TAU_A], __ldcg(&hd->tauA));
+    seg_n[3][g] = over;
+    if (over) sm_red_or(&sh[S_OVER], 1u);
+    sm_red_add(&sh[S_NLIST], (uint32_t)(n0 + n1));
+    sm_red_add(&sh[S_NPRE], (uint32_t)n0);  // (only these entries can be flagged)
+    if (MASKED) sm_red_add(&sh[S_NLISTA], (uint32_t)(n0 + n2));
+    if (__ldcg(&hd->bans) != 0) sm_red_or(&sh[S_BANS], 1u);
+    sm_red_max_u64(&s64[L_TAU_B], __ldcg(&hd->tauB));
+    if (MASKED) sm_red_max_u64(&s64[L_TAU_A], __ldcg(&hd->tauA));
   }
   const RowCfg r = row_cfg<MASKED>(a, b);
   __syncthreads();
@@ -75,7 +85,7 @@ __global__ void __launch_bounds__(kGroup) finish_kernel(const SampleDev a) {
   TR(9);
   const bool bans = sh[S_BANS] != 0;
   // barriers between the rounds of pushes are needed only when a buffer or the stage could overflow
-  const bool careful = sh[S_NLIST] > kCapB - kGroup || (MASKED && sh[S_NLISTA] > 1024) || sh[S_NLIST] > kStage - kGroup;
+  const bool careful = sh[S_OVER] != 0 || sh[S_NLIST] > kCapB || (MASKED && sh[S_NLISTA] > kCapA) || sh[S_NPRE] > kStage;
   const PruneScratch psF{hist, tk, ti, misc, &s64[L_PRUNE_MIN]};
   const Sel selB{bkey, bid, &sh[S_CNT_B], &s64[L_TAU_B], r.kB, kCapB - kGroup, kCapB};  // (pruned only when the buffer is nearly full)
   const Sel selA{akey, aid, &sh[S_CNT_A], &s64[L_TAU_A], ARCS_HEAD, 1024, kCapA};
@@ -107,23 +117,25 @@ __global__ void __launch_bounds__(kGroup) finish_kernel(const SampleDev a) {
     if (nF == 0) return;
     for (int f = gt; f < nF; f += kGroup) fl_cnt[f] = 0u;
     group_sync<2>();
+    TR(22);
     const int32_t w0 = window_start(r);
     for (int i = gt; i < r.NB; i += kGroup) {
       const int32_t t = a.bias_ids[r.q0 + i];
       for (int f = 0; f < nF; ++f)
-        if ((fl_id[f] & (int32_t)kIdMask) == t) atomicOr(&fl_cnt[f], 1u << 30);
+        if ((fl_id[f] & (int32_t)kIdMask) == t) sm_red_or(&fl_cnt[f], 1u << 30);
     }
     if (r.pen_on) {
       for (int i = gt; i < r.H; i += kGroup) {
         const int32_t t = __ldg(&a.hist_ids[r.h0 + i]);
         for (int f = 0; f < nF; ++f)
           if ((fl_id[f] & (int32_t)kIdMask) == t) {
-            atomicAdd(&fl_cnt[f], 1u);
-            if (i >= w0) atomicOr(&fl_cnt[f], 1u << 31);
+            sm_red_add(&fl_cnt[f], 1u);
+            if (i >= w0) sm_red_or(&fl_cnt[f], 1u << 31);
           }
       }
     }
     group_sync<2>();
+    TR(23);
     for (int f0 = 0; f0 < nF; f0 += kGroup) {
       const int f = f0 + gt;
       bool p = f < nF;
@@ -153,6 +165,7 @@ __global__ void __launch_bounds__(kGroup) finish_kernel(const SampleDev a) {
       if (MASKED) sel_push(selA, p && cm > *selA.tau, ky, id, hot, a.status);
       after_push();
     }
+    TR(24);
     if (gt == 0) sh[S_NFLAG] = 0;
     group_sync<2>();
   };
@@ -161,7 +174,7 @@ __global__ void __launch_bounds__(kGroup) finish_kernel(const SampleDev a) {
   // constrained head ranking). The entries of several rounds are fetched together; flagged
   // entries are staged.
   auto take = [&](const unsigned long long* first, int n1, const unsigned long long* second, int n2, bool toA) {
-    constexpr int R = 4;
+    constexpr int R = 8;
     const int n = n1 + n2;
     for (int i0 = 0; i0 < n; i0 += R * kGroup) {
       unsigned long long e[R];
@@ -185,7 +198,7 @@ __global__ void __launch_bounds__(kGroup) finish_kernel(const SampleDev a) {
         if (bf) {
           const int lane = gt & 31, leader = __ffs(bf) - 1;
           int base = 0;
-          if (lane == leader) base = atomicAdd(&sh[S_NFLAG], __popc(bf));
+          if (lane == leader) base = (int)sm_atomic_add(&sh[S_NFLAG], (uint32_t)__popc(bf));
           base = __shfl_sync(0xFFFFFFFFu, base, leader);
           if (fl) {
             const int pos = base + __popc(bf & ((1u << lane) - 1u));  // (inside the stage: it is emptied below before a round could overflow it)
@@ -200,11 +213,57 @@ __global__ void __launch_bounds__(kGroup) finish_kernel(const SampleDev a) {
       }
     }
   };
+  // A segment whose lists overflowed is read again here, element by element, against the
+  // thresholds known by now (slow, and rare: ascending data, masses of equal logits).
+  auto rescan = [&](int g) {
+    constexpr int E = Elem<T>::kPerChunk;
+    const Item<T> it = item_of<T>(a, b * a.nseg + g);
+    const ItemWs w = item_ws(a, b * a.nseg + g);
+    const int bw = bloom_words_of(a.hash_slots);
+    const int nchunk = it.p.body_bytes / 16;
+    for (int c0 = 0; c0 < nchunk; c0 += kGroup) {
+      const int ci = c0 + gt;
+      const uint4 q = ci < nchunk ? ldg128_stream(it.p.body + (size_t)ci * 16) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+      for (int e = 0; e < E; ++e) {
+        const float v = Elem<T>::get(q, e);
+        const int32_t id = it.p.body_first + ci * E + e + a.id_base;
+        const uint32_t ky = key_of(v);
+        const uint64_t cm = comp_of(ky, id);
+        bool p = ci < nchunk && ky != 0u && (cm > *selB.tau || (MASKED && cm > *selA.tau));
+        bool fl = false;
+        if (p && r.touch != kTouchNone) {
+          fl = bloom_has([&](uint32_t wi) { return __ldg(&w.bloom[wi]); }, bw, id - a.id_base);
+        }
+        bool okB = true;
+        if (MASKED && p) okB = ((__ldg(&mrow[id >> 5]) >> (id & 31)) & 1u) && !(bans && v + 0.0f <= ARCS_BANNED);  // tools/sampler.h:118-119
+        sel_push(selB, p && !fl && okB && cm > *selB.tau, ky, id, hot, a.status);
+        if (MASKED) sel_push(selA, p && !fl && cm > *selA.tau, ky, id, hot, a.status);
+        const unsigned bf = __ballot_sync(0xFFFFFFFFu, p && fl);
+        if (bf) {
+          const int lane = gt & 31, leader = __ffs(bf) - 1;
+          int base = 0;
+          if (lane == leader) base = (int)sm_atomic_add(&sh[S_NFLAG], (uint32_t)__popc(bf));
+          base = __shfl_sync(0xFFFFFFFFu, base, leader);
+          if (p && fl) {
+            const int pos = base + __popc(bf & ((1u << lane) - 1u));
+            fl_key[pos] = ky;
+            fl_id[pos] = (int32_t)((uint32_t)id | (okB ? kOkB : 0u));
+          }
+        }
+        after_push();
+        if (sh[S_NFLAG] > kStage - kGroup) settle();
+      }
+    }
+  };
+  TR(20);
   for (int g = 0; g < a.nseg; ++g) {
     const ItemWs w = item_ws(a, b * a.nseg + g);
     take(w.pre, seg_n[0][g], w.candB, seg_n[1][g], false);
     if (MASKED) take(nullptr, 0, w.candA, seg_n[2][g], true);
+    if (seg_n[3][g]) rescan(g);
   }
+  TR(21);
   settle();
   group_sync<2>();
   TR(10);
@@ -240,8 +299,8 @@ __global__ void __launch_bounds__(kGroup) finish_kernel(const SampleDev a) {
     const int nA = min(*selA.cnt, ARCS_HEAD);
     for (int i = gt; i < nA; i += kGroup) {
       const uint64_t c = comp_of(selA.key[i], selA.id[i]);
-      if (!(bans && value_of(selA.key[i]) <= ARCS_BANNED)) atomicMax(&s64[L_TOP], (unsigned long long)c);
-      atomicMin(&s64[L_LOW], (unsigned long long)c);
+      if (!(bans && value_of(selA.key[i]) <= ARCS_BANNED)) sm_red_max_u64(&s64[L_TOP], (unsigned long long)c);
+      sm_red_min_u64(&s64[L_LOW], (unsigned long long)c);
     }
     group_sync<2>();
     if (gt == 0) {
@@ -277,7 +336,7 @@ __global__ void __launch_bounds__(kGroup) finish_kernel(const SampleDev a) {
   {  // equal logits among the candidates kept: the reference's order there is not defined
     bool tie = false;
     for (int i = gt; i + 1 < nc; i += kGroup) tie = tie || sv[i] == sv[i + 1];
-    if (tie) atomicOr(&sh[S_FLAGS], ARCS_FLAG_TIE_TOPK);
+    if (tie) sm_red_or(&sh[S_FLAGS], (uint32_t)ARCS_FLAG_TIE_TOPK);
   }
   TR(12);
   const bool draw = (!r.greedy && nc > 1) || (!MASKED && !r.greedy && nc == 1);
@@ -321,7 +380,7 @@ __global__ void __launch_bounds__(kGroup) finish_kernel(const SampleDev a) {
       int n_i = 0x7FFFFFFF;
       if (r.prm.min_p > 0.0f && spr[i] < mp) n_i = max(1, i);   // :65 (tested before the candidate is added)
       else if (cum[i] >= (double)r.prm.top_p) n_i = i + 1;      // :67
-      if (n_i != 0x7FFFFFFF) atomicMin(&sh[S_NCAND], n_i);
+      if (n_i != 0x7FFFFFFF) sm_red_min_s32(&sh[S_NCAND], n_i);
     }
   }
   group_sync<2>();

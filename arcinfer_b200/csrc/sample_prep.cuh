@@ -17,25 +17,39 @@ namespace arcs {
 constexpr int kBootKeys = 1024;  // most maxima the first threshold is read off (constrained rows; 256 otherwise)
 
 static size_t prep_smem_bytes(int hash_slots) {
-  return 16 + (size_t)hash_slots * 8 + (size_t)kBootKeys * 4 + 5 * (size_t)bloom_words_of(hash_slots) * 4 + 16 * 4;
+  return 16 + (size_t)hash_slots * 8 + (size_t)kBootKeys * 4 + (size_t)bloom_words_of(hash_slots) * 4 + 16 * 4;
 }
 
-// A lower bound of the kth largest (1-based) of n keys (n a multiple of 128), found by ONE warp
-// with a bit-by-bit search on the keys' upper 16 bits (bf16 resolution; exact for bf16 data):
-// the largest t with at least kth keys >= t. No shared-memory atomics, a few hundred instructions.
-__device__ __forceinline__ uint32_t warp_kth16(const uint32_t* keys, int n, int kth) {
+// A lower bound of the kth largest (1-based) of 32 * PER keys, found by ONE warp with a search
+// on the keys' upper 16 bits, two bits a round (bf16 resolution; exact for bf16 data): the
+// largest t with at least kth keys >= t. Keys in registers, no shared-memory atomics.
+template <int PER>
+__device__ __forceinline__ uint32_t warp_kth16(const uint32_t* keys, int kth) {
   const int lane = threadIdx.x & 31;
-  const uint4* k4 = reinterpret_cast<const uint4*>(keys);
+  uint32_t k[PER];
+#pragma unroll
+  for (int i = 0; i < PER / 4; ++i) {
+    const uint4 q = reinterpret_cast<const uint4*>(keys)[i * 32 + lane];
+    k[4 * i] = q.x;
+    k[4 * i + 1] = q.y;
+    k[4 * i + 2] = q.z;
+    k[4 * i + 3] = q.w;
+  }
   uint32_t t = 0;
-  for (int bit = 15; bit >= 0; --bit) {
-    const uint32_t cand = (t | (1u << bit)) << 16;
-    int c = 0;
-    for (int i = lane; i < n / 4; i += 32) {
-      const uint4 q = k4[i];
-      c += (q.x >= cand) + (q.y >= cand) + (q.z >= cand) + (q.w >= cand);
+#pragma unroll 1
+  for (int bit = 14; bit >= 0; bit -= 2) {
+    const uint32_t c1 = (t | (1u << bit)) << 16, c2 = (t | (2u << bit)) << 16, c3 = (t | (3u << bit)) << 16;
+    int n1 = 0, n2 = 0, n3 = 0;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      n1 += k[i] >= c1;
+      n2 += k[i] >= c2;
+      n3 += k[i] >= c3;
     }
-    c = __reduce_add_sync(0xFFFFFFFFu, c);
-    if (c >= kth) t |= 1u << bit;
+    // three counts (each at most 32 * PER <= 1024) in one word, one reduction
+    const uint32_t all = __reduce_add_sync(0xFFFFFFFFu, (uint32_t)n1 | ((uint32_t)n2 << 11) | ((uint32_t)n3 << 22));
+    const int a1 = (int)(all & 0x7FFu), a2 = (int)((all >> 11) & 0x7FFu), a3 = (int)(all >> 22);
+    t |= (a3 >= kth ? 3u : a2 >= kth ? 2u : a1 >= kth ? 1u : 0u) << bit;
   }
   return t << 16;
 }
@@ -48,14 +62,13 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
   uint32_t* hk = reinterpret_cast<uint32_t*>(m64 + 2);                         // [hash_slots] token columns (table mode)
   uint32_t* hi_ = hk + a.hash_slots;                                           // [hash_slots] what applies to them
   uint32_t* ptk = hi_ + a.hash_slots;                                          // [kBootKeys] maxima over pieces of the prefix
-  uint32_t* wb = ptk + kBootKeys;                                              // [4][bw] one filter per warp, merged into ...
-  uint32_t* bl = wb + 4 * bw;                                                  // [bw] ... the item's filter
+  uint32_t* bl = ptk + kBootKeys;                                              // [bw] the item's filter
   int* pmisc = reinterpret_cast<int*>(bl + bw);
   int* n_pre = pmisc + 0;
   int* n_extra = pmisc + 1;
 
   constexpr int E = Elem<T>::kPerChunk;
-  const int gt = threadIdx.x, lane = gt & 31, warp = gt >> 5;
+  const int gt = threadIdx.x, lane = gt & 31;
   const int item = blockIdx.x;
   const int32_t Vg = a.v_global > 0 ? a.v_global : a.V;
   TR(0);
@@ -80,13 +93,26 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
   float m0 = -INFINITY, m1 = -INFINITY;
   bool any0 = false, any1 = false;
   if (!MASKED) {
-    // two maxima per thread, each over every other one of the thread's chunks of the prefix
-    for (int ci = gt; ci < nchunk; ci += 2 * kGroup) {
-      m0 = fmaxf(m0, Elem<T>::chunk_max(ldg128_stream(it.p.body + (size_t)ci * 16)));
-      any0 = true;
-      if (ci + kGroup < nchunk) {
-        m1 = fmaxf(m1, Elem<T>::chunk_max(ldg128_stream(it.p.body + (size_t)(ci + kGroup) * 16)));
-        any1 = true;
+    // two maxima per thread, each over every other one of the thread's (up to four) chunks of
+    // the prefix, all fetched together
+    uint4 q[4];
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      const int ci = gt + x * kGroup;
+      q[x] = ci < nchunk ? ldg128_stream(it.p.body + (size_t)ci * 16) : make_uint4(0, 0, 0, 0);
+    }
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      const int ci = gt + x * kGroup;
+      if (ci < nchunk) {
+        const float m = Elem<T>::chunk_max(q[x]);
+        if (x & 1) {
+          m1 = fmaxf(m1, m);
+          any1 = true;
+        } else {
+          m0 = fmaxf(m0, m);
+          any0 = true;
+        }
       }
     }
   }
@@ -102,15 +128,12 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
     const int32_t c = t - a.id_base;
     return (c < it.lo || c >= it.hi) ? -1 : c;
   };
-  // one more column for the filter (called by whole warps). Each warp fills its own copy without
-  // atomics: lanes that hit the same word combine their bits and one of them writes.
+  // one more column for the filter
   auto bloom_add = [&](bool valid, int32_t c) {
-    const uint32_t bit = bloom_bit(c, bw);
-    const uint32_t word = valid ? (bit >> 5) : (0x80000000u | (uint32_t)lane);
-    const unsigned peers = __match_any_sync(0xFFFFFFFFu, word);
-    const uint32_t comb = __reduce_or_sync(peers, 1u << (bit & 31));
-    if (valid && lane == __ffs(peers) - 1) wb[warp * bw + word] |= comb;
-    __syncwarp();
+    if (!valid) return;
+    const uint32_t b1 = bloom_bit1(c, bw), b2 = bloom_bit2(c, bw);
+    sm_red_or(&bl[b1 >> 5], 1u << (b1 & 31));
+    sm_red_or(&bl[b2 >> 5], 1u << (b2 & 31));
   };
   // one more entry for the finish kernel (called by whole warps; lanes with `valid` supply):
   // v is the logit of column c, final unless the entry is flagged for the finish kernel to settle
@@ -121,7 +144,7 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
     if (bal == 0u) return;
     const int leader = __ffs(bal) - 1;
     int base = 0;
-    if (lane == leader) base = atomicAdd(n_pre, __popc(bal));
+    if (lane == leader) base = (int)sm_atomic_add(n_pre, (uint32_t)__popc(bal));
     base = __shfl_sync(0xFFFFFFFFu, base, leader);
     if (!valid) return;
     const int32_t g = c + a.id_base;
@@ -133,7 +156,7 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
 
   int extra = 0;  // listed columns inside the prefix: they may own a maximum there without counting
   if (r.touch != kTouchNone) {
-    for (int i = gt; i < 4 * bw; i += kGroup) wb[i] = 0u;
+    for (int i = gt; i < bw; i += kGroup) bl[i] = 0u;
     __syncthreads();
   }
   if (r.touch == kTouchLight) {
@@ -202,7 +225,7 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
       if (c < 0) return -1;
       uint32_t h = hash_of(c, a.hash_shift);
       for (int probe = 0; probe < a.hash_slots; ++probe) {
-        const uint32_t old = atomicCAS(&hk[h], kEmpty, (uint32_t)c);
+        const uint32_t old = sm_atomic_cas(&hk[h], kEmpty, (uint32_t)c);
         if (old == kEmpty) return (int)h;                                      // first occurrence
         if (old == (uint32_t)c) return (int)h | 0x40000000;                    // seen before
         h = (h + 1) & (uint32_t)(a.hash_slots - 1);
@@ -212,7 +235,7 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
     // the bias list goes in first: a slot that carries a bias flag was opened by it, any other by the history
     for (int i = gt; i < r.NB; i += kGroup) {
       const int s = insert(a.bias_ids[r.q0 + i]);
-      if (s >= 0) atomicOr(&hi_[s & 0x3FFFFFFF], a.bias_vals[r.q0 + i] > -100.0f ? kInfoBias : kInfoBan);
+      if (s >= 0) sm_red_or(&hi_[s & 0x3FFFFFFF], a.bias_vals[r.q0 + i] > -100.0f ? kInfoBias : kInfoBan);
     }
     __syncthreads();
     const int32_t w0 = window_start(r);
@@ -221,8 +244,8 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
         // one atomic per id, more only for a repeated id (its count is 1 + the additions) and
         // for a window shorter than the history
         const int s = insert(a.hist_ids[r.h0 + i]);
-        if (s >= 0 && (s & 0x40000000)) atomicAdd(&hi_[s & 0x3FFFFFFF], 1u);
-        if (s >= 0 && w0 > 0 && i >= w0) atomicOr(&hi_[s & 0x3FFFFFFF], kInfoWindow);
+        if (s >= 0 && (s & 0x40000000)) sm_red_add(&hi_[s & 0x3FFFFFFF], 1u);
+        if (s >= 0 && w0 > 0 && i >= w0) sm_red_or(&hi_[s & 0x3FFFFFFF], kInfoWindow);
       }
     }
     __syncthreads();
@@ -257,18 +280,12 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
       }
     }
   }
-  if (extra) atomicAdd(n_extra, extra);
+  if (extra) sm_red_add(n_extra, (uint32_t)extra);
   __syncthreads();
   TR(3);
-  // ---- the item's filter: the warps' copies merged, kept here and written out
-  if (r.touch != kTouchNone) {
-    for (int i = gt; i < bw; i += kGroup) {
-      const uint32_t m = wb[i] | wb[bw + i] | wb[2 * bw + i] | wb[3 * bw + i];
-      bl[i] = m;
-      w.bloom[i] = m;
-    }
-    __syncthreads();
-  }
+  // ---- the item's filter goes out
+  if (r.touch != kTouchNone)
+    for (int i = gt; i < bw; i += kGroup) w.bloom[i] = bl[i];
   // the scalar elements before the first and after the last 16-byte boundary; one the filter
   // knows is flagged, like a hot element of the stream, for the finish kernel to settle
   if (gt < 64) {  // (two whole warps: the first takes the head, the second the tail)
@@ -277,8 +294,7 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
     const int32_t c = head ? it.lo + lane : it.p.tail_first + lane;
     bool flagged = false;
     if (valid && r.touch != kTouchNone) {
-      const uint32_t bit = bloom_bit(c, bw);
-      flagged = (bl[bit >> 5] >> (bit & 31)) & 1u;
+      flagged = bloom_has([&](uint32_t wi) { return bl[wi]; }, bw, c);
     }
     supply(valid, valid ? Elem<T>::load(it.row + c) : 0.0f, c, flagged);
   }
@@ -295,7 +311,7 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
     ptk[kGroup + gt] = any1 ? key_of(m1) : 0u;
     __syncthreads();
     if (kth <= min(nchunk, 2 * kGroup)) {
-      if (gt < 32) m64[1] = (unsigned long long)warp_kth16(ptk, 2 * kGroup, kth) << 32;  // keeps ties with it
+      if (gt < 32) m64[1] = (unsigned long long)warp_kth16<2 * kGroup / 32>(ptk, kth) << 32;  // keeps ties with it
       __syncthreads();
       tau0B = m64[1];
     }
@@ -305,7 +321,7 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
       for (int ci = gt; ci < kBootKeys; ci += kGroup)
         ptk[ci] = ci < nchunk ? key_of(Elem<T>::chunk_max(ldg128_stream(it.p.body + (size_t)ci * 16))) : 0u;
       __syncthreads();
-      if (gt < 32) m64[1] = (unsigned long long)warp_kth16(ptk, kBootKeys, kth) << 32;  // keeps ties with it
+      if (gt < 32) m64[1] = (unsigned long long)warp_kth16<kBootKeys / 32>(ptk, kth) << 32;  // keeps ties with it
       __syncthreads();
       tau0A = m64[1];
     }

@@ -3,17 +3,16 @@
 // One persistent CTA per SM walks a list of work items (a row, or a segment of a row when
 // there are few rows). Its warps have fixed roles and never meet at a CTA-wide barrier:
 //   producer   keeps a ring of 8 KB tiles filled with 1-D bulk copies (TMA);
-//   scanners   16 warps, four to a tile: a 16-byte chunk whose maximum is below the item's
+//   scanners   16 warps, two to a tile: a 16-byte chunk whose maximum is below the item's
 //              current threshold costs a handful of instructions; the few other chunks are set
-//              aside, then tested element by element, and the survivors queued;
-//   examiner   one warp owns the candidate buffers: it moves the queued survivors into them,
-//              drops what the threshold has overtaken, and writes what is left to the item's
-//              block of the workspace when every scanner has closed the item;
-//   threshold  one warp fetches the items' tables and first thresholds (written by the prepare
+//              aside, then tested element by element, and the survivors appended to the item's
+//              lists in the workspace. The warp that closes an item last hands it over;
+//   threshold  one warp fetches the items' filters and first thresholds (written by the prepare
 //              kernel) ahead of the stream, and keeps raising the thresholds of the items that
 //              are streaming from the coarse histograms the scanners update.
-// Items rotate over three sets of per-item state and two candidate buffers, so the ring never
-// pauses between items.
+// Items rotate over three sets of per-item state, so the ring never pauses between items.
+// A list that overflows (ascending data, masses of ties) is only counted: the finish kernel
+// sees the count and reads that item again itself.
 #pragma once
 #include "sample_common.cuh"
 
@@ -25,10 +24,9 @@ constexpr int kScanW = 16;                                 // scanner warps
 #endif
 constexpr int kShare = ARCS_SHARE;                         // scanner warps that split one tile between them
 constexpr int kTeams = kScanW / kShare;
-constexpr int kExamWarp = kScanW;                          // examiner warp
-constexpr int kProdWarp = kScanW + 1;                      // producer warp (its first lanes work)
-constexpr int kTauWarp = kScanW + 2;                       // threshold warp
-constexpr int kThreadsS = (kScanW + 3) * 32;               // 608 threads
+constexpr int kProdWarp = kScanW;                          // producer warp (its first lanes work)
+constexpr int kTauWarp = kScanW + 1;                       // threshold warp
+constexpr int kThreadsS = (kScanW + 2) * 32;               // 576 threads
 #ifndef ARCS_PROD_LANES
 #define ARCS_PROD_LANES 2
 #endif
@@ -36,23 +34,20 @@ constexpr int kProdLanes = ARCS_PROD_LANES;                // lanes of the produ
 #ifndef ARCS_TAU_SLEEP
 #define ARCS_TAU_SLEEP 200
 #endif
-#ifndef ARCS_EXAM_SLEEP
-#define ARCS_EXAM_SLEEP 200
-#endif
-constexpr int kExamSleepNs = ARCS_EXAM_SLEEP;              // examiner's pause while the queue is short
 constexpr int kTauSleepNs = ARCS_TAU_SLEEP;                // pause between two threshold updates
 #ifndef ARCS_RING
 #define ARCS_RING 16
 #endif
 constexpr int kRing = ARCS_RING;                           // tiles in the ring (a multiple of kTeams)
 constexpr int kSTile = 8192;                               // bytes per tile (512 chunks)
-constexpr int kStash = 16;                                 // chunks a scanner sets aside per flush
-constexpr int kQueue = 512;                                // queued elements between scanners and examiner
-constexpr uint32_t kMarker = kIdMask;                      // id field of a scanner's end-of-item entry
+#ifndef ARCS_STASH
+#define ARCS_STASH 32
+#endif
+constexpr int kStash = ARCS_STASH;                         // chunks a scanner can set aside (examined one per lane)
 static_assert(kRing % kTeams == 0, "a team always meets its tiles in the same slots");
 
 // indices into the shared scalar arrays
-enum { S_ABORT = 0, S_QTAIL, S_QHEAD, S_PREPARED, S_STREAMED, S_END = 8 };
+enum { S_ABORT = 0, S_PREPARED, S_STREAMED, S_DONE /* [3] */ = 4, S_CNT /* [3 sets][B, A, flagged, -] */ = 8, S_END = 20 };
 enum { L_TAU_B = 0 /* [3] */, L_TAU_A = 3 /* [3] */, L_END = 6 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
@@ -81,33 +76,19 @@ __device__ __forceinline__ float elem_of_words<__nv_bfloat16>(uint32_t w0, uint3
 struct ScanCtx {
   const uint32_t* bloom;   // the item's filter over the columns a penalty or a bias touches
   int32_t bw;              // its size in words
-  int32_t touched, bans, par;
+  int32_t touched, bans;
   const uint32_t* mrow;
   uint32_t* histB;         // coarse histograms of the item
   uint32_t* histA;
   uint32_t baseB, baseA;
-  int* sh;                 // shared scalars (queue head / tail, abort flag)
-  unsigned long long* q_ent;  // queue slots: 0 = empty, else key | (id, flags) << 32
-  int32_t* status;
+  int* cnt;                // the item's list lengths so far: [B, A, flagged]
+  unsigned long long* listB;  // the item's lists in the workspace (key | word y << 32)
+  unsigned long long* listA;
+  unsigned long long* listT;
+  int32_t roomT;           // entries the flagged list still takes
   int32_t id_base;         // global id of column 0
   uint64_t tcB, tcA;       // thresholds the chunk was listed against
 };
-
-// append one entry to the scanner -> examiner queue (the caller holds reservation e)
-__device__ __forceinline__ void queue_write(int* sh, unsigned long long* q_ent, int32_t* status, uint32_t e,
-                                            uint32_t key, uint32_t idp) {
-  uint32_t spins = 0;  // bounded wait for room
-  while ((int32_t)(e - sm_ld_volatile(&sh[S_QHEAD])) >= kQueue && !sm_ld_volatile(&sh[S_ABORT])) {
-    if (++spins > kWaitLimit) {
-      *reinterpret_cast<volatile int*>(&sh[S_ABORT]) = 1;
-      raise_status(status, ARCS_ERR_TIMEOUT);
-    }
-    __nanosleep(32);
-  }
-  // one 64-bit store publishes the entry: a slot is zero until written and zeroed again by the
-  // examiner before it frees it (an entry is never zero: data has a non-zero key, a marker a non-zero id)
-  sm_st_volatile64(&q_ent[e % kQueue], (unsigned long long)key | ((unsigned long long)idp << 32));
-}
 
 // The chunks a scanner warp has set aside (data in sq[], global id of each chunk's first element
 // in sc[]) are examined one chunk per lane: a float compare finds the (usually single) element
@@ -149,32 +130,34 @@ __device__ __noinline__ void scan_examine(const ScanCtx& c, const uint4* sq, con
     // finish kernel to settle, and counts for no threshold
     bool tch = false;
     if ((okB || okA) && c.touched) {
-      const uint32_t bit = bloom_bit(gid - c.id_base, c.bw);
-      tch = (sm_ld(&c.bloom[bit >> 5]) >> (bit & 31)) & 1u;
+      tch = bloom_has([&](uint32_t wi) { return sm_ld(&c.bloom[wi]); }, c.bw, gid - c.id_base);
     }
     // count the survivors by the upper 16 bits of their keys: the threshold warp reads thresholds off these counts
     if (okB && !tch) sm_red_add(&c.histB[coarse_bin(ky, c.baseB)], 1u);
     if (okA && !tch) sm_red_add(&c.histA[coarse_bin(ky, c.baseA)], 1u);
-    const bool pass = okB || okA;
-    const unsigned pb = __ballot_sync(0xFFFFFFFFu, pass);
-    if (pb) {
+    // survivors go straight to the item's lists; a list that is full is only counted
+    const uint32_t y = (uint32_t)gid | (okB ? kOkB : 0u);
+    const unsigned long long ent = (unsigned long long)ky | ((unsigned long long)y << 32);
+    auto append = [&](bool p, int which, unsigned long long* list, int cap, unsigned long long e) {
+      const unsigned pb = __ballot_sync(0xFFFFFFFFu, p);
+      if (pb == 0u) return;
       const int leader = __ffs(pb) - 1;
       uint32_t base = 0;
-      if (lane == leader) base = sm_atomic_add(&c.sh[S_QTAIL], (unsigned)__popc(pb));
+      if (lane == leader) base = sm_atomic_add(&c.cnt[which], (unsigned)__popc(pb));
       base = __shfl_sync(0xFFFFFFFFu, base, leader);
-      if (pass)
-        queue_write(c.sh, c.q_ent, c.status, base + __popc(pb & ((1u << lane) - 1u)), ky,
-                    (uint32_t)gid | (tch ? kTch : 0u) | ((uint32_t)okB << 30) | ((uint32_t)c.par << 31));
-    }
+      const uint32_t pos = base + __popc(pb & ((1u << lane) - 1u));
+      if (p && pos < (uint32_t)cap) list[pos] = e;
+    };
+    append(okB && !tch, 0, c.listB, kListB, ent);
+    if (MASKED) append(okA && !tch, 1, c.listA, kListA, (unsigned long long)ky | ((unsigned long long)(uint32_t)gid << 32));
+    if (c.touched) append(tch && (okB || okA), 2, c.listT, c.roomT, ent | ((unsigned long long)kTch << 32));
   }
 }
 
 static size_t stream_smem_bytes(bool masked, int hash_slots) {
-  size_t n = (size_t)kRing * kSTile + 3 * (size_t)item_tab_bytes(hash_slots) + (size_t)kQueue * 8 + (size_t)kScanW * kStash * 20 +
-             (2 * kRing + 4) * 8 + L_END * 8 + (256 + 6 * 256) * 4 + (size_t)kTmpCap * 8 + S_END * 4;
-  n += (size_t)2 * kCapB * 8;
-  if (masked) n += (size_t)2 * kCapA * 8;
-  return n + 128;
+  (void)masked;
+  return (size_t)kRing * kSTile + 3 * (size_t)item_tab_bytes(hash_slots) + (size_t)kScanW * kStash * 20 + (2 * kRing + 4) * 8 + L_END * 8 +
+         6 * 256 * 4 + S_END * 4 + 128;
 }
 
 template <typename T, bool MASKED>
@@ -184,22 +167,14 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
   const int tab_bytes = item_tab_bytes(a.hash_slots);
   char* ring = smem;                                                          // kRing * kSTile
   char* tabs = ring + (size_t)kRing * kSTile;                                 // [3] item tables as the prepare kernel wrote them
-  unsigned long long* q_ent = reinterpret_cast<unsigned long long*>(tabs + 3 * (size_t)tab_bytes);  // [kQueue]
-  uint4* stash_q = reinterpret_cast<uint4*>(q_ent + kQueue);                   // [kScanW][kStash] chunks set aside by the scanners
+  uint4* stash_q = reinterpret_cast<uint4*>(tabs + 3 * (size_t)tab_bytes);     // [kScanW][kStash] chunks set aside by the scanners
   uint64_t* full = reinterpret_cast<uint64_t*>(stash_q + kScanW * kStash);     // [kRing] tile has landed
   uint64_t* empty = full + kRing;                                             // [kRing] tile has been scanned
   uint64_t* tab_full = empty + kRing;                                         // [3] (+1 pad) table has landed
   unsigned long long* s64 = reinterpret_cast<unsigned long long*>(tab_full + 4);  // [L_END]
   int32_t* stash_c = reinterpret_cast<int32_t*>(s64 + L_END);                 // [kScanW][kStash]
-  uint32_t* xhist = reinterpret_cast<uint32_t*>(stash_c + kScanW * kStash);   // [256] examiner's radix histogram
-  uint32_t* xh = xhist + 256;                                                 // [3 sets][B, A][256] coarse histograms
-  uint32_t* xtk = xh + 6 * 256;                                               // [kTmpCap] examiner's scratch
-  int32_t* xti = reinterpret_cast<int32_t*>(xtk + kTmpCap);
-  int* sh = reinterpret_cast<int*>(xti + kTmpCap);                            // [S_END]
-  uint32_t* bkey = reinterpret_cast<uint32_t*>(sh + S_END);                   // [2][kCapB]
-  int32_t* bid = reinterpret_cast<int32_t*>(bkey + 2 * kCapB);
-  uint32_t* akey = reinterpret_cast<uint32_t*>(bid + 2 * kCapB);              // [2][kCapA] when MASKED
-  int32_t* aid = reinterpret_cast<int32_t*>(akey + (MASKED ? 2 * kCapA : 0));
+  uint32_t* xh = reinterpret_cast<uint32_t*>(stash_c + kScanW * kStash);      // [3 sets][B, A][256] coarse histograms
+  int* sh = reinterpret_cast<int*>(xh + 6 * 256);                             // [S_END]
   volatile int* vsh = sh;
   volatile unsigned long long* v64 = s64;
   auto tab_hdr = [&](int st) { return reinterpret_cast<const ItemHdr*>(tabs + (size_t)st * tab_bytes); };
@@ -220,7 +195,6 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
     for (int i = 0; i < S_END; ++i) sh[i] = 0;
     for (int i = 0; i < L_END; ++i) s64[i] = 0ull;
   }
-  for (int i = tid; i < kQueue; i += kThreadsS) q_ent[i] = 0ull;
   for (int i = tid; i < 6 * 256; i += kThreadsS) xh[i] = 0u;
   __syncthreads();  // the only CTA-wide barrier
   if (tid == 0) TS(0, 0);
@@ -277,14 +251,14 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
     // its warps scans a quarter of the tile, so a slot is held only briefly.
     uint32_t G0 = 0;  // running number of the item's first tile
     for (int j = 0; j < my_n; ++j) {
-      const int par = j & 1, st = j % 3;  // candidate buffers alternate; tables / thresholds / counts rotate over three sets
+      const int st = j % 3;  // filters / thresholds / counts rotate over three sets
       const Item<T> it = item_of<T>(a, (int)blockIdx.x + j * (int)gridDim.x);
       const int T_ = s_tiles(it.p);
-      {  // the item's table and first threshold must be there, and the item two back, which
-         // used the same candidate buffers, handed over (one lane polls)
+      {  // the item's filter and first threshold must be there (one lane polls); the set of
+         // state they live in was free before their copy started
         if (lane == 0) {
           uint32_t spins = 0;
-          while ((vsh[S_PREPARED] <= j || vsh[S_STREAMED] < j - 1) && !vsh[S_ABORT]) {
+          while (vsh[S_PREPARED] <= j && !vsh[S_ABORT]) {
             if (++spins > kWaitLimit) abort_now();
             __nanosleep(64);
           }
@@ -304,15 +278,17 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
       ctx.bw = bloom_words_of(a.hash_slots);
       ctx.touched = hd->touched;
       ctx.bans = MASKED && hd->bans != 0;
-      ctx.par = par;
       ctx.mrow = MASKED ? a.mask + (size_t)(a.mask_row ? a.mask_row[it.b] : it.b) * a.mask_stride : nullptr;
       ctx.histB = xh + (2 * st) * 256;
       ctx.histA = xh + (2 * st + 1) * 256;
       ctx.baseB = (uint32_t)hd->baseB;
       ctx.baseA = (uint32_t)hd->baseA;
-      ctx.sh = sh;
-      ctx.q_ent = q_ent;
-      ctx.status = a.status;
+      ctx.cnt = &sh[S_CNT + 4 * st];
+      const ItemWs w = item_ws(a, (int)blockIdx.x + j * (int)gridDim.x);
+      ctx.listB = w.candB;
+      ctx.listA = w.candA;
+      ctx.listT = w.pre + hd->n_pre;  // (right behind the prepare kernel's entries)
+      ctx.roomT = item_pre_cap(a.hash_slots) - hd->n_pre;
       ctx.id_base = a.id_base;
       const uint32_t* mrow = ctx.mrow;
       for (int t = (int)(((uint32_t)(warp / kShare) - G0) % kTeams); t < T_; t += kTeams) {
@@ -338,9 +314,16 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
         };
         const bool whole = nchunk == kSTile / 16;  // only an item's last tile can be short
         constexpr int kMine = kSTile / 16 / kShare;          // chunks of a tile per warp
-        constexpr int kU = kMine / 32 < 4 ? kMine / 32 : 4;   // chunks per lane per step
+#ifndef ARCS_KU
+#define ARCS_KU 4
+#endif
+        constexpr int kU = kMine / 32 < ARCS_KU ? kMine / 32 : ARCS_KU;   // chunks per lane per step
         const int c_lo = (warp % kShare) * kMine;
+#ifdef ARCS_X_NOSCAN
+        for (int c0 = c_lo; c0 < 0; c0 += kU * 32) {
+#else
         for (int c0 = c_lo; c0 < min(nchunk, c_lo + kMine); c0 += kU * 32) {
+#endif
           uint4 q[kU];
           bool h[kU];
           refresh();
@@ -362,6 +345,9 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
               h[u] = hb || Elem<T>::chunk_reaches(q[u], thA);
             }
             if (!whole) h[u] = h[u] && ci < nchunk;
+#ifdef ARCS_X_NOHOT
+            h[u] = h[u] && a.V < 0;  // (experiment: the test is evaluated, nothing is ever listed)
+#endif
             any = any || h[u];
           }
           if (__any_sync(0xFFFFFFFFu, any)) {  // set the listed chunks aside
@@ -412,12 +398,44 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
       }
       __syncwarp();
       if (tid == 0) TS(3, j);
-#ifdef ARCS_TRACE
-      if (lane == 0 && blockIdx.x == 0 && j < 16) atomicMax((unsigned long long*)&g_trace2[6 * 16 + j], (unsigned long long)clock64());
-#endif
-      if (lane == 0) {  // this warp has queued everything it found in the item
-        const uint32_t e = atomicAdd(reinterpret_cast<unsigned int*>(&sh[S_QTAIL]), 1u);
-        queue_write(sh, q_ent, a.status, e, 0u, kMarker | ((uint32_t)par << 31));
+      // this warp has listed everything it found in the item; the warp that says so last hands
+      // the item over: list lengths and last thresholds to the item's header, the set of state
+      // cleared for the item three on
+      int old = 0;
+      if (lane == 0) {
+        __threadfence_block();
+        old = (int)sm_atomic_add(&sh[S_DONE + st], 1u);
+      }
+      old = __shfl_sync(0xFFFFFFFFu, old, 0);
+      if (old == kScanW - 1) {
+        __threadfence_block();
+        int d, kr;
+        bool ex;
+        find_bin(ctx.histB, hd->K, d, kr, ex);
+        if (d > 0 && lane == 0) sm_red_max_u64(&s64[L_TAU_B + st], (unsigned long long)((ctx.baseB + (uint32_t)d) << 16) << 32);
+        if (MASKED) {
+          find_bin(ctx.histA, ARCS_HEAD, d, kr, ex);
+          if (d > 0 && lane == 0) sm_red_max_u64(&s64[L_TAU_A + st], (unsigned long long)((ctx.baseA + (uint32_t)d) << 16) << 32);
+        }
+        __syncwarp();
+        if (lane == 0) {
+          w.hdr->n_candB = vsh[S_CNT + 4 * st + 0];
+          w.hdr->n_candA = vsh[S_CNT + 4 * st + 1];
+          w.hdr->n_tch = vsh[S_CNT + 4 * st + 2];
+          w.hdr->tauB = v64[L_TAU_B + st];
+          w.hdr->tauA = v64[L_TAU_A + st];
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) xh[(2 * st) * 256 + i * 32 + lane] = 0;  // both histograms of the item's set
+        if (lane < 4) sh[S_CNT + 4 * st + lane] = 0;
+        if (lane == 0) sh[S_DONE + st] = 0;
+        __syncwarp();
+        __threadfence_block();
+        if (lane == 0) {
+          vsh[S_STREAMED] = j + 1;
+          TS(4, j);
+        }
       }
       G0 += (uint32_t)T_;
     }
@@ -472,11 +490,11 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
         bool ex;
         find_bin(xh + (2 * st) * 256, hd->K, d, kr, ex);
         if (d > 0 && lane == 0)
-          atomicMax(&s64[L_TAU_B + st], (unsigned long long)(((uint32_t)hd->baseB + (uint32_t)d) << 16) << 32);
+          sm_red_max_u64(&s64[L_TAU_B + st], (unsigned long long)(((uint32_t)hd->baseB + (uint32_t)d) << 16) << 32);
         if (MASKED) {
           find_bin(xh + (2 * st + 1) * 256, ARCS_HEAD, d, kr, ex);
           if (d > 0 && lane == 0)
-            atomicMax(&s64[L_TAU_A + st], (unsigned long long)(((uint32_t)hd->baseA + (uint32_t)d) << 16) << 32);
+            sm_red_max_u64(&s64[L_TAU_A + st], (unsigned long long)(((uint32_t)hd->baseA + (uint32_t)d) << 16) << 32);
         }
       }
       __syncwarp();
@@ -485,217 +503,6 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
     // (abandoned: a table copy may still be in flight; give it a bounded chance to land)
     if (vsh[S_ABORT] && lane == 0)
       for (int x = prepped; x < issued; ++x) mbar_wait(&tab_full[x % 3], (uint32_t)(x / 3) & 1u);
-  } else if (warp == kExamWarp) {
-    // =================================================================== examiner
-    // Owns the candidate buffers while an item streams: moves the queued survivors into them and
-    // drops buffer entries the threshold has overtaken. The exact radix select runs only when a
-    // buffer still overflows, i.e. when one bin holds very many equal or close keys. When every
-    // scanner has closed an item, what is left goes to the item's block of the workspace.
-    uint32_t head = 0, idle = 0, polls = 0;
-    int streamed = 0;
-    // the two items that can have entries in the queue: the older one is always served first, so
-    // that items are handed over in order
-    struct XItem {
-      int cB, cA, marks, itm, K;
-      uint32_t baseB, baseA;
-      bool loaded;
-      int nT, roomT;                // flagged entries written to the item's block, and the room left there
-      unsigned long long* listT;
-    };
-    auto fresh = [](int itm) { return XItem{0, 0, 0, itm, 1, 0u, 0u, false, 0, 0, nullptr}; };
-    XItem older = fresh(0), newer = fresh(1);
-    constexpr int kStep = 128;     // queue entries taken per step, four per lane
-    constexpr int kFullB = 512, kFullA = 1024;  // buffer fill at which stale entries are dropped
-    // drop what the threshold has overtaken; if the buffer is still too full, select exactly
-    auto shrink = [&](const Sel& sel, int& cnt, int full) {
-      const uint64_t tc = *reinterpret_cast<volatile unsigned long long*>(sel.tau);
-      int out = 0;
-      for (int i0 = 0; i0 < cnt; i0 += 32) {
-        const int i = i0 + lane;
-        uint32_t ky = 0;
-        int32_t id = 0;
-        bool keep = false;
-        if (i < cnt) {
-          ky = sel.key[i];
-          id = sel.id[i];
-          keep = comp_of(ky, id) > tc;
-        }
-        const unsigned b = __ballot_sync(0xFFFFFFFFu, keep);  // (every lane has read its entry before any write below)
-        if (keep) {
-          const int pos = out + __popc(b & ((1u << lane) - 1u));
-          sel.key[pos] = ky;
-          sel.id[pos] = id;
-        }
-        out += __popc(b);
-        __syncwarp();
-      }
-      cnt = out;
-      if (full > 0 && cnt > full - kStep) cnt = sel_prune_warp(sel, cnt, sel.k, xhist, xtk, xti);
-    };
-    // threshold from the scanners' counts
-    auto raise = [&](const Sel& sel, const uint32_t* hst, uint32_t base) {
-      int d, kr;
-      bool ex;
-      find_bin(hst, sel.k, d, kr, ex);
-      if (d <= 0) return;
-      const unsigned long long tc = (unsigned long long)((base + (uint32_t)d) << 16) << 32;  // comp > tc <=> key >= edge of bin d
-      if (lane == 0) atomicMax(sel.tau, tc);
-      __syncwarp();
-    };
-    while (streamed < my_n) {
-      if (vsh[S_ABORT]) break;
-      const uint32_t tail = (uint32_t)vsh[S_QTAIL];
-      const int avail = (int)(tail - head);
-      if (avail == 0) {
-        if (++idle > kWaitLimit) {
-          abort_now();
-          break;
-        }
-        __nanosleep(kExamSleepNs);
-        continue;
-      }
-      if (avail < kStep && polls < 4) {  // let a fuller batch build up
-        ++polls;
-        __nanosleep(kExamSleepNs);
-        continue;
-      }
-      idle = 0;
-      polls = 0;
-      const int nb = min(avail, kStep);
-      uint2 ent[kStep / 32];
-#pragma unroll
-      for (int u = 0; u < kStep / 32; ++u) {
-        const uint32_t e = head + (uint32_t)(u * 32 + lane);
-        unsigned long long w = 0ull;
-        if (u * 32 + lane < nb) {
-          volatile unsigned long long* slot = &q_ent[e % kQueue];
-          uint32_t spins = 0;  // the entry is reserved; its writer stores it right after
-          while ((w = *slot) == 0ull && !vsh[S_ABORT])
-            if (++spins > kWaitLimit) abort_now();
-          *slot = 0ull;  // empty again before the slot is freed below
-        }
-        ent[u] = make_uint2((uint32_t)w, (uint32_t)(w >> 32));
-      }
-      __syncwarp();
-      __threadfence_block();
-      head += (uint32_t)nb;
-      if (lane == 0) vsh[S_QHEAD] = (int)head;
-      // serve one item's entries of this step; true when the item has been handed over
-      auto serve = [&](XItem& x) -> bool {
-        const int par = x.itm & 1, st = x.itm % 3;
-        const Sel sB{bkey + par * kCapB, bid + par * kCapB, nullptr, &s64[L_TAU_B + st], x.K, 0, kCapB};
-        const Sel sA{akey + par * kCapA, aid + par * kCapA, nullptr, &s64[L_TAU_A + st], ARCS_HEAD, 0, kCapA};
-        bool seen = false;
-        int nmark = 0;
-#pragma unroll
-        for (int u = 0; u < kStep / 32; ++u) {
-          const bool valid = u * 32 + lane < nb && (int)(ent[u].y >> 31) == par;
-          const uint32_t gid = ent[u].y & kIdMask;
-          const bool marker = valid && gid == kMarker;
-          nmark += __popc(__ballot_sync(0xFFFFFFFFu, marker));
-          seen = seen || __any_sync(0xFFFFFFFFu, valid);
-        }
-        if (!seen) return false;
-        if (!x.loaded) {  // first entry of a new item: its table was published before anything could be queued
-          mbar_try_wait(&tab_full[st], (uint32_t)(x.itm / 3) & 1u);  // (complete: the copied table is observed through it)
-          const ItemHdr* hd = tab_hdr(st);
-          x.K = hd->K;
-          x.baseB = (uint32_t)hd->baseB;
-          x.baseA = (uint32_t)hd->baseA;
-          x.listT = item_ws(a, (int)blockIdx.x + x.itm * (int)gridDim.x).pre + hd->n_pre;
-          x.roomT = item_pre_cap(a.hash_slots) - hd->n_pre;
-          x.loaded = true;
-        }
-        const Sel sBk{sB.key, sB.id, nullptr, sB.tau, x.K, 0, kCapB};
-#pragma unroll
-        for (int u = 0; u < kStep / 32; ++u) {
-          const bool valid = u * 32 + lane < nb && (int)(ent[u].y >> 31) == par;
-          const uint32_t gid = ent[u].y & kIdMask;
-          const bool mine = valid && gid != kMarker;
-          if (!__any_sync(0xFFFFFFFFu, mine)) continue;
-          const uint64_t cm = comp_of(ent[u].x, (int32_t)gid);
-          const bool tch = mine && (ent[u].y & kTch);
-          if (__any_sync(0xFFFFFFFFu, tch)) {
-            // flagged by the filter: straight to the item's block, raw, unless no threshold lets it matter any more.
-            // (Room: the listed tokens themselves plus the filter's few false alarms among the hot elements.)
-            const bool keep = tch && (cm > v64[L_TAU_B + st] || (MASKED && cm > v64[L_TAU_A + st]));
-            const unsigned bt = __ballot_sync(0xFFFFFFFFu, keep);
-            const int pos = x.nT + __popc(bt & ((1u << lane) - 1u));
-            if (keep) {
-              if (pos < x.roomT) x.listT[pos] = (unsigned long long)ent[u].x | ((unsigned long long)(ent[u].y & ~(1u << 31)) << 32);
-              else raise_status(a.status, ARCS_ERR_LIST);
-            }
-            x.nT = min(x.nT + __popc(bt), x.roomT);
-          }
-          const bool okB = mine && !tch && ((ent[u].y >> 30) & 1u) && cm > v64[L_TAU_B + st];
-          const unsigned bb = __ballot_sync(0xFFFFFFFFu, okB);
-          if (okB) {
-            const int pos = x.cB + __popc(bb & ((1u << lane) - 1u));
-            sB.key[pos] = ent[u].x;
-            sB.id[pos] = (int32_t)gid;
-          }
-          x.cB += __popc(bb);
-          if (MASKED) {
-            const bool okA = mine && !tch && cm > v64[L_TAU_A + st];
-            const unsigned ba = __ballot_sync(0xFFFFFFFFu, okA);
-            if (okA) {
-              const int pos = x.cA + __popc(ba & ((1u << lane) - 1u));
-              sA.key[pos] = ent[u].x;
-              sA.id[pos] = (int32_t)gid;
-            }
-            x.cA += __popc(ba);
-          }
-        }
-        // (the threshold warp raises the thresholds meanwhile)
-        if (x.cB > kFullB - kStep) shrink(sBk, x.cB, kFullB);
-        if (MASKED && x.cA > kFullA - kStep) shrink(sA, x.cA, kFullA);
-        x.marks += nmark;
-        if (x.marks < kScanW) return false;
-        if (lane == 0) TS(5, x.itm);
-        // every scanner has closed the item: write out what the last threshold has not overtaken
-        raise(sBk, xh + (2 * st) * 256, x.baseB);
-        shrink(sBk, x.cB, 0);
-        if (a.nseg > 1 && x.cB > x.K) x.cB = sel_prune_warp(sBk, x.cB, x.K, xhist, xtk, xti);  // (a row's segments are merged later: keep their lists short)
-        if (MASKED) {
-          raise(sA, xh + (2 * st + 1) * 256, x.baseA);
-          shrink(sA, x.cA, 0);
-          if (x.cA > ARCS_HEAD) x.cA = sel_prune_warp(sA, x.cA, ARCS_HEAD, xhist, xtk, xti);
-        }
-        __syncwarp();
-        const ItemWs w = item_ws(a, (int)blockIdx.x + x.itm * (int)gridDim.x);
-        for (int i = lane; i < x.cB; i += 32)
-          w.candB[i] = (unsigned long long)sB.key[i] | ((unsigned long long)((uint32_t)sB.id[i] | kOkB) << 32);
-        if (MASKED)
-          for (int i = lane; i < x.cA; i += 32) w.candA[i] = (unsigned long long)sA.key[i] | ((unsigned long long)(uint32_t)sA.id[i] << 32);
-        if (lane == 0) {
-          w.hdr->n_candB = x.cB;
-          w.hdr->n_candA = MASKED ? x.cA : 0;
-          w.hdr->n_tch = x.nT;
-          w.hdr->tauB = *sBk.tau;
-          w.hdr->tauA = *sA.tau;
-        }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) xh[(2 * st) * 256 + i * 32 + lane] = 0;  // both histograms of the item's set
-        __syncwarp();
-        __threadfence_block();
-        ++streamed;
-        if (lane == 0) vsh[S_STREAMED] = streamed;
-        if (lane == 0) TS(4, x.itm);
-        return true;
-      };
-      const bool done_o = serve(older);
-      const bool done_n = serve(newer) && done_o;  // (the newer item cannot be complete before the older one)
-      if (done_o) {
-        const int next = newer.itm + 1;
-        if (done_n) {
-          older = fresh(next);
-          newer = fresh(next + 1);
-        } else {
-          older = newer;
-          newer = fresh(next);
-        }
-      }
-    }
   }
 }
 

@@ -53,7 +53,7 @@ __device__ __forceinline__ void sel_push(const Sel& s, bool p, uint32_t key, int
   if (b == 0) return;
   const int lane = threadIdx.x & 31, leader = __ffs(b) - 1;
   int base = 0;
-  if (lane == leader) base = atomicAdd(s.cnt, __popc(b));
+  if (lane == leader) base = (int)sm_atomic_add(s.cnt, (uint32_t)__popc(b));
   base = __shfl_sync(0xFFFFFFFFu, base, leader);
   if (p) {
     const int pos = base + __popc(b & ((1u << lane) - 1u));
@@ -130,7 +130,7 @@ __device__ __noinline__ void sel_prune(const Sel& s, int k, const PruneScratch& 
     uint32_t* h = ps.hist + (pass & 1) * 256;
     for (int i = gt; i < n; i += kGroup) {
       const uint64_t c = comp_of(s.key[i], s.id[i]);
-      if ((c & mask) == prefix) atomicAdd(&h[(uint32_t)(c >> shift) & 255u], 1u);
+      if ((c & mask) == prefix) sm_red_add(&h[(uint32_t)(c >> shift) & 255u], 1u);
     }
     for (int i = gt; i < 256; i += kGroup) ps.hist[((pass + 1) & 1) * 256 + i] = 0;
     group_sync<BAR>();
@@ -156,12 +156,12 @@ __device__ __noinline__ void sel_prune(const Sel& s, int k, const PruneScratch& 
     const uint32_t ky = s.key[i];
     const uint64_t c = comp_of(ky, s.id[i]);
     if ((c & mask) >= prefix) {
-      const int pos = atomicAdd(&ps.misc[3], 1);
+      const int pos = (int)sm_atomic_add(&ps.misc[3], 1u);
       if (pos < kTmpCap) {
         ps.tk[pos] = ky;
         ps.ti[pos] = s.id[i];
       }
-      atomicMin(ps.m64, (unsigned long long)c);
+      sm_red_min_u64(ps.m64, (unsigned long long)c);
     }
   }
   group_sync<BAR>();
@@ -191,7 +191,7 @@ __device__ __noinline__ uint32_t group_kth_key(const uint32_t* keys, int n, int 
     group_sync<BAR>();
     for (int i = gt; i < n; i += kGroup) {
       const uint32_t my = keys[i];
-      if ((my & mask) == prefix) atomicAdd(&ps.hist[(my >> shift) & 255u], 1u);
+      if ((my & mask) == prefix) sm_red_add(&ps.hist[(my >> shift) & 255u], 1u);
     }
     group_sync<BAR>();
     if (gt < 32) {
@@ -227,7 +227,7 @@ __device__ __noinline__ int sel_prune_warp(const Sel& s, int n, int k, uint32_t*
     __syncwarp();
     for (int i = lane; i < n; i += 32) {
       const uint64_t c = comp_of(s.key[i], s.id[i]);
-      if ((c & mask) == prefix) atomicAdd(&hist[(uint32_t)(c >> shift) & 255u], 1u);
+      if ((c & mask) == prefix) sm_red_add(&hist[(uint32_t)(c >> shift) & 255u], 1u);
     }
     __syncwarp();
     int d, kr;
@@ -272,7 +272,7 @@ __device__ __noinline__ int sel_prune_warp(const Sel& s, int n, int k, uint32_t*
     s.key[i] = tk[i];
     s.id[i] = ti[i];
   }
-  if (lane == 0) atomicMax(s.tau, cmin - 1ull);  // exclusive threshold; never lowered (another warp raises it too)
+  if (lane == 0) sm_red_max_u64(s.tau, cmin - 1ull);  // exclusive threshold; never lowered (another warp raises it too)
   __syncwarp();
   return out;
 }
@@ -330,7 +330,7 @@ __device__ __forceinline__ void sel_rehist_warp(const Sel& s, int n, uint32_t* h
 #pragma unroll
   for (int j = 0; j < 8; ++j) hist[j * 32 + lane] = 0;
   __syncwarp();
-  for (int i = lane; i < n; i += 32) atomicAdd(&hist[coarse_bin(s.key[i], base)], 1u);
+  for (int i = lane; i < n; i += 32) sm_red_add(&hist[coarse_bin(s.key[i], base)], 1u);
   __syncwarp();
 }
 

@@ -101,6 +101,9 @@ typedef struct {
 /* max_list: max_hist + max_bias of the call (0 without lists) */
 size_t arcs_sample_workspace_bytes(int32_t B, int32_t V, int32_t masked, int32_t max_list);
 int arcs_sample_batch(const arcs_sample_args* args, void* stream);
+/* Measurement aid: the same three launches with CUDA events between them on `stream`; waits for
+ * them and returns the device time of the prepare, stream and finish kernels in ms3[0..2]. */
+int arcs_sample_batch_timed(const arcs_sample_args* args, void* stream, float* ms3);
 
 /* ------------------------------------------------------------------------------------------
  * argmax_batch: first maximum of each row (tools/sampler.h:38; zero/runz.cpp:283;

@@ -70,6 +70,34 @@ def test_many_rows_one_segment():
     check_rows(out, xb, True, params, hists, us, rows=range(0, B, 9))
 
 
+@pytest.mark.parametrize("masked", [False, True])
+def test_ascending_rows_overflow_the_lists(masked):
+    """ascending logits make every element a survivor of the stream: the per-item lists overflow
+    and the rows are read again by the finishing step; same results as ever"""
+    from gpuutil import check_rows, run_gpu_sample
+
+    g = np.random.default_rng(310 + masked)
+    B, V = 5, 40000
+    x = np.sort((g.standard_normal((B, V), dtype=np.float32) * 3).astype(np.float32), axis=1)
+    x[1] = x[1, ::-1]  # one descending row: nothing after the first elements survives
+    x[2, ::7] = x[2, 5]  # and one with masses of equal values
+    ps, biases, hists = [], [], []
+    for b in range(B):
+        p, bias = rand_params(g, V, True, allow_k0=not masked)
+        if masked and p["top_k"][0] > 256:
+            p["top_k"] = 40
+        ps.append(p)
+        biases.append(bias)
+        hists.append(np.concatenate([g.integers(0, V, 60), np.arange(V - 40, V)]).astype(np.int32))  # the best tokens are penalised
+    params = np.concatenate(ps)
+    us = g.random(B)
+    masks = np.stack([rand_mask(g, V, d) for d in (1.0, 0.5, 0.05, 0.5, 0.001)]) if masked else None
+    for bf16 in (False, True):
+        xb = synth.f32_to_bf16_bits(x) if bf16 else x
+        out = run_gpu_sample(xb, bf16, params, hists, us, biases, masks=masks)
+        check_rows(out, xb, bf16, params, hists, us, biases, masks=masks)
+
+
 def test_reference_property_cases():
     """the reference's own property tests (tests/test_sampler.cpp:215-301 there): presence penalty in
     greedy mode, bans by logit_bias <= -100, nothing allowed -> -1"""
