@@ -21,7 +21,10 @@ constexpr int kCapB = 1024;   // finish kernel's candidate buffer: prune trigger
 constexpr int kCapA = 1152;   // ... for the constrained head select (k = 512): fill limit 1024 + one round of 128
 constexpr int kListB = 2048;  // survivors of the stream an item's block holds: selection proper (typically k * (1 + ln(V / 4096)))
 constexpr int kListA = 4096;  // ... constrained head ranking
-constexpr int kBootBytes = 8192;  // prefix of an item read ahead to seed its threshold
+#ifndef ARCS_BOOT
+#define ARCS_BOOT 32768
+#endif
+constexpr int kBootBytes = ARCS_BOOT;  // prefix of an item the prepare kernel reads the first threshold off (a multiple of 8192)
 constexpr uint32_t kEmpty = 0xFFFFFFFFu;
 // per touched token: occurrences in the history (low 20 bits) and what applies to it
 constexpr uint32_t kInfoCount = 0xFFFFFu, kInfoWindow = 1u << 31, kInfoBias = 1u << 30, kInfoBan = 1u << 29;

@@ -14,7 +14,7 @@ constexpr int kStage = 512;    // flagged entries settled together
 constexpr int kSortCap = 160;  // a longer buffer is cut to the k best by the radix select before it is ranked by counting
 
 template <typename T, bool MASKED>
-__global__ void __launch_bounds__(kGroup) finish_kernel(const SampleDev a) {
+__global__ void __launch_bounds__(kGroup, 8) finish_kernel(const SampleDev a) {  // (eight CTAs per SM: a thousand rows are one wave)
   __shared__ unsigned long long s64[8];
   __shared__ double spr[ARCS_KCAP + 1];
   __shared__ __align__(8) uint32_t bkey[kCapB];
@@ -56,6 +56,7 @@ __global__ void __launch_bounds__(kGroup) finish_kernel(const SampleDev a) {
   // what the segments' headers say (fetched together with the row's settings). Nothing at or
   // below the largest threshold a segment's stream ended on can be among the k best: that
   // segment alone holds k above it.
+  const RowCfg r = row_cfg<MASKED>(a, b);  // (its loads travel together with the headers')
   for (int g = gt; g < a.nseg; g += kGroup) {
     const ItemHdr* hd = item_ws(a, b * a.nseg + g).hdr;
     int n0 = __ldcg(&hd->n_pre);
@@ -77,7 +78,6 @@ __global__ void __launch_bounds__(kGroup) finish_kernel(const SampleDev a) {
     sm_red_max_u64(&s64[L_TAU_B], __ldcg(&hd->tauB));
     if (MASKED) sm_red_max_u64(&s64[L_TAU_A], __ldcg(&hd->tauA));
   }
-  const RowCfg r = row_cfg<MASKED>(a, b);
   __syncthreads();
 #ifdef ARCS_TRACE
   if (r.H > 100000000) return;

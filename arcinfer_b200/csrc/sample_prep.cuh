@@ -88,30 +88,34 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
     *n_extra = 0;
   }
   // the prefix is fetched first: its latency hides behind the list work
-  const int nchunk = min(it.p.body_bytes, MASKED ? 2 * kBootBytes : kBootBytes) / 16;
+  const int nchunk = min(it.p.body_bytes, MASKED ? 2 * 8192 : kBootBytes) / 16;
   const int32_t c_lo = it.p.body_first, c_hi = it.p.body_first + nchunk * E;  // columns of the prefix
   float m0 = -INFINITY, m1 = -INFINITY;
   bool any0 = false, any1 = false;
   if (!MASKED) {
-    // two maxima per thread, each over every other one of the thread's (up to four) chunks of
-    // the prefix, all fetched together
-    uint4 q[4];
+    // two maxima per thread, each over every other one of the thread's chunks of the prefix,
+    // fetched four at a time
+    constexpr int kPer = kBootBytes / 16 / kGroup;  // chunks of the prefix per thread
+#pragma unroll 1
+    for (int x0 = 0; x0 < kPer; x0 += 4) {
+      uint4 q[4];
 #pragma unroll
-    for (int x = 0; x < 4; ++x) {
-      const int ci = gt + x * kGroup;
-      q[x] = ci < nchunk ? ldg128_stream(it.p.body + (size_t)ci * 16) : make_uint4(0, 0, 0, 0);
-    }
+      for (int x = 0; x < 4; ++x) {
+        const int ci = gt + (x0 + x) * kGroup;
+        q[x] = ci < nchunk ? ldg128_stream(it.p.body + (size_t)ci * 16) : make_uint4(0, 0, 0, 0);
+      }
 #pragma unroll
-    for (int x = 0; x < 4; ++x) {
-      const int ci = gt + x * kGroup;
-      if (ci < nchunk) {
-        const float m = Elem<T>::chunk_max(q[x]);
-        if (x & 1) {
-          m1 = fmaxf(m1, m);
-          any1 = true;
-        } else {
-          m0 = fmaxf(m0, m);
-          any0 = true;
+      for (int x = 0; x < 4; ++x) {
+        const int ci = gt + (x0 + x) * kGroup;
+        if (ci < nchunk) {
+          const float m = Elem<T>::chunk_max(q[x]);
+          if (x & 1) {
+            m1 = fmaxf(m1, m);
+            any1 = true;
+          } else {
+            m0 = fmaxf(m0, m);
+            any0 = true;
+          }
         }
       }
     }

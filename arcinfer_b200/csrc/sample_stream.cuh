@@ -40,10 +40,8 @@ constexpr int kTauSleepNs = ARCS_TAU_SLEEP;                // pause between two 
 #endif
 constexpr int kRing = ARCS_RING;                           // tiles in the ring (a multiple of kTeams)
 constexpr int kSTile = 8192;                               // bytes per tile (512 chunks)
-#ifndef ARCS_STASH
-#define ARCS_STASH 32
-#endif
-constexpr int kStash = ARCS_STASH;                         // chunks a scanner can set aside (examined one per lane)
+constexpr int kPend = 2;                                   // chunks each lane of a scanner can set aside
+constexpr int kStash = kPend * 32;                         // ... per warp
 static_assert(kRing % kTeams == 0, "a team always meets its tiles in the same slots");
 
 // indices into the shared scalar arrays
@@ -72,7 +70,7 @@ __device__ __forceinline__ float elem_of_words<__nv_bfloat16>(uint32_t w0, uint3
   return __uint_as_float((el & 1) ? (w & 0xFFFF0000u) : (w << 16));
 }
 
-// ---- the scanners' rare path, kept out of line so that the streaming loop stays small
+// ---- the scanners' rare path
 struct ScanCtx {
   const uint32_t* bloom;   // the item's filter over the columns a penalty or a bias touches
   int32_t bw;              // its size in words
@@ -90,13 +88,11 @@ struct ScanCtx {
   uint64_t tcB, tcA;       // thresholds the chunk was listed against
 };
 
-// The chunks a scanner warp has set aside (data in sq[], global id of each chunk's first element
-// in sc[]) are examined one chunk per lane: a float compare finds the (usually single) element
-// that reaches the threshold, then those elements go through the exact test together. Runs
-// after the warp has released the tile's ring slot, so the time spent here never holds up the
-// copy engine.
+// The chunks a scanner warp has set aside are examined one per lane (q: the lane's chunk, g0: global
+// id of its first element, have: the lane has one): a float compare finds the (usually single)
+// element that reaches the threshold, then those elements go through the exact test together.
 template <typename T, bool MASKED>
-__device__ __noinline__ void scan_examine(const ScanCtx& c, const uint4* sq, const int32_t* sc, int n) {
+__device__ __forceinline__ void scan_examine(const ScanCtx& c, bool have, uint4 q, int32_t g0) {
   constexpr int E = Elem<T>::kPerChunk;
   const int lane = threadIdx.x & 31;
   // threshold values (inclusive): the exact comparison on (key, id) follows per element
@@ -104,12 +100,8 @@ __device__ __noinline__ void scan_examine(const ScanCtx& c, const uint4* sq, con
   const float tfB = value_of(kB32 < 0x007FFFFFu ? 0x007FFFFFu : kB32);
   const float tfA = MASKED ? value_of(kA32 < 0x007FFFFFu ? 0x007FFFFFu : kA32) : INFINITY;
   const float tf = fminf(tfB, tfA);
-  uint4 q = make_uint4(0, 0, 0, 0);
-  int32_t g0 = 0;
   uint32_t bits = 0;  // elements of this lane's chunk still to be examined
-  if (lane < n) {
-    q = lds128(&sq[lane]);
-    g0 = (int32_t)sm_ld(&sc[lane]);
+  if (have) {
 #pragma unroll
     for (int e = 0; e < E; ++e) bits |= (Elem<T>::get(q, e) >= tf ? 1u : 0u) << e;
   }
@@ -270,9 +262,9 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
       if (tid == 0) TS(2, j);
       mbar_try_wait(&tab_full[st], (uint32_t)(j / 3) & 1u);  // (complete: every lane observes the copied table through it)
       const ItemHdr* hd = tab_hdr(st);
-      uint4* stq = stash_q + warp * kStash;      // chunks this warp has set aside
-      int32_t* stc = stash_c + warp * kStash;
-      int nst = 0;
+      uint4* stq = stash_q + warp * kStash + lane;      // chunks this lane has set aside: stq[s * 32], s < have
+      int32_t* stc = stash_c + warp * kStash + lane;
+      int have = 0;
       ScanCtx ctx;
       ctx.bloom = tab_bloom(st);
       ctx.bw = bloom_words_of(a.hash_slots);
@@ -291,17 +283,37 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
       ctx.roomT = item_pre_cap(a.hash_slots) - hd->n_pre;
       ctx.id_base = a.id_base;
       const uint32_t* mrow = ctx.mrow;
+      // examine everything the warp has set aside, against the thresholds of this moment
+      auto flush = [&]() {
+        ctx.tcB = v64[L_TAU_B + st];
+        ctx.tcA = MASKED ? v64[L_TAU_A + st] : 0xFFFFFFFFFFFFFFFFull;
+#pragma unroll 1
+        for (int sl = 0; sl < kPend; ++sl) {
+          const bool mine = have > sl;
+          if (!__any_sync(0xFFFFFFFFu, mine)) break;
+          scan_examine<T, MASKED>(ctx, mine, mine ? stq[sl * 32] : make_uint4(0, 0, 0, 0), mine ? stc[sl * 32] : 0);
+        }
+        have = 0;
+        __syncwarp();
+      };
       for (int t = (int)(((uint32_t)(warp / kShare) - G0) % kTeams); t < T_; t += kTeams) {
         const uint32_t g = G0 + (uint32_t)t;
         const int slot = (int)(g % kRing);
         const char* tile = ring + (size_t)slot * kSTile;
+        // What is set aside is examined while the warp would only wait for its next tile: the time
+        // the examination takes then holds nothing up.
+        if (__any_sync(0xFFFFFFFFu, have > 0)) {
+          int landed = 0;
+          if (lane == 0) landed = mbar_test_wait(&full[slot], (g / kRing) & 1u);
+          landed = __shfl_sync(0xFFFFFFFFu, landed, 0);
+          if (!landed) flush();
+        }
         if (!mbar_wait_warp(&full[slot], (g / kRing) & 1u)) {
           abort_now();
           break;
         }
         const int nchunk = (int)(s_tile_bytes(it.p, t) / 16u);
         const int32_t col0 = it.p.body_first + t * (kSTile / (int)sizeof(T)) + a.id_base;  // global id of the tile's first element
-        // thresholds are re-read for every group of chunks: they are raised all the time
         uint64_t tcB = 0, tcA = 0;
         typename Elem<T>::Thr thB, thA;
         auto refresh = [&]() {
@@ -319,83 +331,64 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
 #endif
         constexpr int kU = kMine / 32 < ARCS_KU ? kMine / 32 : ARCS_KU;   // chunks per lane per step
         const int c_lo = (warp % kShare) * kMine;
+        refresh();  // (once per visit: the thresholds move slowly against the few hundred cycles a visit takes)
 #ifdef ARCS_X_NOSCAN
         for (int c0 = c_lo; c0 < 0; c0 += kU * 32) {
 #else
         for (int c0 = c_lo; c0 < min(nchunk, c_lo + kMine); c0 += kU * 32) {
 #endif
           uint4 q[kU];
-          bool h[kU];
-          refresh();
 #pragma unroll
           for (int u = 0; u < kU; ++u) q[u] = lds128(tile + (c0 + u * 32 + lane) * 16);  // (inside the slot even past a short tile's end)
-          bool any = false;
+          uint32_t m = 0;  // this lane's chunks that reach a threshold
 #pragma unroll
           for (int u = 0; u < kU; ++u) {
             const int ci = c0 + u * 32 + lane;
-            h[u] = Elem<T>::chunk_reaches(q[u], thB);
+            bool h = Elem<T>::chunk_reaches(q[u], thB);
             if (MASKED) {
-              bool hb = h[u] && ci < nchunk;
+              bool hb = h && ci < nchunk;
               if (hb) {
                 const int32_t gid = col0 + ci * E;
                 uint32_t bits = __ldg(&mrow[gid >> 5]) >> (gid & 31);
                 if ((gid & 31) + E > 32) bits |= __ldg(&mrow[(gid >> 5) + 1]) << (32 - (gid & 31));
                 hb = (bits & ((1u << E) - 1u)) != 0u;
               }
-              h[u] = hb || Elem<T>::chunk_reaches(q[u], thA);
+              h = hb || Elem<T>::chunk_reaches(q[u], thA);
             }
-            if (!whole) h[u] = h[u] && ci < nchunk;
-#ifdef ARCS_X_NOHOT
-            h[u] = h[u] && a.V < 0;  // (experiment: the test is evaluated, nothing is ever listed)
-#endif
-            any = any || h[u];
+            if (!whole) h = h && ci < nchunk;
+            m |= (h ? 1u : 0u) << u;
           }
-          if (__any_sync(0xFFFFFFFFu, any)) {  // set the listed chunks aside
+          if (!__any_sync(0xFFFFFFFFu, m != 0u)) continue;  // (nearly always)
+          // Set the listed chunks aside, every lane its own: no lane needs to know of another's,
+          // unless one has no room left (then everything pending is examined first).
+          int need = __popc(m);
+          while (__any_sync(0xFFFFFFFFu, have + need > kPend)) {
+            flush();
+            if (need > kPend) {  // (more than the lane can hold at once: the first now, the rest in the next turn)
 #pragma unroll
-            for (int u = 0; u < kU; ++u) {
-              const unsigned all = __ballot_sync(0xFFFFFFFFu, h[u]);
-              if (all == 0u) continue;
-#pragma unroll
-              for (int half = 0; half < 2; ++half) {  // (half a warp at a time: never more than the stash holds)
-                const unsigned bal = all & (half ? 0xFFFF0000u : 0x0000FFFFu);
-                if (bal == 0u) continue;
-                if (nst + __popc(bal) > kStash) {  // rare: make room first
-                  ctx.tcB = tcB;
-                  ctx.tcA = tcA;
-                  __syncwarp();
-                  scan_examine<T, MASKED>(ctx, stq, stc, nst);
-                  nst = 0;
-                  __syncwarp();
+              for (int u = 0; u < kU; ++u)
+                if (((m >> u) & 1u) && have < kPend) {
+                  stq[have * 32] = q[u];
+                  stc[have * 32] = col0 + (c0 + u * 32 + lane) * E;
+                  ++have;
+                  m &= ~(1u << u);
                 }
-                if (h[u] && ((bal >> lane) & 1u)) {
-                  const int pos = nst + __popc(bal & ((1u << lane) - 1u));
-                  stq[pos] = q[u];
-                  stc[pos] = col0 + (c0 + u * 32 + lane) * E;  // global id of the chunk's first element
-                }
-                nst += __popc(bal);
-              }
+              need = __popc(m);
             }
           }
+#pragma unroll
+          for (int u = 0; u < kU; ++u)
+            if ((m >> u) & 1u) {
+              stq[have * 32] = q[u];
+              stc[have * 32] = col0 + (c0 + u * 32 + lane) * E;  // global id of the chunk's first element
+              ++have;
+            }
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[slot]);  // the slot can be refilled while the chunks set aside are examined
-        if (nst >= kStash / 2) {  // examine in batches: full passes, and against a fresher threshold
-          refresh();
-          ctx.tcB = tcB;
-          ctx.tcA = tcA;
-          scan_examine<T, MASKED>(ctx, stq, stc, nst);
-          nst = 0;
-          __syncwarp();
-        }
       }
       if (vsh[S_ABORT]) break;
-      if (nst > 0) {  // what is still set aside
-        ctx.tcB = v64[L_TAU_B + st];
-        ctx.tcA = MASKED ? v64[L_TAU_A + st] : 0xFFFFFFFFFFFFFFFFull;
-        __syncwarp();
-        scan_examine<T, MASKED>(ctx, stq, stc, nst);
-        nst = 0;
-      }
+      if (__any_sync(0xFFFFFFFFu, have > 0)) flush();  // what is still set aside
       __syncwarp();
       if (tid == 0) TS(3, j);
       // this warp has listed everything it found in the item; the warp that says so last hands
