@@ -218,6 +218,13 @@ __device__ __forceinline__ uint4 ldg128_stream(const void* p) {
   return r;
 }
 
+// Programmatic dependent launch: a kernel launched with the attribute may start while the kernel
+// before it on the stream still runs; it must pass pdl_wait() before it touches anything that
+// kernel writes (the wait returns when that kernel has completed and its writes are visible).
+// pdl_trigger() in the earlier kernel lets the later one be scheduled as soon as there is room.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void raise_status(int32_t* status, int code) {
   if (status) atomicCAS(status, 0, code);
 }

@@ -8,7 +8,28 @@
 
 using namespace arcs;
 
+// launch `kernel` so that it may start before the kernel ahead of it on the stream has finished
+// (it waits on the device before reading that kernel's output)
+template <typename K>
+static cudaError_t launch_dependent(K kernel, unsigned grid, unsigned block, size_t smem, cudaStream_t st, const SampleDev& a, bool overlap) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(block);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap ? 1 : 0;  // (without the attribute: an ordinary launch, e.g. when the kernels are timed one by one)
+  return cudaLaunchKernelEx(&cfg, kernel, a);
+}
+
 constexpr int kMaxRows = 65536;
+#ifndef ARCS_FIN
+#define ARCS_FIN 128
+#endif
+constexpr int kFinishThreads = ARCS_FIN;  // threads of the finish kernel's CTA (one CTA per row)
 
 static int table_slots(int max_list) {
   int slots = kGroup;
@@ -116,9 +137,11 @@ static int sample_launch(const arcs_sample_args* g, void* stream, cudaEvent_t* e
     if (events) cudaEventRecord(events[0], st);                                                                    \
     prepare_kernel<T, M><<<(unsigned)items, kGroup, smem_p, st>>>(a);                                              \
     if (events) cudaEventRecord(events[1], st);                                                                    \
-    stream_kernel<T, M><<<grid_s, kThreadsS, smem_s, st>>>(a);                                                     \
+    e = launch_dependent(stream_kernel<T, M>, grid_s, kThreadsS, smem_s, st, a, events == nullptr);                                  \
+    if (e != cudaSuccess) return set_error(ARCS_ERR_CUDA, cudaGetErrorString(e));                                  \
     if (events) cudaEventRecord(events[2], st);                                                                    \
-    finish_kernel<T, M><<<(unsigned)a.B, kGroup, 0, st>>>(a);                                                      \
+    e = launch_dependent(finish_kernel<T, M, kFinishThreads>, (unsigned)a.B, kFinishThreads, 0, st, a, events == nullptr);          \
+    if (e != cudaSuccess) return set_error(ARCS_ERR_CUDA, cudaGetErrorString(e));                                  \
     if (events) cudaEventRecord(events[3], st);                                                                    \
   } while (0)
   if (g->dtype == ARCS_F32) {

@@ -13,8 +13,8 @@ namespace arcs {
 constexpr int kStage = 512;    // flagged entries settled together
 constexpr int kSortCap = 160;  // a longer buffer is cut to the k best by the radix select before it is ranked by counting
 
-template <typename T, bool MASKED>
-__global__ void __launch_bounds__(kGroup, 8) finish_kernel(const SampleDev a) {  // (eight CTAs per SM: a thousand rows are one wave)
+template <typename T, bool MASKED, int G>
+__global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (eight CTAs per SM: a thousand rows are one wave)
   __shared__ unsigned long long s64[8];
   __shared__ double spr[ARCS_KCAP + 1];
   __shared__ __align__(8) uint32_t bkey[kCapB];
@@ -53,11 +53,12 @@ __global__ void __launch_bounds__(kGroup, 8) finish_kernel(const SampleDev a) { 
     s64[L_TAU_A] = 0ull;
   }
   __syncthreads();
+  pdl_wait();  // the stream kernel's lists and headers are read from here on
   // what the segments' headers say (fetched together with the row's settings). Nothing at or
   // below the largest threshold a segment's stream ended on can be among the k best: that
   // segment alone holds k above it.
   const RowCfg r = row_cfg<MASKED>(a, b);  // (its loads travel together with the headers')
-  for (int g = gt; g < a.nseg; g += kGroup) {
+  for (int g = gt; g < a.nseg; g += G) {
     const ItemHdr* hd = item_ws(a, b * a.nseg + g).hdr;
     int n0 = __ldcg(&hd->n_pre);
     const int nt = __ldcg(&hd->n_tch);
@@ -87,22 +88,22 @@ __global__ void __launch_bounds__(kGroup, 8) finish_kernel(const SampleDev a) { 
   // barriers between the rounds of pushes are needed only when a buffer or the stage could overflow
   const bool careful = sh[S_OVER] != 0 || sh[S_NLIST] > kCapB || (MASKED && sh[S_NLISTA] > kCapA) || sh[S_NPRE] > kStage;
   const PruneScratch psF{hist, tk, ti, misc, &s64[L_PRUNE_MIN]};
-  const Sel selB{bkey, bid, &sh[S_CNT_B], &s64[L_TAU_B], r.kB, kCapB - kGroup, kCapB};  // (pruned only when the buffer is nearly full)
+  const Sel selB{bkey, bid, &sh[S_CNT_B], &s64[L_TAU_B], r.kB, kCapB - G, kCapB};  // (pruned only when the buffer is nearly full)
   const Sel selA{akey, aid, &sh[S_CNT_A], &s64[L_TAU_A], ARCS_HEAD, 1024, kCapA};
 
   bool hot = false;
   // called by the whole group after a barrier behind which nobody pushes
   auto maybe_prune = [&]() {
     const bool pb = *selB.cnt > selB.trig, pa = MASKED && *selA.cnt > selA.trig;
-    group_sync<2>();
-    if (pb) sel_prune<2>(selB, selB.k, psF, gt);
-    if (pa) sel_prune<2>(selA, selA.k, psF, gt);
+    group_sync<2, G>();
+    if (pb) sel_prune<2, G>(selB, selB.k, psF, gt);
+    if (pa) sel_prune<2, G>(selA, selA.k, psF, gt);
   };
   const uint32_t* mrow = MASKED ? a.mask + (size_t)(a.mask_row ? a.mask_row[b] : b) * a.mask_stride : nullptr;
   // after a round of pushes: prune when a buffer has grown past its trigger
-  // (at most kGroup pushes on top of a buffer at or below its trigger: inside its capacity)
+  // (at most G pushes on top of a buffer at or below its trigger: inside its capacity)
   auto after_push = [&]() {
-    if (group_sync_or<2>(hot)) {
+    if (group_sync_or<2, G>(hot)) {
       maybe_prune();
       hot = false;
     }
@@ -112,20 +113,20 @@ __global__ void __launch_bounds__(kGroup, 8) finish_kernel(const SampleDev a) { 
   // when the prepare kernel evaluated the history (table mode), else penalised here; one the
   // filter flagged by accident is an ordinary element.
   auto settle = [&]() {
-    group_sync<2>();
+    group_sync<2, G>();
     const int nF = min(sh[S_NFLAG], kStage);
     if (nF == 0) return;
-    for (int f = gt; f < nF; f += kGroup) fl_cnt[f] = 0u;
-    group_sync<2>();
+    for (int f = gt; f < nF; f += G) fl_cnt[f] = 0u;
+    group_sync<2, G>();
     TR(22);
     const int32_t w0 = window_start(r);
-    for (int i = gt; i < r.NB; i += kGroup) {
+    for (int i = gt; i < r.NB; i += G) {
       const int32_t t = a.bias_ids[r.q0 + i];
       for (int f = 0; f < nF; ++f)
         if ((fl_id[f] & (int32_t)kIdMask) == t) sm_red_or(&fl_cnt[f], 1u << 30);
     }
     if (r.pen_on) {
-      for (int i = gt; i < r.H; i += kGroup) {
+      for (int i = gt; i < r.H; i += G) {
         const int32_t t = __ldg(&a.hist_ids[r.h0 + i]);
         for (int f = 0; f < nF; ++f)
           if ((fl_id[f] & (int32_t)kIdMask) == t) {
@@ -134,9 +135,9 @@ __global__ void __launch_bounds__(kGroup, 8) finish_kernel(const SampleDev a) { 
           }
       }
     }
-    group_sync<2>();
+    group_sync<2, G>();
     TR(23);
-    for (int f0 = 0; f0 < nF; f0 += kGroup) {
+    for (int f0 = 0; f0 < nF; f0 += G) {
       const int f = f0 + gt;
       bool p = f < nF;
       uint32_t ky = 0u;
@@ -167,26 +168,26 @@ __global__ void __launch_bounds__(kGroup, 8) finish_kernel(const SampleDev a) { 
     }
     TR(24);
     if (gt == 0) sh[S_NFLAG] = 0;
-    group_sync<2>();
+    group_sync<2, G>();
   };
-  // Two lists of entries (key | word y << 32) into the selections, a round of kGroup at a time:
+  // Two lists of entries (key | word y << 32) into the selections, a round of G at a time:
   // `first` feeds both selections, `second` only one (the selection proper, or with toA the
   // constrained head ranking). The entries of several rounds are fetched together; flagged
   // entries are staged.
   auto take = [&](const unsigned long long* first, int n1, const unsigned long long* second, int n2, bool toA) {
     constexpr int R = 8;
     const int n = n1 + n2;
-    for (int i0 = 0; i0 < n; i0 += R * kGroup) {
+    for (int i0 = 0; i0 < n; i0 += R * G) {
       unsigned long long e[R];
 #pragma unroll
       for (int x = 0; x < R; ++x) {
-        const int i = i0 + x * kGroup + gt;
+        const int i = i0 + x * G + gt;
         e[x] = i < n1 ? __ldcg(&first[i]) : i < n ? __ldcg(&second[i - n1]) : 0ull;
       }
 #pragma unroll
       for (int x = 0; x < R; ++x) {
-        if (i0 + x * kGroup >= n) break;
-        const int i = i0 + x * kGroup + gt;
+        if (i0 + x * G >= n) break;
+        const int i = i0 + x * G + gt;
         const bool p = i < n, one = i < n1;
         const uint32_t ky = (uint32_t)e[x], y = (uint32_t)(e[x] >> 32);
         const int32_t id = (int32_t)(y & kIdMask);
@@ -208,7 +209,7 @@ __global__ void __launch_bounds__(kGroup, 8) finish_kernel(const SampleDev a) { 
         }
         if (careful) {
           after_push();
-          if (sh[S_NFLAG] > kStage - kGroup) settle();
+          if (sh[S_NFLAG] > kStage - G) settle();
         }
       }
     }
@@ -221,7 +222,7 @@ __global__ void __launch_bounds__(kGroup, 8) finish_kernel(const SampleDev a) { 
     const ItemWs w = item_ws(a, b * a.nseg + g);
     const int bw = bloom_words_of(a.hash_slots);
     const int nchunk = it.p.body_bytes / 16;
-    for (int c0 = 0; c0 < nchunk; c0 += kGroup) {
+    for (int c0 = 0; c0 < nchunk; c0 += G) {
       const int ci = c0 + gt;
       const uint4 q = ci < nchunk ? ldg128_stream(it.p.body + (size_t)ci * 16) : make_uint4(0, 0, 0, 0);
 #pragma unroll
@@ -252,7 +253,7 @@ __global__ void __launch_bounds__(kGroup, 8) finish_kernel(const SampleDev a) { 
           }
         }
         after_push();
-        if (sh[S_NFLAG] > kStage - kGroup) settle();
+        if (sh[S_NFLAG] > kStage - G) settle();
       }
     }
   };
@@ -265,18 +266,18 @@ __global__ void __launch_bounds__(kGroup, 8) finish_kernel(const SampleDev a) { 
   }
   TR(21);
   settle();
-  group_sync<2>();
+  group_sync<2, G>();
   TR(10);
-  if (MASKED) sel_prune<2>(selA, selA.k, psF, gt);
+  if (MASKED) sel_prune<2, G>(selA, selA.k, psF, gt);
 
   // ---- candidates best first. A short buffer is ranked by counting, which selects the k best
   // and sorts them in one step; a longer one is cut to the k best by the radix select first.
   const int sort_cap = max(kSortCap, selB.k + 64);
-  if (*selB.cnt > sort_cap) sel_prune<2>(selB, selB.k, psF, gt);
-  group_sync<2>();
+  if (*selB.cnt > sort_cap) sel_prune<2, G>(selB, selB.k, psF, gt);
+  group_sync<2, G>();
   const int nbuf = min(*selB.cnt, sort_cap);
   const int nB = min(nbuf, selB.k);
-  for (int i = gt; i < nbuf; i += kGroup) {
+  for (int i = gt; i < nbuf; i += G) {
     const uint32_t ky = selB.key[i];
     const int32_t id = selB.id[i];
     const uint64_t c = comp_of(ky, id);
@@ -291,18 +292,18 @@ __global__ void __launch_bounds__(kGroup, 8) finish_kernel(const SampleDev a) { 
     s64[L_TOP] = 0ull;                    // best composite among head entries that are not skipped as banned
     s64[L_LOW] = 0xFFFFFFFFFFFFFFFFull;   // smallest composite of the head
   }
-  group_sync<2>();
+  group_sync<2, G>();
   TR(11);
   // ---- tools/sampler.h:54-77 (or :105-143)
   int flags = 0, nc = nB;
   if (MASKED) {
     const int nA = min(*selA.cnt, ARCS_HEAD);
-    for (int i = gt; i < nA; i += kGroup) {
+    for (int i = gt; i < nA; i += G) {
       const uint64_t c = comp_of(selA.key[i], selA.id[i]);
       if (!(bans && value_of(selA.key[i]) <= ARCS_BANNED)) sm_red_max_u64(&s64[L_TOP], (unsigned long long)c);
       sm_red_min_u64(&s64[L_LOW], (unsigned long long)c);
     }
-    group_sync<2>();
+    group_sync<2, G>();
     if (gt == 0) {
       const uint64_t top = s64[L_TOP], low = s64[L_LOW];
       if (top != 0ull && (nB == 0 || comp_of(key_of(sv[0]), sid[0]) != top)) flags |= ARCS_FLAG_FIRST_REFUSED;
@@ -322,7 +323,7 @@ __global__ void __launch_bounds__(kGroup, 8) finish_kernel(const SampleDev a) { 
       sh[S_NCAND] = nc;
       sh[S_FLAGS] = flags;
     }
-    group_sync<2>();
+    group_sync<2, G>();
     nc = sh[S_NCAND];
   } else {
     if (gt == 0) {
@@ -330,34 +331,34 @@ __global__ void __launch_bounds__(kGroup, 8) finish_kernel(const SampleDev a) { 
         while (nc > 1 && sv[nc - 1] <= ARCS_BANNED) --nc;
       sh[S_NCAND] = nc;
     }
-    group_sync<2>();
+    group_sync<2, G>();
     nc = sh[S_NCAND];
   }
   {  // equal logits among the candidates kept: the reference's order there is not defined
     bool tie = false;
-    for (int i = gt; i + 1 < nc; i += kGroup) tie = tie || sv[i] == sv[i + 1];
+    for (int i = gt; i + 1 < nc; i += G) tie = tie || sv[i] == sv[i + 1];
     if (tie) sm_red_or(&sh[S_FLAGS], (uint32_t)ARCS_FLAG_TIE_TOPK);
   }
   TR(12);
   const bool draw = (!r.greedy && nc > 1) || (!MASKED && !r.greedy && nc == 1);
   if (draw) {
     const float mx = sv[0];
-    for (int i = gt; i < nc; i += kGroup) {
+    for (int i = gt; i < nc; i += G) {
       const float x = __fdiv_rn(__fsub_rn(sv[i], mx), r.prm.temperature);  // :60 float arithmetic
       spr[i] = (double)(float)exp((double)x);                              // float exp, widened
     }
-    group_sync<2>();
+    group_sync<2, G>();
     if (gt == 0) {
       double z = 0.0;
 #pragma unroll 8
       for (int i = 0; i < nc; ++i) z = __dadd_rn(z, spr[i]);  // :58-60 in candidate order
       spr[ARCS_KCAP] = z;
     }
-    group_sync<2>();
+    group_sync<2, G>();
     const double z = spr[ARCS_KCAP];
-    for (int i = gt; i < nc; i += kGroup) spr[i] = __ddiv_rn(spr[i], z);  // :64, the same quotients in any order
+    for (int i = gt; i < nc; i += G) spr[i] = __ddiv_rn(spr[i], z);  // :64, the same quotients in any order
   }
-  group_sync<2>();
+  group_sync<2, G>();
   TR(13);
   // :65-72. The running sums are a chain of roundings in candidate order (one thread); where the
   // chain is cut is then found by all threads.
@@ -373,17 +374,17 @@ __global__ void __launch_bounds__(kGroup, 8) finish_kernel(const SampleDev a) { 
       }
     }
   }
-  group_sync<2>();
+  group_sync<2, G>();
   if (draw) {
     const double mp = __dmul_rn((double)r.prm.min_p, spr[0]);
-    for (int i = gt; i < nc; i += kGroup) {
+    for (int i = gt; i < nc; i += G) {
       int n_i = 0x7FFFFFFF;
       if (r.prm.min_p > 0.0f && spr[i] < mp) n_i = max(1, i);   // :65 (tested before the candidate is added)
       else if (cum[i] >= (double)r.prm.top_p) n_i = i + 1;      // :67
       if (n_i != 0x7FFFFFFF) sm_red_min_s32(&sh[S_NCAND], n_i);
     }
   }
-  group_sync<2>();
+  group_sync<2, G>();
   if (gt == 0) {
     int token = nc > 0 ? sid[0] : -1, n = nc > 0 ? 1 : 0;
     if (draw) {
@@ -408,10 +409,10 @@ __global__ void __launch_bounds__(kGroup, 8) finish_kernel(const SampleDev a) { 
     if (a.n_cand) a.n_cand[b] = nc;
     if (a.n_kept) a.n_kept[b] = n;
   }
-  group_sync<2>();
+  group_sync<2, G>();
   TR(14);
   if (gt == 0 && a.flags) a.flags[b] = sh[S_FLAGS];
-  for (int i = gt; i < a.cand_stride && (a.cand_id || a.cand_val || a.cand_pr); i += kGroup) {
+  for (int i = gt; i < a.cand_stride && (a.cand_id || a.cand_val || a.cand_pr); i += G) {
     const size_t o = (size_t)b * a.cand_stride + i;
     const bool in = i < nc;
     if (a.cand_id) a.cand_id[o] = in ? sid[i] : -1;

@@ -71,6 +71,7 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
   const int gt = threadIdx.x, lane = gt & 31;
   const int item = blockIdx.x;
   const int32_t Vg = a.v_global > 0 ? a.v_global : a.V;
+  pdl_trigger();  // (the stream kernel may move in as CTAs of this one retire; it waits before it reads their output)
   TR(0);
   const Item<T> it = item_of<T>(a, item);
   const RowCfg r = row_cfg<MASKED>(a, it.b);

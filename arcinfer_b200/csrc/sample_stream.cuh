@@ -189,6 +189,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
   }
   for (int i = tid; i < 6 * 256; i += kThreadsS) xh[i] = 0u;
   __syncthreads();  // the only CTA-wide barrier
+  pdl_trigger();    // (the finish kernel's CTAs may take their places; they wait for this kernel before they read)
   if (tid == 0) TS(0, 0);
 
   auto abort_now = [&]() {
@@ -440,6 +441,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
     // lower edge of the bin holding the k-th best survivor counted so far.
     int issued = 0, prepped = 0;
     uint32_t idle = 0;
+    pdl_wait();  // the prepare kernel's output is read from here on (everything else in this CTA follows this warp's flags)
     for (;;) {
       if (vsh[S_ABORT]) break;
       const int done = vsh[S_STREAMED];

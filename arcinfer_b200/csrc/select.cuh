@@ -11,9 +11,9 @@ constexpr int kTmpCap = ARCS_HEAD;  // most entries a prune keeps (the constrain
 constexpr int kGroup = 128;         // threads of each helper group (one prepares items, one finishes them)
 
 // named-barrier synchronisation of one helper group (BAR: barrier number, kGroup threads)
-template <int BAR>
-__device__ __forceinline__ void group_sync() { asm volatile("bar.sync %0, %1;" ::"n"(BAR), "n"(kGroup) : "memory"); }
-template <int BAR>
+template <int BAR, int G = kGroup>
+__device__ __forceinline__ void group_sync() { asm volatile("bar.sync %0, %1;" ::"n"(BAR), "n"(G) : "memory"); }
+template <int BAR, int G = kGroup>
 __device__ __forceinline__ bool group_sync_or(bool pred) {
   uint32_t r;
   asm volatile(
@@ -22,7 +22,7 @@ __device__ __forceinline__ bool group_sync_or(bool pred) {
       "bar.red.or.pred p, %2, %3, q;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(r)
-      : "r"((uint32_t)pred), "n"(BAR), "n"(kGroup)
+      : "r"((uint32_t)pred), "n"(BAR), "n"(G)
       : "memory");
   return r != 0;
 }
@@ -113,27 +113,27 @@ __device__ __forceinline__ void find_bin(const uint32_t* h, int krem, int& digit
 // finishing group (gt = thread index inside the group) with the buffer quiescent. Radix
 // select, most significant byte first, over the composite (key << 32 | ~id): composites are
 // unique, so the k-th is found exactly, ties included.
-template <int BAR>
+template <int BAR, int G = kGroup>
 __device__ __noinline__ void sel_prune(const Sel& s, int k, const PruneScratch& ps, int gt) {
   const int n = min(*s.cnt, s.cap);
   if (n <= k) return;
-  for (int i = gt; i < 512; i += kGroup) ps.hist[i] = 0;
+  for (int i = gt; i < 512; i += G) ps.hist[i] = 0;
   if (gt == 0) {
     ps.misc[3] = 0;
     *ps.m64 = 0xFFFFFFFFFFFFFFFFull;
   }
-  group_sync<BAR>();
+  group_sync<BAR, G>();
   uint64_t prefix = 0, mask = 0;
   int krem = k;
   for (int pass = 0; pass < 8; ++pass) {
     const int shift = 56 - 8 * pass;
     uint32_t* h = ps.hist + (pass & 1) * 256;
-    for (int i = gt; i < n; i += kGroup) {
+    for (int i = gt; i < n; i += G) {
       const uint64_t c = comp_of(s.key[i], s.id[i]);
       if ((c & mask) == prefix) sm_red_add(&h[(uint32_t)(c >> shift) & 255u], 1u);
     }
-    for (int i = gt; i < 256; i += kGroup) ps.hist[((pass + 1) & 1) * 256 + i] = 0;
-    group_sync<BAR>();
+    for (int i = gt; i < 256; i += G) ps.hist[((pass + 1) & 1) * 256 + i] = 0;
+    group_sync<BAR, G>();
     if (gt < 32) {
       int d, kr;
       bool ex;
@@ -144,7 +144,7 @@ __device__ __noinline__ void sel_prune(const Sel& s, int k, const PruneScratch& 
         ps.misc[2] = ex;
       }
     }
-    group_sync<BAR>();
+    group_sync<BAR, G>();
     const int d = ps.misc[0];
     krem = ps.misc[1];
     const bool exact = ps.misc[2] != 0;
@@ -152,7 +152,7 @@ __device__ __noinline__ void sel_prune(const Sel& s, int k, const PruneScratch& 
     mask |= 0xFFull << shift;
     if (exact) break;
   }
-  for (int i = gt; i < n; i += kGroup) {
+  for (int i = gt; i < n; i += G) {
     const uint32_t ky = s.key[i];
     const uint64_t c = comp_of(ky, s.id[i]);
     if ((c & mask) >= prefix) {
@@ -164,9 +164,9 @@ __device__ __noinline__ void sel_prune(const Sel& s, int k, const PruneScratch& 
       sm_red_min_u64(ps.m64, (unsigned long long)c);
     }
   }
-  group_sync<BAR>();
+  group_sync<BAR, G>();
   const int m = min(ps.misc[3], kTmpCap);
-  for (int i = gt; i < m; i += kGroup) {
+  for (int i = gt; i < m; i += G) {
     s.key[i] = ps.tk[i];
     s.id[i] = ps.ti[i];
   }
@@ -174,7 +174,7 @@ __device__ __noinline__ void sel_prune(const Sel& s, int k, const PruneScratch& 
     *s.cnt = m;
     *s.tau = *ps.m64 - 1ull;  // exclusive: the smallest kept composite itself still passes
   }
-  group_sync<BAR>();
+  group_sync<BAR, G>();
 }
 
 
