@@ -13,5 +13,6 @@ from .capi import (  # noqa: F401
     dfa_mask,
     lib,
     make_params,
+    merge_batch,
     sample_batch,
 )

@@ -75,6 +75,22 @@ lib.arcs_sample_workspace_bytes.restype = C.c_size_t
 lib.arcs_sample_workspace_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32]
 lib.arcs_sample_batch.restype = C.c_int
 lib.arcs_sample_batch.argtypes = [C.POINTER(SampleArgs), C.c_void_p]
+
+
+class MergeArgs(C.Structure):
+    _fields_ = [
+        ("G", C.c_int32), ("B", C.c_int32), ("cand_stride", C.c_int32),
+        ("cand_id", C.c_void_p), ("cand_val", C.c_void_p), ("n_cand", C.c_void_p),
+        ("params", C.c_void_p), ("u", C.c_void_p), ("bias_off", C.c_void_p), ("bias_vals", C.c_void_p),
+        ("v_global", C.c_int32),
+        ("token", C.c_void_p), ("n_cand_out", C.c_void_p), ("n_kept", C.c_void_p), ("flags", C.c_void_p),
+        ("out_id", C.c_void_p), ("out_val", C.c_void_p), ("out_pr", C.c_void_p), ("out_stride", C.c_int32),
+        ("status", C.c_void_p),
+    ]
+
+
+lib.arcs_merge_batch.restype = C.c_int
+lib.arcs_merge_batch.argtypes = [C.POINTER(MergeArgs), C.c_void_p]
 lib.arcs_sample_batch_timed.restype = C.c_int
 lib.arcs_sample_batch_timed.argtypes = [C.POINTER(SampleArgs), C.c_void_p, C.POINTER(C.c_float)]
 lib.arcs_argmax_workspace_bytes.restype = C.c_size_t
@@ -306,6 +322,33 @@ class HostContext:
         a.slots = 0 if row_off is None else len(row_off) - 1
         a.row_off, a.draft, a.draft_off, a.accepted, a.next = _hp(row_off), _hp(draft), _hp(draft_off), _hp(accepted), _hp(next_)
         _check(lib.arcs_argmax_batch_host(self._h, C.byref(a)), "arcs_argmax_batch_host")
+
+
+def merge_batch(cand_id, cand_val, n_cand, params, u, v_global, bias_off=None, bias_vals=None, want_cands=False, status=None):
+    """arcs_merge_batch: the global choice from the shards' gathered candidate lists.
+    cand_id / cand_val: [G, B, stride] int32 / float32; n_cand: [G, B] int32 (device tensors)."""
+    G, B, stride = cand_id.shape
+    dev = cand_id.device
+    out = {k: torch.empty(B, dtype=torch.int32, device=dev) for k in ("token", "n_cand", "n_kept", "flags")}
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out["status"] = status
+    a = MergeArgs()
+    a.G, a.B, a.cand_stride = G, B, stride
+    a.cand_id, a.cand_val, a.n_cand = cand_id.data_ptr(), cand_val.data_ptr(), n_cand.data_ptr()
+    a.params, a.u = params.data_ptr(), u.data_ptr()
+    a.bias_off, a.bias_vals = _ptr(bias_off), _ptr(bias_vals)
+    a.v_global = v_global
+    a.token, a.n_cand_out, a.n_kept, a.flags = (out[k].data_ptr() for k in ("token", "n_cand", "n_kept", "flags"))
+    if want_cands:
+        out["cand_id"] = torch.empty(B, KCAP, dtype=torch.int32, device=dev)
+        out["cand_val"] = torch.empty(B, KCAP, dtype=torch.float32, device=dev)
+        out["cand_pr"] = torch.empty(B, KCAP, dtype=torch.float32, device=dev)
+        a.out_id, a.out_val, a.out_pr = out["cand_id"].data_ptr(), out["cand_val"].data_ptr(), out["cand_pr"].data_ptr()
+    a.out_stride = KCAP
+    a.status = status.data_ptr()
+    _check(lib.arcs_merge_batch(C.byref(a), _stream(dev)), "arcs_merge_batch")
+    return out
 
 
 class SamplePlan:

@@ -118,6 +118,11 @@ static int sample_launch(const arcs_sample_args* g, void* stream, cudaEvent_t* e
   a.ws_items = static_cast<char*>(g->workspace);
   a.item_block = item_block_bytes(masked, slots);
   a.status = g->status;
+  a.merge_G = 0;
+  a.merge_stride = 0;
+  a.merge_id = nullptr;
+  a.merge_val = nullptr;
+  a.merge_n = nullptr;
   if (!g->workspace || g->workspace_bytes < arcs_sample_workspace_bytes(g->B, g->V, masked, max_list))
     return set_error(ARCS_ERR_WORKSPACE, "sample_batch: workspace too small");
   if ((reinterpret_cast<uintptr_t>(g->workspace) & 15u) != 0) return set_error(ARCS_ERR_WORKSPACE, "sample_batch: workspace must be 16-byte aligned");
@@ -168,4 +173,42 @@ extern "C" int arcs_sample_batch_timed(const arcs_sample_args* g, void* stream, 
     if (cudaEventElapsedTime(&ms3[i], ev[i], ev[i + 1]) != cudaSuccess) rc = set_error(ARCS_ERR_CUDA, "sample_batch_timed: elapsed time failed");
   for (auto& e : ev) cudaEventDestroy(e);
   return rc;
+}
+
+// ---- vocabulary shards: the global choice from the shards' gathered candidate lists
+extern "C" int arcs_merge_batch(const arcs_merge_args* g, void* stream) {
+  if (int inj = fault_injected()) return inj;
+  if (!g || g->G <= 0 || g->G > 64 || g->B <= 0 || g->B > kMaxRows || g->cand_stride <= 0 || !g->cand_id || !g->cand_val || !g->n_cand ||
+      !g->params || !g->u || !g->token || g->v_global <= 0 || g->v_global >= (int32_t)kIdMask)
+    return set_error(ARCS_ERR_ARG, "merge_batch: bad argument");
+  if (g->bias_off && !g->bias_vals) return set_error(ARCS_ERR_ARG, "merge_batch: bias offsets without the values");
+  if ((g->out_id || g->out_val || g->out_pr) && g->out_stride < ARCS_KCAP)
+    return set_error(ARCS_ERR_ARG, "merge_batch: out_stride must be at least ARCS_KCAP");
+  SampleDev a = {};
+  a.B = g->B;
+  a.V = g->v_global;
+  a.v_global = g->v_global;
+  a.nseg = 1;
+  a.params = g->params;
+  a.u = g->u;
+  a.bias_off = g->bias_off;
+  a.bias_vals = g->bias_vals;
+  a.max_bias = 1 << 30;
+  a.hash_slots = kGroup;
+  a.token = g->token;
+  a.n_cand = g->n_cand_out;
+  a.n_kept = g->n_kept;
+  a.flags = g->flags;
+  a.cand_id = g->out_id;
+  a.cand_val = g->out_val;
+  a.cand_pr = g->out_pr;
+  a.cand_stride = g->out_stride;
+  a.status = g->status;
+  a.merge_G = g->G;
+  a.merge_stride = g->cand_stride;
+  a.merge_id = g->cand_id;
+  a.merge_val = g->cand_val;
+  a.merge_n = g->n_cand;
+  finish_kernel<float, false, kFinishThreads><<<(unsigned)g->B, kFinishThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return check_launch("merge_batch");
 }

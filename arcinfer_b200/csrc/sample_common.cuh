@@ -58,6 +58,11 @@ struct SampleDev {
   char* ws_items;           // [B * nseg] blocks of item_block bytes
   int64_t item_block;
   int32_t* status;
+  // merge mode of the finish kernel (vocabulary shards): the candidates come from gathered per-shard lists
+  int32_t merge_G, merge_stride;
+  const int32_t* merge_id;   // [G][B][merge_stride] global ids, best first
+  const float* merge_val;    // [G][B][merge_stride] adjusted logits
+  const int32_t* merge_n;    // [G][B] entries per list
 };
 
 // ---- one item's block of the workspace

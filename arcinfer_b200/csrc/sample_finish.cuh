@@ -58,7 +58,14 @@ __global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (
   // below the largest threshold a segment's stream ended on can be among the k best: that
   // segment alone holds k above it.
   const RowCfg r = row_cfg<MASKED>(a, b);  // (its loads travel together with the headers')
-  for (int g = gt; g < a.nseg; g += G) {
+  const bool merging = a.merge_G > 0;
+  if (merging) {  // the banned-tail rule needs to know whether the row's bias list bans anything (tools/sampler.h:34)
+    bool any = false;
+    for (int i = gt; i < r.NB; i += G) any = any || a.bias_vals[r.q0 + i] <= -100.0f;
+    if (any) sm_red_or(&sh[S_BANS], 1u);
+    if (gt == 0) sh[S_NLIST] = a.merge_G * a.merge_stride;
+  }
+  for (int g = gt; g < a.nseg && !merging; g += G) {
     const ItemHdr* hd = item_ws(a, b * a.nseg + g).hdr;
     int n0 = __ldcg(&hd->n_pre);
     const int nt = __ldcg(&hd->n_tch);
@@ -258,13 +265,29 @@ __global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (
     }
   };
   TR(20);
-  for (int g = 0; g < a.nseg; ++g) {
-    const ItemWs w = item_ws(a, b * a.nseg + g);
-    take(w.pre, seg_n[0][g], w.candB, seg_n[1][g], false);
-    if (MASKED) take(nullptr, 0, w.candA, seg_n[2][g], true);
-    if (seg_n[3][g]) rescan(g);
+  if (!merging) {
+    for (int g = 0; g < a.nseg; ++g) {
+      const ItemWs w = item_ws(a, b * a.nseg + g);
+      take(w.pre, seg_n[0][g], w.candB, seg_n[1][g], false);
+      if (MASKED) take(nullptr, 0, w.candA, seg_n[2][g], true);
+      if (seg_n[3][g]) rescan(g);
+    }
+  } else {
+    // the shards' lists: each already holds that shard's k best under the same order
+    for (int g = 0; g < a.merge_G; ++g) {
+      const size_t row = (size_t)g * a.B + b;
+      const int n = min(__ldg(&a.merge_n[row]), a.merge_stride);
+      for (int i0 = 0; i0 < n; i0 += G) {
+        const int i = i0 + gt;
+        const bool p = i < n;
+        const float v = p ? __ldg(&a.merge_val[row * a.merge_stride + i]) : 0.0f;
+        const int32_t id = p ? __ldg(&a.merge_id[row * a.merge_stride + i]) : 0;
+        const uint32_t ky = key_of(v);
+        sel_push(selB, p && ky != 0u && comp_of(ky, id) > *selB.tau, ky, id, hot, a.status);
+        if (careful) after_push();
+      }
+    }
   }
-  TR(21);
   settle();
   group_sync<2, G>();
   TR(10);

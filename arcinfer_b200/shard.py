@@ -30,3 +30,22 @@ def gather_tokens(local_tokens, n_rows, world, all_gather):
     parts = [torch.empty_like(pad) for _ in range(world)]
     all_gather(parts, pad)
     return torch.cat([p[: hi - lo] for p, (lo, hi) in zip(parts, sizes)])
+
+
+def vocab_sharded_sample(local_logits, lo, v_global, params, u, all_gather, world, sample_batch, merge_batch, **lists):
+    """The vocabulary-sharded step on one rank: this rank's columns [lo, lo + local V) of every row
+    go through sample_batch under global ids, the per-row candidate lists of all ranks are gathered
+    (`all_gather(list_of_tensors, tensor)`: torch.distributed.all_gather over NCCL, or a stand-in),
+    and merge_batch takes the global choice. The one collective on the data path carries
+    B * (k * 8 + 4) bytes per rank."""
+    import torch
+
+    out = sample_batch(local_logits, params, u, id_base=lo, v_global=v_global, want_cands=True, **lists)
+    parts = {}
+    for name in ("cand_id", "cand_val", "n_cand"):
+        t = out[name].contiguous()
+        got = [torch.empty_like(t) for _ in range(world)]
+        all_gather(got, t)
+        parts[name] = torch.stack(got)
+    return merge_batch(parts["cand_id"], parts["cand_val"], parts["n_cand"], params, u, v_global,
+                       bias_off=lists.get("bias_off"), bias_vals=lists.get("bias_vals"), want_cands=True)

@@ -59,6 +59,32 @@ enum {
 const char* arcs_last_error(void); /* text of the calling thread's last failure */
 int arcs_version(void);
 
+/* Vocabulary shards (no counterpart in the reference, which has one device): every GPU runs
+ * arcs_sample_batch on its columns of all rows (`id_base`, `v_global`; lists are filtered by range)
+ * with candidate outputs, the lists are all-gathered (NCCL, by the caller), and this call takes the
+ * global k best of the G lists under the same order and finishes as the single-GPU path does. */
+typedef struct arcs_merge_args {
+  int32_t G, B, cand_stride;   /* shards, rows, stride of the gathered lists */
+  const int32_t* cand_id;      /* [G][B][cand_stride] global ids, best first (device) */
+  const float* cand_val;       /* [G][B][cand_stride] their adjusted logits */
+  const int32_t* n_cand;       /* [G][B] entries per list */
+  const arcs_row_params* params;
+  const double* u;
+  const int32_t* bias_off;     /* optional: only "does the row ban anything" is read from the bias list */
+  const float* bias_vals;
+  int32_t v_global;            /* whole vocabulary size */
+  int32_t* token;              /* outputs as in arcs_sample_args */
+  int32_t* n_cand_out;
+  int32_t* n_kept;
+  int32_t* flags;
+  int32_t* out_id;
+  float* out_val;
+  float* out_pr;
+  int32_t out_stride;
+  int32_t* status;
+} arcs_merge_args;
+int arcs_merge_batch(const arcs_merge_args* args, void* stream);
+
 /* ------------------------------------------------------------------------------------------
  * sample_batch: Sampler::adjusted + Sampler::sample for B rows in one launch
  * (tools/sampler.h:36-78, :147-176); with a mask, Sampler::sample_allowed (:82-144) where
