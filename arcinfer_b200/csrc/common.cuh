@@ -137,9 +137,7 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
   for (uint32_t it = 0; it < kWaitLimit; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-#ifndef ARCS_X_NOSLEEP
     if (it > 16) __nanosleep(it > 256 ? 256 : 32);  // (try_wait itself suspends the thread for a while)
-#endif
   }
   return false;
 }

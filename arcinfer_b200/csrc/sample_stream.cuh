@@ -42,6 +42,10 @@ constexpr int kRing = ARCS_RING;                           // tiles in the ring 
 constexpr int kSTile = 8192;                               // bytes per tile (512 chunks)
 constexpr int kPend = 2;                                   // chunks each lane of a scanner can set aside
 constexpr int kStash = kPend * 32;                         // ... per warp
+#ifndef ARCS_FLUSH_MIN
+#define ARCS_FLUSH_MIN 1
+#endif
+constexpr int kFlushMin = ARCS_FLUSH_MIN;                  // chunks pending before a warp examines them while it waits
 static_assert(kRing % kTeams == 0, "a team always meets its tiles in the same slots");
 
 // indices into the shared scalar arrays
@@ -223,7 +227,12 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
           ok = mbar_wait(&empty[slot], ((g / kRing) & 1u) ^ 1u);
         } else {  // (no sleeping: the other producer lanes of the warp would sleep too)
           ok = false;
-          for (uint32_t tries = 0; tries < kWaitLimit && !ok; ++tries) ok = mbar_try_wait(&empty[slot], ((g / kRing) & 1u) ^ 1u);
+          for (uint32_t tries = 0; tries < kWaitLimit && !ok; ++tries) {
+            ok = mbar_try_wait(&empty[slot], ((g / kRing) & 1u) ^ 1u);
+#ifdef ARCS_PROD_SLEEP
+            if (!ok) __nanosleep(ARCS_PROD_SLEEP);
+#endif
+          }
         }
         if (!ok) {
           abort_now();
@@ -303,11 +312,14 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
         const char* tile = ring + (size_t)slot * kSTile;
         // What is set aside is examined while the warp would only wait for its next tile: the time
         // the examination takes then holds nothing up.
-        if (__any_sync(0xFFFFFFFFu, have > 0)) {
-          int landed = 0;
-          if (lane == 0) landed = mbar_test_wait(&full[slot], (g / kRing) & 1u);
-          landed = __shfl_sync(0xFFFFFFFFu, landed, 0);
-          if (!landed) flush();
+        {
+          const int pending = __popc(__ballot_sync(0xFFFFFFFFu, have > 0)) + __popc(__ballot_sync(0xFFFFFFFFu, have > 1));
+          if (pending >= kFlushMin) {  // (fuller passes cost fewer instructions per chunk: the kernel is bound by issue)
+            int landed = 0;
+            if (lane == 0) landed = mbar_test_wait(&full[slot], (g / kRing) & 1u);
+            landed = __shfl_sync(0xFFFFFFFFu, landed, 0);
+            if (!landed) flush();
+          }
         }
         if (!mbar_wait_warp(&full[slot], (g / kRing) & 1u)) {
           abort_now();
@@ -336,7 +348,11 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
 #ifdef ARCS_X_NOSCAN
         for (int c0 = c_lo; c0 < 0; c0 += kU * 32) {
 #else
+#ifdef ARCS_X_NOSCAN
+        for (int c0 = c_lo; c0 < 0; c0 += kU * 32) {
+#else
         for (int c0 = c_lo; c0 < min(nchunk, c_lo + kMine); c0 += kU * 32) {
+#endif
 #endif
           uint4 q[kU];
 #pragma unroll

@@ -41,11 +41,14 @@ def vocab_sharded_sample(local_logits, lo, v_global, params, u, all_gather, worl
     import torch
 
     out = sample_batch(local_logits, params, u, id_base=lo, v_global=v_global, want_cands=True, **lists)
-    parts = {}
-    for name in ("cand_id", "cand_val", "n_cand"):
-        t = out[name].contiguous()
-        got = [torch.empty_like(t) for _ in range(world)]
-        all_gather(got, t)
-        parts[name] = torch.stack(got)
-    return merge_batch(parts["cand_id"], parts["cand_val"], parts["n_cand"], params, u, v_global,
+    # one message per rank: ids, values (bit patterns) and list lengths side by side
+    k = out["cand_id"].shape[1]
+    mine = torch.cat([out["cand_id"], out["cand_val"].view(torch.int32), out["n_cand"][:, None]], dim=1).contiguous()
+    got = [torch.empty_like(mine) for _ in range(world)]
+    all_gather(got, mine)
+    allp = torch.stack(got)
+    cand_id = allp[:, :, :k].contiguous()
+    cand_val = allp[:, :, k : 2 * k].contiguous().view(torch.float32)
+    n_cand = allp[:, :, 2 * k].contiguous()
+    return merge_batch(cand_id, cand_val, n_cand, params, u, v_global,
                        bias_off=lists.get("bias_off"), bias_vals=lists.get("bias_vals"), want_cands=True)

@@ -129,6 +129,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--rows", type=int, default=B_ROWS, help="rows per GPU (default: the measured workload)")
     ap.add_argument("--vocab", type=int, default=VOCAB)
+    ap.add_argument("--shard", default="rows", choices=["rows", "vocab"],
+                    help="how N GPUs split the work: rows (default, no collective) or vocabulary columns (one all-gather)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
@@ -198,6 +200,53 @@ def main():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    if args.shard == "vocab" and world > 1:
+        # ---- every rank holds its columns of ALL rows: strong scaling, one all-gather of candidate lists per step
+        from arcinfer_b200 import shard
+
+        lo, hi = shard.vocab_range(V, rank, world)
+        gen = torch.Generator(device=dev)
+        gen.manual_seed(synth.BASE_SEED + 5 + 1000 * rank)
+        local_logits = torch.empty(B, hi - lo, dtype=torch.bfloat16, device=dev)
+        for r0 in range(0, B, 128):
+            r1 = min(B, r0 + 128)
+            local_logits[r0:r1] = (torch.randn(r1 - r0, hi - lo, generator=gen, device=dev) * 3.0).to(torch.bfloat16)
+        gen.manual_seed(synth.BASE_SEED + 6)  # lists and draws are the same on every rank
+        hist = torch.randint(0, V, (B, H), generator=gen, device=dev, dtype=torch.int32)
+        hist_off = (torch.arange(B + 1, device=dev, dtype=torch.int32) * H).contiguous()
+        u = torch.rand(B, generator=gen, device=dev, dtype=torch.float64)
+        p_dev = ab.capi.params_to_device(params, dev)
+        lists = dict(hist_off=hist_off, hist_ids=hist.reshape(-1), max_hist=H)
+
+        def step():
+            return shard.vocab_sharded_sample(local_logits, lo, V, p_dev, u, dist.all_gather, world, ab.sample_batch, ab.merge_batch, **lists)
+
+        for _ in range(args.warmup):
+            out = step()
+        barrier()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        for _ in range(args.steps):
+            out = step()
+        ev1.record()
+        barrier()
+        t = torch.tensor([ev0.elapsed_time(ev1)], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_step = float(t.item()) / args.steps
+        toks = [torch.empty_like(out["token"]) for _ in range(world)]
+        dist.all_gather(toks, out["token"])
+        same = all(bool((x == toks[0]).all()) for x in toks)
+        if rank == 0:
+            config["partition"] = f"vocabulary columns x{world}"
+            config["rows_per_gpu"] = B
+            print(json.dumps({"metric": METRIC, "value": B / (ms_step * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                              "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+                              "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": config,
+                              "gpu_launches": 4 * args.steps, "collective_bytes_per_rank_per_step": B * (ab.capi.KCAP * 8 + 4),
+                              "all_ranks_agree": same}))
+        dist.destroy_process_group()
+        return
 
     # ---- synthetic inputs, generated on the device from a per-rank seed
     gen = torch.Generator(device=dev)
