@@ -95,18 +95,19 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
   bool any0 = false, any1 = false;
   if (!MASKED) {
     // two maxima per thread, each over every other one of the thread's chunks of the prefix,
-    // fetched four at a time
+    // fetched eight at a time
     constexpr int kPer = kBootBytes / 16 / kGroup;  // chunks of the prefix per thread
 #pragma unroll 1
-    for (int x0 = 0; x0 < kPer; x0 += 4) {
-      uint4 q[4];
+    constexpr int kBatch = kPer < 8 ? kPer : 8;  // chunks in flight per thread
+    for (int x0 = 0; x0 < kPer; x0 += kBatch) {
+      uint4 q[kBatch];
 #pragma unroll
-      for (int x = 0; x < 4; ++x) {
+      for (int x = 0; x < kBatch; ++x) {
         const int ci = gt + (x0 + x) * kGroup;
         q[x] = ci < nchunk ? ldg128_stream(it.p.body + (size_t)ci * 16) : make_uint4(0, 0, 0, 0);
       }
 #pragma unroll
-      for (int x = 0; x < 4; ++x) {
+      for (int x = 0; x < kBatch; ++x) {
         const int ci = gt + (x0 + x) * kGroup;
         if (ci < nchunk) {
           const float m = Elem<T>::chunk_max(q[x]);
