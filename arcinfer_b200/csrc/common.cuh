@@ -144,17 +144,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
 // The same wait for a whole warp: every lane tries (one instruction for the warp; the hardware
 // suspends the warp inside the try for a while, so that few tries are issued).
 __device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity) {
-#ifdef ARCS_X_LANE0_WAIT
-  int ok = 1;
-  if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity);
-  ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-  if (ok) mbar_try_wait(bar, parity);
-  return ok != 0;
-#else
   for (uint32_t it = 0; it < kWaitLimit; ++it)
     if (mbar_try_wait(bar, parity)) return true;
   return false;
-#endif
 }
 // global -> shared bulk copy of `bytes` (multiple of 16; both addresses 16-byte aligned),
 // completion counted on `bar`. No multicast: the destination is this CTA's own shared memory.

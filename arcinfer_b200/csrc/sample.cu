@@ -37,23 +37,6 @@ static int table_slots(int max_list) {
   return slots;
 }
 
-#ifdef ARCS_TRACE
-extern "C" int arcs_debug_trace(long long* out64) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out64, g_trace, sizeof(long long) * 64);
-  return 0;
-}
-extern "C" int arcs_debug_clear() {
-  static long long z[128];
-  cudaMemcpyToSymbol(g_trace2, z, sizeof(z));
-  return 0;
-}
-extern "C" int arcs_debug_trace2(long long* out128) {
-  cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(out128, g_trace2, sizeof(long long) * 128);
-  return 0;
-}
-#endif
 
 extern "C" size_t arcs_sample_workspace_bytes(int32_t B, int32_t V, int32_t masked, int32_t max_list) {
   if (B <= 0 || V <= 0 || max_list < 0) return 0;

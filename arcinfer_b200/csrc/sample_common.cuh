@@ -125,15 +125,6 @@ __device__ __forceinline__ bool bloom_has(LOAD load, int bloom_words, int32_t c)
   return ((load(b1 >> 5) >> (b1 & 31)) & (load(b2 >> 5) >> (b2 & 31)) & 1u) != 0u;
 }
 
-#ifdef ARCS_TRACE
-__device__ long long g_trace[64];
-#define TR(i) do { if (blockIdx.x == 300 && threadIdx.x == 0) g_trace[i] = clock64(); } while (0)
-__device__ long long g_trace2[8 * 16];
-#define TS(ev, j) do { if (blockIdx.x == 0 && (j) < 16) g_trace2[(ev) * 16 + (j)] = clock64(); } while (0)
-#else
-#define TR(i)
-#define TS(ev, j)
-#endif
 __device__ __forceinline__ uint32_t hash_of(int32_t id, int shift) { return ((uint32_t)id * 2654435761u) >> shift; }
 
 // what every kernel derives from an item number

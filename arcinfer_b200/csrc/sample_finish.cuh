@@ -38,7 +38,6 @@ __global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (
   const int gt = threadIdx.x;
   const int b = blockIdx.x;
   const int32_t Vg = a.v_global > 0 ? a.v_global : a.V;
-  TR(8);
   if (gt == 0) {
     sh[S_CNT_B] = 0;
     sh[S_CNT_A] = 0;
@@ -87,10 +86,6 @@ __global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (
     if (MASKED) sm_red_max_u64(&s64[L_TAU_A], __ldcg(&hd->tauA));
   }
   __syncthreads();
-#ifdef ARCS_TRACE
-  if (r.H > 100000000) return;
-#endif
-  TR(9);
   const bool bans = sh[S_BANS] != 0;
   // barriers between the rounds of pushes are needed only when a buffer or the stage could overflow
   const bool careful = sh[S_OVER] != 0 || sh[S_NLIST] > kCapB || (MASKED && sh[S_NLISTA] > kCapA) || sh[S_NPRE] > kStage;
@@ -125,7 +120,6 @@ __global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (
     if (nF == 0) return;
     for (int f = gt; f < nF; f += G) fl_cnt[f] = 0u;
     group_sync<2, G>();
-    TR(22);
     const int32_t w0 = window_start(r);
     for (int i = gt; i < r.NB; i += G) {
       const int32_t t = a.bias_ids[r.q0 + i];
@@ -143,7 +137,6 @@ __global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (
       }
     }
     group_sync<2, G>();
-    TR(23);
     for (int f0 = 0; f0 < nF; f0 += G) {
       const int f = f0 + gt;
       bool p = f < nF;
@@ -173,7 +166,6 @@ __global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (
       if (MASKED) sel_push(selA, p && cm > *selA.tau, ky, id, hot, a.status);
       after_push();
     }
-    TR(24);
     if (gt == 0) sh[S_NFLAG] = 0;
     group_sync<2, G>();
   };
@@ -264,7 +256,6 @@ __global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (
       }
     }
   };
-  TR(20);
   if (!merging) {
     for (int g = 0; g < a.nseg; ++g) {
       const ItemWs w = item_ws(a, b * a.nseg + g);
@@ -290,7 +281,6 @@ __global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (
   }
   settle();
   group_sync<2, G>();
-  TR(10);
   if (MASKED) sel_prune<2, G>(selA, selA.k, psF, gt);
 
   // ---- candidates best first. A short buffer is ranked by counting, which selects the k best
@@ -316,7 +306,6 @@ __global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (
     s64[L_LOW] = 0xFFFFFFFFFFFFFFFFull;   // smallest composite of the head
   }
   group_sync<2, G>();
-  TR(11);
   // ---- tools/sampler.h:54-77 (or :105-143)
   int flags = 0, nc = nB;
   if (MASKED) {
@@ -362,7 +351,6 @@ __global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (
     for (int i = gt; i + 1 < nc; i += G) tie = tie || sv[i] == sv[i + 1];
     if (tie) sm_red_or(&sh[S_FLAGS], (uint32_t)ARCS_FLAG_TIE_TOPK);
   }
-  TR(12);
   const bool draw = (!r.greedy && nc > 1) || (!MASKED && !r.greedy && nc == 1);
   if (draw) {
     const float mx = sv[0];
@@ -382,7 +370,6 @@ __global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (
     for (int i = gt; i < nc; i += G) spr[i] = __ddiv_rn(spr[i], z);  // :64, the same quotients in any order
   }
   group_sync<2, G>();
-  TR(13);
   // :65-72. The running sums are a chain of roundings in candidate order (one thread); where the
   // chain is cut is then found by all threads.
   double* cum = reinterpret_cast<double*>(bkey);  // (the buffer is no longer needed: 256 doubles fit)
@@ -433,7 +420,6 @@ __global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (
     if (a.n_kept) a.n_kept[b] = n;
   }
   group_sync<2, G>();
-  TR(14);
   if (gt == 0 && a.flags) a.flags[b] = sh[S_FLAGS];
   for (int i = gt; i < a.cand_stride && (a.cand_id || a.cand_val || a.cand_pr); i += G) {
     const size_t o = (size_t)b * a.cand_stride + i;

@@ -72,13 +72,8 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
   const int item = blockIdx.x;
   const int32_t Vg = a.v_global > 0 ? a.v_global : a.V;
   pdl_trigger();  // (the stream kernel may move in as CTAs of this one retire; it waits before it reads their output)
-  TR(0);
   const Item<T> it = item_of<T>(a, item);
   const RowCfg r = row_cfg<MASKED>(a, it.b);
-#ifdef ARCS_TRACE
-  if (r.H > 100000000) return;  // (wait for the settings, so that the trace separates the phases)
-#endif
-  TR(1);
   const ItemWs w = item_ws(a, item);
   const uint32_t* mrow = MASKED ? a.mask + (size_t)(a.mask_row ? a.mask_row[it.b] : it.b) * a.mask_stride : nullptr;
 
@@ -97,8 +92,8 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
     // two maxima per thread, each over every other one of the thread's chunks of the prefix,
     // fetched eight at a time
     constexpr int kPer = kBootBytes / 16 / kGroup;  // chunks of the prefix per thread
-#pragma unroll 1
     constexpr int kBatch = kPer < 8 ? kPer : 8;  // chunks in flight per thread
+#pragma unroll 1
     for (int x0 = 0; x0 < kPer; x0 += kBatch) {
       uint4 q[kBatch];
 #pragma unroll
@@ -122,7 +117,6 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
       }
     }
   }
-  TR(2);
 
   bool bans = false;  // Sampler::bans_: any bias entry <= -100, in range or not (tools/sampler.h:34)
   for (int i = gt; i < r.NB && r.lists_ok; i += kGroup) bans = bans || a.bias_vals[r.q0 + i] <= -100.0f;
@@ -288,7 +282,6 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
   }
   if (extra) sm_red_add(n_extra, (uint32_t)extra);
   __syncthreads();
-  TR(3);
   // ---- the item's filter goes out
   if (r.touch != kTouchNone)
     for (int i = gt; i < bw; i += kGroup) w.bloom[i] = bl[i];
@@ -305,7 +298,6 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
     supply(valid, valid ? Elem<T>::load(it.row + c) : 0.0f, c, flagged);
   }
   __syncthreads();
-  TR(4);
 
   // first threshold: the k-th largest of 256 (or, constrained, 1024) maxima over disjoint pieces
   // of the prefix is a lower bound of the k-th best element; listed columns inside the prefix
@@ -332,7 +324,6 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
       tau0A = m64[1];
     }
   }
-  TR(5);
   // ---- the item's header
   if (gt == 0) {
     ItemHdr h;
@@ -352,7 +343,6 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
     for (int i = 0; i < 7; ++i) h.pad[i] = 0;
     *w.hdr = h;
   }
-  TR(6);
 }
 
 }  // namespace arcs

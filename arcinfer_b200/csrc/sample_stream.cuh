@@ -194,7 +194,6 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
   for (int i = tid; i < 6 * 256; i += kThreadsS) xh[i] = 0u;
   __syncthreads();  // the only CTA-wide barrier
   pdl_trigger();    // (the finish kernel's CTAs may take their places; they wait for this kernel before they read)
-  if (tid == 0) TS(0, 0);
 
   auto abort_now = [&]() {
     vsh[S_ABORT] = 1;
@@ -229,9 +228,6 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
           ok = false;
           for (uint32_t tries = 0; tries < kWaitLimit && !ok; ++tries) {
             ok = mbar_try_wait(&empty[slot], ((g / kRing) & 1u) ^ 1u);
-#ifdef ARCS_PROD_SLEEP
-            if (!ok) __nanosleep(ARCS_PROD_SLEEP);
-#endif
           }
         }
         if (!ok) {
@@ -269,7 +265,6 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
         __threadfence_block();
       }
       if (vsh[S_ABORT]) break;
-      if (tid == 0) TS(2, j);
       mbar_try_wait(&tab_full[st], (uint32_t)(j / 3) & 1u);  // (complete: every lane observes the copied table through it)
       const ItemHdr* hd = tab_hdr(st);
       uint4* stq = stash_q + warp * kStash + lane;      // chunks this lane has set aside: stq[s * 32], s < have
@@ -345,15 +340,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
         constexpr int kU = kMine / 32 < ARCS_KU ? kMine / 32 : ARCS_KU;   // chunks per lane per step
         const int c_lo = (warp % kShare) * kMine;
         refresh();  // (once per visit: the thresholds move slowly against the few hundred cycles a visit takes)
-#ifdef ARCS_X_NOSCAN
-        for (int c0 = c_lo; c0 < 0; c0 += kU * 32) {
-#else
-#ifdef ARCS_X_NOSCAN
-        for (int c0 = c_lo; c0 < 0; c0 += kU * 32) {
-#else
         for (int c0 = c_lo; c0 < min(nchunk, c_lo + kMine); c0 += kU * 32) {
-#endif
-#endif
           uint4 q[kU];
 #pragma unroll
           for (int u = 0; u < kU; ++u) q[u] = lds128(tile + (c0 + u * 32 + lane) * 16);  // (inside the slot even past a short tile's end)
@@ -407,7 +394,6 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
       if (vsh[S_ABORT]) break;
       if (__any_sync(0xFFFFFFFFu, have > 0)) flush();  // what is still set aside
       __syncwarp();
-      if (tid == 0) TS(3, j);
       // this warp has listed everything it found in the item; the warp that says so last hands
       // the item over: list lengths and last thresholds to the item's header, the set of state
       // cleared for the item three on
@@ -444,7 +430,6 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
         __threadfence_block();
         if (lane == 0) {
           vsh[S_STREAMED] = j + 1;
-          TS(4, j);
         }
       }
       G0 += (uint32_t)T_;
@@ -482,7 +467,6 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
             s64[L_TAU_A + st] = hd->tau0A;
             __threadfence_block();
             vsh[S_PREPARED] = prepped + 1;
-            TS(1, prepped);
           }
           ++prepped;
           idle = 0;
