@@ -42,10 +42,10 @@ constexpr int kRing = ARCS_RING;                           // tiles in the ring 
 constexpr int kSTile = 8192;                               // bytes per tile (512 chunks)
 constexpr int kPend = 2;                                   // chunks each lane of a scanner can set aside
 constexpr int kStash = kPend * 32;                         // ... per warp
-#ifndef ARCS_FLUSH_MIN
-#define ARCS_FLUSH_MIN 1
+#ifndef ARCS_FLUSH_EVERY
+#define ARCS_FLUSH_EVERY 2
 #endif
-constexpr int kFlushMin = ARCS_FLUSH_MIN;                  // chunks pending before a warp examines them while it waits
+constexpr int kFlushEvery = ARCS_FLUSH_EVERY;              // visits after which a warp examines what it has set aside even if its next tile is there
 static_assert(kRing % kTeams == 0, "a team always meets its tiles in the same slots");
 
 // indices into the shared scalar arrays
@@ -269,7 +269,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
       const ItemHdr* hd = tab_hdr(st);
       uint4* stq = stash_q + warp * kStash + lane;      // chunks this lane has set aside: stq[s * 32], s < have
       int32_t* stc = stash_c + warp * kStash + lane;
-      int have = 0;
+      int have = 0, since = 0;
       ScanCtx ctx;
       ctx.bloom = tab_bloom(st);
       ctx.bw = bloom_words_of(a.hash_slots);
@@ -307,13 +307,19 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
         const char* tile = ring + (size_t)slot * kSTile;
         // What is set aside is examined while the warp would only wait for its next tile: the time
         // the examination takes then holds nothing up.
-        {
-          const int pending = __popc(__ballot_sync(0xFFFFFFFFu, have > 0)) + __popc(__ballot_sync(0xFFFFFFFFu, have > 1));
-          if (pending >= kFlushMin) {  // (fuller passes cost fewer instructions per chunk: the kernel is bound by issue)
+        // What is set aside is examined while the warp would only wait for its next tile (the time
+        // the examination takes then holds nothing up), and in any case every few visits: the
+        // thresholds rise only from what has been examined.
+        if (__any_sync(0xFFFFFFFFu, have > 0)) {
+          bool now = ++since >= kFlushEvery;
+          if (!now) {
             int landed = 0;
             if (lane == 0) landed = mbar_test_wait(&full[slot], (g / kRing) & 1u);
-            landed = __shfl_sync(0xFFFFFFFFu, landed, 0);
-            if (!landed) flush();
+            now = __shfl_sync(0xFFFFFFFFu, landed, 0) == 0;
+          }
+          if (now) {
+            flush();
+            since = 0;
           }
         }
         if (!mbar_wait_warp(&full[slot], (g / kRing) & 1u)) {
