@@ -13,10 +13,12 @@ constexpr int kSmCount = 148;  // B200
 constexpr int kMaxSeg = 64;
 
 // How a [rows][V] problem is cut into CTAs: each row is split into nseg segments of seg_len
-// elements (a multiple of 2048, at least 8192) so that about four CTAs per SM exist even when
-// there are few rows. The same function sizes the workspaces, so it depends on (rows, V) only.
-inline void plan_segments(int rows, int V, int* nseg, int* seg_len) {
-  const int target = kSmCount * 4;
+// elements (a multiple of 2048, at least 8192) so that about per_sm work items per SM exist even
+// when there are few rows (four for the argmax grid; one for the persistent stream kernel of the
+// sampler, whose finishing step pays for every segment it has to merge). The same function sizes
+// the workspaces, so it depends on (rows, V) only.
+inline void plan_segments(int rows, int V, int* nseg, int* seg_len, int per_sm = 4) {
+  const int target = kSmCount * per_sm;
   int want = (target + rows - 1) / rows;
   if (want < 1) want = 1;
   if (want > kMaxSeg) want = kMaxSeg;

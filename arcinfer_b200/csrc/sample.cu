@@ -26,6 +26,10 @@ static cudaError_t launch_dependent(K kernel, unsigned grid, unsigned block, siz
 }
 
 constexpr int kMaxRows = 65536;
+#ifndef ARCS_ITEMS_PER_SM
+#define ARCS_ITEMS_PER_SM 1
+#endif
+constexpr int kItemsPerSm = ARCS_ITEMS_PER_SM;  // work items per SM that few rows are cut into
 #ifndef ARCS_FIN
 #define ARCS_FIN 128
 #endif
@@ -41,7 +45,7 @@ static int table_slots(int max_list) {
 extern "C" size_t arcs_sample_workspace_bytes(int32_t B, int32_t V, int32_t masked, int32_t max_list) {
   if (B <= 0 || V <= 0 || max_list < 0) return 0;
   int nseg, seg_len;
-  plan_segments(B, V, &nseg, &seg_len);
+  plan_segments(B, V, &nseg, &seg_len, kItemsPerSm);
   return (size_t)B * nseg * (size_t)item_block_bytes(masked != 0, table_slots(max_list));
 }
 
@@ -70,7 +74,7 @@ static int sample_launch(const arcs_sample_args* g, void* stream, cudaEvent_t* e
   a.row_stride = g->row_stride;
   a.B = g->B;
   a.V = g->V;
-  plan_segments(g->B, g->V, &a.nseg, &a.seg_len);
+  plan_segments(g->B, g->V, &a.nseg, &a.seg_len, kItemsPerSm);
   a.params = g->params;
   a.hist_off = g->hist_off;
   a.hist_ids = g->hist_ids;

@@ -10,7 +10,7 @@
 
 namespace arcs {
 
-constexpr int kStage = 512;    // flagged entries settled together
+constexpr int kStage = 1024;   // flagged entries settled together
 constexpr int kSortCap = 160;  // a longer buffer is cut to the k best by the radix select before it is ranked by counting
 
 template <typename T, bool MASKED, int G>
@@ -90,8 +90,9 @@ __global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (
   // barriers between the rounds of pushes are needed only when a buffer or the stage could overflow
   const bool careful = sh[S_OVER] != 0 || sh[S_NLIST] > kCapB || (MASKED && sh[S_NLISTA] > kCapA) || sh[S_NPRE] > kStage;
   const PruneScratch psF{hist, tk, ti, misc, &s64[L_PRUNE_MIN]};
-  const Sel selB{bkey, bid, &sh[S_CNT_B], &s64[L_TAU_B], r.kB, kCapB - G, kCapB};  // (pruned only when the buffer is nearly full)
-  const Sel selA{akey, aid, &sh[S_CNT_A], &s64[L_TAU_A], ARCS_HEAD, 1024, kCapA};
+  // (a buffer is pruned only when it is nearly full: looked at after every four rounds of G pushes)
+  const Sel selB{bkey, bid, &sh[S_CNT_B], &s64[L_TAU_B], r.kB, kCapB - 4 * G, kCapB};
+  const Sel selA{akey, aid, &sh[S_CNT_A], &s64[L_TAU_A], ARCS_HEAD, kCapA - 4 * G, kCapA};
 
   bool hot = false;
   // called by the whole group after a barrier behind which nobody pushes
@@ -206,9 +207,9 @@ __global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (
             fl_id[pos] = (int32_t)(y & (kIdMask | kOkB));
           }
         }
-        if (careful) {
+        if (careful && ((x & 3) == 3 || i0 + (x + 1) * G >= n)) {
           after_push();
-          if (sh[S_NFLAG] > kStage - G) settle();
+          if (sh[S_NFLAG] > kStage - 4 * G) settle();
         }
       }
     }

@@ -17,7 +17,7 @@ namespace arcs {
 constexpr int kBootKeys = 1024;  // most maxima the first threshold is read off (constrained rows; 256 otherwise)
 
 static size_t prep_smem_bytes(int hash_slots) {
-  return 16 + (size_t)hash_slots * 8 + (size_t)kBootKeys * 4 + (size_t)bloom_words_of(hash_slots) * 4 + 16 * 4;
+  return 16 + (size_t)hash_slots * 8 + 2 * (size_t)kBootKeys * 4 + (size_t)bloom_words_of(hash_slots) * 4 + 16 * 4;
 }
 
 // A lower bound of the kth largest (1-based) of 32 * PER keys, found by ONE warp with a search
@@ -62,7 +62,8 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
   uint32_t* hk = reinterpret_cast<uint32_t*>(m64 + 2);                         // [hash_slots] token columns (table mode)
   uint32_t* hi_ = hk + a.hash_slots;                                           // [hash_slots] what applies to them
   uint32_t* ptk = hi_ + a.hash_slots;                                          // [kBootKeys] maxima over pieces of the prefix
-  uint32_t* bl = ptk + kBootKeys;                                              // [bw] the item's filter
+  uint32_t* ptk2 = ptk + kBootKeys;                                            // [kBootKeys] ... over their allowed elements only
+  uint32_t* bl = ptk2 + kBootKeys;                                             // [bw] the item's filter
   int* pmisc = reinterpret_cast<int*>(bl + bw);
   int* n_pre = pmisc + 0;
   int* n_extra = pmisc + 1;
@@ -314,14 +315,44 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
       tau0B = m64[1];
     }
   } else {
-    // constrained rows rank the whole vocabulary's best 512: k-th largest of up to 1024 chunk maxima
-    if (kth <= nchunk && nchunk <= kBootKeys) {
-      for (int ci = gt; ci < kBootKeys; ci += kGroup)
-        ptk[ci] = ci < nchunk ? key_of(Elem<T>::chunk_max(ldg128_stream(it.p.body + (size_t)ci * 16))) : 0u;
+    // constrained rows rank the whole vocabulary's best 512: k-th largest of up to 1024 chunk
+    // maxima; and the selection proper gets its first threshold from the maxima over the allowed
+    // elements of the same chunks (without one, every allowed token of a dense mask would be listed)
+    if (nchunk <= kBootKeys) {
+      for (int ci = gt; ci < kBootKeys; ci += kGroup) {
+        uint32_t kA = 0u, kB = 0u;
+        if (ci < nchunk) {
+          const uint4 q = ldg128_stream(it.p.body + (size_t)ci * 16);
+          kA = key_of(Elem<T>::chunk_max(q));
+          const int32_t gid = it.p.body_first + ci * E + a.id_base;
+          uint32_t bits = __ldg(&mrow[gid >> 5]) >> (gid & 31);
+          if ((gid & 31) + E > 32) bits |= __ldg(&mrow[(gid >> 5) + 1]) << (32 - (gid & 31));
+          float mB = -INFINITY;
+          bool anyB = false;
+#pragma unroll
+          for (int e = 0; e < E; ++e)
+            if ((bits >> e) & 1u) {
+              const float v = Elem<T>::get(q, e);
+              if (!(v != v)) {  // (a NaN is never selected)
+                mB = fmaxf(mB, v);
+                anyB = true;
+              }
+            }
+          if (anyB) kB = key_of(mB);
+        }
+        ptk[ci] = kA;
+        ptk2[ci] = kB;
+      }
       __syncthreads();
-      if (gt < 32) m64[1] = (unsigned long long)warp_kth16<kBootKeys / 32>(ptk, kth) << 32;  // keeps ties with it
+      const int kthB = r.kB + *n_extra;
+      if (gt < 32) {
+        if (kth <= nchunk) m64[1] = (unsigned long long)warp_kth16<kBootKeys / 32>(ptk, kth) << 32;  // keeps ties with it
+      } else if (gt < 64) {
+        if (kthB <= nchunk) m64[0] = (unsigned long long)warp_kth16<kBootKeys / 32>(ptk2, kthB) << 32;
+      }
       __syncthreads();
-      tau0A = m64[1];
+      if (kth <= nchunk) tau0A = m64[1];
+      if (kthB <= nchunk) tau0B = m64[0];
     }
   }
   // ---- the item's header
