@@ -1,16 +1,15 @@
 // Exact top-k selection in shared memory over 64-bit (key, ~id) composites: a candidate
-// buffer with a rising threshold, pruned by an 8-bit radix select. Two forms: one run by a
-// single warp on a buffer only that warp touches, one run by a helper group of warps that
-// synchronises on a named barrier (the other warps of the CTA keep streaming meanwhile).
+// buffer with a rising threshold, pruned by an 8-bit radix select run by the whole CTA
+// (synchronised on a named barrier), and the coarse histogram binning the stream kernel uses.
 #pragma once
 #include "common.cuh"
 
 namespace arcs {
 
 constexpr int kTmpCap = ARCS_HEAD;  // most entries a prune keeps (the constrained head select keeps 512)
-constexpr int kGroup = 128;         // threads of each helper group (one prepares items, one finishes them)
+constexpr int kGroup = 128;         // threads of the small per-item / per-row CTAs (prepare and finish kernels)
 
-// named-barrier synchronisation of one helper group (BAR: barrier number, kGroup threads)
+// named-barrier synchronisation of G threads (BAR: barrier number)
 template <int BAR, int G = kGroup>
 __device__ __forceinline__ void group_sync() { asm volatile("bar.sync %0, %1;" ::"n"(BAR), "n"(G) : "memory"); }
 template <int BAR, int G = kGroup>
@@ -109,8 +108,8 @@ __device__ __forceinline__ void find_bin(const uint32_t* h, int krem, int& digit
   exact = __shfl_sync(0xFFFFFFFFu, (int)ex, src) != 0;
 }
 
-// Keep exactly the k best entries of the buffer. Called by all kGroup threads of the
-// finishing group (gt = thread index inside the group) with the buffer quiescent. Radix
+// Keep exactly the k best entries of the buffer. Called by all G threads of the CTA (gt = thread
+// index) with the buffer quiescent. Radix
 // select, most significant byte first, over the composite (key << 32 | ~id): composites are
 // unique, so the k-th is found exactly, ties included.
 template <int BAR, int G = kGroup>
@@ -178,160 +177,11 @@ __device__ __noinline__ void sel_prune(const Sel& s, int k, const PruneScratch& 
 }
 
 
-// The kth largest (1-based) of the n keys in keys[] (n a multiple of kGroup, at most 8 * kGroup),
-// found by the whole group with a 4-pass radix select on the 32-bit keys. Every thread returns
-// the same value.
-template <int BAR>
-__device__ __noinline__ uint32_t group_kth_key(const uint32_t* keys, int n, int kth, const PruneScratch& ps, int gt) {
-  uint32_t prefix = 0, mask = 0;
-  int krem = kth;
-  for (int pass = 0; pass < 4; ++pass) {
-    const int shift = 24 - 8 * pass;
-    for (int i = gt; i < 256; i += kGroup) ps.hist[i] = 0;
-    group_sync<BAR>();
-    for (int i = gt; i < n; i += kGroup) {
-      const uint32_t my = keys[i];
-      if ((my & mask) == prefix) sm_red_add(&ps.hist[(my >> shift) & 255u], 1u);
-    }
-    group_sync<BAR>();
-    if (gt < 32) {
-      int d, kr;
-      bool ex;
-      find_bin(ps.hist, krem, d, kr, ex);
-      if (gt == 0) {
-        ps.misc[0] = d;
-        ps.misc[1] = kr;
-      }
-    }
-    group_sync<BAR>();
-    prefix |= (uint32_t)ps.misc[0] << shift;
-    mask |= 0xFFu << shift;
-    krem = ps.misc[1];
-  }
-  group_sync<BAR>();
-  return prefix;
-}
-
-// The same selection run by ONE warp on a buffer only that warp touches (the examiner warp
-// while a row streams). n: entries in the buffer; returns the new count and publishes *s.tau.
-// hist: 256 words, tk / ti: kTmpCap entries, all private to the calling warp.
-__device__ __noinline__ int sel_prune_warp(const Sel& s, int n, int k, uint32_t* hist, uint32_t* tk, int32_t* ti) {
-  const int lane = threadIdx.x & 31;
-  if (n <= k) return n;
-  uint64_t prefix = 0, mask = 0;
-  int krem = k;
-  for (int pass = 0; pass < 8; ++pass) {
-    const int shift = 56 - 8 * pass;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) hist[j * 32 + lane] = 0;
-    __syncwarp();
-    for (int i = lane; i < n; i += 32) {
-      const uint64_t c = comp_of(s.key[i], s.id[i]);
-      if ((c & mask) == prefix) sm_red_add(&hist[(uint32_t)(c >> shift) & 255u], 1u);
-    }
-    __syncwarp();
-    int d, kr;
-    bool ex;
-    find_bin(hist, krem, d, kr, ex);
-    krem = kr;
-    prefix |= (uint64_t)d << shift;
-    mask |= 0xFFull << shift;
-    __syncwarp();
-    if (ex) break;
-  }
-  int out = 0;
-  uint64_t cmin = 0xFFFFFFFFFFFFFFFFull;
-  for (int i0 = 0; i0 < n; i0 += 32) {
-    const int i = i0 + lane;
-    uint32_t ky = 0;
-    int32_t id = 0;
-    bool keep = false;
-    if (i < n) {
-      ky = s.key[i];
-      id = s.id[i];
-      const uint64_t c = comp_of(ky, id);
-      keep = (c & mask) >= prefix;
-      if (keep && c < cmin) cmin = c;
-    }
-    const unsigned b = __ballot_sync(0xFFFFFFFFu, keep);
-    const int pos = out + __popc(b & ((1u << lane) - 1u));
-    if (keep && pos < kTmpCap) {
-      tk[pos] = ky;
-      ti[pos] = id;
-    }
-    out += __popc(b);
-  }
-  out = min(out, kTmpCap);
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    const uint64_t w = __shfl_xor_sync(0xFFFFFFFFu, cmin, o);
-    cmin = w < cmin ? w : cmin;
-  }
-  __syncwarp();
-  for (int i = lane; i < out; i += 32) {
-    s.key[i] = tk[i];
-    s.id[i] = ti[i];
-  }
-  if (lane == 0) sm_red_max_u64(s.tau, cmin - 1ull);  // exclusive threshold; never lowered (another warp raises it too)
-  __syncwarp();
-  return out;
-}
-
-
-// Bin of a key in the coarse histogram an owner warp keeps beside its buffer: the key's upper
-// 16 bits (bf16 resolution) relative to `base`, the last bin taking everything above.
+// Bin of a key in an item's coarse histogram: the key's upper 16 bits (bf16 resolution) relative
+// to `base`, the last bin taking everything above.
 __device__ __forceinline__ uint32_t coarse_bin(uint32_t key, uint32_t base) {
   const uint32_t b = (key >> 16) - base;
   return b < 255u ? b : 255u;
-}
-
-// Cheap threshold raise for a buffer one warp owns. hist[256] counts the buffer's entries by
-// coarse_bin. The bin holding the k-th best entry is found, its lower edge becomes the
-// threshold (so every entry of that bin stays: at least k remain) and the entries below are
-// dropped in place. Returns the new count; n > k on entry.
-__device__ __forceinline__ int sel_raise_warp(const Sel& s, int n, int k, uint32_t* hist, uint32_t base) {
-  const int lane = threadIdx.x & 31;
-  int d, kr;
-  bool ex;
-  find_bin(hist, k, d, kr, ex);
-  if (d <= 0) return n;  // the k-th best lies in the lowest bin: nothing can be dropped this way
-  const uint64_t tc = (uint64_t)((base + (uint32_t)d) << 16) << 32;  // comp > tc  <=>  key >= edge of bin d
-  int out = 0;
-  for (int i0 = 0; i0 < n; i0 += 32) {
-    const int i = i0 + lane;
-    uint32_t ky = 0;
-    int32_t id = 0;
-    bool keep = false;
-    if (i < n) {
-      ky = s.key[i];
-      id = s.id[i];
-      keep = comp_of(ky, id) > tc;
-    }
-    const unsigned b = __ballot_sync(0xFFFFFFFFu, keep);  // (every lane has read its entry before any write below)
-    if (keep) {
-      const int pos = out + __popc(b & ((1u << lane) - 1u));
-      s.key[pos] = ky;
-      s.id[pos] = id;
-    }
-    out += __popc(b);
-    __syncwarp();
-  }
-#pragma unroll
-  for (int j = 0; j < 8; ++j)
-    if (j * 32 + lane < d) hist[j * 32 + lane] = 0;
-  if (lane == 0 && tc > *s.tau) *reinterpret_cast<volatile unsigned long long*>(s.tau) = tc;
-  __syncwarp();
-  return out;
-}
-
-// rebuild the coarse histogram of a buffer after its entries changed wholesale
-__device__ __forceinline__ void sel_rehist_warp(const Sel& s, int n, uint32_t* hist, uint32_t base) {
-  const int lane = threadIdx.x & 31;
-#pragma unroll
-  for (int j = 0; j < 8; ++j) hist[j * 32 + lane] = 0;
-  __syncwarp();
-  for (int i = lane; i < n; i += 32) sm_red_add(&hist[coarse_bin(s.key[i], base)], 1u);
-  __syncwarp();
 }
 
 }  // namespace arcs
