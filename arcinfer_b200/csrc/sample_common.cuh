@@ -19,7 +19,7 @@ constexpr uint32_t kIdMask = 0x1FFFFFFFu;  // entry word y: id | flagged by the 
 constexpr uint32_t kTch = 1u << 29, kOkB = 1u << 30;
 constexpr int kCapB = 1024;   // finish kernel's candidate buffer: prune trigger + one round of pushes
 constexpr int kCapA = 1280;   // ... for the constrained head select (k = 512): trigger 768 + four rounds of 128
-constexpr int kListB = 2048;  // survivors of the stream an item's block holds: selection proper (typically k * (1 + ln(V / 4096)))
+constexpr int kListB = 4096;  // survivors of the stream an item's block holds: selection proper (typically k * (1 + ln(V / 4096)))
 constexpr int kListA = 4096;  // ... constrained head ranking
 #ifndef ARCS_BOOT
 #define ARCS_BOOT 32768

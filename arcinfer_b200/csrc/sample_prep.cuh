@@ -14,7 +14,7 @@
 
 namespace arcs {
 
-constexpr int kBootKeys = 1024;  // most maxima the first threshold is read off (constrained rows; 256 otherwise)
+constexpr int kBootKeys = 1024;  // piece maxima the first threshold is read off
 
 static size_t prep_smem_bytes(int hash_slots) {
   return 16 + (size_t)hash_slots * 8 + 2 * (size_t)kBootKeys * 4 + (size_t)bloom_words_of(hash_slots) * 4 + 16 * 4;
@@ -87,14 +87,21 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
   // the prefix is fetched first: its latency hides behind the list work
   const int nchunk = min(it.p.body_bytes, MASKED ? 2 * 8192 : kBootBytes) / 16;
   const int32_t c_lo = it.p.body_first, c_hi = it.p.body_first + nchunk * E;  // columns of the prefix
-  float m0 = -INFINITY, m1 = -INFINITY;
-  bool any0 = false, any1 = false;
+  constexpr int kPer = kBootBytes / 16 / kGroup;               // chunks of the prefix per thread
+  constexpr int kMaxima = kBootKeys / kGroup;                   // maxima each thread keeps (1024 pieces in all)
+  constexpr int kPiece = kPer / kMaxima > 0 ? kPer / kMaxima : 1;  // chunks per piece
+  float pm[kMaxima];
+  bool pany[kMaxima];
+#pragma unroll
+  for (int i = 0; i < kMaxima; ++i) {
+    pm[i] = -INFINITY;
+    pany[i] = false;
+  }
   if (!MASKED) {
-    // two maxima per thread, each over every other one of the thread's chunks of the prefix,
-    // fetched eight at a time
-    constexpr int kPer = kBootBytes / 16 / kGroup;  // chunks of the prefix per thread
-    constexpr int kBatch = kPer < 8 ? kPer : 8;  // chunks in flight per thread
-#pragma unroll 1
+    // the maxima of the thread's pieces of the prefix (disjoint pieces of kPiece chunks), the
+    // chunks fetched eight at a time
+    constexpr int kBatch = kPer < 8 ? kPer : 8;
+#pragma unroll
     for (int x0 = 0; x0 < kPer; x0 += kBatch) {
       uint4 q[kBatch];
 #pragma unroll
@@ -106,14 +113,9 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
       for (int x = 0; x < kBatch; ++x) {
         const int ci = gt + (x0 + x) * kGroup;
         if (ci < nchunk) {
-          const float m = Elem<T>::chunk_max(q[x]);
-          if (x & 1) {
-            m1 = fmaxf(m1, m);
-            any1 = true;
-          } else {
-            m0 = fmaxf(m0, m);
-            any0 = true;
-          }
+          const int pi = ((x0 + x) / kPiece) % kMaxima;
+          pm[pi] = fmaxf(pm[pi], Elem<T>::chunk_max(q[x]));
+          pany[pi] = true;
         }
       }
     }
@@ -300,17 +302,34 @@ __global__ void __launch_bounds__(kGroup) prepare_kernel(const SampleDev a) {
   }
   __syncthreads();
 
-  // first threshold: the k-th largest of 256 (or, constrained, 1024) maxima over disjoint pieces
+  // first threshold: the k-th largest of up to 1024 maxima over disjoint pieces
   // of the prefix is a lower bound of the k-th best element; listed columns inside the prefix
   // may own a maximum without counting, so that many more are skipped
   const int kth = (MASKED ? ARCS_HEAD : r.kB) + *n_extra;
   unsigned long long tau0B = 0ull, tau0A = 0ull;
   if (!MASKED) {
-    ptk[gt] = any0 ? key_of(m0) : 0u;
-    ptk[kGroup + gt] = any1 ? key_of(m1) : 0u;
+    // (pieces are merged four and four when 256 maxima are enough: the search is a quarter the work)
+    const bool fine = kth > 2 * kGroup;
+    if (fine) {
+#pragma unroll
+      for (int i = 0; i < kMaxima; ++i) ptk[i * kGroup + gt] = pany[i] ? key_of(pm[i]) : 0u;
+    } else {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float m = -INFINITY;
+        bool any = false;
+#pragma unroll
+        for (int i = h * (kMaxima / 2); i < (h + 1) * (kMaxima / 2); ++i) {
+          m = fmaxf(m, pm[i]);
+          any = any || pany[i];
+        }
+        ptk[h * kGroup + gt] = any ? key_of(m) : 0u;
+      }
+    }
     __syncthreads();
-    if (kth <= min(nchunk, 2 * kGroup)) {
-      if (gt < 32) m64[1] = (unsigned long long)warp_kth16<2 * kGroup / 32>(ptk, kth) << 32;  // keeps ties with it
+    if (kth <= min(nchunk / (fine ? kPiece : kPiece * (kMaxima / 2)), fine ? kBootKeys : 2 * kGroup)) {
+      if (gt < 32)
+        m64[1] = (unsigned long long)(fine ? warp_kth16<kBootKeys / 32>(ptk, kth) : warp_kth16<2 * kGroup / 32>(ptk, kth)) << 32;  // keeps ties with it
       __syncthreads();
       tau0B = m64[1];
     }
