@@ -59,6 +59,54 @@ enum {
 const char* arcs_last_error(void); /* text of the calling thread's last failure */
 int arcs_version(void);
 
+/* ------------------------------------------------------------------------------------------
+ * sample_batch: Sampler::adjusted + Sampler::sample for B rows in one call (three launches on
+ * the stream: a small per-row prepare, the single pass over the logits, a small per-row finish)
+ * (tools/sampler.h:36-78, :147-176); with a mask, Sampler::sample_allowed (:82-144) where
+ * the predicate ok(t) is bit t of the row's mask.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  /* inputs (device pointers) */
+  const void* logits;        /* [B][row_stride] of dtype; row b starts at b*row_stride elements */
+  int32_t dtype;             /* arcs_dtype */
+  int32_t B, V;              /* B <= 65536; token ids (id_base + V, v_global) below 2^29 - 1 */
+  int64_t row_stride;        /* in elements, >= V */
+  const arcs_row_params* params; /* [B] */
+  const int32_t* hist_off;   /* [B+1] CSR offsets into hist_ids, or NULL: no history (`recent`) */
+  const int32_t* hist_ids;   /* token ids generated so far, oldest first; ids outside [0,V) ignored */
+  const int32_t* bias_off;   /* [B+1] CSR offsets of the logit_bias lists, or NULL */
+  const int32_t* bias_ids;
+  const float* bias_vals;    /* <= -100 bans the token (tools/sampler.h:24) */
+  const double* u;           /* [B] uniform draws in [0,1); the reference's draw is u*tot */
+  const uint32_t* mask;      /* NULL: unconstrained. Else packed allowed-token bits, rows of mask_stride words */
+  const int32_t* mask_row;   /* [B] mask row used by each batch row, or NULL: row b uses mask row b */
+  int64_t mask_stride;       /* words per mask row, >= ceil(V/32) */
+  int32_t max_hist, max_bias;/* upper bounds on any row's list length (size the on-chip filter: together at most
+                                2048, else ARCS_ERR_LIST) */
+  int32_t id_base;           /* global id of column 0 (vocabulary shards); 0 otherwise */
+  int32_t v_global;          /* whole vocabulary size when sharded; 0 means V */
+  /* outputs (device pointers; optional ones may be NULL) */
+  int32_t* token;            /* [B] chosen id, -1 when no token is allowed */
+  int32_t* n_cand;           /* [B] optional: candidates after top-k / banned trimming */
+  int32_t* n_kept;           /* [B] optional: candidates left after min-p / top-p */
+  int32_t* flags;            /* [B] optional: ARCS_FLAG_* */
+  int32_t* cand_id;          /* [B][cand_stride] optional: candidate ids in order */
+  float* cand_val;           /* [B][cand_stride] optional: their adjusted logits */
+  float* cand_pr;            /* [B][cand_stride] optional: their probabilities pr[i]/z */
+  int32_t cand_stride;       /* >= ARCS_KCAP when any cand_* is given */
+  /* scratch */
+  void* workspace;           /* arcs_sample_workspace_bytes() bytes, 16-byte aligned; needs no initialisation */
+  size_t workspace_bytes;
+  int32_t* status;           /* optional device word: 0 or an arcs_status set by the kernels */
+} arcs_sample_args;
+
+/* max_list: max_hist + max_bias of the call (0 without lists) */
+size_t arcs_sample_workspace_bytes(int32_t B, int32_t V, int32_t masked, int32_t max_list);
+int arcs_sample_batch(const arcs_sample_args* args, void* stream);
+/* Measurement aid: the same three launches with CUDA events between them on `stream`; waits for
+ * them and returns the device time of the prepare, stream and finish kernels in ms3[0..2]. */
+int arcs_sample_batch_timed(const arcs_sample_args* args, void* stream, float* ms3);
+
 /* Vocabulary shards (no counterpart in the reference, which has one device): every GPU runs
  * arcs_sample_batch on its columns of all rows (`id_base`, `v_global`; lists are filtered by range)
  * with candidate outputs, the lists are all-gathered (NCCL, by the caller), and this call takes the
@@ -84,52 +132,6 @@ typedef struct arcs_merge_args {
   int32_t* status;
 } arcs_merge_args;
 int arcs_merge_batch(const arcs_merge_args* args, void* stream);
-
-/* ------------------------------------------------------------------------------------------
- * sample_batch: Sampler::adjusted + Sampler::sample for B rows in one launch
- * (tools/sampler.h:36-78, :147-176); with a mask, Sampler::sample_allowed (:82-144) where
- * the predicate ok(t) is bit t of the row's mask.
- * ---------------------------------------------------------------------------------------- */
-typedef struct {
-  /* inputs (device pointers) */
-  const void* logits;        /* [B][row_stride] of dtype; row b starts at b*row_stride elements */
-  int32_t dtype;             /* arcs_dtype */
-  int32_t B, V;
-  int64_t row_stride;        /* in elements, >= V */
-  const arcs_row_params* params; /* [B] */
-  const int32_t* hist_off;   /* [B+1] CSR offsets into hist_ids, or NULL: no history (`recent`) */
-  const int32_t* hist_ids;   /* token ids generated so far, oldest first; ids outside [0,V) ignored */
-  const int32_t* bias_off;   /* [B+1] CSR offsets of the logit_bias lists, or NULL */
-  const int32_t* bias_ids;
-  const float* bias_vals;    /* <= -100 bans the token (tools/sampler.h:24) */
-  const double* u;           /* [B] uniform draws in [0,1); the reference's draw is u*tot */
-  const uint32_t* mask;      /* NULL: unconstrained. Else packed allowed-token bits, rows of mask_stride words */
-  const int32_t* mask_row;   /* [B] mask row used by each batch row, or NULL: row b uses mask row b */
-  int64_t mask_stride;       /* words per mask row, >= ceil(V/32) */
-  int32_t max_hist, max_bias;/* upper bounds on any row's list length (sizes the on-chip tables) */
-  int32_t id_base;           /* global id of column 0 (vocabulary shards); 0 otherwise */
-  int32_t v_global;          /* whole vocabulary size when sharded; 0 means V */
-  /* outputs (device pointers; optional ones may be NULL) */
-  int32_t* token;            /* [B] chosen id, -1 when no token is allowed */
-  int32_t* n_cand;           /* [B] optional: candidates after top-k / banned trimming */
-  int32_t* n_kept;           /* [B] optional: candidates left after min-p / top-p */
-  int32_t* flags;            /* [B] optional: ARCS_FLAG_* */
-  int32_t* cand_id;          /* [B][cand_stride] optional: candidate ids in order */
-  float* cand_val;           /* [B][cand_stride] optional: their adjusted logits */
-  float* cand_pr;            /* [B][cand_stride] optional: their probabilities pr[i]/z */
-  int32_t cand_stride;       /* >= ARCS_KCAP when any cand_* is given */
-  /* scratch */
-  void* workspace;           /* arcs_sample_workspace_bytes() bytes, 16-byte aligned; needs no initialisation */
-  size_t workspace_bytes;
-  int32_t* status;           /* optional device word: 0 or an arcs_status set by the kernels */
-} arcs_sample_args;
-
-/* max_list: max_hist + max_bias of the call (0 without lists) */
-size_t arcs_sample_workspace_bytes(int32_t B, int32_t V, int32_t masked, int32_t max_list);
-int arcs_sample_batch(const arcs_sample_args* args, void* stream);
-/* Measurement aid: the same three launches with CUDA events between them on `stream`; waits for
- * them and returns the device time of the prepare, stream and finish kernels in ms3[0..2]. */
-int arcs_sample_batch_timed(const arcs_sample_args* args, void* stream, float* ms3);
 
 /* ------------------------------------------------------------------------------------------
  * argmax_batch: first maximum of each row (tools/sampler.h:38; zero/runz.cpp:283;
