@@ -71,3 +71,75 @@ def test_two_ranks_equal_one_process():
         assert p.exitcode == 0
     x, p, hist, u = _rows(5, B, V)
     assert np.array_equal(got, _tokens(x, p, hist, u, 0, B))
+
+
+# ---- the vocabulary-sharded step (shard.vocab_sharded_sample) with stand-ins for the two kernels:
+# every rank ranks its own columns with the CPU oracle, the lists travel through one gloo
+# all-gather in the packed layout the real path uses, and the merge picks from the gathered lists.
+KCAP = 256
+
+
+def _fake_sample(x_rows, hist, p_rows):
+    def f(local_logits, params, u, id_base=0, v_global=0, want_cands=True, **_):
+        B, Vl = local_logits.shape
+        ids = torch.full((B, KCAP), -1, dtype=torch.int32)
+        vals = torch.zeros(B, KCAP, dtype=torch.float32)
+        n = torch.zeros(B, dtype=torch.int32)
+        for b in range(B):
+            adj = orc.adjusted(x_rows[b], p_rows[b : b + 1], hist[b])[id_base : id_base + Vl]
+            k = min(int(p_rows[b]["top_k"]), Vl)
+            order = np.lexsort((np.arange(Vl), -adj.astype(np.float64)))[:k]  # value desc, id asc
+            ids[b, :k] = torch.from_numpy((order + id_base).astype(np.int32))
+            vals[b, :k] = torch.from_numpy(adj[order])
+            n[b] = k
+        return {"cand_id": ids, "cand_val": vals, "n_cand": n}
+
+    return f
+
+
+def _fake_merge(p_rows, V):
+    def f(cand_id, cand_val, n_cand, params, u, v_global, **_):
+        G, B, _ = cand_id.shape
+        tok = torch.zeros(B, dtype=torch.int32)
+        plain = p_rows.copy()
+        for name in ("presence_penalty", "frequency_penalty"):
+            plain[name] = 0.0
+        plain["repeat_penalty"] = 1.0  # the gathered values are already adjusted
+        for b in range(B):
+            row = np.full(V, -3.0e38, np.float32)
+            for g in range(G):
+                k = int(n_cand[g, b])
+                row[cand_id[g, b, :k].numpy()] = cand_val[g, b, :k].numpy()
+            tok[b] = orc.sample(row, plain[b : b + 1], np.zeros(0, np.int32), float(u[b]))["token"]
+        return {"token": tok}
+
+    return f
+
+
+def _vocab_worker(rank, world, port, B, V, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    x, p, hist, u = _rows(6, B, V)
+    lo, hi = shard.vocab_range(V, rank, world, align=256)
+    local = torch.from_numpy(np.ascontiguousarray(x[:, lo:hi]))
+    res = shard.vocab_sharded_sample(local, lo, V, p, torch.from_numpy(u), dist.all_gather, world, _fake_sample(x, hist, p), _fake_merge(p, V))
+    if rank == 0:
+        out.put(res["token"].numpy())
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_vocab_shards_two_ranks_equal_one_process():
+    B, V, world = 5, 3000, 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    ps = [ctx.Process(target=_vocab_worker, args=(r, world, port, B, V, q)) for r in range(world)]
+    for p in ps:
+        p.start()
+    got = q.get(timeout=120)
+    for p in ps:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    x, p, hist, u = _rows(6, B, V)
+    assert np.array_equal(got, _tokens(x, p, hist, u, 0, B))
