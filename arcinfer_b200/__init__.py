@@ -12,6 +12,7 @@ from .capi import (  # noqa: F401
     argmax_batch,
     dfa_mask,
     lib,
+    logprobs_batch,
     make_params,
     merge_batch,
     sample_batch,

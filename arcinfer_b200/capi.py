@@ -253,6 +253,45 @@ def dfa_mask(table, dead, states, byte_off, bytes_, special=None, special_ok=Fal
     return out
 
 
+class LogprobArgs(C.Structure):
+    _fields_ = [
+        ("logits", C.c_void_p), ("dtype", C.c_int32), ("B", C.c_int32), ("V", C.c_int32),
+        ("row_stride", C.c_int64), ("token", C.c_void_p), ("top_n", C.c_int32), ("top_stride", C.c_int32),
+        ("logprob", C.c_void_p), ("lse", C.c_void_p), ("top_id", C.c_void_p), ("top_logprob", C.c_void_p),
+        ("status", C.c_void_p),
+    ]  # fmt: skip
+
+
+lib.arcs_logprobs_batch.restype = C.c_int
+lib.arcs_logprobs_batch.argtypes = [C.POINTER(LogprobArgs), C.c_void_p]
+
+
+def logprobs_batch(logits, token=None, top_n=0, V=None, status=None):
+    """arcs_logprobs_batch: logits [B, >=V] fp32 / bf16 on the device, token int32 [B] or None.
+    Returns a dict: lse [B] float64, logprob [B] float64 (when token is given), top_id [B, top_n]
+    int32 and top_logprob [B, top_n] float64 (when top_n > 0), status."""
+    dev = logits.device
+    B = logits.shape[0]
+    V = logits.shape[1] if V is None else V
+    out = {"lse": torch.empty(B, dtype=torch.float64, device=dev)}
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out["status"] = status
+    if token is not None:
+        out["logprob"] = torch.empty(B, dtype=torch.float64, device=dev)
+    if top_n > 0:
+        out["top_id"] = torch.full((B, top_n), -1, dtype=torch.int32, device=dev)
+        out["top_logprob"] = torch.full((B, top_n), float("nan"), dtype=torch.float64, device=dev)
+    a = LogprobArgs()
+    a.logits, a.dtype, a.B, a.V, a.row_stride = logits.data_ptr(), _dtype_code(logits), B, V, logits.stride(0)
+    a.token, a.top_n, a.top_stride = _ptr(token), top_n, top_n
+    a.logprob, a.lse = _ptr(out.get("logprob")), out["lse"].data_ptr()
+    a.top_id, a.top_logprob = _ptr(out.get("top_id")), _ptr(out.get("top_logprob"))
+    a.status = status.data_ptr()
+    _check(lib.arcs_logprobs_batch(C.byref(a), _stream(dev)), "arcs_logprobs_batch")
+    return out
+
+
 # ---------------------------------------------------------------- host-buffer entry points
 lib.arcs_host_create.restype = C.c_int
 lib.arcs_host_create.argtypes = [C.POINTER(C.c_void_p), C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int64, C.c_int64]

@@ -190,6 +190,35 @@ int arcs_dfa_mask(const uint16_t* table, int32_t n_table_states, int32_t dead, c
                   int32_t special_ok, int32_t V, uint32_t* out, int64_t out_stride, void* stream);
 
 /* ------------------------------------------------------------------------------------------
+ * logprobs_batch: per row, the log probability of one token and the top_n most likely
+ * alternatives, from the RAW logits (no penalty, no bias): the `logprobs` entry of
+ * tools/server_chat.h:417-441, and the log-softmax that scores perplexity and KL
+ * (zero/runz.cpp:478-484, :639-646). One pass over the logits, one launch, no workspace.
+ *   mx = max; z = sum exp(l - mx) accumulated in fp64; lse = mx + log(z);
+ *   logprob[b] = l[token[b]] - lse;  top_id / top_logprob: the top_n largest logits, best first
+ *   (equal logits: lower id first), as log probabilities.
+ * The reference sums fp64 exponentials in index order; here each term is a float exponential of
+ * the exactly compensated difference, summed in fp64 in another order: log probabilities agree
+ * to about 1e-7 absolute. NaN logits are skipped.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* logits;     /* [B][row_stride] device */
+  int32_t dtype;          /* arcs_dtype */
+  int32_t B, V;
+  int64_t row_stride;     /* elements */
+  const int32_t* token;   /* [B] token whose log probability is wanted; NULL or an id < 0: none */
+  int32_t top_n;          /* alternatives per row, 0 .. ARCS_KCAP (the reference serves 0 .. 20) */
+  int32_t top_stride;     /* >= top_n */
+  double* logprob;        /* [B] (NaN where no token was given); may be NULL when token is */
+  double* lse;            /* [B] optional: log of the sum of exponentials */
+  int32_t* top_id;        /* [B][top_stride]; entries past min(top_n, V) are not written */
+  double* top_logprob;    /* [B][top_stride] */
+  int32_t* status;        /* device status word (OR-free: first error wins), may be NULL */
+} arcs_logprob_args;
+
+int arcs_logprobs_batch(const arcs_logprob_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------
  * Host-buffer entry points: what a host application that keeps its logits in host memory
  * (the reference reads every row back from the GPU, zero/engine.h:255-258, and hands
  * Sampler::sample a std::vector<float>, tools/server_chat.h:561) calls instead of

@@ -360,6 +360,42 @@ double orc_softmax_den_exact(const float* l, int64_t n, float mx) {
   return z;
 }
 
+/* ---------------------------------------------------------------- log probabilities */
+double orc_logprobs(const float* l, int V, int32_t token, int top_n, double* logprob,
+                    int32_t* top_id, double* top_logprob) {
+  float mx = l[0];                                   /* tools/server_chat.h:419 */
+  for (int i = 1; i < V; ++i)
+    if (l[i] > mx) mx = l[i];
+  double z = 0;
+  for (int i = 0; i < V; ++i) z += exp((double)l[i] - mx);   /* :420-421 */
+  const double lse = mx + log(z);                             /* :422 */
+  if (token >= 0 && token < V && logprob) *logprob = (double)l[token] - lse;  /* :427 */
+  if (top_n > V) top_n = V;
+  /* :433-438: the top_n largest, best first; selection by repeated scan (top_n <= 256) */
+  double last_v = INFINITY;
+  int last_id = -1;
+  for (int r = 0; r < top_n; ++r) {
+    int best = -1;
+    for (int i = 0; i < V; ++i) {
+      const double v = l[i];
+      if (v != v) continue;
+      /* after (last_v, last_id) in the order (value desc, id asc) */
+      if (!(v < last_v || (v == last_v && i > last_id))) continue;
+      if (best < 0 || v > (double)l[best]) best = i;
+    }
+    if (best < 0) {
+      top_id[r] = -1;
+      top_logprob[r] = NAN;
+      continue;
+    }
+    top_id[r] = best;
+    top_logprob[r] = (double)l[best] - lse;
+    last_v = l[best];
+    last_id = best;
+  }
+  return lse;
+}
+
 /* ---------------------------------------------------------------- byte automaton */
 void orc_dfa_mask(const uint16_t* table, int S, int dead, int state, const uint32_t* byte_off,
                   const uint8_t* bytes, const uint8_t* special, int special_ok, int V,

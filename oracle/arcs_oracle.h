@@ -86,6 +86,15 @@ void orc_verify_greedy(const int32_t* sel, const int32_t* row_off, const int32_t
 double orc_softmax_den(const float* l, int64_t n, float mx);
 double orc_softmax_den_exact(const float* l, int64_t n, float mx);
 
+/* a token's log probability and the top_n most likely alternatives from the raw logits
+ * (tools/server_chat.h:417-441; the same log-softmax scores perplexity, zero/runz.cpp:478-484):
+ * mx = max; z = sum exp((double)l - mx) in index order; lse = mx + log(z);
+ * logprob(t) = (double)l[t] - lse. The alternatives are the top_n largest logits; the reference
+ * leaves the order of equal logits to std::partial_sort, here the lower id comes first.
+ * token < 0: no per-token entry (*logprob untouched). Returns lse. */
+double orc_logprobs(const float* l, int V, int32_t token, int top_n, double* logprob,
+                    int32_t* top_id, double* top_logprob);
+
 /* allowed(t) over a vocabulary for a byte automaton (tools/server_chat.h:539-557 with the
  * checker replaced by a transition table): token t is allowed iff its byte string is not
  * empty, it is not special (or special_ok), and walking its bytes from `state` never

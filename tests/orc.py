@@ -33,6 +33,7 @@ ref = C.CDLL(REF_SO) if os.path.exists(REF_SO) else None
 orc.orc_softmax_den.restype = C.c_double
 orc.orc_softmax_den_exact.restype = C.c_double
 orc.orc_argmax.restype = C.c_int32
+orc.orc_logprobs.restype = C.c_double
 if ref is not None:
     ref.ref_sample_batch.restype = C.c_double
     ref.ref_hardware_threads.restype = C.c_int
@@ -107,6 +108,15 @@ def softmax_den(row, mx, exact=False):
     row = _f32(row)
     f = orc.orc_softmax_den_exact if exact else orc.orc_softmax_den
     return f(_p(row), C.c_int64(len(row)), C.c_float(mx))
+
+
+def logprobs(row, token=-1, top_n=0):
+    """lse, logprob of `token` (nan when token < 0), top ids, top log probabilities"""
+    row = _f32(row)
+    lp = np.full(1, np.nan, np.float64)
+    ids, tlp = np.full(max(top_n, 1), -1, np.int32), np.full(max(top_n, 1), np.nan, np.float64)
+    lse = orc.orc_logprobs(_p(row), len(row), int(token), int(top_n), _p(lp), _p(ids), _p(tlp))
+    return lse, lp[0], ids[:top_n], tlp[:top_n]
 
 
 def dfa_mask(table, dead, state, byte_off, by, special=None, special_ok=False):

@@ -13,7 +13,7 @@ def test_library_exports_every_declared_symbol():
     hdr = open(os.path.join(ROOT, "include", "arcsample.h")).read()
     names = set(re.findall(r"\b(arcs_[a-z_0-9]+)\s*\(", hdr))
     assert {"arcs_sample_batch", "arcs_argmax_batch", "arcs_dfa_mask", "arcs_sample_batch_host",
-            "arcs_argmax_batch_static"} <= names
+            "arcs_argmax_batch_static", "arcs_logprobs_batch"} <= names
     for n in sorted(names):
         assert hasattr(ab.lib, n), n
     assert ab.lib.arcs_version() == 1
@@ -27,6 +27,8 @@ def test_argument_checks_need_no_device():
     assert b"bad argument" in ab.lib.arcs_last_error()
     g = ab.capi.ArgmaxArgs()
     assert ab.lib.arcs_argmax_batch(C.byref(g), None) == 1
+    lp = ab.capi.LogprobArgs()
+    assert ab.lib.arcs_logprobs_batch(C.byref(lp), None) == 1
     assert ab.lib.arcs_sample_workspace_bytes(1024, 262144, 0, 0) >= 1024 * 4
     assert ab.lib.arcs_sample_workspace_bytes(8, 262144, 1, 0) > ab.lib.arcs_sample_workspace_bytes(8, 262144, 0, 0)
     assert ab.lib.arcs_sample_workspace_bytes(8, 262144, 0, 512) > ab.lib.arcs_sample_workspace_bytes(8, 262144, 0, 0)

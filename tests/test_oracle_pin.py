@@ -109,3 +109,22 @@ def test_sample_allowed_matches_reference(pen):
           f"{bad} tokens differ, {badfirst} first-refused flags differ")
     assert bad == 0 and badfirst == 0
     assert tails > 0 and n - ties > n // 3
+
+
+def test_logprobs_restatement_against_numpy():
+    """orc_logprobs (tools/server_chat.h:417-441) against an independent fp64 computation: the
+    reference's lambda sits inside Server::chat and cannot be compiled alone, so the restatement
+    is pinned by numpy's log-sum-exp and a stable sort (ties: lower id first)."""
+    g = np.random.default_rng(5)
+    for V, top_n in [(1, 1), (5, 3), (1000, 20), (151936, 20), (4096, 256)]:
+        for mode in range(2):
+            x = (g.standard_normal(V) * 3).astype(np.float32) if mode == 0 else (0.5 * g.integers(0, 6, V)).astype(np.float32)
+            tok = int(g.integers(0, V))
+            lse, lp, ids, tlp = orc.logprobs(x, tok, min(top_n, V))
+            xd = x.astype(np.float64)
+            want_lse = xd.max() + np.log(np.exp(xd - xd.max()).sum())
+            assert abs(lse - want_lse) <= 1e-12 * max(1.0, abs(want_lse))
+            assert abs(lp - (xd[tok] - want_lse)) <= 1e-11
+            order = np.argsort(-xd, kind="stable")[: min(top_n, V)]
+            assert np.array_equal(ids, order.astype(np.int32))
+            assert np.allclose(tlp, xd[order] - want_lse, rtol=0, atol=1e-11)
