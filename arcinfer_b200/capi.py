@@ -258,10 +258,12 @@ class LogprobArgs(C.Structure):
         ("logits", C.c_void_p), ("dtype", C.c_int32), ("B", C.c_int32), ("V", C.c_int32),
         ("row_stride", C.c_int64), ("token", C.c_void_p), ("top_n", C.c_int32), ("top_stride", C.c_int32),
         ("logprob", C.c_void_p), ("lse", C.c_void_p), ("top_id", C.c_void_p), ("top_logprob", C.c_void_p),
-        ("status", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
     ]  # fmt: skip
 
 
+lib.arcs_logprobs_workspace_bytes.restype = C.c_size_t
+lib.arcs_logprobs_workspace_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int32]
 lib.arcs_logprobs_batch.restype = C.c_int
 lib.arcs_logprobs_batch.argtypes = [C.POINTER(LogprobArgs), C.c_void_p]
 
@@ -287,6 +289,8 @@ def logprobs_batch(logits, token=None, top_n=0, V=None, status=None):
     a.token, a.top_n, a.top_stride = _ptr(token), top_n, top_n
     a.logprob, a.lse = _ptr(out.get("logprob")), out["lse"].data_ptr()
     a.top_id, a.top_logprob = _ptr(out.get("top_id")), _ptr(out.get("top_logprob"))
+    ws = _workspace("logprobs", dev, lib.arcs_logprobs_workspace_bytes(B, V, top_n))
+    a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
     a.status = status.data_ptr()
     _check(lib.arcs_logprobs_batch(C.byref(a), _stream(dev)), "arcs_logprobs_batch")
     return out

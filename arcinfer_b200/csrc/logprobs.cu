@@ -1,38 +1,86 @@
 // logprobs_batch: per row the log-softmax of one token and the top_n largest raw logits as log
 // probabilities (tools/server_chat.h:417-441; zero/runz.cpp:478-484 scores perplexity with the
-// same sum). One CTA streams one row once through a ring of bulk-copied tiles and keeps
+// same sum). One launch. A CTA streams one segment of one row once through a ring of bulk-copied
+// tiles and keeps
 //  - per thread a running (reference value, sum of exponentials relative to it), the sum in fp64;
 //  - for the whole CTA a candidate buffer with a rising threshold: the top_n best so far.
+// Rows are cut into segments when there are few of them; the CTA that finishes a row last merges
+// the segments' results (left in the workspace) and writes the row's output.
 #include "plan.h"
 #include "select.cuh"
 #include "stream.cuh"
 
 namespace arcs {
 
-constexpr int kLpCap = 1024;                  // candidate buffer of a row
-constexpr int kLpTrig = kLpCap - kThreads;    // prune when a further round of pushes might not fit
+constexpr int kLpCap = 1024;                  // candidate buffer of a CTA
+constexpr int kLpTrig = kLpCap - kThreads;    // prune once it has grown past this
+constexpr int kLpPerSm = 3;                   // CTAs per SM the segments are planned for
+
+struct LpPart {      // what a segment leaves for the merge
+  double z;          // sum of exp(l - M) over the segment
+  float M;           // the segment's maximum (-inf: nothing but NaN or -inf)
+  int32_t cnt;       // entries in its candidate list
+};
 
 struct LogprobDev {
   const void* logits;
   int64_t row_stride;
-  int32_t B, V;
+  int32_t B, V, nseg, seg_len;
   const int32_t* token;
   int32_t top_n, top_stride;
   double* logprob;
   double* lse;
   int32_t* top_id;
   double* top_logprob;
+  unsigned int* ws_ctr;            // [B] segments of the row that have finished, 0 between launches
+  LpPart* ws_part;                 // [B][nseg]
+  unsigned long long* ws_list;     // [B][nseg][top_n] composites
   int32_t* status;
 };
 
-// exp(v - m) for v <= m: a float exponential of the float difference, with the rounding error of
-// that difference (recovered exactly by a two-sum) put back to first order
+// exp(v - m) for v <= m: 2^t with t = (v - m) * log2(e) rounded to float, corrected to first
+// order by everything the roundings dropped: the error of the float difference (recovered by a
+// two-sum; EXACT8: both operands carry 8 significant bits, bf16 data, where the difference is
+// nearly always exact and the three-operation form recovers what is not), of the product, and
+// the low part of log2(e). NaN and -inf give 0.
+template <bool EXACT8>
 __device__ __forceinline__ float exp_diff(float v, float m) {
+  constexpr float kL2eHi = 1.44269502162933349609375f, kL2eLo = 1.92596299112661746e-8f, kLn2 = 0.693147180559945f;
+  v = fmaxf(v, -1e38f);
   const float s = __fsub_rn(v, m);
-  const float bb = __fsub_rn(s, v);
-  const float err = __fadd_rn(__fsub_rn(v, __fsub_rn(s, bb)), __fsub_rn(-m, bb));
-  const float e = expf(s);
-  return e > 0.0f ? fmaf(e, err, e) : 0.0f;  // (also keeps the NaN of inf - inf out when v is -inf)
+  float err;
+  if (EXACT8) {
+    err = __fsub_rn(v, __fadd_rn(s, m));
+  } else {
+    const float bb = __fsub_rn(s, v);
+    err = __fadd_rn(__fsub_rn(v, __fsub_rn(s, bb)), __fsub_rn(-m, bb));
+  }
+  const float t = __fmul_rn(s, kL2eHi);
+  float c = fmaf(s, kL2eHi, -t);
+  c = fmaf(s, kL2eLo, c);
+  c = fmaf(err, kL2eHi, c);
+  float e;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t));
+  return fmaf(e, c * kLn2, e);
+}
+
+// Warp-collective append to the candidate buffer; lanes with p set store (key, id). Returns true
+// for a lane whose entry found no room (the caller offers it again after the next prune); `hot`
+// is set once the buffer has grown past the prune trigger.
+__device__ __forceinline__ bool lp_push(const Sel& s, bool p, uint32_t key, int32_t id, bool& hot) {
+  const unsigned b = __ballot_sync(0xFFFFFFFFu, p);
+  if (b == 0) return false;
+  const int lane = threadIdx.x & 31, leader = __ffs(b) - 1;
+  int base = 0;
+  if (lane == leader) base = (int)sm_atomic_add(s.cnt, (uint32_t)__popc(b));
+  base = __shfl_sync(0xFFFFFFFFu, base, leader);
+  if (!p) return false;
+  const int pos = base + __popc(b & ((1u << lane) - 1u));
+  hot = hot || pos + 1 > s.trig;
+  if (pos >= s.cap) return true;
+  s.key[pos] = key;
+  s.id[pos] = id;
+  return false;
 }
 
 constexpr size_t kLpSmem = (size_t)kStages * kTileBytes + (size_t)kLpCap * 8 + 512 * 4 + (size_t)kTmpCap * 8;
@@ -48,16 +96,18 @@ __global__ void __launch_bounds__(kThreads) logprob_kernel(const LogprobDev a) {
   int32_t* ti = reinterpret_cast<int32_t*>(tk + kTmpCap);
   __shared__ __align__(8) uint64_t bars[kStages];
   __shared__ unsigned long long s_tau, s_m64;
-  __shared__ int s_cnt, s_misc[8];
+  __shared__ int s_cnt, s_misc[8], s_flag;
   __shared__ float red_m[kThreads / 32];
   __shared__ double red_s[kThreads / 32], s_lse;
+  __shared__ __align__(16) uint32_t s_keys[kThreads];
 
   constexpr int E = Elem<T>::kPerChunk;
   constexpr int kChunks = kTileBytes / 16 / kThreads;
   static_assert(kChunks * E <= 32, "a thread's elements of one tile are tracked in a 32-bit mask");
-  const int tid = threadIdx.x, b = blockIdx.x;
+  const int tid = threadIdx.x, b = blockIdx.x / a.nseg, seg = blockIdx.x % a.nseg;
   const T* row = reinterpret_cast<const T*>(a.logits) + (size_t)b * a.row_stride;
-  const SegPlan p = make_plan(row, 0, a.V);
+  const int32_t lo = seg * a.seg_len, hi = min(a.V, lo + a.seg_len);
+  const SegPlan p = make_plan(row, lo, hi);
   const int n = min(a.top_n, a.V);
 
   Sel sel{bkey, bid, &s_cnt, &s_tau, n, kLpTrig, kLpCap};
@@ -75,23 +125,47 @@ __global__ void __launch_bounds__(kThreads) logprob_kernel(const LogprobDev a) {
 
   float lm = -INFINITY;  // what this thread's exponentials are relative to: at least every value it has seen
   double ls = 0.0;
-  unsigned long long tau = 0ull;  // exclusive threshold of the candidate buffer (this thread's copy)
+  unsigned long long tau = 0ull;  // exclusive threshold of the candidate buffer (every thread's copy is current)
 
-  // one more value for the sum (NaN skipped)
+  // one more value for the sum
   auto lse_one = [&](float v) {
     if (v > lm) {
       ls *= exp((double)lm - (double)v);
       lm = v;
     }
-    if (v == v && lm > -INFINITY) ls += (double)exp_diff(v, lm);
+    if (lm > -INFINITY) ls += (double)exp_diff<false>(v, lm);
   };
-  // Every thread calls: those with p set put (ky, id) into the buffer; when it has grown past the
-  // trigger the CTA keeps the n best and the threshold rises.
-  auto offer = [&](bool pr, uint32_t ky, int32_t id) {
+  // Every thread calls with the mask of its own elements that may belong to the n best;
+  // elem(idx, key, id) names element idx. The elements above the threshold go into the buffer as
+  // they come; when the buffer has grown past the trigger, or had no room for some, the CTA keeps
+  // the n best, the threshold rises and the elements left out are offered again.
+  auto push_all = [&](uint32_t bits, auto elem) {
+    uint32_t again = 0;
     bool hot = false;
-    sel_push(sel, pr, ky, id, hot, a.status);
-    if (__syncthreads_or(hot)) sel_prune<1, kThreads>(sel, n, ps, tid);
-    tau = s_tau;
+    for (;;) {
+      while (__any_sync(0xFFFFFFFFu, bits != 0u)) {
+        const bool valid = bits != 0u;
+        const int idx = valid ? __ffs(bits) - 1 : 0;
+        bits &= bits - 1u;
+        uint32_t ky = 0;
+        int32_t id = 0;
+        if (valid) elem(idx, ky, id);
+        const bool pr = valid && ky != 0u && comp_of(ky, id) > tau;
+        if (lp_push(sel, pr, ky, id, hot)) again |= 1u << idx;
+      }
+      if (!__syncthreads_or(hot || again != 0u)) break;
+      const unsigned long long before = tau;
+      sel_prune<1, kThreads>(sel, n, ps, tid);  // (more than kLpTrig >= n entries: it does not return early)
+      if (s_tau < before) {  // (entries offered again were not in the buffer: its n-th best may lie below the threshold)
+        __syncthreads();
+        if (tid == 0) s_tau = before;
+        __syncthreads();
+      }
+      tau = s_tau;
+      hot = false;
+      bits = again;
+      again = 0;
+    }
   };
 
   bool failed = false;
@@ -117,11 +191,14 @@ __global__ void __launch_bounds__(kThreads) logprob_kernel(const LogprobDev a) {
     if (tid == 0 && t + kStages < p.tiles) issue_tile(p, t + kStages, stage, bars);
 
     // ---- the sum of exponentials
+    float cmax[kChunks];
 #pragma unroll
     for (int j = 0; j < kChunks; ++j) {
       const uint32_t off = (uint32_t)(j * kThreads + tid) * 16u;
+      cmax[j] = NAN;  // (a chunk past the end of the tile reaches no threshold, not even -inf)
       if (off >= nbytes) continue;
       const float cm = Elem<T>::chunk_max(q[j]);
+      cmax[j] = cm;
       if (cm > lm) {
         ls *= exp((double)lm - (double)cm);
         lm = cm;
@@ -129,10 +206,7 @@ __global__ void __launch_bounds__(kThreads) logprob_kernel(const LogprobDev a) {
       if (lm > -INFINITY) {
         float ev[E];
 #pragma unroll
-        for (int e = 0; e < E; ++e) {
-          const float v = Elem<T>::get(q[j], e);
-          ev[e] = v == v ? exp_diff(v, lm) : 0.0f;
-        }
+        for (int e = 0; e < E; ++e) ev[e] = exp_diff<sizeof(T) == 2>(Elem<T>::get(q[j], e), lm);
 #pragma unroll
         for (int w = E / 2; w > 0; w >>= 1)
 #pragma unroll
@@ -143,102 +217,167 @@ __global__ void __launch_bounds__(kThreads) logprob_kernel(const LogprobDev a) {
     if (n <= 0) continue;
 
     // ---- the candidates
-    // element idx (chunk idx / E, position idx % E) of this thread's part of the tile
-    auto pick = [&](int idx, int32_t& id) -> float {
-      const int j = idx / E;
-      uint4 c = q[0];
-#pragma unroll
-      for (int x = 1; x < kChunks; ++x)
-        if (j == x) c = q[x];
-      id = p.body_first + (int32_t)(((uint32_t)t * kTileBytes + (uint32_t)(j * kThreads + tid) * 16u) / sizeof(T)) + idx % E;
-      return Elem<T>::get(c, idx % E);
-    };
-    if (t == 0) {
-      // first threshold: the n-th largest of the threads' own maxima over this tile is a lower
-      // bound of the n-th largest element (the maxima belong to disjoint pieces)
-      float bv = -INFINITY;
-      int32_t bi = -1;
-#pragma unroll
-      for (int j = 0; j < kChunks; ++j) {
-        const uint32_t off = (uint32_t)(j * kThreads + tid) * 16u;
-        if (off >= nbytes) continue;
-#pragma unroll
-        for (int e = 0; e < E; ++e) {
-          const float v = Elem<T>::get(q[j], e);
-          if (v > bv || (bi < 0 && v == v)) {
-            bv = v;
-            bi = p.body_first + (int32_t)(off / sizeof(T)) + e;
-          }
-        }
-      }
-      offer(bi >= 0, key_of(bv), bi);
-      if (s_cnt > n) sel_prune<1, kThreads>(sel, n, ps, tid);  // (uniform: nothing is pushed between the barrier in offer and here)
+    const int32_t tile_first = p.body_first + (int32_t)((uint32_t)t * kTileBytes / sizeof(T));
+    if (t == 0 || t == 3 || t == 15 || t == 63) {
+      // The threads' own maxima so far (lm) belong to disjoint sets of elements, so the n-th
+      // largest of them is a lower bound of the n-th largest element: the threshold can rise to
+      // it without a look at the buffer. Taken at 16-bit key resolution by one warp.
+      __syncthreads();  // (s_keys may still be read from the last time)
+      s_keys[tid] = lm > -INFINITY ? key_of(lm) : 0u;
       __syncthreads();
-      if (tid == 0) s_cnt = 0;  // only the threshold is kept: the tile is gone through again below
+      if (tid < 32) {
+        const uint32_t k = warp_kth16<kThreads / 32>(s_keys, n);
+        const unsigned long long cand = k ? ((unsigned long long)k << 32) - 1ull : 0ull;
+        if (tid == 0 && cand > s_tau) s_tau = cand;
+      }
       __syncthreads();
       tau = s_tau;
     }
     const uint32_t tkey = (uint32_t)(tau >> 32);
     const float tf = value_of(tkey < 0x007FFFFFu ? 0x007FFFFFu : tkey);  // inclusive value threshold
-    uint32_t bits = 0;  // this thread's elements that may still belong to the n best
+    // the chunks whose maximum reaches the threshold are few: only they are looked into, in a
+    // loop the warp leaves as soon as no lane has one
+    uint32_t hotc = 0;
 #pragma unroll
-    for (int j = 0; j < kChunks; ++j) {
-      const uint32_t off = (uint32_t)(j * kThreads + tid) * 16u;
-      if (off >= nbytes) continue;
-      if (!(Elem<T>::chunk_max(q[j]) >= tf)) continue;
+    for (int j = 0; j < kChunks; ++j) hotc |= (cmax[j] >= tf ? 1u : 0u) << j;
+    uint32_t bits = 0;
+    while (__any_sync(0xFFFFFFFFu, hotc != 0u)) {
+      if (hotc != 0u) {
+        const int j = __ffs(hotc) - 1;
+        hotc &= hotc - 1u;
+        uint4 c = q[0];
 #pragma unroll
-      for (int e = 0; e < E; ++e) bits |= (Elem<T>::get(q[j], e) >= tf ? 1u : 0u) << (j * E + e);
-    }
-    if (__syncthreads_or(bits != 0u)) {
-      for (;;) {
-        // this thread's next element above the (current) threshold
-        bool pr = false;
-        uint32_t ky = 0;
-        int32_t id = 0;
-        while (bits != 0u && !pr) {
-          const int idx = __ffs(bits) - 1;
-          bits &= bits - 1u;
-          ky = key_of(pick(idx, id));
-          pr = ky != 0u && comp_of(ky, id) > tau;
-        }
-        if (!__syncthreads_or(pr)) break;
-        offer(pr, ky, id);
+        for (int x = 1; x < kChunks; ++x)
+          if (j == x) c = q[x];
+#pragma unroll
+        for (int e = 0; e < E; ++e) bits |= (Elem<T>::get(c, e) >= tf ? 1u : 0u) << (j * E + e);
       }
     }
+    push_all(bits, [&](int idx, uint32_t& ky, int32_t& id) {
+      const int j = idx / E;
+      uint4 c = q[0];
+#pragma unroll
+      for (int x = 1; x < kChunks; ++x)
+        if (j == x) c = q[x];
+      id = tile_first + (int32_t)((uint32_t)(j * kThreads + tid) * 16u / sizeof(T)) + idx % E;
+      ky = key_of(Elem<T>::get(c, idx % E));
+    });
   }
 
   // ---- the few elements outside the 16-byte aligned body
   {
     const bool hv = tid < p.head_n, tv = tid < p.tail_n;
-    const float vh = hv ? Elem<T>::load(row + tid) : 0.0f;
+    const float vh = hv ? Elem<T>::load(row + lo + tid) : 0.0f;
     const float vt = tv ? Elem<T>::load(row + p.tail_first + tid) : 0.0f;
     if (hv) lse_one(vh);
     if (tv) lse_one(vt);
+    if (n > 0)
+      push_all((hv ? 1u : 0u) | (tv ? 2u : 0u), [&](int idx, uint32_t& ky, int32_t& id) {
+        ky = key_of(idx == 0 ? vh : vt);
+        id = idx == 0 ? lo + tid : p.tail_first + tid;
+      });
+  }
+
+  // the CTA's (maximum, sum of exponentials relative to it) from the threads' pairs; the sum is
+  // returned to thread 0
+  auto cta_lse = [&](float m_t, double s_t, float& M) -> double {
+    M = m_t;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
+    __syncthreads();  // (red_m / red_s may still be read from an earlier call)
+    if ((tid & 31) == 0) red_m[tid >> 5] = M;
+    __syncthreads();
+    M = red_m[0];
+#pragma unroll
+    for (int w = 1; w < kThreads / 32; ++w) M = fmaxf(M, red_m[w]);
+    double part = m_t > -INFINITY ? s_t * exp((double)m_t - (double)M) : 0.0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xFFFFFFFFu, part, o);
+    if ((tid & 31) == 0) red_s[tid >> 5] = part;
+    __syncthreads();
+    double z = 0.0;
+    if (tid == 0)
+      for (int w = 0; w < kThreads / 32; ++w) z += red_s[w];
+    return z;
+  };
+  float M;
+  double z = cta_lse(lm, ls, M);
+  // The buffer is left as it is unless it is long: where the n best are needed, an entry's place
+  // is the number of entries above it (composites are unique).
+  auto settle = [&]() -> int {
+    __syncthreads();
+    if (s_cnt > 512) {
+      sel_prune<1, kThreads>(sel, n, ps, tid);
+      __syncthreads();
+    }
+    return min(s_cnt, kLpCap);
+  };
+  auto rank_of = [&](int i, int c) -> int {
+    const uint64_t ci = comp_of(bkey[i], bid[i]);
+    int rank = 0;
+    for (int j = 0; j < c; ++j) rank += comp_of(bkey[j], bid[j]) > ci;
+    return rank;
+  };
+
+  if (a.nseg > 1) {
+    // ---- leave the segment's results; the CTA that finishes the row last merges them
+    const size_t slot = (size_t)b * a.nseg + seg;
+    const int c = n > 0 ? settle() : 0, m = min(c, n);
+    for (int i = tid; i < c; i += kThreads) {
+      const int rank = rank_of(i, c);
+      if (rank < n) a.ws_list[slot * n + rank] = comp_of(bkey[i], bid[i]);
+    }
+    if (tid == 0) {
+      LpPart pt;
+      pt.z = z;
+      pt.M = M;
+      pt.cnt = m;
+      a.ws_part[slot] = pt;
+    }
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      s_flag = atomicAdd(&a.ws_ctr[b], 1u) == (unsigned)a.nseg - 1u;
+      if (s_flag) a.ws_ctr[b] = 0u;  // left at zero for the next launch
+    }
+    __syncthreads();
+    if (!s_flag) return;
+    __threadfence();
+    float pm = -INFINITY;
+    double pz = 0.0;
+    int pc = 0;
+    if (tid < a.nseg) {
+      const LpPart* src = &a.ws_part[(size_t)b * a.nseg + tid];
+      pz = __ldcg(&src->z);
+      pm = __ldcg(&src->M);
+      pc = __ldcg(&src->cnt);
+    }
+    z = cta_lse(pm, pz, M);
     if (n > 0) {
-      uint32_t ky = hv ? key_of(vh) : 0u;
-      offer(ky != 0u && comp_of(ky, tid) > tau, ky, tid);
-      ky = tv ? key_of(vt) : 0u;
-      offer(ky != 0u && comp_of(ky, p.tail_first + tid) > tau, ky, p.tail_first + tid);
+      if (tid == 0) {
+        s_cnt = 0;
+        s_tau = 0ull;
+      }
+      __syncthreads();
+      tau = 0ull;
+      // the segments' lists go through the buffer, kThreads entries at a time
+      __shared__ int s_cnts[kMaxSeg];
+      if (tid < a.nseg) s_cnts[tid] = pc;
+      __syncthreads();
+      for (int e0 = 0; e0 < a.nseg * n; e0 += kThreads) {
+        const int e = e0 + tid, g = e / n, i = e % n;
+        const bool have = e < a.nseg * n && i < s_cnts[g];
+        const unsigned long long c = have ? __ldcg(&a.ws_list[((size_t)b * a.nseg + g) * n + i]) : 0ull;
+        push_all(have ? 1u : 0u, [&](int, uint32_t& ky, int32_t& id) {
+          ky = comp_key(c);
+          id = comp_id(c);
+        });
+      }
     }
   }
 
-  // ---- log of the sum: the threads' sums brought to the row's maximum
-  float M = lm;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
-  if ((tid & 31) == 0) red_m[tid >> 5] = M;
-  __syncthreads();
-  M = red_m[0];
-#pragma unroll
-  for (int w = 1; w < kThreads / 32; ++w) M = fmaxf(M, red_m[w]);
-  double part = lm > -INFINITY ? ls * exp((double)lm - (double)M) : 0.0;
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xFFFFFFFFu, part, o);
-  if ((tid & 31) == 0) red_s[tid >> 5] = part;
-  __syncthreads();
+  // ---- the row's output
   if (tid == 0) {
-    double z = 0.0;
-    for (int w = 0; w < kThreads / 32; ++w) z += red_s[w];
     const double lse = (double)M + log(z);  // tools/server_chat.h:422
     s_lse = lse;
     if (a.lse) a.lse[b] = lse;
@@ -249,24 +388,30 @@ __global__ void __launch_bounds__(kThreads) logprob_kernel(const LogprobDev a) {
     }
   }
   if (n <= 0) return;
-  __syncthreads();
-  if (s_cnt > n) sel_prune<1, kThreads>(sel, n, ps, tid);
-  __syncthreads();
-  // ---- best first: an entry's place is the number of entries above it (composites are unique)
-  const int m = min(s_cnt, n);
+  const int c = settle();  // (its barrier also publishes s_lse)
   const double lse = s_lse;
-  for (int i = tid; i < m; i += kThreads) {
-    const uint64_t c = comp_of(bkey[i], bid[i]);
-    int rank = 0;
-    for (int j = 0; j < m; ++j) rank += comp_of(bkey[j], bid[j]) > c;
-    a.top_id[(size_t)b * a.top_stride + rank] = bid[i];
-    a.top_logprob[(size_t)b * a.top_stride + rank] = (double)value_of(bkey[i]) - lse;
+  for (int i = tid; i < c; i += kThreads) {
+    const int rank = rank_of(i, c);
+    if (rank < n) {
+      a.top_id[(size_t)b * a.top_stride + rank] = bid[i];
+      a.top_logprob[(size_t)b * a.top_stride + rank] = (double)value_of(bkey[i]) - lse;
+    }
   }
 }
 
 }  // namespace arcs
 
 using namespace arcs;
+
+static void lp_plan(int32_t B, int32_t V, int* nseg, int* seg_len) { plan_segments(B, V, nseg, seg_len, kLpPerSm); }
+
+extern "C" size_t arcs_logprobs_workspace_bytes(int32_t B, int32_t V, int32_t top_n) {
+  if (B <= 0 || V <= 0 || top_n < 0) return 0;
+  int nseg, seg_len;
+  lp_plan(B, V, &nseg, &seg_len);
+  if (nseg == 1) return 16;  // whole rows: nothing is handed over
+  return 256 + (((size_t)B * 4 + 255) & ~(size_t)255) + (size_t)B * nseg * sizeof(LpPart) + (size_t)B * nseg * (size_t)top_n * 8;
+}
 
 extern "C" int arcs_logprobs_batch(const arcs_logprob_args* g, void* stream) {
   if (int inj = fault_injected()) return inj;
@@ -281,6 +426,7 @@ extern "C" int arcs_logprobs_batch(const arcs_logprob_args* g, void* stream) {
   a.row_stride = g->row_stride;
   a.B = g->B;
   a.V = g->V;
+  lp_plan(g->B, g->V, &a.nseg, &a.seg_len);
   a.token = g->token;
   a.top_n = g->top_n;
   a.top_stride = g->top_stride;
@@ -289,12 +435,27 @@ extern "C" int arcs_logprobs_batch(const arcs_logprob_args* g, void* stream) {
   a.top_id = g->top_id;
   a.top_logprob = g->top_logprob;
   a.status = g->status;
+  a.ws_ctr = nullptr;
+  a.ws_part = nullptr;
+  a.ws_list = nullptr;
+  if (a.nseg > 1) {
+    if (!g->workspace || g->workspace_bytes < arcs_logprobs_workspace_bytes(g->B, g->V, g->top_n))
+      return set_error(ARCS_ERR_WORKSPACE, "logprobs_batch: workspace too small");
+    if ((reinterpret_cast<uintptr_t>(g->workspace) & 15u) != 0) return set_error(ARCS_ERR_WORKSPACE, "logprobs_batch: workspace must be 16-byte aligned");
+    char* ws = static_cast<char*>(g->workspace);
+    a.ws_ctr = reinterpret_cast<unsigned int*>(ws);
+    ws += ((size_t)g->B * 4 + 255) & ~(size_t)255;
+    a.ws_part = reinterpret_cast<LpPart*>(ws);
+    ws += (size_t)g->B * a.nseg * sizeof(LpPart);
+    a.ws_list = reinterpret_cast<unsigned long long*>(ws);
+  }
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned grid = (unsigned)g->B * (unsigned)a.nseg;
 #define ARCS_LAUNCH(T)                                                                                               \
   do {                                                                                                               \
     cudaError_t e = cudaFuncSetAttribute(logprob_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLpSmem); \
     if (e != cudaSuccess) return set_error(ARCS_ERR_CUDA, cudaGetErrorString(e));                                    \
-    logprob_kernel<T><<<(unsigned)g->B, kThreads, kLpSmem, st>>>(a);                                                 \
+    logprob_kernel<T><<<grid, kThreads, kLpSmem, st>>>(a);                                                           \
   } while (0)
   if (g->dtype == ARCS_F32) ARCS_LAUNCH(float);
   else ARCS_LAUNCH(__nv_bfloat16);

@@ -177,6 +177,40 @@ __device__ __noinline__ void sel_prune(const Sel& s, int k, const PruneScratch& 
 }
 
 
+// A lower bound of the kth largest (1-based) of 32 * PER keys, found by ONE warp with a search
+// on the keys' upper 16 bits, two bits a round (bf16 resolution; exact for bf16 data): the
+// largest t with at least kth keys >= t. Keys in registers, no shared-memory atomics.
+template <int PER>
+__device__ __forceinline__ uint32_t warp_kth16(const uint32_t* keys, int kth) {
+  const int lane = threadIdx.x & 31;
+  uint32_t k[PER];
+#pragma unroll
+  for (int i = 0; i < PER / 4; ++i) {
+    const uint4 q = reinterpret_cast<const uint4*>(keys)[i * 32 + lane];
+    k[4 * i] = q.x;
+    k[4 * i + 1] = q.y;
+    k[4 * i + 2] = q.z;
+    k[4 * i + 3] = q.w;
+  }
+  uint32_t t = 0;
+#pragma unroll 1
+  for (int bit = 14; bit >= 0; bit -= 2) {
+    const uint32_t c1 = (t | (1u << bit)) << 16, c2 = (t | (2u << bit)) << 16, c3 = (t | (3u << bit)) << 16;
+    int n1 = 0, n2 = 0, n3 = 0;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) {
+      n1 += k[i] >= c1;
+      n2 += k[i] >= c2;
+      n3 += k[i] >= c3;
+    }
+    // three counts (each at most 32 * PER <= 1024) in one word, one reduction
+    const uint32_t all = __reduce_add_sync(0xFFFFFFFFu, (uint32_t)n1 | ((uint32_t)n2 << 11) | ((uint32_t)n3 << 22));
+    const int a1 = (int)(all & 0x7FFu), a2 = (int)((all >> 11) & 0x7FFu), a3 = (int)(all >> 22);
+    t |= (a3 >= kth ? 3u : a2 >= kth ? 2u : a1 >= kth ? 1u : 0u) << bit;
+  }
+  return t << 16;
+}
+
 // Bin of a key in an item's coarse histogram: the key's upper 16 bits (bf16 resolution) relative
 // to `base`, the last bin taking everything above.
 __device__ __forceinline__ uint32_t coarse_bin(uint32_t key, uint32_t base) {

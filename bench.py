@@ -121,6 +121,64 @@ def cpu_reference_rate(logits_f32, params, hist_off, hist_ids, seeds, threads, m
     return total_rows / total_t, out
 
 
+def bench_logprobs(args):
+    """Secondary workload (--workload logprobs, one GPU): arcs_logprobs_batch, the log probability
+    of one token per row and the 20 most likely alternatives (tools/server_chat.h:417-441), on the
+    same 1024 x 262144 bf16 logits. Prints its own JSON line."""
+    import numpy as np
+    import torch
+
+    import arcinfer_b200 as ab
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+    B, V, top_n = args.rows, args.vocab, 20
+    torch.cuda.set_device(0)
+    gen = torch.Generator(device="cuda").manual_seed(20261125)
+    logits = (torch.randn(B, V, device="cuda", generator=gen) * 3).to(torch.bfloat16)
+    token = torch.randint(0, V, (B,), device="cuda", dtype=torch.int32, generator=gen)
+    for _ in range(args.warmup):
+        out = ab.logprobs_batch(logits, token, top_n)
+    torch.cuda.synchronize()
+    assert int(out["status"][0]) == 0
+    clocks = ClockSampler(0)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        ab.logprobs_batch(logits, token, top_n)
+    e1.record()
+    torch.cuda.synchronize()
+    t_end = time.perf_counter() + 0.6  # (the timed steps take milliseconds: keep the same load up until the clocks have been sampled)
+    while time.perf_counter() < t_end:
+        ab.logprobs_batch(logits, token, top_n)
+        torch.cuda.synchronize()
+    clk = clocks.stop()
+    ms = e0.elapsed_time(e1) / args.steps
+    peak, which = measured_peak()
+    by = B * V * logits.element_size()
+    line = {
+        "metric": "logprob_rows_per_sec", "value": B / (ms * 1e-3), "unit": "rows/s", "n_gpus": 1, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16 logits, fp32 exponentials, fp64 sums", "data": "synthetic",
+        "config": {"workload": "logprobs", "rows_per_gpu": B, "vocab": V, "top_logprobs": top_n,
+                   "l2": "inputs (%d MiB) larger than L2" % (by >> 20)},
+        "roofline": {"bound": "hbm", "kernel": "logprob_kernel", "achieved": by / (ms * 1e-3) / 1e9, "peak": peak,
+                     "peak_source": which, "unit": "GB/s", "frac": by / (ms * 1e-3) / 1e9 / peak, "traffic": ncu_traffic("logprob_kernel_bf16_wide_batch"),
+                     "note": "issue-bound on the exponentials, not on HBM"},
+        "gpu_launches": args.steps, "clocks": clk,
+    }
+    if not args.no_cpu:
+        import orc  # the CPU restatement, as the timed baseline only
+
+        x = logits[:4].float().cpu().numpy()
+        tk = token[:4].cpu().numpy()
+        t0 = time.perf_counter()
+        for r in range(4):
+            orc.logprobs(x[r], int(tk[r]), top_n)
+        dt = time.perf_counter() - t0
+        line["cpu_baseline"] = {"value": 4 / dt, "unit": "rows/s", "cores": 1, "kind": "port", "sample": "4 rows of the workload, one thread"}
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -131,11 +189,17 @@ def main():
     ap.add_argument("--vocab", type=int, default=VOCAB)
     ap.add_argument("--shard", default="rows", choices=["rows", "vocab"],
                     help="how N GPUs split the work: rows (default, no collective) or vocabulary columns (one all-gather)")
+    ap.add_argument("--workload", default="wide-batch", choices=["wide-batch", "logprobs"],
+                    help="wide-batch: the sampling step (the headline); logprobs: arcs_logprobs_batch on the same logits, one GPU")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload == "logprobs" and args.impl == "ours":
+        if int(os.environ.get("RANK", "0")) == 0:
+            bench_logprobs(args)
+        return
 
     import numpy as np
     import torch

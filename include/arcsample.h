@@ -193,7 +193,8 @@ int arcs_dfa_mask(const uint16_t* table, int32_t n_table_states, int32_t dead, c
  * logprobs_batch: per row, the log probability of one token and the top_n most likely
  * alternatives, from the RAW logits (no penalty, no bias): the `logprobs` entry of
  * tools/server_chat.h:417-441, and the log-softmax that scores perplexity and KL
- * (zero/runz.cpp:478-484, :639-646). One pass over the logits, one launch, no workspace.
+ * (zero/runz.cpp:478-484, :639-646). One pass over the logits, one launch. When there are few
+ * rows each is cut into segments, whose results meet in the workspace.
  *   mx = max; z = sum exp(l - mx) accumulated in fp64; lse = mx + log(z);
  *   logprob[b] = l[token[b]] - lse;  top_id / top_logprob: the top_n largest logits, best first
  *   (equal logits: lower id first), as log probabilities.
@@ -213,9 +214,12 @@ typedef struct {
   double* lse;            /* [B] optional: log of the sum of exponentials */
   int32_t* top_id;        /* [B][top_stride]; entries past min(top_n, V) are not written */
   double* top_logprob;    /* [B][top_stride] */
-  int32_t* status;        /* device status word (OR-free: first error wins), may be NULL */
+  void* workspace;        /* arcs_logprobs_workspace_bytes(), zeroed once before first use */
+  size_t workspace_bytes;
+  int32_t* status;        /* device status word (first error wins), may be NULL */
 } arcs_logprob_args;
 
+size_t arcs_logprobs_workspace_bytes(int32_t B, int32_t V, int32_t top_n);
 int arcs_logprobs_batch(const arcs_logprob_args* args, void* stream);
 
 /* ------------------------------------------------------------------------------------------

@@ -371,27 +371,27 @@ double orc_logprobs(const float* l, int V, int32_t token, int top_n, double* log
   const double lse = mx + log(z);                             /* :422 */
   if (token >= 0 && token < V && logprob) *logprob = (double)l[token] - lse;  /* :427 */
   if (top_n > V) top_n = V;
-  /* :433-438: the top_n largest, best first; selection by repeated scan (top_n <= 256) */
-  double last_v = INFINITY;
-  int last_id = -1;
-  for (int r = 0; r < top_n; ++r) {
-    int best = -1;
-    for (int i = 0; i < V; ++i) {
-      const double v = l[i];
-      if (v != v) continue;
-      /* after (last_v, last_id) in the order (value desc, id asc) */
-      if (!(v < last_v || (v == last_v && i > last_id))) continue;
-      if (best < 0 || v > (double)l[best]) best = i;
+  /* :433-438: the top_n largest, best first: one scan that keeps a sorted list (top_n <= 256);
+   * a precedes b when l[a] > l[b], or they are equal and a < b */
+  int m = 0;
+  for (int i = 0; i < V && top_n > 0; ++i) {
+    const float v = l[i];
+    if (v != v) continue;
+    if (m == top_n && !(v > l[top_id[m - 1]])) continue; /* (equal to the last: the later id loses) */
+    int pos = m < top_n ? m : top_n - 1;
+    while (pos > 0 && v > l[top_id[pos - 1]]) {
+      top_id[pos] = top_id[pos - 1];
+      --pos;
     }
-    if (best < 0) {
+    top_id[pos] = i;
+    if (m < top_n) ++m;
+  }
+  for (int r = 0; r < top_n; ++r) {
+    if (r < m) top_logprob[r] = (double)l[top_id[r]] - lse;
+    else {
       top_id[r] = -1;
       top_logprob[r] = NAN;
-      continue;
     }
-    top_id[r] = best;
-    top_logprob[r] = (double)l[best] - lse;
-    last_v = l[best];
-    last_id = best;
   }
   return lse;
 }

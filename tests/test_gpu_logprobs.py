@@ -70,7 +70,7 @@ def test_logprobs_full_rows(bf16):
     """rows of the reference's vocabularies; alternatives 20 (the reference's maximum) and 256"""
     g = np.random.default_rng(22)
     worst = 0.0
-    for V, B, top_n in [(151936, 8, 20), (262144, 4, 20), (262144, 2, 256), (151936, 2, 5)]:
+    for V, B, top_n in [(151936, 8, 20), (262144, 4, 20), (262144, 2, 256), (151936, 2, 5), (50000, 64, 20), (30000, 600, 3)]:
         x = (g.standard_normal((B, V), dtype=np.float32) * 3).astype(np.float32)
         x[0, :: max(1, V // 50)] += 9.0
         xb = synth.f32_to_bf16_bits(x) if bf16 else x
