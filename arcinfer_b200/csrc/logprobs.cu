@@ -38,30 +38,15 @@ struct LogprobDev {
   int32_t* status;
 };
 
-// exp(v - m) for v <= m: 2^t with t = (v - m) * log2(e) rounded to float, corrected to first
-// order by everything the roundings dropped: the error of the float difference (recovered by a
-// two-sum; EXACT8: both operands carry 8 significant bits, bf16 data, where the difference is
-// nearly always exact and the three-operation form recovers what is not), of the product, and
-// the low part of log2(e). NaN and -inf give 0.
-template <bool EXACT8>
+// exp(v - m) for v <= m as 2^((v - m) * log2 e) by the special-function unit. Measured against
+// fp64 sums the log of a row's sum comes out within 4e-8 whatever is done about the roundings of
+// the difference and of the product (first-order corrections were tried: the unit's own error
+// dominates), so nothing is. NaN and -inf give 0.
 __device__ __forceinline__ float exp_diff(float v, float m) {
-  constexpr float kL2eHi = 1.44269502162933349609375f, kL2eLo = 1.92596299112661746e-8f, kLn2 = 0.693147180559945f;
-  v = fmaxf(v, -1e38f);
-  const float s = __fsub_rn(v, m);
-  float err;
-  if (EXACT8) {
-    err = __fsub_rn(v, __fadd_rn(s, m));
-  } else {
-    const float bb = __fsub_rn(s, v);
-    err = __fadd_rn(__fsub_rn(v, __fsub_rn(s, bb)), __fsub_rn(-m, bb));
-  }
-  const float t = __fmul_rn(s, kL2eHi);
-  float c = fmaf(s, kL2eHi, -t);
-  c = fmaf(s, kL2eLo, c);
-  c = fmaf(err, kL2eHi, c);
+  constexpr float kL2e = 1.44269502162933349609375f;
   float e;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(t));
-  return fmaf(e, c * kLn2, e);
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(__fmul_rn(__fsub_rn(fmaxf(v, -1e38f), m), kL2e)));
+  return e;
 }
 
 // Warp-collective append to the candidate buffer; lanes with p set store (key, id). Returns true
@@ -97,6 +82,7 @@ __global__ void __launch_bounds__(kThreads) logprob_kernel(const LogprobDev a) {
   __shared__ __align__(8) uint64_t bars[kStages];
   __shared__ unsigned long long s_tau, s_m64;
   __shared__ int s_cnt, s_misc[8], s_flag;
+  __shared__ uint32_t s_maxkey;
   __shared__ float red_m[kThreads / 32];
   __shared__ double red_s[kThreads / 32], s_lse;
   __shared__ __align__(16) uint32_t s_keys[kThreads];
@@ -125,38 +111,98 @@ __global__ void __launch_bounds__(kThreads) logprob_kernel(const LogprobDev a) {
 
   float lm = -INFINITY;  // what this thread's exponentials are relative to: at least every value it has seen
   double ls = 0.0;
+  float own = -INFINITY;  // the largest value this thread itself has seen
   unsigned long long tau = 0ull;  // exclusive threshold of the candidate buffer (every thread's copy is current)
 
   // one more value for the sum
   auto lse_one = [&](float v) {
+    own = fmaxf(own, v);
     if (v > lm) {
       ls *= exp((double)lm - (double)v);
       lm = v;
     }
-    if (lm > -INFINITY) ls += (double)exp_diff<false>(v, lm);
+    if (lm > -INFINITY) ls += (double)exp_diff(v, lm);
+  };
+  // All threads call. The threads' own maxima belong to disjoint sets of elements, so the n-th
+  // largest of them is a lower bound of the n-th largest element: the threshold rises to it
+  // without a look at the buffer (16-bit key resolution, one warp). The largest of them becomes
+  // every thread's reference for its exponentials: a thread then meets a larger value, and pays
+  // for the fp64 rescaling of its sum, only where the CTA as a whole does.
+  auto share_maxima = [&](bool reference) {
+    __syncthreads();  // (s_keys may still be read from the last time)
+    s_keys[tid] = own > -INFINITY ? key_of(own) : 0u;
+    __syncthreads();
+    if (tid < 32) {
+      uint32_t mk = 0;
+#pragma unroll
+      for (int i = 0; i < kThreads / 32; ++i) mk = max(mk, s_keys[i * 32 + tid]);
+      mk = __reduce_max_sync(0xFFFFFFFFu, mk);
+      const uint32_t k = n > 0 ? warp_kth16<kThreads / 32>(s_keys, n) : 0u;
+      const unsigned long long cand = k ? ((unsigned long long)k << 32) - 1ull : 0ull;
+      if (tid == 0) {
+        s_maxkey = mk;
+        if (cand > s_tau) s_tau = cand;
+      }
+    }
+    __syncthreads();
+    tau = s_tau;
+    if (reference && s_maxkey != 0u) {
+      const float top = value_of(s_maxkey);
+      if (top > lm) {
+        ls *= exp((double)lm - (double)top);
+        lm = top;
+      }
+    }
+  };
+  // A lane sets the (few) elements it finds above the threshold aside, two at most, and the warp
+  // appends what its lanes hold to the buffer in one go, now and then: an append costs the warp
+  // a round trip to a shared counter.
+  uint32_t sk0 = 0, sk1 = 0;
+  int32_t si0 = 0, si1 = 0;
+  int ns = 0;
+  bool hot = false;
+  auto warp_flush = [&]() {
+    const bool lost1 = lp_push(sel, ns == 2 && comp_of(sk1, si1) > tau, sk1, si1, hot);
+    if (ns == 2 && !lost1) ns = 1;
+    const bool lost0 = lp_push(sel, ns == 1 && comp_of(sk0, si0) > tau, sk0, si0, hot);
+    if (ns == 1 && !lost0) ns = 0;
   };
   // Every thread calls with the mask of its own elements that may belong to the n best;
-  // elem(idx, key, id) names element idx. The elements above the threshold go into the buffer as
-  // they come; when the buffer has grown past the trigger, or had no room for some, the CTA keeps
-  // the n best, the threshold rises and the elements left out are offered again.
-  auto push_all = [&](uint32_t bits, auto elem) {
+  // elem(idx, key, id) names element idx. `flush`: what the lanes hold goes to the buffer before
+  // the call returns. When the buffer has grown past the trigger, or had no room for some entry,
+  // the CTA keeps the n best, the threshold rises and what was left out is offered again.
+  auto push_all = [&](uint32_t bits, bool flush, auto elem) {
     uint32_t again = 0;
-    bool hot = false;
     for (;;) {
       while (__any_sync(0xFFFFFFFFu, bits != 0u)) {
-        const bool valid = bits != 0u;
-        const int idx = valid ? __ffs(bits) - 1 : 0;
-        bits &= bits - 1u;
-        uint32_t ky = 0;
-        int32_t id = 0;
-        if (valid) elem(idx, ky, id);
-        const bool pr = valid && ky != 0u && comp_of(ky, id) > tau;
-        if (lp_push(sel, pr, ky, id, hot)) again |= 1u << idx;
+        if (__any_sync(0xFFFFFFFFu, bits != 0u && ns == 2)) warp_flush();
+        if (bits != 0u) {
+          const int idx = __ffs(bits) - 1;
+          bits &= bits - 1u;
+          if (ns < 2) {
+            uint32_t ky = 0;
+            int32_t id = 0;
+            elem(idx, ky, id);
+            if (ky != 0u && comp_of(ky, id) > tau) {
+              if (ns == 0) {
+                sk0 = ky;
+                si0 = id;
+              } else {
+                sk1 = ky;
+                si1 = id;
+              }
+              ++ns;
+            }
+          } else {
+            again |= 1u << idx;  // (the buffer is full: after the prune)
+          }
+        }
       }
-      if (!__syncthreads_or(hot || again != 0u)) break;
+      if (flush) warp_flush();
+      if (!__syncthreads_or(hot || again != 0u || (flush && ns > 0))) break;
       const unsigned long long before = tau;
-      sel_prune<1, kThreads>(sel, n, ps, tid);  // (more than kLpTrig >= n entries: it does not return early)
-      if (s_tau < before) {  // (entries offered again were not in the buffer: its n-th best may lie below the threshold)
+      sel_prune<1, kThreads>(sel, n, ps, tid);
+      if (s_tau < before) {  // (entries still held by lanes were not in the buffer: its n-th best may lie below the threshold)
         __syncthreads();
         if (tid == 0) s_tau = before;
         __syncthreads();
@@ -199,6 +245,7 @@ __global__ void __launch_bounds__(kThreads) logprob_kernel(const LogprobDev a) {
       if (off >= nbytes) continue;
       const float cm = Elem<T>::chunk_max(q[j]);
       cmax[j] = cm;
+      own = fmaxf(own, cm);
       if (cm > lm) {
         ls *= exp((double)lm - (double)cm);
         lm = cm;
@@ -206,7 +253,7 @@ __global__ void __launch_bounds__(kThreads) logprob_kernel(const LogprobDev a) {
       if (lm > -INFINITY) {
         float ev[E];
 #pragma unroll
-        for (int e = 0; e < E; ++e) ev[e] = exp_diff<sizeof(T) == 2>(Elem<T>::get(q[j], e), lm);
+        for (int e = 0; e < E; ++e) ev[e] = exp_diff(Elem<T>::get(q[j], e), lm);
 #pragma unroll
         for (int w = E / 2; w > 0; w >>= 1)
 #pragma unroll
@@ -214,25 +261,11 @@ __global__ void __launch_bounds__(kThreads) logprob_kernel(const LogprobDev a) {
         ls += (double)ev[0];
       }
     }
+    if (t == 0 || t == 3 || t == 15 || t == 63) share_maxima(true);
     if (n <= 0) continue;
 
     // ---- the candidates
     const int32_t tile_first = p.body_first + (int32_t)((uint32_t)t * kTileBytes / sizeof(T));
-    if (t == 0 || t == 3 || t == 15 || t == 63) {
-      // The threads' own maxima so far (lm) belong to disjoint sets of elements, so the n-th
-      // largest of them is a lower bound of the n-th largest element: the threshold can rise to
-      // it without a look at the buffer. Taken at 16-bit key resolution by one warp.
-      __syncthreads();  // (s_keys may still be read from the last time)
-      s_keys[tid] = lm > -INFINITY ? key_of(lm) : 0u;
-      __syncthreads();
-      if (tid < 32) {
-        const uint32_t k = warp_kth16<kThreads / 32>(s_keys, n);
-        const unsigned long long cand = k ? ((unsigned long long)k << 32) - 1ull : 0ull;
-        if (tid == 0 && cand > s_tau) s_tau = cand;
-      }
-      __syncthreads();
-      tau = s_tau;
-    }
     const uint32_t tkey = (uint32_t)(tau >> 32);
     const float tf = value_of(tkey < 0x007FFFFFu ? 0x007FFFFFu : tkey);  // inclusive value threshold
     // the chunks whose maximum reaches the threshold are few: only they are looked into, in a
@@ -253,7 +286,7 @@ __global__ void __launch_bounds__(kThreads) logprob_kernel(const LogprobDev a) {
         for (int e = 0; e < E; ++e) bits |= (Elem<T>::get(c, e) >= tf ? 1u : 0u) << (j * E + e);
       }
     }
-    push_all(bits, [&](int idx, uint32_t& ky, int32_t& id) {
+    push_all(bits, (t & 7) == 7 || t + 1 == p.tiles, [&](int idx, uint32_t& ky, int32_t& id) {
       const int j = idx / E;
       uint4 c = q[0];
 #pragma unroll
@@ -272,7 +305,7 @@ __global__ void __launch_bounds__(kThreads) logprob_kernel(const LogprobDev a) {
     if (hv) lse_one(vh);
     if (tv) lse_one(vt);
     if (n > 0)
-      push_all((hv ? 1u : 0u) | (tv ? 2u : 0u), [&](int idx, uint32_t& ky, int32_t& id) {
+      push_all((hv ? 1u : 0u) | (tv ? 2u : 0u), true, [&](int idx, uint32_t& ky, int32_t& id) {
         ky = key_of(idx == 0 ? vh : vt);
         id = idx == 0 ? lo + tid : p.tail_first + tid;
       });
@@ -302,9 +335,26 @@ __global__ void __launch_bounds__(kThreads) logprob_kernel(const LogprobDev a) {
   };
   float M;
   double z = cta_lse(lm, ls, M);
-  // The buffer is left as it is unless it is long: where the n best are needed, an entry's place
-  // is the number of entries above it (composites are unique).
-  auto settle = [&]() -> int {
+  // What is left of the buffer once a last threshold (from the threads' own maxima, where the
+  // buffer holds this CTA's own elements) has been applied: a little more than n entries as a
+  // rule. Where the n best are needed, an entry's place is the number of entries above it
+  // (composites are unique).
+  auto settle = [&](bool own_elements) -> int {
+    if (own_elements) share_maxima(false);
+    else __syncthreads();
+    const int c0 = min(s_cnt, kLpCap);
+    unsigned long long mine[kLpCap / kThreads];
+#pragma unroll
+    for (int x = 0; x < kLpCap / kThreads; ++x) {
+      const int i = tid + x * kThreads;
+      mine[x] = i < c0 ? comp_of(bkey[i], bid[i]) : 0ull;
+    }
+    __syncthreads();
+    if (tid == 0) s_cnt = 0;
+    __syncthreads();
+    bool hot = false;
+#pragma unroll
+    for (int x = 0; x < kLpCap / kThreads; ++x) lp_push(sel, mine[x] > tau, comp_key(mine[x]), comp_id(mine[x]), hot);
     __syncthreads();
     if (s_cnt > 512) {
       sel_prune<1, kThreads>(sel, n, ps, tid);
@@ -322,7 +372,7 @@ __global__ void __launch_bounds__(kThreads) logprob_kernel(const LogprobDev a) {
   if (a.nseg > 1) {
     // ---- leave the segment's results; the CTA that finishes the row last merges them
     const size_t slot = (size_t)b * a.nseg + seg;
-    const int c = n > 0 ? settle() : 0, m = min(c, n);
+    const int c = n > 0 ? settle(true) : 0, m = min(c, n);
     for (int i = tid; i < c; i += kThreads) {
       const int rank = rank_of(i, c);
       if (rank < n) a.ws_list[slot * n + rank] = comp_of(bkey[i], bid[i]);
@@ -368,7 +418,7 @@ __global__ void __launch_bounds__(kThreads) logprob_kernel(const LogprobDev a) {
         const int e = e0 + tid, g = e / n, i = e % n;
         const bool have = e < a.nseg * n && i < s_cnts[g];
         const unsigned long long c = have ? __ldcg(&a.ws_list[((size_t)b * a.nseg + g) * n + i]) : 0ull;
-        push_all(have ? 1u : 0u, [&](int, uint32_t& ky, int32_t& id) {
+        push_all(have ? 1u : 0u, true, [&](int, uint32_t& ky, int32_t& id) {
           ky = comp_key(c);
           id = comp_id(c);
         });
@@ -388,7 +438,7 @@ __global__ void __launch_bounds__(kThreads) logprob_kernel(const LogprobDev a) {
     }
   }
   if (n <= 0) return;
-  const int c = settle();  // (its barrier also publishes s_lse)
+  const int c = settle(a.nseg == 1);  // (its barriers also publish s_lse)
   const double lse = s_lse;
   for (int i = tid; i < c; i += kThreads) {
     const int rank = rank_of(i, c);
