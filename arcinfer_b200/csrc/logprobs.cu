@@ -269,7 +269,7 @@ __global__ void __launch_bounds__(kThreads) logprob_kernel(const LogprobDev a) {
     const uint32_t tkey = (uint32_t)(tau >> 32);
     const float tf = value_of(tkey < 0x007FFFFFu ? 0x007FFFFFu : tkey);  // inclusive value threshold
     // the chunks whose maximum reaches the threshold are few: only they are looked into, in a
-    // loop the warp leaves as soon as no lane has one
+    // loop the warp leaves as soon as no lane has one; what passes is set aside by the lane
     uint32_t hotc = 0;
 #pragma unroll
     for (int j = 0; j < kChunks; ++j) hotc |= (cmax[j] >= tf ? 1u : 0u) << j;
@@ -282,8 +282,27 @@ __global__ void __launch_bounds__(kThreads) logprob_kernel(const LogprobDev a) {
 #pragma unroll
         for (int x = 1; x < kChunks; ++x)
           if (j == x) c = q[x];
+        const int32_t id0 = tile_first + (int32_t)((uint32_t)(j * kThreads + tid) * 16u / sizeof(T));
 #pragma unroll
-        for (int e = 0; e < E; ++e) bits |= (Elem<T>::get(c, e) >= tf ? 1u : 0u) << (j * E + e);
+        for (int e = 0; e < E; ++e) {
+          const float v = Elem<T>::get(c, e);
+          if (v >= tf) {
+            const uint32_t ky = key_of(v);
+            if (ky != 0u && comp_of(ky, id0 + e) > tau) {
+              if (ns == 0) {
+                sk0 = ky;
+                si0 = id0 + e;
+                ns = 1;
+              } else if (ns == 1) {
+                sk1 = ky;
+                si1 = id0 + e;
+                ns = 2;
+              } else {
+                bits |= 1u << (j * E + e);  // (no room in the lane: the general path below)
+              }
+            }
+          }
+        }
       }
     }
     push_all(bits, (t & 7) == 7 || t + 1 == p.tiles, [&](int idx, uint32_t& ky, int32_t& id) {
