@@ -3,17 +3,20 @@ greedy draft acceptance) behind the sampler interface of rizagp/arcinfer.
 
 The compute path is the CUDA library ``lib/libarcsample.so`` (sources in ``csrc/``, C ABI in
 ``include/arcsample.h``); this package is the thin Python binding used by the tests and the
-benchmark. There is no CPU fallback: importing :mod:`arcinfer_b200.capi` fails when the
-library has not been built.
+benchmark. There is no CPU fallback: the first use of any binding name below imports
+:mod:`arcinfer_b200.capi`, which fails when the library has not been built. Importing the
+package alone (or :mod:`arcinfer_b200.synth`, :mod:`arcinfer_b200.params`) loads nothing, so a
+process that only generates inputs does not map the CUDA library.
 """
-from .capi import (  # noqa: F401
-    ArcsError,
-    PARAMS_DTYPE,
-    argmax_batch,
-    dfa_mask,
-    lib,
-    logprobs_batch,
-    make_params,
-    merge_batch,
-    sample_batch,
-)
+from .params import PARAMS_DTYPE, make_params  # noqa: F401
+
+_CAPI_NAMES = ("ArcsError", "argmax_batch", "dfa_mask", "lib", "logprobs_batch", "merge_batch", "sample_batch")
+
+
+def __getattr__(name):
+    if name == "capi" or name in _CAPI_NAMES:
+        import importlib
+
+        capi = importlib.import_module(".capi", __name__)
+        return capi if name == "capi" else getattr(capi, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

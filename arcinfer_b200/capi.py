@@ -14,19 +14,7 @@ HEAD = 512
 F32, BF16 = 0, 1
 FLAG_TIE_TOPK, FLAG_FIRST_REFUSED, FLAG_TAIL_SKIPPED, FLAG_TAIL_USED = 1, 2, 4, 8
 
-# arcs_row_params: SamplingParams of the reference (tools/sampler.h:15-26) without seed / logit_bias
-PARAMS_DTYPE = np.dtype(
-    [
-        ("temperature", "<f4"),
-        ("top_p", "<f4"),
-        ("min_p", "<f4"),
-        ("presence_penalty", "<f4"),
-        ("frequency_penalty", "<f4"),
-        ("repeat_penalty", "<f4"),
-        ("repeat_last_n", "<i4"),
-        ("top_k", "<i4"),
-    ]
-)
+from .params import PARAMS_DTYPE, make_params  # noqa: E402,F401
 
 
 class ArcsError(RuntimeError):
@@ -126,15 +114,6 @@ def _dtype_code(t):
     if t.dtype == torch.bfloat16:
         return BF16
     raise ArcsError(f"logits must be float32 or bfloat16, not {t.dtype}")
-
-
-def make_params(n=1, **kw):
-    """n rows of SamplingParams defaults (tools/sampler.h:16-22), fields overridden by kw."""
-    p = np.zeros(n, PARAMS_DTYPE)
-    p["temperature"], p["top_p"], p["repeat_penalty"], p["repeat_last_n"], p["top_k"] = 1.0, 0.95, 1.0, 64, 20
-    for k, v in kw.items():
-        p[k] = v
-    return p
 
 
 def params_to_device(p, device):

@@ -2,7 +2,7 @@
 // draft-acceptance count per slot. One launch: every CTA streams one segment of one row, folds
 // its (value, id) into a 64-bit atomic max per row, and the CTA that finishes last decodes the
 // rows and walks the slots.
-#include <atomic>
+#include <mutex>
 
 #include "plan.h"
 #include "stream.cuh"
@@ -91,12 +91,14 @@ __global__ void __launch_bounds__(kThreads) argmax_kernel(const ArgmaxDev a) {
     }
     // every thread has taken its chunks: the slot can be refilled
     if (__syncthreads_or(failed)) {
+      // A bounded wait ran out: the status word marks the call's results invalid. The CTA still
+      // takes part in the count below, so that the last CTA leaves the scratch clean for the next call.
       if (tid == 0) {
         raise_status(a.status, ARCS_ERR_TIMEOUT);
         drain_tiles(p, t, bars);
       }
       __syncthreads();
-      return;
+      break;
     }
     if (tid == 0 && t + kStages < p.tiles) issue_tile(p, t + kStages, stage, bars);
 #pragma unroll
@@ -263,7 +265,7 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 namespace {
 constexpr int kMaxDevices = 64;
 void* g_static_ptr[kMaxDevices];           // device address of g_static_scratch, per device
-std::atomic<int> g_static_ready[kMaxDevices];
+std::mutex g_static_mu;                    // guards the per-device set-up
 }  // namespace
 
 extern "C" size_t arcs_argmax_static_scratch_bytes(void) { return kStaticScratchBytes; }
@@ -276,24 +278,37 @@ extern "C" int arcs_argmax_batch_static(const arcs_argmax_args* g, void* stream)
              g->R, g->V, need, kStaticScratchBytes);
     return ARCS_ERR_WORKSPACE;
   }
+  // The array that is used is the one of the device the stream belongs to, which must be the
+  // current device (a launch on another device's stream fails anyway).
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return set_error(ARCS_ERR_CUDA, cudaGetErrorString(e));
-  if (dev < 0 || dev >= kMaxDevices) return set_error(ARCS_ERR_ARG, "argmax_batch_static: device index out of range");
-  if (!g_static_ready[dev].load(std::memory_order_acquire)) {
-    // Set-up, once per device, with that device current: in host code the array's name is only a
-    // handle; the address a kernel can use comes from the runtime. The array is cleared here
-    // because the kernels rely on finding (and leaving) their counters at zero.
-    void* p = nullptr;
-    e = cudaGetSymbolAddress(&p, g_static_scratch);
-    if (e != cudaSuccess || !p) return set_error(ARCS_ERR_CUDA, e != cudaSuccess ? cudaGetErrorString(e) : "no address for the scratch array");
-    e = cudaMemsetAsync(p, 0, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
+  if (stream) {
+    int sdev = dev;
+    e = cudaStreamGetDevice(static_cast<cudaStream_t>(stream), &sdev);
     if (e != cudaSuccess) return set_error(ARCS_ERR_CUDA, cudaGetErrorString(e));
-    g_static_ptr[dev] = p;
-    g_static_ready[dev].store(1, std::memory_order_release);
+    if (sdev != dev) return set_error(ARCS_ERR_ARG, "argmax_batch_static: the stream belongs to another device than the current one");
+  }
+  if (dev < 0 || dev >= kMaxDevices) return set_error(ARCS_ERR_ARG, "argmax_batch_static: device index out of range");
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_ptr[dev]) {
+      // Set-up, once per device, with that device current: in host code the array's name is only a
+      // handle; the address a kernel can use comes from the runtime. The array is cleared here
+      // (one thread at a time does this, so the clearing is enqueued once) because the kernels
+      // rely on finding, and leaving, their counters at zero.
+      void* p = nullptr;
+      e = cudaGetSymbolAddress(&p, g_static_scratch);
+      if (e != cudaSuccess || !p) return set_error(ARCS_ERR_CUDA, e != cudaSuccess ? cudaGetErrorString(e) : "no address for the scratch array");
+      e = cudaMemsetAsync(p, 0, kStaticScratchBytes, static_cast<cudaStream_t>(stream));
+      if (e != cudaSuccess) return set_error(ARCS_ERR_CUDA, cudaGetErrorString(e));
+      g_static_ptr[dev] = p;
+    }
+    scratch = g_static_ptr[dev];
   }
   arcs_argmax_args a = *g;
-  a.workspace = g_static_ptr[dev];
+  a.workspace = scratch;
   a.workspace_bytes = kStaticScratchBytes;
   return arcs_argmax_batch(&a, stream);
 }

@@ -134,8 +134,10 @@ static int32_t chunk_rows(const arcs_host_ctx* c, int32_t B, int32_t V) {
 }
 
 static int finish(arcs_host_ctx* c) {
-  CU(cudaMemcpyAsync(&c->last_status, c->status, sizeof(int32_t), cudaMemcpyDeviceToHost, c->st[0]));
+  // the status word is read after the kernels of BOTH streams have ended: row chunks alternate
+  // between the streams, and a chunk on the second one may be the one that raises it
   CU(cudaStreamSynchronize(c->st[1]));
+  CU(cudaMemcpyAsync(&c->last_status, c->status, sizeof(int32_t), cudaMemcpyDeviceToHost, c->st[0]));
   CU(cudaStreamSynchronize(c->st[0]));
   if (c->last_status != 0) {  // leave the scratch clean for the next call
     CU(cudaMemset(c->ws_argmax, 0, c->ws_bytes));

@@ -4,7 +4,7 @@ the host; bf16 data are fp32 draws rounded to nearest-even and carried as uint16
 """
 import numpy as np
 
-from .capi import PARAMS_DTYPE, make_params
+from .params import PARAMS_DTYPE, make_params  # noqa: F401
 
 BASE_SEED = 20261125
 

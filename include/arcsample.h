@@ -172,7 +172,10 @@ int arcs_argmax_batch(const arcs_argmax_args* args, void* stream);
  * ARCS_ERR_WORKSPACE. The first call on a device looks the array's device address up and clears
  * it on the given stream: make that call before capturing a stream. All calls on a device share
  * the array: two calls that overlap on the GPU (different streams) race; calls on one stream are
- * safe, each leaves the array clean for the next. No allocation is made by this call. */
+ * safe, each leaves the array clean for the next (also a call whose bounded device wait ran out
+ * and set ARCS_ERR_TIMEOUT in the status word). The set-up is guarded by a lock, so first calls
+ * from several host threads enqueue the clearing once. The stream must belong to the current
+ * device. No allocation is made by this call. */
 size_t arcs_argmax_static_scratch_bytes(void);
 int arcs_argmax_batch_static(const arcs_argmax_args* args, void* stream);
 
@@ -198,9 +201,10 @@ int arcs_dfa_mask(const uint16_t* table, int32_t n_table_states, int32_t dead, c
  *   mx = max; z = sum exp(l - mx) accumulated in fp64; lse = mx + log(z);
  *   logprob[b] = l[token[b]] - lse;  top_id / top_logprob: the top_n largest logits, best first
  *   (equal logits: lower id first), as log probabilities.
- * The reference sums fp64 exponentials in index order; here each term is a float exponential of
- * the exactly compensated difference, summed in fp64 in another order: log probabilities agree
- * to about 1e-7 absolute. NaN logits are skipped.
+ * The reference sums fp64 exponentials in index order; here each term is a single-precision
+ * exponential (ex2.approx of the rounded product (l - m) * log2 e), summed pairwise in fp32 per
+ * 16-byte chunk and then in fp64, in another order: lse agrees with an fp64 log-sum-exp to about
+ * 4e-8 absolute on the tested distributions (the tests hold it to 1e-6). NaN logits are skipped.
  * ---------------------------------------------------------------------------------------- */
 typedef struct {
   const void* logits;     /* [B][row_stride] device */

@@ -10,6 +10,7 @@ import numpy as np
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 ORC_SO = os.path.join(ROOT, "oracle", "_build", "libarcs_oracle.so")
 REF_SO = os.path.join(ROOT, "oracle", "_ref", "libarcs_ref.so")
+REFSLICES_SO = os.path.join(ROOT, "oracle", "_ref", "libarcs_refslices.so")
 
 PARAMS_DTYPE = np.dtype(
     [("temperature", "<f4"), ("top_p", "<f4"), ("min_p", "<f4"), ("presence_penalty", "<f4"),
@@ -29,11 +30,16 @@ def _build_oracle():
 
 orc = _build_oracle()
 ref = C.CDLL(REF_SO) if os.path.exists(REF_SO) else None
+# fragments of reference files that do not compile here as a whole (oracle/ref_slices.cpp)
+refslices = C.CDLL(REFSLICES_SO) if os.path.exists(REFSLICES_SO) else None
 
 orc.orc_softmax_den.restype = C.c_double
 orc.orc_softmax_den_exact.restype = C.c_double
 orc.orc_argmax.restype = C.c_int32
 orc.orc_logprobs.restype = C.c_double
+if refslices is not None:
+    refslices.ref_softmax_den.restype = C.c_double
+    refslices.ref_lp_entry.restype = C.c_double
 if ref is not None:
     ref.ref_sample_batch.restype = C.c_double
     ref.ref_hardware_threads.restype = C.c_int
@@ -161,3 +167,20 @@ def ref_uniform(seed, tot, n):
     out = np.zeros(n, np.float64)
     ref.ref_uniform(C.c_uint64(seed), C.c_double(tot), n, _p(out))
     return out
+
+
+def ref_softmax_den(row, mx):
+    """the reference's own softmax_den (zero/engine_drafters.h), cut out of its file at build time"""
+    assert refslices is not None
+    row = _f32(row)
+    return refslices.ref_softmax_den(_p(row), C.c_int64(len(row)), C.c_float(mx))
+
+
+def ref_lp_entry(row, token=-1, top_n=0):
+    """the arithmetic of the reference's lp_entry lambda (tools/server_chat.h), cut out at build time"""
+    assert refslices is not None
+    row = _f32(row)
+    lp = np.full(1, np.nan, np.float64)
+    ids, tlp = np.full(max(top_n, 1), -1, np.int32), np.full(max(top_n, 1), np.nan, np.float64)
+    lse = refslices.ref_lp_entry(_p(row), len(row), int(token), int(top_n), _p(lp), _p(ids), _p(tlp))
+    return lse, lp[0], ids[:top_n], tlp[:top_n]

@@ -58,8 +58,9 @@ def test_spec_verify_config3():
         mx = xf[r].max()
         assert got["max_sumexp"][r, 0] == mx
         z = orc.softmax_den(xf[r], mx, exact=True)
-        assert abs(got["max_sumexp"][r, 1] - z) <= 1e-6 * z
-        assert abs(got["max_sumexp"][r, 1] - orc.softmax_den(xf[r], mx)) <= 5e-6 * z  # the reference's float blocks
+        assert abs(got["max_sumexp"][r, 1] - z) <= 5e-7 * z
+        # the reference's own arithmetic (float sums over blocks of 4096) lies up to ~5e-7 from the exact sum itself
+        assert abs(got["max_sumexp"][r, 1] - orc.softmax_den(xf[r], mx)) <= 1e-6 * z
 
 
 def test_verify_ragged_slots():

@@ -10,6 +10,7 @@ import orc
 from cases import rand_logits, rand_mask, rand_params, rand_recent
 
 needs_ref = pytest.mark.skipif(orc.ref is None, reason="oracle/_ref/libarcs_ref.so not built")
+needs_slices = pytest.mark.skipif(orc.refslices is None, reason="oracle/_ref/libarcs_refslices.so not built")
 
 
 @needs_ref
@@ -128,3 +129,42 @@ def test_logprobs_restatement_against_numpy():
             order = np.argsort(-xd, kind="stable")[: min(top_n, V)]
             assert np.array_equal(ids, order.astype(np.int32))
             assert np.allclose(tlp, xd[order] - want_lse, rtol=0, atol=1e-11)
+
+
+@needs_slices
+def test_logprobs_pinned_to_the_reference_lines():
+    """orc_logprobs against the reference's own lp_entry arithmetic (the lines are cut out of
+    tools/server_chat.h at build time and compiled): lse and log probabilities bit for bit (the
+    same fp64 operations in the same order), the alternatives' ids wherever the logits that
+    decide the order are distinct (equal logits: the reference leaves the order to
+    std::partial_sort, the restatement puts the lower id first)."""
+    g = np.random.default_rng(7)
+    ties = 0
+    for V, top_n in [(1, 1), (5, 3), (1000, 20), (151936, 20), (262144, 20), (4096, 256), (3000, 0)]:
+        for mode in range(3):
+            x = rand_logits(g, V, mode)
+            tok = int(g.integers(0, V))
+            n = min(top_n, V)
+            lse, lp, ids, tlp = orc.logprobs(x, tok, n)
+            rlse, rlp, rids, rtlp = orc.ref_lp_entry(x, tok, n)
+            assert lse == rlse and lp == rlp
+            srt = np.sort(x)[::-1][: n + 1]
+            if len(srt) > 1 and np.any(srt[1:] == srt[:-1]):
+                ties += 1
+                assert np.array_equal(np.sort(x[ids])[::-1], np.sort(x[rids])[::-1])  # the same values either way
+            else:
+                assert np.array_equal(ids, rids)
+            assert np.array_equal(tlp, rtlp)
+    assert ties > 0
+
+
+@needs_slices
+def test_softmax_den_pinned_to_the_reference_function():
+    """orc_softmax_den against the reference's own softmax_den (zero/engine_drafters.h, cut out at
+    build time): bit for bit, including rows that are not a multiple of the 4096-element block."""
+    g = np.random.default_rng(8)
+    for V in [1, 7, 4095, 4096, 4097, 50000, 151936, 262144]:
+        for mode in range(3):
+            x = rand_logits(g, V, mode)
+            mx = float(x.max())
+            assert orc.softmax_den(x, mx) == orc.ref_softmax_den(x, mx)
