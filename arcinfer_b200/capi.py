@@ -217,12 +217,13 @@ def argmax_batch(logits, V=None, want_lse=False, row_off=None, draft=None, draft
     return out
 
 
-def dfa_mask(table, dead, states, byte_off, bytes_, special=None, special_ok=False, V=None):
+def dfa_mask(table, dead, states, byte_off, bytes_, special=None, special_ok=False, V=None, out_stride=None):
     """arcs_dfa_mask: table [S,256] uint16-as-int16 tensor, states int32 [n], byte_off
-    uint32-as-int32 [V+1], bytes_ uint8. Returns int32 [n, ceil(V/32)] packed bits."""
+    uint32-as-int32 [V+1], bytes_ uint8. Returns int32 [n, out_stride] packed bits (out_stride
+    defaults to ceil(V/32); words past that are left zero)."""
     dev = table.device
     V = byte_off.numel() - 1 if V is None else V
-    W = (V + 31) // 32
+    W = (V + 31) // 32 if out_stride is None else out_stride
     out = torch.zeros(states.numel(), W, dtype=torch.int32, device=dev)
     _check(
         lib.arcs_dfa_mask(table.data_ptr(), table.shape[0], dead, states.data_ptr(), states.numel(), byte_off.data_ptr(),

@@ -17,7 +17,7 @@ __global__ void __launch_bounds__(256) dfa_mask_kernel(const uint16_t* __restric
   if (t < V) {
     const uint32_t b0 = byte_off[t], b1 = byte_off[t + 1];
     // an empty piece is never allowed; a control token only where the caller says so
-    ok = b1 > b0 && !(special && special[t] && !special_ok);
+    ok = b1 > b0 && start != dead && !(special && special[t] && !special_ok);
     int32_t s = start;
     for (uint32_t i = b0; ok && i < b1; ++i) {
       s = __ldg(&table[(size_t)s * 256 + __ldg(&bytes[i])]);

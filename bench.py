@@ -15,7 +15,8 @@ inputs resident in HBM (512 MiB of logits per step: larger than L2); `e2e` is th
 through the host-buffer entry point (pinned host logits copied in every step, token ids copied
 back); `roofline` is the dominant kernel's (the pass over the logits) algorithmic bytes over its
 average launch time, measured with CUDA events between the kernels, against the measured copy
-bandwidth of this pool's B200s, with the whole step's figure beside it; `cpu_baseline` is the reference's own CPU sampler
+bandwidth (MEASURED_PEAKS.json), with the whole step's figure beside it; `parity` compares the
+tokens of 129 rows spread over the whole batch with the CPU checker after the timed region; `cpu_baseline` is the reference's own CPU sampler
 (compiled from its sources into oracle/_ref) timed on this box's host cores.
 """
 import argparse
@@ -193,6 +194,7 @@ def main():
                     help="wide-batch: the sampling step (the headline); logprobs: arcs_logprobs_batch on the same logits, one GPU")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the timed launch's tokens")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
@@ -348,6 +350,29 @@ def main():
     ms_step = ms / args.steps
     value = world * B / (ms_step * 1e-3)
 
+    # ---- parity of the timed launch itself (rank 0): every eighth row of the batch, so that every
+    # persistent CTA and each of its rotating sets of per-item state is hit, against the CPU checker
+    parity = None
+    if rank == 0 and not args.no_parity:
+        sys.path.insert(0, os.path.join(ROOT, "tests"))
+        import orc  # the checker; never on the timed path
+
+        rows = sorted(set(list(range(0, B, max(1, B // 128))) + [B - 1]))
+        idx = torch.tensor(rows, device=dev)
+        xf = logits[idx].float().cpu().numpy()
+        hh, uu, tk = hist[idx].cpu().numpy(), u[idx].cpu().numpy(), tok[idx].cpu().numpy()
+        bad, ties = [], 0
+        for i, b in enumerate(rows):
+            want = orc.sample(xf[i], params[b:b + 1], hh[i], float(uu[i]))
+            ties += int((want["flags"] & 1) != 0)
+            if int(tk[i]) != int(want["token"]):
+                bad.append(b)
+        parity = {"rows_checked": len(rows), "mismatches": len(bad), "tie_rows": ties,
+                  "against": "oracle/arcs_oracle.c (value desc, id asc), same logits, histories and uniform draws"}
+        if bad:
+            print(json.dumps({"parity": parity, "mismatched_rows": bad[:16]}), flush=True)
+            sys.exit(3)
+
     # ---- end to end through the host-buffer entry point: pinned host logits in, token ids out
     e2e = None
     if not args.no_e2e:
@@ -374,7 +399,10 @@ def main():
             dt = float(t.item())
         h2d = B * V * 2 + B * H * 4 + (B + 1) * 4 + B * 8 + B * 32
         e2e = {"value": world * B * esteps / dt, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": B * 4 + 4,
-               "steps": esteps, "ms_per_step": 1e3 * dt / esteps, "same_tokens_as_device_path": same}
+               "steps": esteps, "ms_per_step": 1e3 * dt / esteps, "same_tokens_as_device_path": same,
+               # every rank copies its own batch from its own pinned buffer: the step is the host-to-device
+               # copy, and what N ranks reach together is bounded by the host side they share
+               "h2d_gbs_per_rank": h2d / dt * esteps / 1e9, "h2d_gbs_all_ranks": world * h2d / dt * esteps / 1e9}
         ctx.close()
         del h_logits
     clk = clocks.stop() if clocks else None
@@ -418,7 +446,7 @@ def main():
                          "kernel": "stream_kernel", "algorithmic_bytes_per_launch": abytes,
                          "kernel_ms": {"prepare": k_prep, "stream": k_stream, "finish": k_fin},
                          "whole_step": {"achieved": step_gbs, "frac": step_gbs / peak}},
-            "cpu_baseline": cpu,
+            "cpu_baseline": cpu, "parity": parity,
         }
         print(json.dumps(line))
     if world > 1:

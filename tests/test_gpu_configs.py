@@ -70,6 +70,40 @@ def test_config5_wide_batch_subset_and_properties():
     assert np.array_equal(out["token"], out2["token"])
 
 
+def test_config5_full_shape_rows_spread_over_every_cta():
+    """The measured shape itself: 1024 x 262144 bf16, 512-id histories. Every eighth row (128 rows:
+    every persistent CTA and each of its three rotating sets of per-item state is hit) is compared
+    with the CPU checker; inputs are generated on the device and the checked rows copied back."""
+    import arcinfer_b200 as ab
+
+    B, V, H = 1024, 262144, 512
+    gen = torch.Generator(device="cuda").manual_seed(synth.BASE_SEED + 55)
+    logits = torch.empty(B, V, dtype=torch.bfloat16, device="cuda")
+    for r0 in range(0, B, 128):
+        logits[r0 : r0 + 128] = (torch.randn(128, V, generator=gen, device="cuda") * 3.0).to(torch.bfloat16)
+    hist = torch.randint(0, V, (B, H), generator=gen, device="cuda", dtype=torch.int32)
+    hist_off = (torch.arange(B + 1, device="cuda", dtype=torch.int32) * H).contiguous()
+    u = torch.rand(B, generator=gen, device="cuda", dtype=torch.float64)
+    params = synth.make_params(B, top_k=50, top_p=0.95, repeat_penalty=1.1, repeat_last_n=-1)
+    out = ab.sample_batch(logits, ab.capi.params_to_device(params, "cuda"), u, hist_off=hist_off, hist_ids=hist.reshape(-1),
+                          max_hist=H, want_cands=True)
+    torch.cuda.synchronize()
+    assert int(out["status"].item()) == 0
+    rows = list(range(0, B, 8)) + [B - 1]
+    idx = torch.tensor(rows, device="cuda")
+    xf = logits[idx].float().cpu().numpy()
+    hh, uu = hist[idx].cpu().numpy(), u[idx].cpu().numpy()
+    tok, ncand, cid = out["token"].cpu().numpy(), out["n_cand"].cpu().numpy(), out["cand_id"].cpu().numpy()
+    ties = 0
+    for i, b in enumerate(rows):
+        want = orc.sample(xf[i], params[b : b + 1], hh[i], float(uu[i]))
+        ties += (want["flags"] & 1) != 0
+        assert tok[b] == want["token"] and ncand[b] == want["n_cand"], (b, tok[b], want["token"])
+        assert np.array_equal(cid[b][: want["n_cand"]], want["cand_id"]), b
+    assert ties > 0  # bf16 logits: the 50 best of a row live in about as many representable values
+    assert int(tok.min()) >= 0 and int(tok.max()) < V
+
+
 def test_host_buffer_entry_points():
     import arcinfer_b200 as ab
 
@@ -86,6 +120,30 @@ def test_host_buffer_entry_points():
     am = np.zeros(B, np.int32)
     ctx.argmax(c["logits"], am)
     assert np.array_equal(am, np.array([orc.argmax(r) for r in xf], np.int32))
+    ctx.close()
+
+
+def test_host_status_of_the_second_stream_is_reported_by_the_same_call():
+    """Row chunks alternate between the context's two streams. A row of the second chunk that asks
+    for more candidates than a row can keep must make THIS call return ARCS_ERR_TOPK, and the next
+    call must be clean."""
+    import arcinfer_b200 as ab
+
+    B, V = 12, 400000  # 1.6 MB rows of fp32: two chunks of six rows
+    g = synth.rng(91)
+    x = synth.normal_logits(g, B, V, 3.0)
+    params = synth.make_params(B, top_k=20)
+    params["top_k"][B - 2] = 300
+    us = g.random(B)
+    ctx = ab.capi.HostContext(0, B, V, False)
+    tok = np.zeros(B, np.int32)
+    with pytest.raises(ab.ArcsError) as e:
+        ctx.sample(x, params, us, tok)
+    assert "status 2" in str(e.value)
+    params["top_k"][B - 2] = 20
+    ctx.sample(x, params, us, tok)
+    for b in range(B):
+        assert tok[b] == orc.sample(x[b], params[b : b + 1], np.zeros(0, np.int32), float(us[b]))["token"]
     ctx.close()
 
 

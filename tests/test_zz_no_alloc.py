@@ -7,6 +7,7 @@ import numpy as np
 import pytest
 import torch
 
+import orc
 from arcinfer_b200 import synth
 
 pytestmark = pytest.mark.gpu
@@ -21,6 +22,12 @@ def test_static_scratch_matches_workspace_entry_point():
               draft_off=torch.from_numpy(c["draft_off"]).cuda(), want_lse=True)
     want = ab.argmax_batch(lg, **kw)
     torch.cuda.synchronize()
+    # the plain entry point itself against the CPU checker
+    xf = synth.bf16_bits_to_f32(c["logits"])
+    sel = np.array([orc.argmax(r) for r in xf], np.int32)
+    acc, nxt = orc.verify_greedy(sel, c["row_off"], c["draft"], c["draft_off"])
+    assert np.array_equal(want["argmax"].cpu().numpy(), sel)
+    assert np.array_equal(want["accepted"].cpu().numpy(), acc) and np.array_equal(want["next"].cpu().numpy(), nxt)
     for call in range(2):  # two calls in a row share the array
         got = ab.argmax_batch(lg, static_scratch=True, **kw)
         torch.cuda.synchronize()
@@ -29,6 +36,8 @@ def test_static_scratch_matches_workspace_entry_point():
             assert torch.equal(got[k], want[k]), (call, k)
         assert torch.equal(got["max_sumexp"][:, 0], want["max_sumexp"][:, 0])
         torch.testing.assert_close(got["max_sumexp"][:, 1], want["max_sumexp"][:, 1], rtol=1e-6, atol=0)
+        assert np.array_equal(got["argmax"].cpu().numpy(), sel)  # and against the CPU checker directly
+        assert np.array_equal(got["accepted"].cpu().numpy(), acc) and np.array_equal(got["next"].cpu().numpy(), nxt)
 
 
 def test_static_scratch_refuses_oversized_shapes():
