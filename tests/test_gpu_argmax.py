@@ -59,8 +59,10 @@ def test_spec_verify_config3():
         assert got["max_sumexp"][r, 0] == mx
         z = orc.softmax_den(xf[r], mx, exact=True)
         assert abs(got["max_sumexp"][r, 1] - z) <= 5e-7 * z
-        # the reference's own arithmetic (float sums over blocks of 4096) lies up to ~5e-7 from the exact sum itself
-        assert abs(got["max_sumexp"][r, 1] - orc.softmax_den(xf[r], mx)) <= 1e-6 * z
+        # The reference's own arithmetic (float running sums over blocks of 4096 terms, pinned bit for bit in
+        # test_oracle_pin.py) lies about 2e-6 from the exact sum on these rows: the kernel is held to the exact
+        # sum above, and can be no closer to the reference's figure than the reference is to the truth.
+        assert abs(got["max_sumexp"][r, 1] - orc.softmax_den(xf[r], mx)) <= 5e-6 * z
 
 
 def test_verify_ragged_slots():
