@@ -412,8 +412,8 @@ class SamplePlan:
         return self.out
 
     def launch_timed(self, stream=None):
-        """One call with CUDA events between its kernels: (prepare, stream, finish) milliseconds."""
+        """One call with CUDA events between its kernels: (stream, finish) milliseconds."""
         s = _stream(self.device) if stream is None else stream
-        ms = (C.c_float * 3)()
+        ms = (C.c_float * 2)()
         _check(lib.arcs_sample_batch_timed(C.byref(self.args), s, ms), "arcs_sample_batch_timed")
         return tuple(ms)

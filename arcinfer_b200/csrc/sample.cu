@@ -1,9 +1,9 @@
 // sample_batch: penalties + temperature / top-k / top-p / min-p (+ allowed-token mask) with one
-// pass over the logits. Three launches on the caller's stream: prepare (per item: touched
-// tokens, first threshold), stream (the pass itself), finish (per row: order, softmax, cuts,
-// draw). The kernels hand their results on through the workspace.
+// pass over the logits. Two launches on the caller's stream: stream (the pass itself, which also
+// prepares each item's touched tokens ahead of the pass) and finish (per row: order, softmax,
+// cuts, draw), which runs beside the stream kernel and takes each row as it is released. The
+// kernels hand their results on through the workspace.
 #include "sample_finish.cuh"
-#include "sample_prep.cuh"
 #include "sample_stream.cuh"
 
 using namespace arcs;
@@ -26,21 +26,14 @@ static cudaError_t launch_dependent(K kernel, unsigned grid, unsigned block, siz
 }
 
 constexpr int kMaxRows = 65536;
-#ifndef ARCS_ITEMS_PER_SM
-#define ARCS_ITEMS_PER_SM 1
-#endif
-constexpr int kItemsPerSm = ARCS_ITEMS_PER_SM;  // work items per SM that few rows are cut into
-#ifndef ARCS_FIN
-#define ARCS_FIN 128
-#endif
-constexpr int kFinishThreads = ARCS_FIN;  // threads of the finish kernel's CTA (one CTA per row)
+constexpr int kItemsPerSm = 1;        // work items per SM that few rows are cut into
+constexpr int kFinishThreads = 128;   // threads of the finish kernel's CTA (one CTA per row)
 
 static int table_slots(int max_list) {
   int slots = kGroup;
-  while (slots < 2 * max_list) slots <<= 1;
+  while (slots < 2 * max_list && slots < kMaxTableSlots) slots <<= 1;
   return slots;
 }
-
 
 extern "C" size_t arcs_sample_workspace_bytes(int32_t B, int32_t V, int32_t masked, int32_t max_list) {
   if (B <= 0 || V <= 0 || max_list < 0) return 0;
@@ -49,7 +42,7 @@ extern "C" size_t arcs_sample_workspace_bytes(int32_t B, int32_t V, int32_t mask
   return (size_t)B * nseg * (size_t)item_block_bytes(masked != 0, table_slots(max_list));
 }
 
-// events[0..3], when given, are recorded before the first launch and after each of the three
+// events[0..2], when given, are recorded before the first launch and after each of the two
 static int sample_launch(const arcs_sample_args* g, void* stream, cudaEvent_t* events) {
   if (int inj = fault_injected()) return inj;
   if (!g || !g->logits || !g->params || !g->u || !g->token || g->B <= 0 || g->V <= 0 || g->row_stride < g->V ||
@@ -114,27 +107,21 @@ static int sample_launch(const arcs_sample_args* g, void* stream, cudaEvent_t* e
     return set_error(ARCS_ERR_WORKSPACE, "sample_batch: workspace too small");
   if ((reinterpret_cast<uintptr_t>(g->workspace) & 15u) != 0) return set_error(ARCS_ERR_WORKSPACE, "sample_batch: workspace must be 16-byte aligned");
 
-  const size_t smem_s = stream_smem_bytes(masked, slots), smem_p = prep_smem_bytes(slots);
-  if (smem_s > 227 * 1024 || smem_p > 227 * 1024)
-    return set_error(ARCS_ERR_LIST, "sample_batch: history / bias lists too long for the on-chip table");
+  const size_t smem_s = stream_smem_bytes(slots);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int items = a.nseg * a.B;
   const unsigned grid_s = (unsigned)(items < kSmCount ? items : kSmCount);
 #define ARCS_LAUNCH(T, M)                                                                                          \
   do {                                                                                                             \
-    cudaError_t e = cudaFuncSetAttribute(stream_kernel<T, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_s); \
-    if (e == cudaSuccess && smem_p > 48 * 1024)                                                                    \
-      e = cudaFuncSetAttribute(prepare_kernel<T, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_p);    \
-    if (e != cudaSuccess) return set_error(ARCS_ERR_CUDA, cudaGetErrorString(e));                                  \
+    static const cudaError_t attr_rc =                                                                             \
+        cudaFuncSetAttribute(stream_kernel<T, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);        \
+    if (attr_rc != cudaSuccess) return set_error(ARCS_ERR_CUDA, cudaGetErrorString(attr_rc));                      \
     if (events) cudaEventRecord(events[0], st);                                                                    \
-    prepare_kernel<T, M><<<(unsigned)items, kGroup, smem_p, st>>>(a);                                              \
+    stream_kernel<T, M><<<grid_s, kThreadsS, smem_s, st>>>(a);                                                     \
     if (events) cudaEventRecord(events[1], st);                                                                    \
-    e = launch_dependent(stream_kernel<T, M>, grid_s, kThreadsS, smem_s, st, a, events == nullptr);                                  \
+    const cudaError_t e = launch_dependent(finish_kernel<T, M, kFinishThreads>, (unsigned)a.B, kFinishThreads, 0, st, a, events == nullptr); \
     if (e != cudaSuccess) return set_error(ARCS_ERR_CUDA, cudaGetErrorString(e));                                  \
     if (events) cudaEventRecord(events[2], st);                                                                    \
-    e = launch_dependent(finish_kernel<T, M, kFinishThreads>, (unsigned)a.B, kFinishThreads, 0, st, a, events == nullptr);          \
-    if (e != cudaSuccess) return set_error(ARCS_ERR_CUDA, cudaGetErrorString(e));                                  \
-    if (events) cudaEventRecord(events[3], st);                                                                    \
   } while (0)
   if (g->dtype == ARCS_F32) {
     if (masked) ARCS_LAUNCH(float, true);
@@ -149,15 +136,15 @@ static int sample_launch(const arcs_sample_args* g, void* stream, cudaEvent_t* e
 
 extern "C" int arcs_sample_batch(const arcs_sample_args* g, void* stream) { return sample_launch(g, stream, nullptr); }
 
-extern "C" int arcs_sample_batch_timed(const arcs_sample_args* g, void* stream, float* ms3) {
-  if (!ms3) return set_error(ARCS_ERR_ARG, "sample_batch_timed: no output");
-  cudaEvent_t ev[4];
+extern "C" int arcs_sample_batch_timed(const arcs_sample_args* g, void* stream, float* ms2) {
+  if (!ms2) return set_error(ARCS_ERR_ARG, "sample_batch_timed: no output");
+  cudaEvent_t ev[3];
   for (auto& e : ev)
     if (cudaEventCreate(&e) != cudaSuccess) return set_error(ARCS_ERR_CUDA, "sample_batch_timed: cannot create events");
   int rc = sample_launch(g, stream, ev);
-  if (rc == ARCS_OK && cudaEventSynchronize(ev[3]) != cudaSuccess) rc = set_error(ARCS_ERR_CUDA, "sample_batch_timed: synchronize failed");
-  for (int i = 0; i < 3 && rc == ARCS_OK; ++i)
-    if (cudaEventElapsedTime(&ms3[i], ev[i], ev[i + 1]) != cudaSuccess) rc = set_error(ARCS_ERR_CUDA, "sample_batch_timed: elapsed time failed");
+  if (rc == ARCS_OK && cudaEventSynchronize(ev[2]) != cudaSuccess) rc = set_error(ARCS_ERR_CUDA, "sample_batch_timed: synchronize failed");
+  for (int i = 0; i < 2 && rc == ARCS_OK; ++i)
+    if (cudaEventElapsedTime(&ms2[i], ev[i], ev[i + 1]) != cudaSuccess) rc = set_error(ARCS_ERR_CUDA, "sample_batch_timed: elapsed time failed");
   for (auto& e : ev) cudaEventDestroy(e);
   return rc;
 }

@@ -1,13 +1,14 @@
-// What the three kernels of sample_batch share: the argument block, the work items, the
-// per-item block of the workspace through which the kernels hand their results on, and the
-// row settings of tools/sampler.h.
+// What the two kernels of sample_batch share: the argument block, the work items, the per-item
+// block of the workspace through which they hand their results on, and the row settings of
+// tools/sampler.h.
 //
-//   prepare_kernel  one small CTA per item: table of the tokens a penalty or a bias touches,
-//                   their adjusted logits (exact fp32 arithmetic of Sampler::adjusted), a first
-//                   threshold from a short prefix of the item;
-//   stream_kernel   one persistent CTA per SM: the single pass over the logits, which keeps
-//                   what can still be among the k best of an item;
-//   finish_kernel   one small CTA per row: final order, fp64 softmax, cuts, draw.
+//   stream_kernel   one persistent CTA per SM: the single pass over the logits, which keeps what
+//                   can still be among the k best of an item. Two of its warps prepare the items
+//                   ahead of the stream (table of the tokens a penalty or a bias touches, their
+//                   adjusted logits with the exact fp32 arithmetic of Sampler::adjusted);
+//   finish_kernel   one small CTA per row: final order, fp64 softmax, cuts, draw. It is launched
+//                   behind the stream kernel, runs beside it, and takes a row as soon as the stream
+//                   has released the row's items.
 #pragma once
 #include "plan.h"
 #include "select.cuh"
@@ -21,10 +22,6 @@ constexpr int kCapB = 1024;   // finish kernel's candidate buffer: prune trigger
 constexpr int kCapA = 1280;   // ... for the constrained head select (k = 512): trigger 768 + four rounds of 128
 constexpr int kListB = 4096;  // survivors of the stream an item's block holds: selection proper (typically k * (1 + ln(V / 4096)))
 constexpr int kListA = 4096;  // ... constrained head ranking
-#ifndef ARCS_BOOT
-#define ARCS_BOOT 32768
-#endif
-constexpr int kBootBytes = ARCS_BOOT;  // prefix of an item the prepare kernel reads the first threshold off (a multiple of 8192)
 constexpr uint32_t kEmpty = 0xFFFFFFFFu;
 // per touched token: occurrences in the history (low 20 bits) and what applies to it
 constexpr uint32_t kInfoCount = 0xFFFFFu, kInfoWindow = 1u << 31, kInfoBias = 1u << 30, kInfoBan = 1u << 29;
@@ -65,24 +62,34 @@ struct SampleDev {
   const int32_t* merge_n;    // [G][B] entries per list
 };
 
+// ---- geometry of the stream (shared with the preparing warps, which count the listed columns
+// that fall into each scanner warp's share of an item's first tiles)
+constexpr int kScanW = 16;                   // scanner warps
+constexpr int kShare = 2;                    // scanner warps that split one tile between them
+constexpr int kTeams = kScanW / kShare;      // teams: team x takes the tiles whose running number is x modulo kTeams
+constexpr int kSTile = 8192;                 // bytes per tile (512 chunks of 16 bytes)
+constexpr int kMine = kSTile / 16 / kShare;  // chunks of a tile per scanner warp
+constexpr int kBootTiles = 2;                // first tiles of an item the first threshold is read off
+constexpr int kBootWin = kBootTiles * kShare; // shares of those tiles: one per scanner warp that takes part
+
 // ---- one item's block of the workspace
-// [ItemHdr][filter bloom_words words]                                  <- copied to shared memory by the stream kernel
-// [entries with final values, from the prepare kernel, then hot elements the filter flagged, from
-//  the stream kernel, raw: hash_slots + kMaxScalars]                   (key | word y << 32)
+// [ItemHdr][filter bloom_words words: written only when a list of the stream overflowed]
+// [entries with final values, from the preparing warps, then hot elements the filter flagged, from
+//  the scanners, raw: hash_slots + kMaxScalars]                        (key | word y << 32)
 // [survivors of the stream, selection proper: kListB][constrained head ranking: kListA when masked]
 struct ItemHdr {
-  unsigned long long tau0B, tau0A;  // first thresholds (exclusive composites)
   unsigned long long tauB, tauA;    // last thresholds of the stream: at least K (512) eligible elements of the item lie above
   int32_t K;                        // entries the selection proper keeps
   int32_t touched;                  // kTouchNone / kTouchLight / kTouchTable
   int32_t bans;                     // a bias entry <= -100 exists (tools/sampler.h:34)
-  int32_t baseB, baseA;             // upper 16 key bits the coarse histograms start at
-  int32_t n_pre;                    // entries supplied by the prepare kernel
-  int32_t n_tch;                    // flagged hot elements appended by the stream kernel
-  int32_t n_candB, n_candA;         // survivors written by the stream kernel
-  int32_t pad[7];
+  int32_t n_pre;                    // entries supplied by the preparing warps
+  int32_t n_tch;                    // flagged hot elements appended by the scanners
+  int32_t n_candB, n_candA;         // survivors written by the scanners
+  int32_t streamed;                 // 1 (released at gpu scope) once everything above and the lists are final
+  uint8_t boot_extra[kBootWin];     // listed columns inside each scanner warp's share of the first tiles (saturating)
+  int32_t pad[11];
 };
-static_assert(sizeof(ItemHdr) == 96, "ItemHdr is copied as 96 bytes");
+static_assert(sizeof(ItemHdr) == 96, "ItemHdr is 96 bytes");
 // How an item's penalised / biased tokens reach the finish kernel.
 //  light: penalties can only lower a logit, so a history token matters only if its raw logit is
 //         hot: the stream flags hot elements the filter knows and the finish kernel adjusts them;
@@ -92,8 +99,11 @@ static_assert(sizeof(ItemHdr) == 96, "ItemHdr is copied as 96 bytes");
 constexpr int kTouchNone = 0, kTouchLight = 1, kTouchTable = 2;
 constexpr int kLightBias = 64;  // longest bias list handled without the table
 
-// filter size: 64 bits per listed id or more, two bits set per id: about one false alarm in a thousand lookups
-__host__ __device__ inline int32_t bloom_words_of(int hash_slots) { return hash_slots < 256 ? 256 : hash_slots; }
+// filter size: 64 bits per listed id while the lists are short (two bits set per id: about one false
+// alarm in a thousand lookups), at most 2048 words: longer lists only raise the false-alarm rate,
+// and a false alarm costs one more entry for the finish kernel to settle
+constexpr int kMaxTableSlots = 4096;  // most distinct listed tokens x 2 the on-chip table holds
+__host__ __device__ inline int32_t bloom_words_of(int hash_slots) { return hash_slots < 256 ? 256 : hash_slots > 2048 ? 2048 : hash_slots; }
 __host__ __device__ inline int32_t item_tab_bytes(int hash_slots) { return (int32_t)sizeof(ItemHdr) + bloom_words_of(hash_slots) * 4; }
 __host__ __device__ inline int32_t item_pre_cap(int hash_slots) { return hash_slots + kMaxScalars; }
 __host__ __device__ inline int64_t item_block_bytes(bool masked, int hash_slots) {
@@ -176,6 +186,13 @@ __device__ __forceinline__ RowCfg row_cfg(const SampleDev& a, int b) {
   r.touched_on = (r.pen_on || r.NB > 0) && r.lists_ok;
   const bool lowering = (!r.rp_on || r.prm.repeat_penalty >= 1.0f) && !(r.prm.frequency_penalty < 0.0f) && !(r.prm.presence_penalty < 0.0f);
   r.touch = !r.touched_on ? kTouchNone : ((r.pen_on && !lowering) || r.NB > kLightBias) ? kTouchTable : kTouchLight;
+  // the table holds every listed token of the row: a row whose lists are longer than it is refused
+  // (rows in light mode, whose penalties only lower logits, take histories of any length)
+  if (r.touch == kTouchTable && (r.pen_on ? r.H : 0) + r.NB > a.hash_slots / 2) {
+    r.lists_ok = false;
+    r.touched_on = false;
+    r.touch = kTouchNone;
+  }
   return r;
 }
 

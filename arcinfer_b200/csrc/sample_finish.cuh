@@ -1,7 +1,8 @@
 // finish_kernel: from an item's survivors to the row's token.
 //
-// One CTA of kGroup threads per row. It merges what the prepare kernel supplied (touched tokens
-// with their adjusted logits, elements outside the aligned body) with what the stream kernel
+// One CTA of kGroup threads per row. It runs beside the stream kernel: it waits until that kernel
+// has released every item of its row, then merges what the preparing warps supplied (touched
+// tokens with their adjusted logits, elements outside the aligned body) with what the scanners
 // kept, for every segment of the row, selects the k best under (value desc, id asc), and then
 // follows tools/sampler.h:54-77 (or :105-143 with an allowed-token mask) to the letter: fp64
 // softmax in candidate order, min-p / top-p cuts, the draw.
@@ -11,6 +12,14 @@
 namespace arcs {
 
 constexpr int kStage = 1024;   // flagged entries settled together
+constexpr uint32_t kFlagWaitLimit = 1u << 21;  // bounded wait for an item's release (about a second)
+
+__device__ __forceinline__ int32_t ld_acquire_gpu(const int32_t* p) {
+  int32_t v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
 constexpr int kSortCap = 160;  // a longer buffer is cut to the k best by the radix select before it is ranked by counting
 
 template <typename T, bool MASKED, int G>
@@ -52,12 +61,35 @@ __global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (
     s64[L_TAU_A] = 0ull;
   }
   __syncthreads();
-  pdl_wait();  // the stream kernel's lists and headers are read from here on
+  const bool merging = a.merge_G > 0;
+  // The stream kernel's lists and headers are read from here on. That kernel may still be running
+  // (this one is launched behind it with programmatic stream serialization and does not wait for
+  // its end): a row is taken when all its items have been released. The wait is bounded.
+  if (!merging) {
+    bool late = false;
+    for (int g = gt; g < a.nseg; g += G) {
+      const int32_t* flag = &item_ws(a, b * a.nseg + g).hdr->streamed;
+      uint32_t spins = 0;
+      while (ld_acquire_gpu(flag) == 0) {
+        if (++spins > kFlagWaitLimit) {
+          late = true;
+          break;
+        }
+        __nanosleep(spins < 64 ? 100 : 400);
+      }
+    }
+    if (__syncthreads_or(late)) {
+      if (gt == 0) {
+        raise_status(a.status, ARCS_ERR_TIMEOUT);
+        a.token[b] = -1;
+      }
+      return;
+    }
+  }
   // what the segments' headers say (fetched together with the row's settings). Nothing at or
   // below the largest threshold a segment's stream ended on can be among the k best: that
   // segment alone holds k above it.
   const RowCfg r = row_cfg<MASKED>(a, b);  // (its loads travel together with the headers')
-  const bool merging = a.merge_G > 0;
   if (merging) {  // the banned-tail rule needs to know whether the row's bias list bans anything (tools/sampler.h:34)
     bool any = false;
     for (int i = gt; i < r.NB; i += G) any = any || a.bias_vals[r.q0 + i] <= -100.0f;

@@ -1,56 +1,48 @@
 // stream_kernel: the single pass over the logits.
 //
 // One persistent CTA per SM walks a list of work items (a row, or a segment of a row when
-// there are few rows). Its warps have fixed roles and never meet at a CTA-wide barrier:
+// there are few rows). Its warps have fixed roles and never meet at a CTA-wide barrier after
+// start-up:
 //   producer   keeps a ring of 8 KB tiles filled with 1-D bulk copies (TMA);
 //   scanners   16 warps, two to a tile: a 16-byte chunk whose maximum is below the item's
 //              current threshold costs a handful of instructions; the few other chunks are set
 //              aside, then tested element by element, and the survivors appended to the item's
-//              lists in the workspace. The warp that closes an item last hands it over;
-//   threshold  one warp fetches the items' filters and first thresholds (written by the prepare
-//              kernel) ahead of the stream, and keeps raising the thresholds of the items that
-//              are streaming from the coarse histograms the scanners update.
+//              lists in the workspace. On their first tiles of an item the scanners find the
+//              item's first threshold together (boot). The warp that closes an item last
+//              releases it to the finish kernel;
+//   threshold  one warp keeps raising the thresholds of the items that are streaming from the
+//              coarse histograms the scanners update;
+//   preparing  two warps build the filters and headers of the items ahead of the stream
+//              (sample_prep.cuh).
 // Items rotate over three sets of per-item state, so the ring never pauses between items.
 // A list that overflows (ascending data, masses of ties) is only counted: the finish kernel
 // sees the count and reads that item again itself.
 #pragma once
-#include "sample_common.cuh"
+#include "sample_prep.cuh"
 
 namespace arcs {
 
-constexpr int kScanW = 16;                                 // scanner warps
-#ifndef ARCS_SHARE
-#define ARCS_SHARE 2
-#endif
-constexpr int kShare = ARCS_SHARE;                         // scanner warps that split one tile between them
-constexpr int kTeams = kScanW / kShare;
 constexpr int kProdWarp = kScanW;                          // producer warp (its first lanes work)
 constexpr int kTauWarp = kScanW + 1;                       // threshold warp
-constexpr int kThreadsS = (kScanW + 2) * 32;               // 576 threads
-#ifndef ARCS_PROD_LANES
-#define ARCS_PROD_LANES 2
-#endif
-constexpr int kProdLanes = ARCS_PROD_LANES;                // lanes of the producer warp that issue copies
-#ifndef ARCS_TAU_SLEEP
-#define ARCS_TAU_SLEEP 200
-#endif
-constexpr int kTauSleepNs = ARCS_TAU_SLEEP;                // pause between two threshold updates
-#ifndef ARCS_RING
-#define ARCS_RING 16
-#endif
-constexpr int kRing = ARCS_RING;                           // tiles in the ring (a multiple of kTeams)
-constexpr int kSTile = 8192;                               // bytes per tile (512 chunks)
+constexpr int kPrepWarp0 = kScanW + 2;                     // first preparing warp
+constexpr int kThreadsS = (kScanW + 2 + kPrepW) * 32;      // 640 threads
+constexpr int kProdLanes = 2;                              // lanes of the producer warp that issue copies (one thread cannot issue 8 KB copies fast enough)
+constexpr int kTauSleepNs = 200;                           // pause between two threshold updates
+constexpr int kRing = 16;                                  // tiles in the ring (a multiple of kTeams)
 constexpr int kPend = 2;                                   // chunks each lane of a scanner can set aside
 constexpr int kStash = kPend * 32;                         // ... per warp
-#ifndef ARCS_FLUSH_EVERY
-#define ARCS_FLUSH_EVERY 2
-#endif
-constexpr int kFlushEvery = ARCS_FLUSH_EVERY;              // visits after which a warp examines what it has set aside even if its next tile is there
+constexpr int kFlushEvery = 2;                             // visits after which a warp examines what it has set aside even if its next tile is there
+constexpr int kU = 4;                                      // chunks per lane per step of the scan
 static_assert(kRing % kTeams == 0, "a team always meets its tiles in the same slots");
+static_assert(kMine % (32 * kU) == 0 && kMine / 32 <= 8, "a warp's share of a tile: whole steps, at most 8 chunks per lane");
 
 // indices into the shared scalar arrays
-enum { S_ABORT = 0, S_PREPARED, S_STREAMED, S_DONE /* [3] */ = 4, S_CNT /* [3 sets][B, A, flagged, -] */ = 8, S_END = 20 };
-enum { L_TAU_B = 0 /* [3] */, L_TAU_A = 3 /* [3] */, L_END = 6 };
+enum {
+  S_ABORT = 0, S_PREPARED, S_STREAMED,
+  S_DONE = 4 /* [3] */, S_CNT = 8 /* [3 sets][B, A, flagged, -] */,
+  S_BOOTCNT = 20 /* [3] */, S_BOOTOK = 23 /* [3] */, S_BASEB = 26 /* [3] */, S_BASEA = 29 /* [3] */, S_END = 32
+};
+enum { L_TAU_B = 0 /* [3] */, L_TAU_A = 3 /* [3] */, L_BOOT_B = 6 /* [3] */, L_BOOT_A = 9 /* [3] */, L_END = 12 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
@@ -59,6 +51,9 @@ __device__ __forceinline__ int s_tiles(const SegPlan& p) { return (p.body_bytes 
 __device__ __forceinline__ uint32_t s_tile_bytes(const SegPlan& p, int t) {
   const int32_t rem = p.body_bytes - t * kSTile;
   return (uint32_t)(rem < kSTile ? rem : kSTile);
+}
+__device__ __forceinline__ void st_release_gpu(int32_t* p, int32_t v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 // element `el` of the 16-byte chunk held as four words
@@ -150,10 +145,17 @@ __device__ __forceinline__ void scan_examine(const ScanCtx& c, bool have, uint4 
   }
 }
 
-static size_t stream_smem_bytes(bool masked, int hash_slots) {
-  (void)masked;
-  return (size_t)kRing * kSTile + 3 * (size_t)item_tab_bytes(hash_slots) + (size_t)kScanW * kStash * 20 + (2 * kRing + 4) * 8 + L_END * 8 +
-         6 * 256 * 4 + S_END * 4 + 128;
+// bits [0, E) : the allowed-token bits of the chunk whose first element has global id gid
+template <int E>
+__device__ __forceinline__ uint32_t mask_bits_of(const uint32_t* mrow, int32_t gid) {
+  uint32_t bits = __ldg(&mrow[gid >> 5]) >> (gid & 31);
+  if ((gid & 31) + E > 32) bits |= __ldg(&mrow[(gid >> 5) + 1]) << (32 - (gid & 31));
+  return bits & ((1u << E) - 1u);
+}
+
+static size_t stream_smem_bytes(int hash_slots) {
+  return (size_t)kRing * kSTile + 3 * (size_t)item_tab_bytes(hash_slots) + (size_t)kScanW * kStash * 20 + 2 * kRing * 8 + L_END * 8 +
+         6 * 256 * 4 + (size_t)hash_slots * 8 + S_END * 4 + P_END * 4 + 128;
 }
 
 template <typename T, bool MASKED>
@@ -162,19 +164,21 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
   // ---- carve shared memory (ordered by alignment)
   const int tab_bytes = item_tab_bytes(a.hash_slots);
   char* ring = smem;                                                          // kRing * kSTile
-  char* tabs = ring + (size_t)kRing * kSTile;                                 // [3] item tables as the prepare kernel wrote them
+  char* tabs = ring + (size_t)kRing * kSTile;                                 // [3] header + filter of the items in flight
   uint4* stash_q = reinterpret_cast<uint4*>(tabs + 3 * (size_t)tab_bytes);     // [kScanW][kStash] chunks set aside by the scanners
   uint64_t* full = reinterpret_cast<uint64_t*>(stash_q + kScanW * kStash);     // [kRing] tile has landed
   uint64_t* empty = full + kRing;                                             // [kRing] tile has been scanned
-  uint64_t* tab_full = empty + kRing;                                         // [3] (+1 pad) table has landed
-  unsigned long long* s64 = reinterpret_cast<unsigned long long*>(tab_full + 4);  // [L_END]
+  unsigned long long* s64 = reinterpret_cast<unsigned long long*>(empty + kRing);  // [L_END]
   int32_t* stash_c = reinterpret_cast<int32_t*>(s64 + L_END);                 // [kScanW][kStash]
   uint32_t* xh = reinterpret_cast<uint32_t*>(stash_c + kScanW * kStash);      // [3 sets][B, A][256] coarse histograms
-  int* sh = reinterpret_cast<int*>(xh + 6 * 256);                             // [S_END]
+  uint32_t* hk = xh + 6 * 256;                                                // [hash_slots] the preparing warps' table: columns
+  uint32_t* hi_ = hk + a.hash_slots;                                          // [hash_slots] ... what applies to them
+  int* sh = reinterpret_cast<int*>(hi_ + a.hash_slots);                       // [S_END]
+  int* pmisc = sh + S_END;                                                    // [P_END]
   volatile int* vsh = sh;
   volatile unsigned long long* v64 = s64;
-  auto tab_hdr = [&](int st) { return reinterpret_cast<const ItemHdr*>(tabs + (size_t)st * tab_bytes); };
-  auto tab_bloom = [&](int st) { return reinterpret_cast<const uint32_t*>(tabs + (size_t)st * tab_bytes + sizeof(ItemHdr)); };
+  auto tab_hdr = [&](int st) { return reinterpret_cast<ItemHdr*>(tabs + (size_t)st * tab_bytes); };
+  auto tab_bloom = [&](int st) { return reinterpret_cast<uint32_t*>(tabs + (size_t)st * tab_bytes + sizeof(ItemHdr)); };
 
   constexpr int E = Elem<T>::kPerChunk;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -186,14 +190,17 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
       mbar_init(&full[i], 1);
       mbar_init(&empty[i], kShare);
     }
-    for (int i = 0; i < 3; ++i) mbar_init(&tab_full[i], 1);
     mbar_init_fence();
     for (int i = 0; i < S_END; ++i) sh[i] = 0;
-    for (int i = 0; i < L_END; ++i) s64[i] = 0ull;
+    for (int i = 0; i < L_END; ++i) s64[i] = i >= L_BOOT_B ? 0xFFFFFFFFFFFFFFFFull : 0ull;
   }
   for (int i = tid; i < 6 * 256; i += kThreadsS) xh[i] = 0u;
+  // This call's items are not released yet: the flags the finish kernel waits on are cleared
+  // before that kernel is allowed to start.
+  for (int j = tid; j < my_n; j += kThreadsS) item_ws(a, (int)blockIdx.x + j * (int)gridDim.x).hdr->streamed = 0;
+  __threadfence();
   __syncthreads();  // the only CTA-wide barrier
-  pdl_trigger();    // (the finish kernel's CTAs may take their places; they wait for this kernel before they read)
+  if (tid == 0) pdl_trigger();  // the finish kernel's CTAs may take their places beside this kernel: each waits for its row's items
 
   auto abort_now = [&]() {
     vsh[S_ABORT] = 1;
@@ -221,14 +228,10 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
         if (j >= my_n || vsh[S_ABORT]) break;
         const int slot = (int)(g % kRing);
         const int t = (int)(g - G0);
-        bool ok;
-        if (kProdLanes == 1) {
-          ok = mbar_wait(&empty[slot], ((g / kRing) & 1u) ^ 1u);
-        } else {  // (no sleeping: the other producer lanes of the warp would sleep too)
-          ok = false;
-          for (uint32_t tries = 0; tries < kWaitLimit && !ok; ++tries) {
-            ok = mbar_try_wait(&empty[slot], ((g / kRing) & 1u) ^ 1u);
-          }
+        bool ok = false;  // (no sleeping: the other producer lane of the warp would sleep too)
+        for (uint32_t tries = 0; tries < kWaitLimit && !ok; ++tries) {
+          ok = mbar_try_wait(&empty[slot], ((g / kRing) & 1u) ^ 1u);
+          if (!ok && (tries & 1023u) == 1023u && vsh[S_ABORT]) break;
         }
         if (!ok) {
           abort_now();
@@ -246,14 +249,13 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
   } else if (warp < kScanW) {
     // =================================================================== scanners
     // Team w / kShare takes the tiles whose running number is its own modulo kTeams; each of
-    // its warps scans a quarter of the tile, so a slot is held only briefly.
+    // its warps scans its share of the tile, so a slot is held only briefly.
     uint32_t G0 = 0;  // running number of the item's first tile
     for (int j = 0; j < my_n; ++j) {
       const int st = j % 3;  // filters / thresholds / counts rotate over three sets
       const Item<T> it = item_of<T>(a, (int)blockIdx.x + j * (int)gridDim.x);
       const int T_ = s_tiles(it.p);
-      {  // the item's filter and first threshold must be there (one lane polls); the set of
-         // state they live in was free before their copy started
+      {  // the item's filter and header must be there (one lane polls)
         if (lane == 0) {
           uint32_t spins = 0;
           while (vsh[S_PREPARED] <= j && !vsh[S_ABORT]) {
@@ -265,7 +267,6 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
         __threadfence_block();
       }
       if (vsh[S_ABORT]) break;
-      mbar_try_wait(&tab_full[st], (uint32_t)(j / 3) & 1u);  // (complete: every lane observes the copied table through it)
       const ItemHdr* hd = tab_hdr(st);
       uint4* stq = stash_q + warp * kStash + lane;      // chunks this lane has set aside: stq[s * 32], s < have
       int32_t* stc = stash_c + warp * kStash + lane;
@@ -278,13 +279,13 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
       ctx.mrow = MASKED ? a.mask + (size_t)(a.mask_row ? a.mask_row[it.b] : it.b) * a.mask_stride : nullptr;
       ctx.histB = xh + (2 * st) * 256;
       ctx.histA = xh + (2 * st + 1) * 256;
-      ctx.baseB = (uint32_t)hd->baseB;
-      ctx.baseA = (uint32_t)hd->baseA;
+      ctx.baseB = 0;
+      ctx.baseA = 0;
       ctx.cnt = &sh[S_CNT + 4 * st];
       const ItemWs w = item_ws(a, (int)blockIdx.x + j * (int)gridDim.x);
       ctx.listB = w.candB;
       ctx.listA = w.candA;
-      ctx.listT = w.pre + hd->n_pre;  // (right behind the prepare kernel's entries)
+      ctx.listT = w.pre + hd->n_pre;  // (right behind the preparing warps' entries)
       ctx.roomT = item_pre_cap(a.hash_slots) - hd->n_pre;
       ctx.id_base = a.id_base;
       const uint32_t* mrow = ctx.mrow;
@@ -301,12 +302,12 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
         have = 0;
         __syncwarp();
       };
-      for (int t = (int)(((uint32_t)(warp / kShare) - G0) % kTeams); t < T_; t += kTeams) {
+      const int t_first = (int)(((uint32_t)(warp / kShare) - G0) % kTeams);
+      const int c_lo = (warp % kShare) * kMine;
+      for (int t = t_first; t < T_; t += kTeams) {
         const uint32_t g = G0 + (uint32_t)t;
         const int slot = (int)(g % kRing);
         const char* tile = ring + (size_t)slot * kSTile;
-        // What is set aside is examined while the warp would only wait for its next tile: the time
-        // the examination takes then holds nothing up.
         // What is set aside is examined while the warp would only wait for its next tile (the time
         // the examination takes then holds nothing up), and in any case every few visits: the
         // thresholds rise only from what has been examined.
@@ -328,6 +329,111 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
         }
         const int nchunk = (int)(s_tile_bytes(it.p, t) / 16u);
         const int32_t col0 = it.p.body_first + t * (kSTile / (int)sizeof(T)) + a.id_base;  // global id of the tile's first element
+#ifdef ARCS_DEV_FAKEBOOT
+        if (t == t_first) {
+          if (lane == 0) {
+            const unsigned long long tB = (unsigned long long)(key_of(ARCS_DEV_FAKEBOOT) & 0xFFFF0000u) << 32;
+            sm_red_max_u64(&s64[L_TAU_B + st], tB);
+            sh[S_BASEB + st] = (int)(tB >> 48);
+            sh[S_BASEA + st] = 0;
+            __threadfence_block();
+            vsh[S_BOOTOK + st] = j + 1;
+          }
+          __syncwarp();
+        }
+        if (false) {
+#else
+        if (t == t_first && t < kBootTiles && c_lo < nchunk) {
+#endif
+          // ---- boot: the item's first threshold, found together by the scanner warps that meet the
+          // item's first kBootTiles tiles. A warp's kth-largest chunk maximum bounds kth elements of
+          // its share from below; with kth = ceil(K / warps taking part) in every share, the smallest
+          // of the warps' bounds has at least K elements of the item at or above it. Listed columns
+          // inside a share (the header counts them) may own a maximum there without counting, so
+          // that many more are skipped.
+          int n_part = 0;
+          for (int tt = 0; tt < min(T_, kBootTiles); ++tt) {
+            const int nc = (int)(s_tile_bytes(it.p, tt) / 16u);
+            n_part += min(kShare, (nc + kMine - 1) / kMine);
+          }
+          constexpr int PER = kMine / 32;
+          uint32_t kA[PER], kBm[PER];  // (kBm: maxima over the allowed elements, constrained rows only)
+#pragma unroll
+          for (int u = 0; u < PER; ++u) {
+            const int ci = c_lo + u * 32 + lane;
+            kA[u] = 0u;
+            if (MASKED) kBm[u] = 0u;
+            if (ci < nchunk) {
+              const uint4 q = lds128(tile + ci * 16);
+              kA[u] = key_of(Elem<T>::chunk_max(q));
+              if (MASKED) {  // the selection proper counts allowed elements only
+                const uint32_t bits = mask_bits_of<E>(mrow, col0 + ci * E);
+                float mB = -INFINITY;
+                bool anyB = false;
+#pragma unroll
+                for (int e = 0; e < E; ++e)
+                  if ((bits >> e) & 1u) {
+                    const float v = Elem<T>::get(q, e);
+                    if (!(v != v)) {  // (a NaN is never selected)
+                      mB = fmaxf(mB, v);
+                      anyB = true;
+                    }
+                  }
+                if (anyB) kBm[u] = key_of(mB);
+              }
+            }
+          }
+          const int my_chunks = min(kMine, nchunk - c_lo);
+          const int extra = hd->boot_extra[t * kShare + warp % kShare];
+          // A small kth is read off the lanes' own maxima (disjoint sets of chunks: as good a bound,
+          // a fraction of the work); a large one off all chunk maxima, upper 16 key bits.
+          auto kth_of = [&](const uint32_t (&k)[PER], int kth) -> uint32_t {
+            if (extra >= 255 || kth > my_chunks) return 0u;
+            if (kth <= 8) {
+              uint32_t m = k[0];
+#pragma unroll
+              for (int u = 1; u < PER; ++u) m = max(m, k[u]);
+              return warp_kth_lane(m, kth) & 0xFFFF0000u;
+            }
+            return warp_kth16_regs<PER>(k, kth);
+          };
+          const int kthB = (hd->K + n_part - 1) / n_part + extra;
+          const uint64_t bB = (uint64_t)(MASKED ? kth_of(kBm, kthB) : kth_of(kA, kthB)) << 32;  // keeps ties with it
+          uint64_t bA = 0ull;
+          if (MASKED) bA = (uint64_t)kth_of(kA, (ARCS_HEAD + n_part - 1) / n_part + extra) << 32;
+          if (lane == 0) {
+            sm_red_min_u64(&s64[L_BOOT_B + st], (unsigned long long)bB);
+            if (MASKED) sm_red_min_u64(&s64[L_BOOT_A + st], (unsigned long long)bA);
+            __threadfence_block();
+            if ((int)sm_atomic_add(&sh[S_BOOTCNT + st], 1u) == n_part - 1) {
+              // the warp that comes last publishes the item's first thresholds
+              __threadfence_block();
+              const unsigned long long tB = v64[L_BOOT_B + st], tA = MASKED ? v64[L_BOOT_A + st] : 0ull;
+              if (tB) sm_red_max_u64(&s64[L_TAU_B + st], tB);
+              if (MASKED && tA) sm_red_max_u64(&s64[L_TAU_A + st], tA);
+              sh[S_BASEB + st] = (int)(tB >> 48);
+              sh[S_BASEA + st] = (int)(tA >> 48);
+              __threadfence_block();
+              vsh[S_BOOTOK + st] = j + 1;
+            }
+          }
+          __syncwarp();
+        }
+        if (t == t_first) {
+          // nothing of the item is scanned before its first thresholds are there
+          if (lane == 0) {
+            uint32_t spins = 0;
+            while (vsh[S_BOOTOK + st] != j + 1 && !vsh[S_ABORT]) {
+              if (++spins > kWaitLimit) abort_now();
+              __nanosleep(32);  // (a waiting lane must not take issue slots from the warps still at work)
+            }
+          }
+          __syncwarp();
+          __threadfence_block();
+          if (vsh[S_ABORT]) break;
+          ctx.baseB = (uint32_t)vsh[S_BASEB + st];
+          ctx.baseA = (uint32_t)vsh[S_BASEA + st];
+        }
         uint64_t tcB = 0, tcA = 0;
         typename Elem<T>::Thr thB, thA;
         auto refresh = [&]() {
@@ -339,12 +445,6 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
           thA = Elem<T>::make_thr(MASKED ? value_of(kA32 < 0x007FFFFFu ? 0x007FFFFFu : kA32) : INFINITY);
         };
         const bool whole = nchunk == kSTile / 16;  // only an item's last tile can be short
-        constexpr int kMine = kSTile / 16 / kShare;          // chunks of a tile per warp
-#ifndef ARCS_KU
-#define ARCS_KU 4
-#endif
-        constexpr int kU = kMine / 32 < ARCS_KU ? kMine / 32 : ARCS_KU;   // chunks per lane per step
-        const int c_lo = (warp % kShare) * kMine;
         refresh();  // (once per visit: the thresholds move slowly against the few hundred cycles a visit takes)
         for (int c0 = c_lo; c0 < min(nchunk, c_lo + kMine); c0 += kU * 32) {
           uint4 q[kU];
@@ -357,12 +457,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
             bool h = Elem<T>::chunk_reaches(q[u], thB);
             if (MASKED) {
               bool hb = h && ci < nchunk;
-              if (hb) {
-                const int32_t gid = col0 + ci * E;
-                uint32_t bits = __ldg(&mrow[gid >> 5]) >> (gid & 31);
-                if ((gid & 31) + E > 32) bits |= __ldg(&mrow[(gid >> 5) + 1]) << (32 - (gid & 31));
-                hb = (bits & ((1u << E) - 1u)) != 0u;
-              }
+              if (hb) hb = mask_bits_of<E>(mrow, col0 + ci * E) != 0u;
               h = hb || Elem<T>::chunk_reaches(q[u], thA);
             }
             if (!whole) h = h && ci < nchunk;
@@ -400,110 +495,129 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
       if (vsh[S_ABORT]) break;
       if (__any_sync(0xFFFFFFFFu, have > 0)) flush();  // what is still set aside
       __syncwarp();
-      // this warp has listed everything it found in the item; the warp that says so last hands
-      // the item over: list lengths and last thresholds to the item's header, the set of state
-      // cleared for the item three on
-      int old = 0;
+      // this warp has listed everything it found in the item; the threshold warp hands the item
+      // over when all scanners have said so
       if (lane == 0) {
         __threadfence_block();
-        old = (int)sm_atomic_add(&sh[S_DONE + st], 1u);
-      }
-      old = __shfl_sync(0xFFFFFFFFu, old, 0);
-      if (old == kScanW - 1) {
-        __threadfence_block();
-        int d, kr;
-        bool ex;
-        find_bin(ctx.histB, hd->K, d, kr, ex);
-        if (d > 0 && lane == 0) sm_red_max_u64(&s64[L_TAU_B + st], (unsigned long long)((ctx.baseB + (uint32_t)d) << 16) << 32);
-        if (MASKED) {
-          find_bin(ctx.histA, ARCS_HEAD, d, kr, ex);
-          if (d > 0 && lane == 0) sm_red_max_u64(&s64[L_TAU_A + st], (unsigned long long)((ctx.baseA + (uint32_t)d) << 16) << 32);
-        }
-        __syncwarp();
-        if (lane == 0) {
-          w.hdr->n_candB = vsh[S_CNT + 4 * st + 0];
-          w.hdr->n_candA = vsh[S_CNT + 4 * st + 1];
-          w.hdr->n_tch = vsh[S_CNT + 4 * st + 2];
-          w.hdr->tauB = v64[L_TAU_B + st];
-          w.hdr->tauA = v64[L_TAU_A + st];
-        }
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) xh[(2 * st) * 256 + i * 32 + lane] = 0;  // both histograms of the item's set
-        if (lane < 4) sh[S_CNT + 4 * st + lane] = 0;
-        if (lane == 0) sh[S_DONE + st] = 0;
-        __syncwarp();
-        __threadfence_block();
-        if (lane == 0) {
-          vsh[S_STREAMED] = j + 1;
-        }
+        sm_red_add(&sh[S_DONE + st], 1u);
       }
       G0 += (uint32_t)T_;
     }
   } else if (warp == kTauWarp) {
     // =================================================================== threshold warp
-    // Fetches the tables of the items ahead (an item may take a set of state once the item
-    // three back has been handed over), publishes an item when its table has landed, and keeps
-    // reading new thresholds off the coarse histograms of the items that are streaming: the
-    // lower edge of the bin holding the k-th best survivor counted so far.
-    int issued = 0, prepped = 0;
+    // Keeps reading new thresholds off the coarse histograms of the items that are streaming (the
+    // lower edge of the bin holding the k-th best survivor counted so far), and hands an item over
+    // when every scanner has listed what it found in it: list lengths and last thresholds to the
+    // item's header in the workspace, the item released to the finish kernel, the set of state
+    // cleared for the item three on.
     uint32_t idle = 0;
-    pdl_wait();  // the prepare kernel's output is read from here on (everything else in this CTA follows this warp's flags)
     for (;;) {
       if (vsh[S_ABORT]) break;
       const int done = vsh[S_STREAMED];
       if (done >= my_n) break;
+      const int prepped = vsh[S_PREPARED];
       __threadfence_block();
-      while (issued < my_n && issued < done + 3) {
+      if (done < prepped && vsh[S_DONE + done % 3] == kScanW) {
+        const int j = done, st = j % 3;
+        __threadfence_block();
+        const ItemHdr* hd = tab_hdr(st);
+        const ItemWs w = item_ws(a, (int)blockIdx.x + j * (int)gridDim.x);
+        const bool booted = vsh[S_BOOTOK + st] == j + 1;
+        const uint32_t baseB = (uint32_t)vsh[S_BASEB + st], baseA = (uint32_t)vsh[S_BASEA + st];
+        int d, kr;
+        bool ex;
+        find_bin(xh + (2 * st) * 256, hd->K, d, kr, ex);
+        if (booted && d > 0 && lane == 0) sm_red_max_u64(&s64[L_TAU_B + st], (unsigned long long)((baseB + (uint32_t)d) << 16) << 32);
+        if (MASKED) {
+          find_bin(xh + (2 * st + 1) * 256, ARCS_HEAD, d, kr, ex);
+          if (booted && d > 0 && lane == 0) sm_red_max_u64(&s64[L_TAU_A + st], (unsigned long long)((baseA + (uint32_t)d) << 16) << 32);
+        }
+        __syncwarp();
+        const int nB = vsh[S_CNT + 4 * st + 0], nA = vsh[S_CNT + 4 * st + 1], nT = vsh[S_CNT + 4 * st + 2];
+        const int n_pre = hd->n_pre;
+        if (nB > kListB || nA > kListA || nT > item_pre_cap(a.hash_slots) - n_pre) {
+          // a list overflowed: the finish kernel will read the item again and needs its filter
+          const uint32_t* bl = tab_bloom(st);
+          for (int i = lane; i < bloom_words_of(a.hash_slots); i += 32) w.bloom[i] = bl[i];
+        }
+        __syncwarp();
         if (lane == 0) {
-          const int st = issued % 3;
-          fence_proxy_async();  // the set's last readers are done (their item was handed over); order them before the copy
-          mbar_expect_tx(&tab_full[st], (uint32_t)tab_bytes);
-          bulk_load(tabs + (size_t)st * tab_bytes, a.ws_items + (size_t)((int)blockIdx.x + issued * (int)gridDim.x) * a.item_block,
-                    (uint32_t)tab_bytes, &tab_full[st]);
+          w.hdr->tauB = v64[L_TAU_B + st];
+          w.hdr->tauA = v64[L_TAU_A + st];
+          w.hdr->K = hd->K;
+          w.hdr->touched = hd->touched;
+          w.hdr->bans = hd->bans;
+          w.hdr->n_pre = n_pre;
+          w.hdr->n_tch = nT;
+          w.hdr->n_candB = nB;
+          w.hdr->n_candA = nA;
         }
-        ++issued;
-      }
-      if (prepped < issued) {
-        const int st = prepped % 3;
-        if (mbar_try_wait(&tab_full[st], (uint32_t)(prepped / 3) & 1u)) {
-          if (lane == 0) {
-            const ItemHdr* hd = tab_hdr(st);
-            s64[L_TAU_B + st] = hd->tau0B;
-            s64[L_TAU_A + st] = hd->tau0A;
-            __threadfence_block();
-            vsh[S_PREPARED] = prepped + 1;
-          }
-          ++prepped;
-          idle = 0;
-          __syncwarp();
-          continue;
+        __syncwarp();
+        if (lane == 0) {
+          // (gpu scope: the scanners' list entries, ordered before their arrival at CTA scope, and
+          //  the header are read by another kernel once the item is released)
+          __threadfence();
+          st_release_gpu(&w.hdr->streamed, 1);
         }
-        if (prepped == done && ++idle > kWaitLimit) {  // the stream waits for this table
-          abort_now();
-          break;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) xh[(2 * st) * 256 + i * 32 + lane] = 0;  // both histograms of the item's set
+        if (lane < 4) sh[S_CNT + 4 * st + lane] = 0;
+        if (lane == 0) {
+          sh[S_DONE + st] = 0;
+          sh[S_BOOTCNT + st] = 0;
+          s64[L_BOOT_B + st] = 0xFFFFFFFFFFFFFFFFull;
+          s64[L_BOOT_A + st] = 0xFFFFFFFFFFFFFFFFull;
         }
+        __syncwarp();
+        __threadfence_block();
+        if (lane == 0) vsh[S_STREAMED] = j + 1;
+        idle = 0;
+        continue;
       }
       for (int j = done; j < min(prepped, done + 2); ++j) {
         const int st = j % 3;
+        if (vsh[S_BOOTOK + st] != j + 1) continue;  // (the bins' base is known once the scanners have found the first threshold)
+        __threadfence_block();
         const ItemHdr* hd = tab_hdr(st);
         int d, kr;
         bool ex;
         find_bin(xh + (2 * st) * 256, hd->K, d, kr, ex);
         if (d > 0 && lane == 0)
-          sm_red_max_u64(&s64[L_TAU_B + st], (unsigned long long)(((uint32_t)hd->baseB + (uint32_t)d) << 16) << 32);
+          sm_red_max_u64(&s64[L_TAU_B + st], (unsigned long long)(((uint32_t)vsh[S_BASEB + st] + (uint32_t)d) << 16) << 32);
         if (MASKED) {
           find_bin(xh + (2 * st + 1) * 256, ARCS_HEAD, d, kr, ex);
           if (d > 0 && lane == 0)
-            sm_red_max_u64(&s64[L_TAU_A + st], (unsigned long long)(((uint32_t)hd->baseA + (uint32_t)d) << 16) << 32);
+            sm_red_max_u64(&s64[L_TAU_A + st], (unsigned long long)(((uint32_t)vsh[S_BASEA + st] + (uint32_t)d) << 16) << 32);
         }
       }
       __syncwarp();
+      if (++idle > kWaitLimit) {  // (nothing was handed over for seconds)
+        abort_now();
+        break;
+      }
       __nanosleep(kTauSleepNs);
     }
-    // (abandoned: a table copy may still be in flight; give it a bounded chance to land)
-    if (vsh[S_ABORT] && lane == 0)
-      for (int x = prepped; x < issued; ++x) mbar_wait(&tab_full[x % 3], (uint32_t)(x / 3) & 1u);
+  } else {
+    // =================================================================== preparing warps
+    // An item may take a set of state once the item three back has been handed over.
+    const int gt = tid - kPrepWarp0 * 32;
+    for (int j = 0; j < my_n; ++j) {
+      const int st = j % 3;
+      uint32_t spins = 0;
+      while (vsh[S_STREAMED] < j - 2 && !vsh[S_ABORT]) {
+        if (++spins > kWaitLimit) abort_now();
+        __nanosleep(100);
+      }
+      if (group_sync_or<3, kPrepG>(vsh[S_ABORT] != 0)) break;
+      __threadfence_block();
+      prep_item<T, MASKED>(a, (int)blockIdx.x + j * (int)gridDim.x, tab_hdr(st), tab_bloom(st), hk, hi_, pmisc, gt);
+      if (gt == 0) {
+        s64[L_TAU_B + st] = 0ull;
+        s64[L_TAU_A + st] = 0ull;
+        __threadfence();  // (gpu scope as well: the entries written to the workspace are read by the finish kernel)
+        vsh[S_PREPARED] = j + 1;
+      }
+    }
   }
 }
 

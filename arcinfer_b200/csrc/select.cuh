@@ -177,21 +177,11 @@ __device__ __noinline__ void sel_prune(const Sel& s, int k, const PruneScratch& 
 }
 
 
-// A lower bound of the kth largest (1-based) of 32 * PER keys, found by ONE warp with a search
-// on the keys' upper 16 bits, two bits a round (bf16 resolution; exact for bf16 data): the
-// largest t with at least kth keys >= t. Keys in registers, no shared-memory atomics.
+// A lower bound of the kth largest (1-based) of 32 * PER keys held PER to a lane, found by ONE
+// warp with a search on the keys' upper 16 bits, two bits a round (bf16 resolution; exact for
+// bf16 data): the largest t with at least kth keys >= t. No shared-memory traffic.
 template <int PER>
-__device__ __forceinline__ uint32_t warp_kth16(const uint32_t* keys, int kth) {
-  const int lane = threadIdx.x & 31;
-  uint32_t k[PER];
-#pragma unroll
-  for (int i = 0; i < PER / 4; ++i) {
-    const uint4 q = reinterpret_cast<const uint4*>(keys)[i * 32 + lane];
-    k[4 * i] = q.x;
-    k[4 * i + 1] = q.y;
-    k[4 * i + 2] = q.z;
-    k[4 * i + 3] = q.w;
-  }
+__device__ __forceinline__ uint32_t warp_kth16_regs(const uint32_t (&k)[PER], int kth) {
   uint32_t t = 0;
 #pragma unroll 1
   for (int bit = 14; bit >= 0; bit -= 2) {
@@ -209,6 +199,37 @@ __device__ __forceinline__ uint32_t warp_kth16(const uint32_t* keys, int kth) {
     t |= (a3 >= kth ? 3u : a2 >= kth ? 2u : a1 >= kth ? 1u : 0u) << bit;
   }
   return t << 16;
+}
+// The kth largest (1-based, kth <= 32) of one key per lane, ties counted: the largest key t with at
+// least kth lanes holding a key >= t. A handful of warp-wide maxima, no search over bits.
+__device__ __forceinline__ uint32_t warp_kth_lane(uint32_t key, int kth) {
+  uint32_t t = 0u;
+  int taken = 0;
+  bool in = true;
+#pragma unroll 1
+  while (taken < kth) {
+    t = __reduce_max_sync(0xFFFFFFFFu, in ? key : 0u);
+    if (t == 0u) break;  // fewer than kth keys above zero
+    const bool hit = in && key == t;
+    taken += __popc(__ballot_sync(0xFFFFFFFFu, hit));
+    in = in && !hit;
+  }
+  return taken >= kth ? t : 0u;
+}
+// the same with the keys in shared memory (32 * PER of them, 16-byte aligned)
+template <int PER>
+__device__ __forceinline__ uint32_t warp_kth16(const uint32_t* keys, int kth) {
+  const int lane = threadIdx.x & 31;
+  uint32_t k[PER];
+#pragma unroll
+  for (int i = 0; i < PER / 4; ++i) {
+    const uint4 q = reinterpret_cast<const uint4*>(keys)[i * 32 + lane];
+    k[4 * i] = q.x;
+    k[4 * i + 1] = q.y;
+    k[4 * i + 2] = q.z;
+    k[4 * i + 3] = q.w;
+  }
+  return warp_kth16_regs<PER>(k, kth);
 }
 
 // Bin of a key in an item's coarse histogram: the key's upper 16 bits (bf16 resolution) relative

@@ -60,8 +60,8 @@ const char* arcs_last_error(void); /* text of the calling thread's last failure 
 int arcs_version(void);
 
 /* ------------------------------------------------------------------------------------------
- * sample_batch: Sampler::adjusted + Sampler::sample for B rows in one call (three launches on
- * the stream: a small per-row prepare, the single pass over the logits, a small per-row finish)
+ * sample_batch: Sampler::adjusted + Sampler::sample for B rows in one call (two launches on the
+ * stream: the single pass over the logits, and a small per-row finish that runs beside it)
  * (tools/sampler.h:36-78, :147-176); with a mask, Sampler::sample_allowed (:82-144) where
  * the predicate ok(t) is bit t of the row's mask.
  * ---------------------------------------------------------------------------------------- */
@@ -81,8 +81,10 @@ typedef struct {
   const uint32_t* mask;      /* NULL: unconstrained. Else packed allowed-token bits, rows of mask_stride words */
   const int32_t* mask_row;   /* [B] mask row used by each batch row, or NULL: row b uses mask row b */
   int64_t mask_stride;       /* words per mask row, >= ceil(V/32) */
-  int32_t max_hist, max_bias;/* upper bounds on any row's list length (size the on-chip filter: together at most
-                                2048, else ARCS_ERR_LIST) */
+  int32_t max_hist, max_bias;/* upper bounds on any row's list length (they size the on-chip filter and table). A row
+                                whose penalties can only lower logits (repeat_penalty >= 1, presence and frequency
+                                >= 0) and whose bias list has at most 64 entries takes a history of any length up to
+                                max_hist; any other row's lists may hold 2048 entries together, else ARCS_ERR_LIST */
   int32_t id_base;           /* global id of column 0 (vocabulary shards); 0 otherwise */
   int32_t v_global;          /* whole vocabulary size when sharded; 0 means V */
   /* outputs (device pointers; optional ones may be NULL) */
@@ -103,9 +105,10 @@ typedef struct {
 /* max_list: max_hist + max_bias of the call (0 without lists) */
 size_t arcs_sample_workspace_bytes(int32_t B, int32_t V, int32_t masked, int32_t max_list);
 int arcs_sample_batch(const arcs_sample_args* args, void* stream);
-/* Measurement aid: the same three launches with CUDA events between them on `stream`; waits for
- * them and returns the device time of the prepare, stream and finish kernels in ms3[0..2]. */
-int arcs_sample_batch_timed(const arcs_sample_args* args, void* stream, float* ms3);
+/* Measurement aid: the same two launches, one after the other (the finish kernel does not run
+ * beside the stream kernel here), with CUDA events between them on `stream`; waits for them and
+ * returns the device time of the stream and finish kernels in ms2[0..1]. */
+int arcs_sample_batch_timed(const arcs_sample_args* args, void* stream, float* ms2);
 
 /* Vocabulary shards (no counterpart in the reference, which has one device): every GPU runs
  * arcs_sample_batch on its columns of all rows (`id_base`, `v_global`; lists are filtered by range)
