@@ -63,14 +63,20 @@ struct SampleDev {
 };
 
 // ---- geometry of the stream (shared with the preparing warps, which count the listed columns
-// that fall into each scanner warp's share of an item's first tiles)
+// that fall into an item's first tiles)
 constexpr int kScanW = 16;                   // scanner warps
 constexpr int kShare = 2;                    // scanner warps that split one tile between them
 constexpr int kTeams = kScanW / kShare;      // teams: team x takes the tiles whose running number is x modulo kTeams
 constexpr int kSTile = 8192;                 // bytes per tile (512 chunks of 16 bytes)
 constexpr int kMine = kSTile / 16 / kShare;  // chunks of a tile per scanner warp
-constexpr int kBootTiles = 2;                // first tiles of an item the first threshold is read off
-constexpr int kBootWin = kBootTiles * kShare; // shares of those tiles: one per scanner warp that takes part
+constexpr int kBootTiles = 4;                // first tiles of an item its first threshold is read off
+constexpr int kBootBytes = kBootTiles * kSTile;
+constexpr int kPrepW = 4;                    // preparing warps of the stream kernel
+constexpr int kPrepG = kPrepW * 32;          // ... threads (named barrier 3)
+// One bit per 16-byte chunk of those tiles: the chunk holds a listed column. Chunk c is bit
+// c / kPrepG of word c % kPrepG: the chunks one preparing thread looks at share a word.
+constexpr int kBootSkipWords = kPrepG;
+static_assert(kBootBytes / 16 / kPrepG <= 32, "a preparing thread's chunks of the first tiles fit one word of bits");
 
 // ---- one item's block of the workspace
 // [ItemHdr][filter bloom_words words: written only when a list of the stream overflowed]
@@ -86,8 +92,7 @@ struct ItemHdr {
   int32_t n_tch;                    // flagged hot elements appended by the scanners
   int32_t n_candB, n_candA;         // survivors written by the scanners
   int32_t streamed;                 // 1 (released at gpu scope) once everything above and the lists are final
-  uint8_t boot_extra[kBootWin];     // listed columns inside each scanner warp's share of the first tiles (saturating)
-  int32_t pad[11];
+  int32_t pad[12];
 };
 static_assert(sizeof(ItemHdr) == 96, "ItemHdr is 96 bytes");
 // How an item's penalised / biased tokens reach the finish kernel.
@@ -100,11 +105,12 @@ constexpr int kTouchNone = 0, kTouchLight = 1, kTouchTable = 2;
 constexpr int kLightBias = 64;  // longest bias list handled without the table
 
 // filter size: 64 bits per listed id while the lists are short (two bits set per id: about one false
-// alarm in a thousand lookups), at most 2048 words: longer lists only raise the false-alarm rate,
+// alarm in a thousand lookups), at most 1024 words: longer lists only raise the false-alarm rate,
 // and a false alarm costs one more entry for the finish kernel to settle
-constexpr int kMaxTableSlots = 4096;  // most distinct listed tokens x 2 the on-chip table holds
-__host__ __device__ inline int32_t bloom_words_of(int hash_slots) { return hash_slots < 256 ? 256 : hash_slots > 2048 ? 2048 : hash_slots; }
+constexpr int kMaxTableSlots = 2048;  // most distinct listed tokens x 2 the on-chip table holds
+__host__ __device__ inline int32_t bloom_words_of(int hash_slots) { return hash_slots < 256 ? 256 : hash_slots > 1024 ? 1024 : hash_slots; }
 __host__ __device__ inline int32_t item_tab_bytes(int hash_slots) { return (int32_t)sizeof(ItemHdr) + bloom_words_of(hash_slots) * 4; }
+// (in shared memory a set of per-item state also carries kBootSkipWords words behind the filter)
 __host__ __device__ inline int32_t item_pre_cap(int hash_slots) { return hash_slots + kMaxScalars; }
 __host__ __device__ inline int64_t item_block_bytes(bool masked, int hash_slots) {
   return (int64_t)item_tab_bytes(hash_slots) + (int64_t)item_pre_cap(hash_slots) * 8 + (int64_t)kListB * 8 + (masked ? (int64_t)kListA * 8 : 0);

@@ -5,8 +5,9 @@
 // per-item state the scanners will read:
 //  - a filter over the columns a penalty or a bias touches (tools/sampler.h:154-174), which the
 //    scanners consult for their hot elements;
-//  - the item's header (how many candidates the row keeps, how touched tokens are handled, how
-//    many listed columns fall into each scanner warp's share of the item's first tiles);
+//  - the item's header (how many candidates the row keeps, how touched tokens are handled), and
+//    one bit per 16-byte chunk of the item's first tiles that holds a listed column (those chunks
+//    are left out when the item's first threshold is read off these tiles);
 // and writes to the item's block of the workspace entries with final values for the tokens it
 // evaluates itself, with the exact fp32 arithmetic of Sampler::adjusted: the bias tokens, and -
 // when some penalty can raise a logit, so that a token may matter although its raw logit is not
@@ -16,20 +17,18 @@
 
 namespace arcs {
 
-constexpr int kPrepW = 2;             // preparing warps of the stream kernel
-constexpr int kPrepG = kPrepW * 32;   // ... threads (named barrier 3)
 static_assert(kPrepG >= 64, "two whole warps take the scalar elements at either end of an item");
 
 // indices into the group's small scratch
-enum { P_NPRE = 0, P_WIN = 1 /* [kBootWin] */, P_END = 1 + kBootWin };
+enum { P_NPRE = 0, P_CMD = 1, P_END = 4 };
 
 // hk / hi_: [hash_slots] table of the distinct listed columns (table mode only); bl: the set's
-// filter; shdr: the set's header; pmisc: [P_END]. Called by all kPrepG threads (gt = index in the group).
+// filter; skip: the set's [kBootSkipWords] chunk bits; shdr: the set's header; pmisc: [P_END].
+// Called by all kPrepG threads (gt = index in the group).
 template <typename T, bool MASKED>
-__device__ __forceinline__ void prep_item(const SampleDev& a, int item, ItemHdr* shdr, uint32_t* bl, uint32_t* hk, uint32_t* hi_,
-                                          int* pmisc, int gt) {
+__device__ __forceinline__ void prep_item(const SampleDev& a, int item, ItemHdr* shdr, uint32_t* bl, uint32_t* skip, uint32_t* hk,
+                                          uint32_t* hi_, int* pmisc, int gt) {
   constexpr int G = kPrepG;
-  constexpr int E = Elem<T>::kPerChunk;
   const int bw = bloom_words_of(a.hash_slots);
   const int lane = gt & 31;
   const int32_t Vg = a.v_global > 0 ? a.v_global : a.V;
@@ -42,7 +41,8 @@ __device__ __forceinline__ void prep_item(const SampleDev& a, int item, ItemHdr*
     if (r.k_bad) raise_status(a.status, ARCS_ERR_TOPK);
     if (!r.lists_ok) raise_status(a.status, ARCS_ERR_LIST);
   }
-  if (gt < P_END) pmisc[gt] = 0;
+  if (gt == 0) pmisc[P_NPRE] = 0;
+  for (int i = gt; i < kBootSkipWords; i += G) skip[i] = 0u;
   bool bans = false;  // Sampler::bans_: any bias entry <= -100, in range or not (tools/sampler.h:34)
   for (int i = gt; i < r.NB && r.lists_ok; i += G) bans = bans || a.bias_vals[r.q0 + i] <= -100.0f;
   bans = group_sync_or<3, G>(bans);
@@ -53,15 +53,15 @@ __device__ __forceinline__ void prep_item(const SampleDev& a, int item, ItemHdr*
     const int32_t c = t - a.id_base;
     return (c < it.lo || c >= it.hi) ? -1 : c;
   };
-  // A listed column inside the item's first kBootTiles tiles is counted for the scanner warp whose
-  // share it lies in: it may own a chunk maximum there without counting for the first threshold.
+  // A listed column inside the item's first kBootTiles tiles marks its 16-byte chunk: the chunk's
+  // maximum may be that token's raw logit, which counts for no threshold.
   auto count_window = [&](bool valid, int32_t c) {
     if (!valid) return;
     const int32_t rel = c - it.p.body_first;
-    constexpr int32_t kTileElems = kSTile / (int)sizeof(T);
-    if (rel < 0 || rel >= kBootTiles * kTileElems) return;
-    const int t = rel / kTileElems, h = (rel % kTileElems) / (kMine * E);
-    sm_red_add(&pmisc[P_WIN + t * kShare + h], 1u);
+    if (rel >= 0 && rel < kBootBytes / (int)sizeof(T)) {
+      const int ch = rel / (16 / (int)sizeof(T));
+      sm_red_or(&skip[ch % kPrepG], 1u << (ch / kPrepG));
+    }
   };
   // one more column for the filter
   auto bloom_add = [&](bool valid, int32_t c) {
@@ -241,7 +241,6 @@ __device__ __forceinline__ void prep_item(const SampleDev& a, int item, ItemHdr*
     shdr->n_candA = 0;
     shdr->streamed = 0;
   }
-  if (gt < kBootWin) shdr->boot_extra[gt] = (uint8_t)min(pmisc[P_WIN + gt], 255);
   group_sync<3, G>();
 }
 

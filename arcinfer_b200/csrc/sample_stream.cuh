@@ -7,13 +7,15 @@
 //   scanners   16 warps, two to a tile: a 16-byte chunk whose maximum is below the item's
 //              current threshold costs a handful of instructions; the few other chunks are set
 //              aside, then tested element by element, and the survivors appended to the item's
-//              lists in the workspace. On their first tiles of an item the scanners find the
-//              item's first threshold together (boot). The warp that closes an item last
-//              releases it to the finish kernel;
+//              lists in the workspace;
 //   threshold  one warp keeps raising the thresholds of the items that are streaming from the
-//              coarse histograms the scanners update;
+//              coarse histograms the scanners update, and releases an item to the finish kernel
+//              when all scanners are through with it;
 //   preparing  two warps build the filters and headers of the items ahead of the stream
-//              (sample_prep.cuh).
+//              (sample_prep.cuh), and find each item's first threshold: ahead of the stream they
+//              fetch the item's first tiles into a side buffer (the ring's own copy of those
+//              tiles then comes out of the L2 cache) and read the threshold off the maxima of
+//              their 16-byte chunks.
 // Items rotate over three sets of per-item state, so the ring never pauses between items.
 // A list that overflows (ascending data, masses of ties) is only counted: the finish kernel
 // sees the count and reads that item again itself.
@@ -22,10 +24,25 @@
 
 namespace arcs {
 
+#ifdef ARCS_DEV_TRACE
+__device__ long long g_trace[148 * 64];
+#define ARCS_TRACE(slot) do { if ((slot) < 64) g_trace[blockIdx.x * 64 + (slot)] = clock64(); } while (0)
+#define ARCS_TACC_BEGIN long long tacc0_ = clock64()
+#define ARCS_TACC_END(slot) do { if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == 3) { g_trace[blockIdx.x * 64 + (slot)] += clock64() - tacc0_; g_trace[blockIdx.x * 64 + (slot) + 1] += 1; } } while (0)
+#else
+#define ARCS_TACC_BEGIN do { } while (0)
+#define ARCS_TACC_END(slot) do { } while (0)
+#define ARCS_TRACE(slot) do { } while (0)
+#endif
+
 constexpr int kProdWarp = kScanW;                          // producer warp (its first lanes work)
 constexpr int kTauWarp = kScanW + 1;                       // threshold warp
-constexpr int kPrepWarp0 = kScanW + 2;                     // first preparing warp
-constexpr int kThreadsS = (kScanW + 2 + kPrepW) * 32;      // 640 threads
+constexpr int kCloseWarp = kScanW + 2;                     // the warp that hands items over
+constexpr int kPrepWarp0 = kScanW + 3;                     // first preparing warp
+constexpr int kThreadsS = (kScanW + 3 + kPrepW) * 32;      // 736 threads
+// The register file is shared with one CTA of the finish kernel, which runs beside this kernel
+// (128 threads x 64 registers): the bound below keeps this kernel at 72 registers a thread.
+constexpr int kRegBoundThreads = 896;
 constexpr int kProdLanes = 2;                              // lanes of the producer warp that issue copies (one thread cannot issue 8 KB copies fast enough)
 constexpr int kTauSleepNs = 200;                           // pause between two threshold updates
 constexpr int kRing = 16;                                  // tiles in the ring (a multiple of kTeams)
@@ -33,6 +50,7 @@ constexpr int kPend = 2;                                   // chunks each lane o
 constexpr int kStash = kPend * 32;                         // ... per warp
 constexpr int kFlushEvery = 2;                             // visits after which a warp examines what it has set aside even if its next tile is there
 constexpr int kU = 4;                                      // chunks per lane per step of the scan
+constexpr int kBootLead = 72;                              // tiles the producer is short of an item when that item's first tiles are fetched for its first threshold
 static_assert(kRing % kTeams == 0, "a team always meets its tiles in the same slots");
 static_assert(kMine % (32 * kU) == 0 && kMine / 32 <= 8, "a warp's share of a tile: whole steps, at most 8 chunks per lane");
 
@@ -40,9 +58,10 @@ static_assert(kMine % (32 * kU) == 0 && kMine / 32 <= 8, "a warp's share of a ti
 enum {
   S_ABORT = 0, S_PREPARED, S_STREAMED,
   S_DONE = 4 /* [3] */, S_CNT = 8 /* [3 sets][B, A, flagged, -] */,
-  S_BOOTCNT = 20 /* [3] */, S_BOOTOK = 23 /* [3] */, S_BASEB = 26 /* [3] */, S_BASEA = 29 /* [3] */, S_END = 32
+  S_PROG = 20 /* the producer's place: item << 16 | tile */,
+  S_BOOTOK = 23 /* [3] */, S_BASEB = 26 /* [3] */, S_BASEA = 29 /* [3] */, S_END = 32
 };
-enum { L_TAU_B = 0 /* [3] */, L_TAU_A = 3 /* [3] */, L_BOOT_B = 6 /* [3] */, L_BOOT_A = 9 /* [3] */, L_END = 12 };
+enum { L_TAU_B = 0 /* [3] */, L_TAU_A = 3 /* [3] */, L_END = 6 };
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
@@ -153,25 +172,117 @@ __device__ __forceinline__ uint32_t mask_bits_of(const uint32_t* mrow, int32_t g
   return bits & ((1u << E) - 1u);
 }
 
+// An item's first thresholds, read by the preparing warps off the item's first tiles (buf: nbytes of
+// them in the side buffer): the maxima of the 16-byte chunks are distinct elements, so the k-th
+// largest of them bounds the k-th largest element from below. Chunks that hold a listed column
+// (skip: a word of chunk bits per thread) are left out: their maximum may be a token whose logit
+// a penalty changes. One pass: every thread keeps the RT largest maxima of its own chunks; the
+// k-th largest of all threads' kept values (a subset of the maxima, so still a lower bound) is
+// then found by one warp. Two kept values a thread serve k <= 256, four the 512 of the
+// constrained head ranking. tm: [2][kPrepG * RT] words of scratch.
+template <typename T, bool MASKED>
+__device__ __forceinline__ void boot_item(const SampleDev& a, const Item<T>& it, const ItemHdr* hd, const char* buf, int nbytes,
+                                          const uint32_t* skip, uint32_t* tm, unsigned long long* tauB, unsigned long long* tauA,
+                                          int* baseB, int* baseA, int gt) {
+  constexpr int G = kPrepG;
+  constexpr int E = Elem<T>::kPerChunk;
+  constexpr int RT = MASKED ? 4 : 2;
+  constexpr int R = 4;  // chunks a thread takes together: their loads and maxima overlap
+  static_assert(RT * G >= (MASKED ? ARCS_HEAD : ARCS_KCAP), "enough kept values for the largest k");
+  const int lane = gt & 31;
+  const int nchunk = nbytes / 16;
+  const uint32_t* mrow = MASKED ? a.mask + (size_t)(a.mask_row ? a.mask_row[it.b] : it.b) * a.mask_stride : nullptr;
+  const int32_t gid0 = it.p.body_first + a.id_base;
+  const uint32_t myskip = skip[gt];
+  float topB[RT], topA[RT];
+#pragma unroll
+  for (int i = 0; i < RT; ++i) topB[i] = topA[i] = -INFINITY;
+  // keep the RT largest, best first (a NaN is never kept: fmaxf / fminf return the other operand)
+  auto keep = [&](float (&top)[RT], float v) {
+#pragma unroll
+    for (int i = 0; i < RT; ++i) {
+      const float hi = fmaxf(top[i], v);
+      v = fminf(top[i], v);
+      top[i] = hi;
+    }
+  };
+  for (int i0 = 0; i0 * G + gt < nchunk; i0 += R) {
+    uint4 q[R];
+#pragma unroll
+    for (int x = 0; x < R; ++x) q[x] = (i0 + x) * G + gt < nchunk ? lds128(buf + ((i0 + x) * G + gt) * 16) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+    for (int x = 0; x < R; ++x) {
+      const int ci = (i0 + x) * G + gt;
+      if (ci >= nchunk || ((myskip >> (i0 + x)) & 1u)) continue;
+      const float mA = Elem<T>::chunk_max(q[x]);
+      if (!MASKED) {
+        keep(topB, mA);
+      } else {  // the selection proper counts allowed elements only; the head ranking all
+        keep(topA, mA);
+        const uint32_t bits = mask_bits_of<E>(mrow, gid0 + ci * E);
+        float mB = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < E; ++e)
+          if ((bits >> e) & 1u) mB = fmaxf(mB, Elem<T>::get(q[x], e));
+        keep(topB, mB);
+      }
+    }
+  }
+  // (nothing kept, or -inf itself: key zero, no number's)
+#pragma unroll
+  for (int i = 0; i < RT; ++i) {
+    tm[i * G + gt] = topB[i] > -INFINITY ? key_of(topB[i]) : 0u;
+    if (MASKED) tm[RT * G + i * G + gt] = topA[i] > -INFINITY ? key_of(topA[i]) : 0u;
+  }
+  group_sync<3, G>();
+  if (gt < 32) {
+    constexpr int PER = RT * G / 32;
+    uint32_t k[PER];
+#pragma unroll
+    for (int i = 0; i < PER; ++i) k[i] = tm[i * 32 + lane];
+    const uint32_t fB = warp_kth16_regs<PER>(k, hd->K);  // keeps ties with it
+    uint32_t fA = 0u;
+    if (MASKED) {
+#pragma unroll
+      for (int i = 0; i < PER; ++i) k[i] = tm[RT * G + i * 32 + lane];
+      fA = warp_kth16_regs<PER>(k, ARCS_HEAD);
+    }
+    if (lane == 0) {
+      // (zero: fewer than k chunks were there, no threshold)
+      const unsigned long long tB = (unsigned long long)fB << 32, tA = (unsigned long long)fA << 32;
+      if (tB) sm_red_max_u64(tauB, tB);
+      if (MASKED && tA) sm_red_max_u64(tauA, tA);
+      *baseB = (int)(tB >> 48);
+      *baseA = (int)(tA >> 48);
+    }
+  }
+  group_sync<3, G>();
+}
+
 static size_t stream_smem_bytes(int hash_slots) {
-  return (size_t)kRing * kSTile + 3 * (size_t)item_tab_bytes(hash_slots) + (size_t)kScanW * kStash * 20 + 2 * kRing * 8 + L_END * 8 +
-         6 * 256 * 4 + (size_t)hash_slots * 8 + S_END * 4 + P_END * 4 + 128;
+  return (size_t)kRing * kSTile + kBootBytes + 3 * ((size_t)item_tab_bytes(hash_slots) + kBootSkipWords * 4) + (size_t)kScanW * kStash * 20 + (2 * kRing + 8) * 8 +
+         L_END * 8 + 6 * 256 * 4 + 8 * kPrepG * 4 + (size_t)hash_slots * 8 + S_END * 4 + P_END * 4 + 128;
 }
 
 template <typename T, bool MASKED>
-__global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a) {
+__global__ void __launch_bounds__(kRegBoundThreads, 1) stream_kernel(const SampleDev a) {
   extern __shared__ __align__(128) char smem[];
   // ---- carve shared memory (ordered by alignment)
-  const int tab_bytes = item_tab_bytes(a.hash_slots);
+  const int tab_bytes = item_tab_bytes(a.hash_slots) + kBootSkipWords * 4;
   char* ring = smem;                                                          // kRing * kSTile
-  char* tabs = ring + (size_t)kRing * kSTile;                                 // [3] header + filter of the items in flight
+  char* bootbuf = ring + (size_t)kRing * kSTile;                              // kBootBytes: an item's first tiles, fetched ahead of the stream
+  char* tabs = bootbuf + kBootBytes;                                          // [3] header + filter of the items in flight
   uint4* stash_q = reinterpret_cast<uint4*>(tabs + 3 * (size_t)tab_bytes);     // [kScanW][kStash] chunks set aside by the scanners
   uint64_t* full = reinterpret_cast<uint64_t*>(stash_q + kScanW * kStash);     // [kRing] tile has landed
   uint64_t* empty = full + kRing;                                             // [kRing] tile has been scanned
-  unsigned long long* s64 = reinterpret_cast<unsigned long long*>(empty + kRing);  // [L_END]
+  uint64_t* boot_full = empty + kRing;                                        // the side buffer has landed (a phase per item)
+  uint64_t* prep_bar = boot_full + 2;                                         // [3] the set's item is prepared (a phase per use of the set)
+  uint64_t* bootok_bar = prep_bar + 3;                                        // [3] the set's item has its first thresholds
+  unsigned long long* s64 = reinterpret_cast<unsigned long long*>(bootok_bar + 3);  // [L_END]
   int32_t* stash_c = reinterpret_cast<int32_t*>(s64 + L_END);                 // [kScanW][kStash]
   uint32_t* xh = reinterpret_cast<uint32_t*>(stash_c + kScanW * kStash);      // [3 sets][B, A][256] coarse histograms
-  uint32_t* hk = xh + 6 * 256;                                                // [hash_slots] the preparing warps' table: columns
+  uint32_t* boot_tm = xh + 6 * 256;                                           // [2][4 * kPrepG] the preparing threads' largest chunk maxima
+  uint32_t* hk = boot_tm + 8 * kPrepG;                                       // [hash_slots] the preparing warps' table: columns
   uint32_t* hi_ = hk + a.hash_slots;                                          // [hash_slots] ... what applies to them
   int* sh = reinterpret_cast<int*>(hi_ + a.hash_slots);                       // [S_END]
   int* pmisc = sh + S_END;                                                    // [P_END]
@@ -179,6 +290,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
   volatile unsigned long long* v64 = s64;
   auto tab_hdr = [&](int st) { return reinterpret_cast<ItemHdr*>(tabs + (size_t)st * tab_bytes); };
   auto tab_bloom = [&](int st) { return reinterpret_cast<uint32_t*>(tabs + (size_t)st * tab_bytes + sizeof(ItemHdr)); };
+  auto tab_skip = [&](int st) { return tab_bloom(st) + bloom_words_of(a.hash_slots); };
 
   constexpr int E = Elem<T>::kPerChunk;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -190,9 +302,14 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
       mbar_init(&full[i], 1);
       mbar_init(&empty[i], kShare);
     }
-    mbar_init_fence();
     for (int i = 0; i < S_END; ++i) sh[i] = 0;
-    for (int i = 0; i < L_END; ++i) s64[i] = i >= L_BOOT_B ? 0xFFFFFFFFFFFFFFFFull : 0ull;
+    for (int i = 0; i < L_END; ++i) s64[i] = 0ull;
+    mbar_init(boot_full, 1);
+    for (int i = 0; i < 3; ++i) {
+      mbar_init(&prep_bar[i], 1);
+      mbar_init(&bootok_bar[i], 1);
+    }
+    mbar_init_fence();
   }
   for (int i = tid; i < 6 * 256; i += kThreadsS) xh[i] = 0u;
   // This call's items are not released yet: the flags the finish kernel waits on are cleared
@@ -200,6 +317,10 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
   for (int j = tid; j < my_n; j += kThreadsS) item_ws(a, (int)blockIdx.x + j * (int)gridDim.x).hdr->streamed = 0;
   __threadfence();
   __syncthreads();  // the only CTA-wide barrier
+#ifdef ARCS_DEV_TRACE
+  if (tid < 24) g_trace[blockIdx.x * 64 + 40 + tid] = 0;
+#endif
+  if (tid == 0) ARCS_TRACE(0);
   if (tid == 0) pdl_trigger();  // the finish kernel's CTAs may take their places beside this kernel: each waits for its row's items
 
   auto abort_now = [&]() {
@@ -237,10 +358,12 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
           abort_now();
           break;
         }
+        if (lane == 0) vsh[S_PROG] = (j << 16) | min(t, 0xFFFF);
         const uint32_t n = s_tile_bytes(it.p, t);
         mbar_expect_tx(&full[slot], n);
         bulk_load(ring + (size_t)slot * kSTile, it.p.body + (size_t)t * kSTile, n, &full[slot]);
       }
+      if (lane == 0) vsh[S_PROG] = my_n << 16;
       if (vsh[S_ABORT]) {  // give this lane's copies in flight a bounded chance to land before the CTA ends
         for (uint32_t x = g % kProdLanes; x < g; x += kProdLanes)
           if (x + kRing >= g) mbar_wait(&full[x % kRing], (x / kRing) & 1u);
@@ -255,16 +378,11 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
       const int st = j % 3;  // filters / thresholds / counts rotate over three sets
       const Item<T> it = item_of<T>(a, (int)blockIdx.x + j * (int)gridDim.x);
       const int T_ = s_tiles(it.p);
-      {  // the item's filter and header must be there (one lane polls)
-        if (lane == 0) {
-          uint32_t spins = 0;
-          while (vsh[S_PREPARED] <= j && !vsh[S_ABORT]) {
-            if (++spins > kWaitLimit) abort_now();
-            __nanosleep(64);
-          }
-        }
-        __syncwarp();
+      {  // the item's filter, header and first thresholds must be there
+        ARCS_TACC_BEGIN;
+        if (!mbar_wait_warp(&prep_bar[st], (uint32_t)(j / 3) & 1u) || !mbar_wait_warp(&bootok_bar[st], (uint32_t)(j / 3) & 1u)) abort_now();
         __threadfence_block();
+        ARCS_TACC_END(46);
       }
       if (vsh[S_ABORT]) break;
       const ItemHdr* hd = tab_hdr(st);
@@ -279,8 +397,8 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
       ctx.mrow = MASKED ? a.mask + (size_t)(a.mask_row ? a.mask_row[it.b] : it.b) * a.mask_stride : nullptr;
       ctx.histB = xh + (2 * st) * 256;
       ctx.histA = xh + (2 * st + 1) * 256;
-      ctx.baseB = 0;
-      ctx.baseA = 0;
+      ctx.baseB = (uint32_t)vsh[S_BASEB + st];
+      ctx.baseA = (uint32_t)vsh[S_BASEA + st];
       ctx.cnt = &sh[S_CNT + 4 * st];
       const ItemWs w = item_ws(a, (int)blockIdx.x + j * (int)gridDim.x);
       ctx.listB = w.candB;
@@ -291,6 +409,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
       const uint32_t* mrow = ctx.mrow;
       // examine everything the warp has set aside, against the thresholds of this moment
       auto flush = [&]() {
+        ARCS_TACC_BEGIN;
         ctx.tcB = v64[L_TAU_B + st];
         ctx.tcA = MASKED ? v64[L_TAU_A + st] : 0xFFFFFFFFFFFFFFFFull;
 #pragma unroll 1
@@ -301,6 +420,7 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
         }
         have = 0;
         __syncwarp();
+        ARCS_TACC_END(40);
       };
       const int t_first = (int)(((uint32_t)(warp / kShare) - G0) % kTeams);
       const int c_lo = (warp % kShare) * kMine;
@@ -323,117 +443,16 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
             since = 0;
           }
         }
-        if (!mbar_wait_warp(&full[slot], (g / kRing) & 1u)) {
-          abort_now();
-          break;
+        {
+          ARCS_TACC_BEGIN;
+          if (!mbar_wait_warp(&full[slot], (g / kRing) & 1u)) {
+            abort_now();
+            break;
+          }
+          ARCS_TACC_END(42);
         }
         const int nchunk = (int)(s_tile_bytes(it.p, t) / 16u);
         const int32_t col0 = it.p.body_first + t * (kSTile / (int)sizeof(T)) + a.id_base;  // global id of the tile's first element
-#ifdef ARCS_DEV_FAKEBOOT
-        if (t == t_first) {
-          if (lane == 0) {
-            const unsigned long long tB = (unsigned long long)(key_of(ARCS_DEV_FAKEBOOT) & 0xFFFF0000u) << 32;
-            sm_red_max_u64(&s64[L_TAU_B + st], tB);
-            sh[S_BASEB + st] = (int)(tB >> 48);
-            sh[S_BASEA + st] = 0;
-            __threadfence_block();
-            vsh[S_BOOTOK + st] = j + 1;
-          }
-          __syncwarp();
-        }
-        if (false) {
-#else
-        if (t == t_first && t < kBootTiles && c_lo < nchunk) {
-#endif
-          // ---- boot: the item's first threshold, found together by the scanner warps that meet the
-          // item's first kBootTiles tiles. A warp's kth-largest chunk maximum bounds kth elements of
-          // its share from below; with kth = ceil(K / warps taking part) in every share, the smallest
-          // of the warps' bounds has at least K elements of the item at or above it. Listed columns
-          // inside a share (the header counts them) may own a maximum there without counting, so
-          // that many more are skipped.
-          int n_part = 0;
-          for (int tt = 0; tt < min(T_, kBootTiles); ++tt) {
-            const int nc = (int)(s_tile_bytes(it.p, tt) / 16u);
-            n_part += min(kShare, (nc + kMine - 1) / kMine);
-          }
-          constexpr int PER = kMine / 32;
-          uint32_t kA[PER], kBm[PER];  // (kBm: maxima over the allowed elements, constrained rows only)
-#pragma unroll
-          for (int u = 0; u < PER; ++u) {
-            const int ci = c_lo + u * 32 + lane;
-            kA[u] = 0u;
-            if (MASKED) kBm[u] = 0u;
-            if (ci < nchunk) {
-              const uint4 q = lds128(tile + ci * 16);
-              kA[u] = key_of(Elem<T>::chunk_max(q));
-              if (MASKED) {  // the selection proper counts allowed elements only
-                const uint32_t bits = mask_bits_of<E>(mrow, col0 + ci * E);
-                float mB = -INFINITY;
-                bool anyB = false;
-#pragma unroll
-                for (int e = 0; e < E; ++e)
-                  if ((bits >> e) & 1u) {
-                    const float v = Elem<T>::get(q, e);
-                    if (!(v != v)) {  // (a NaN is never selected)
-                      mB = fmaxf(mB, v);
-                      anyB = true;
-                    }
-                  }
-                if (anyB) kBm[u] = key_of(mB);
-              }
-            }
-          }
-          const int my_chunks = min(kMine, nchunk - c_lo);
-          const int extra = hd->boot_extra[t * kShare + warp % kShare];
-          // A small kth is read off the lanes' own maxima (disjoint sets of chunks: as good a bound,
-          // a fraction of the work); a large one off all chunk maxima, upper 16 key bits.
-          auto kth_of = [&](const uint32_t (&k)[PER], int kth) -> uint32_t {
-            if (extra >= 255 || kth > my_chunks) return 0u;
-            if (kth <= 8) {
-              uint32_t m = k[0];
-#pragma unroll
-              for (int u = 1; u < PER; ++u) m = max(m, k[u]);
-              return warp_kth_lane(m, kth) & 0xFFFF0000u;
-            }
-            return warp_kth16_regs<PER>(k, kth);
-          };
-          const int kthB = (hd->K + n_part - 1) / n_part + extra;
-          const uint64_t bB = (uint64_t)(MASKED ? kth_of(kBm, kthB) : kth_of(kA, kthB)) << 32;  // keeps ties with it
-          uint64_t bA = 0ull;
-          if (MASKED) bA = (uint64_t)kth_of(kA, (ARCS_HEAD + n_part - 1) / n_part + extra) << 32;
-          if (lane == 0) {
-            sm_red_min_u64(&s64[L_BOOT_B + st], (unsigned long long)bB);
-            if (MASKED) sm_red_min_u64(&s64[L_BOOT_A + st], (unsigned long long)bA);
-            __threadfence_block();
-            if ((int)sm_atomic_add(&sh[S_BOOTCNT + st], 1u) == n_part - 1) {
-              // the warp that comes last publishes the item's first thresholds
-              __threadfence_block();
-              const unsigned long long tB = v64[L_BOOT_B + st], tA = MASKED ? v64[L_BOOT_A + st] : 0ull;
-              if (tB) sm_red_max_u64(&s64[L_TAU_B + st], tB);
-              if (MASKED && tA) sm_red_max_u64(&s64[L_TAU_A + st], tA);
-              sh[S_BASEB + st] = (int)(tB >> 48);
-              sh[S_BASEA + st] = (int)(tA >> 48);
-              __threadfence_block();
-              vsh[S_BOOTOK + st] = j + 1;
-            }
-          }
-          __syncwarp();
-        }
-        if (t == t_first) {
-          // nothing of the item is scanned before its first thresholds are there
-          if (lane == 0) {
-            uint32_t spins = 0;
-            while (vsh[S_BOOTOK + st] != j + 1 && !vsh[S_ABORT]) {
-              if (++spins > kWaitLimit) abort_now();
-              __nanosleep(32);  // (a waiting lane must not take issue slots from the warps still at work)
-            }
-          }
-          __syncwarp();
-          __threadfence_block();
-          if (vsh[S_ABORT]) break;
-          ctx.baseB = (uint32_t)vsh[S_BASEB + st];
-          ctx.baseA = (uint32_t)vsh[S_BASEA + st];
-        }
         uint64_t tcB = 0, tcA = 0;
         typename Elem<T>::Thr thB, thA;
         auto refresh = [&]() {
@@ -505,78 +524,23 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
     }
   } else if (warp == kTauWarp) {
     // =================================================================== threshold warp
-    // Keeps reading new thresholds off the coarse histograms of the items that are streaming (the
-    // lower edge of the bin holding the k-th best survivor counted so far), and hands an item over
-    // when every scanner has listed what it found in it: list lengths and last thresholds to the
-    // item's header in the workspace, the item released to the finish kernel, the set of state
-    // cleared for the item three on.
+    // Keeps reading new thresholds off the coarse histograms of the items that are streaming: the
+    // lower edge of the bin holding the k-th best survivor counted so far.
     uint32_t idle = 0;
+    int seen = 0;
     for (;;) {
       if (vsh[S_ABORT]) break;
       const int done = vsh[S_STREAMED];
       if (done >= my_n) break;
+      if (done != seen) {
+        seen = done;
+        idle = 0;
+      }
       const int prepped = vsh[S_PREPARED];
       __threadfence_block();
-      if (done < prepped && vsh[S_DONE + done % 3] == kScanW) {
-        const int j = done, st = j % 3;
-        __threadfence_block();
-        const ItemHdr* hd = tab_hdr(st);
-        const ItemWs w = item_ws(a, (int)blockIdx.x + j * (int)gridDim.x);
-        const bool booted = vsh[S_BOOTOK + st] == j + 1;
-        const uint32_t baseB = (uint32_t)vsh[S_BASEB + st], baseA = (uint32_t)vsh[S_BASEA + st];
-        int d, kr;
-        bool ex;
-        find_bin(xh + (2 * st) * 256, hd->K, d, kr, ex);
-        if (booted && d > 0 && lane == 0) sm_red_max_u64(&s64[L_TAU_B + st], (unsigned long long)((baseB + (uint32_t)d) << 16) << 32);
-        if (MASKED) {
-          find_bin(xh + (2 * st + 1) * 256, ARCS_HEAD, d, kr, ex);
-          if (booted && d > 0 && lane == 0) sm_red_max_u64(&s64[L_TAU_A + st], (unsigned long long)((baseA + (uint32_t)d) << 16) << 32);
-        }
-        __syncwarp();
-        const int nB = vsh[S_CNT + 4 * st + 0], nA = vsh[S_CNT + 4 * st + 1], nT = vsh[S_CNT + 4 * st + 2];
-        const int n_pre = hd->n_pre;
-        if (nB > kListB || nA > kListA || nT > item_pre_cap(a.hash_slots) - n_pre) {
-          // a list overflowed: the finish kernel will read the item again and needs its filter
-          const uint32_t* bl = tab_bloom(st);
-          for (int i = lane; i < bloom_words_of(a.hash_slots); i += 32) w.bloom[i] = bl[i];
-        }
-        __syncwarp();
-        if (lane == 0) {
-          w.hdr->tauB = v64[L_TAU_B + st];
-          w.hdr->tauA = v64[L_TAU_A + st];
-          w.hdr->K = hd->K;
-          w.hdr->touched = hd->touched;
-          w.hdr->bans = hd->bans;
-          w.hdr->n_pre = n_pre;
-          w.hdr->n_tch = nT;
-          w.hdr->n_candB = nB;
-          w.hdr->n_candA = nA;
-        }
-        __syncwarp();
-        if (lane == 0) {
-          // (gpu scope: the scanners' list entries, ordered before their arrival at CTA scope, and
-          //  the header are read by another kernel once the item is released)
-          __threadfence();
-          st_release_gpu(&w.hdr->streamed, 1);
-        }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) xh[(2 * st) * 256 + i * 32 + lane] = 0;  // both histograms of the item's set
-        if (lane < 4) sh[S_CNT + 4 * st + lane] = 0;
-        if (lane == 0) {
-          sh[S_DONE + st] = 0;
-          sh[S_BOOTCNT + st] = 0;
-          s64[L_BOOT_B + st] = 0xFFFFFFFFFFFFFFFFull;
-          s64[L_BOOT_A + st] = 0xFFFFFFFFFFFFFFFFull;
-        }
-        __syncwarp();
-        __threadfence_block();
-        if (lane == 0) vsh[S_STREAMED] = j + 1;
-        idle = 0;
-        continue;
-      }
       for (int j = done; j < min(prepped, done + 2); ++j) {
         const int st = j % 3;
-        if (vsh[S_BOOTOK + st] != j + 1) continue;  // (the bins' base is known once the scanners have found the first threshold)
+        if (vsh[S_BOOTOK + st] != j + 1) continue;  // (the bins' base is known once the item has its first threshold)
         __threadfence_block();
         const ItemHdr* hd = tab_hdr(st);
         int d, kr;
@@ -597,25 +561,171 @@ __global__ void __launch_bounds__(kThreadsS, 1) stream_kernel(const SampleDev a)
       }
       __nanosleep(kTauSleepNs);
     }
-  } else {
-    // =================================================================== preparing warps
-    // An item may take a set of state once the item three back has been handed over.
-    const int gt = tid - kPrepWarp0 * 32;
+  } else if (warp == kCloseWarp) {
+    // =================================================================== closing warp
+    // Hands an item over when every scanner has listed what it found in it: list lengths and last
+    // thresholds to the item's header in the workspace, the item released to the finish kernel
+    // (a release at gpu scope, which takes microseconds while the memory pipes are full: the reason
+    // this is a warp of its own), the set of state cleared for the item three on.
     for (int j = 0; j < my_n; ++j) {
       const int st = j % 3;
       uint32_t spins = 0;
-      while (vsh[S_STREAMED] < j - 2 && !vsh[S_ABORT]) {
+      while ((vsh[S_PREPARED] <= j || vsh[S_DONE + st] != kScanW) && !vsh[S_ABORT]) {
         if (++spins > kWaitLimit) abort_now();
         __nanosleep(100);
       }
-      if (group_sync_or<3, kPrepG>(vsh[S_ABORT] != 0)) break;
+      if (vsh[S_ABORT]) break;
+      if (lane == 0) ARCS_TRACE(3 + 4 * j);
       __threadfence_block();
-      prep_item<T, MASKED>(a, (int)blockIdx.x + j * (int)gridDim.x, tab_hdr(st), tab_bloom(st), hk, hi_, pmisc, gt);
+      const ItemHdr* hd = tab_hdr(st);
+      const ItemWs w = item_ws(a, (int)blockIdx.x + j * (int)gridDim.x);
+      const bool booted = vsh[S_BOOTOK + st] == j + 1;
+      const uint32_t baseB = (uint32_t)vsh[S_BASEB + st], baseA = (uint32_t)vsh[S_BASEA + st];
+      int d, kr;
+      bool ex;
+      find_bin(xh + (2 * st) * 256, hd->K, d, kr, ex);
+      if (booted && d > 0 && lane == 0) sm_red_max_u64(&s64[L_TAU_B + st], (unsigned long long)((baseB + (uint32_t)d) << 16) << 32);
+      if (MASKED) {
+        find_bin(xh + (2 * st + 1) * 256, ARCS_HEAD, d, kr, ex);
+        if (booted && d > 0 && lane == 0) sm_red_max_u64(&s64[L_TAU_A + st], (unsigned long long)((baseA + (uint32_t)d) << 16) << 32);
+      }
+      __syncwarp();
+      const int nB = vsh[S_CNT + 4 * st + 0], nA = vsh[S_CNT + 4 * st + 1], nT = vsh[S_CNT + 4 * st + 2];
+      const int n_pre = hd->n_pre;
+      if (nB > kListB || nA > kListA || nT > item_pre_cap(a.hash_slots) - n_pre) {
+        // a list overflowed: the finish kernel will read the item again and needs its filter
+        const uint32_t* bl = tab_bloom(st);
+        for (int i = lane; i < bloom_words_of(a.hash_slots); i += 32) w.bloom[i] = bl[i];
+      }
+      __syncwarp();
+      if (lane == 0) {
+        w.hdr->tauB = v64[L_TAU_B + st];
+        w.hdr->tauA = v64[L_TAU_A + st];
+        w.hdr->K = hd->K;
+        w.hdr->touched = hd->touched;
+        w.hdr->bans = hd->bans;
+        w.hdr->n_pre = n_pre;
+        w.hdr->n_tch = nT;
+        w.hdr->n_candB = nB;
+        w.hdr->n_candA = nA;
+      }
+      __syncwarp();
+      // The set is free for the item three on before the release is through: nothing of the set is
+      // read below.
+#pragma unroll
+      for (int i = 0; i < 16; ++i) xh[(2 * st) * 256 + i * 32 + lane] = 0;  // both histograms of the item's set
+      if (lane < 4) sh[S_CNT + 4 * st + lane] = 0;
+      if (lane == 0) sh[S_DONE + st] = 0;
+      __syncwarp();
+      __threadfence_block();
+      if (lane == 0) vsh[S_STREAMED] = j + 1;
+      if (lane == 0) {
+        // (gpu scope: the scanners' list entries, ordered before their arrival at CTA scope, and
+        //  the header are read by another kernel once the item is released)
+        st_release_gpu(&w.hdr->streamed, 1);
+        ARCS_TRACE(4 + 4 * j);
+      }
+      __syncwarp();
+    }
+  } else {
+    // =================================================================== preparing warps
+    // Three kinds of work, decided by the group's first thread and done by all of it:
+    //  - an item is prepared when the set of state it takes is free (the item three back has
+    //    been handed over);
+    //  - an item's first tiles are fetched into the side buffer when the producer is kBootLead
+    //    tiles short of the item: late enough for the ring's own copy of these tiles to come out
+    //    of the L2 cache, early enough for the threshold to be there when the scanners want it;
+    //  - the item's first threshold is read off that buffer once it has landed.
+    const int gt = tid - kPrepWarp0 * 32;
+    int next_prep = 0, boot_issued = 0, boot_done = 0;
+    int need_prog = 0;   // the producer's place from which item boot_issued may be fetched
+    uint32_t idle = 0;
+    while (boot_done < my_n) {
       if (gt == 0) {
-        s64[L_TAU_B + st] = 0ull;
-        s64[L_TAU_A + st] = 0ull;
-        __threadfence();  // (gpu scope as well: the entries written to the workspace are read by the finish kernel)
-        vsh[S_PREPARED] = j + 1;
+        int cmd = 0;
+        if (vsh[S_ABORT]) cmd = 9;
+        else if (boot_issued == boot_done && vsh[S_PROG] >= need_prog) cmd = 1;
+        else if (boot_issued > boot_done && next_prep > boot_done && mbar_test_wait(boot_full, (uint32_t)boot_done & 1u)) cmd = 2;
+        else if (next_prep < my_n && vsh[S_STREAMED] >= next_prep - 2) cmd = 3;
+        pmisc[P_CMD] = cmd;
+      }
+      group_sync<3, kPrepG>();
+      const int cmd = pmisc[P_CMD];
+      group_sync<3, kPrepG>();
+      if (cmd == 9) break;
+      if (cmd == 0) {  // (nothing to do yet: none of this is urgent, so the group sleeps between looks)
+        if (++idle > kWaitLimit) {
+          abort_now();
+          break;
+        }
+#ifdef ARCS_DEV_TRACE
+        { long long t0_ = clock64(); __nanosleep(200); if (gt == 0) { g_trace[blockIdx.x * 64 + 48] += clock64() - t0_; g_trace[blockIdx.x * 64 + 49] += 1; } }
+#else
+        __nanosleep(200);
+#endif
+        continue;
+      }
+      idle = 0;
+      if (cmd == 1) {
+        // ---- fetch the first tiles of item boot_issued
+        const Item<T> it = item_of<T>(a, (int)blockIdx.x + boot_issued * (int)gridDim.x);
+        const int boot_bytes = min(it.p.body_bytes, kBootBytes);
+        if (gt == 0) {
+          if (boot_bytes > 0) {
+            fence_proxy_async();  // (the group's reads of the buffer for the item before are done)
+            mbar_expect_tx(boot_full, (uint32_t)boot_bytes);
+            bulk_load(bootbuf, it.p.body, (uint32_t)boot_bytes, boot_full);
+          } else {
+            mbar_arrive(boot_full);
+          }
+        }
+        // the place of the producer from which the next item may be fetched
+        need_prog = (boot_issued << 16) | min(0xFFFF, max(0, s_tiles(it.p) - kBootLead));
+        ++boot_issued;
+      } else if (cmd == 2) {
+        // ---- the first thresholds of item boot_done
+        const int jb = boot_done, st = jb % 3;
+        const Item<T> it = item_of<T>(a, (int)blockIdx.x + jb * (int)gridDim.x);
+        const int nb = min(it.p.body_bytes, kBootBytes);
+        const ItemHdr* hb = tab_hdr(st);
+#ifdef ARCS_DEV_TRACE
+        long long tb0_ = clock64();
+#endif
+        unsigned long long* tB = &s64[L_TAU_B + st];
+        unsigned long long* tA = &s64[L_TAU_A + st];
+        boot_item<T, MASKED>(a, it, hb, bootbuf, nb, tab_skip(st), boot_tm, tB, tA, &sh[S_BASEB + st], &sh[S_BASEA + st], gt);
+#ifdef ARCS_DEV_TRACE
+        if (gt == 0) { g_trace[blockIdx.x * 64 + 52] += clock64() - tb0_; g_trace[blockIdx.x * 64 + 53] += 1; }
+#endif
+        if (gt == 0) {
+          __threadfence_block();
+          vsh[S_BOOTOK + st] = jb + 1;
+          mbar_arrive(&bootok_bar[st]);
+          ARCS_TRACE(2 + 4 * jb);
+        }
+        ++boot_done;
+      } else {
+        // ---- prepare item next_prep
+        const int j = next_prep, st = j % 3;
+        __threadfence_block();
+        if (gt == 0) {  // (the set is free: nobody reads its thresholds now)
+          s64[L_TAU_B + st] = 0ull;
+          s64[L_TAU_A + st] = 0ull;
+        }
+#ifdef ARCS_DEV_TRACE
+        long long tp0_ = clock64();
+#endif
+        prep_item<T, MASKED>(a, (int)blockIdx.x + j * (int)gridDim.x, tab_hdr(st), tab_bloom(st), tab_skip(st), hk, hi_, pmisc, gt);
+#ifdef ARCS_DEV_TRACE
+        if (gt == 0) { g_trace[blockIdx.x * 64 + 50] += clock64() - tp0_; g_trace[blockIdx.x * 64 + 51] += 1; }
+#endif
+        if (gt == 0) {
+          __threadfence();  // (gpu scope as well: the entries written to the workspace are read by the finish kernel)
+          vsh[S_PREPARED] = j + 1;
+          mbar_arrive(&prep_bar[st]);
+          ARCS_TRACE(1 + 4 * j);
+        }
+        ++next_prep;
       }
     }
   }

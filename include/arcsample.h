@@ -84,7 +84,7 @@ typedef struct {
   int32_t max_hist, max_bias;/* upper bounds on any row's list length (they size the on-chip filter and table). A row
                                 whose penalties can only lower logits (repeat_penalty >= 1, presence and frequency
                                 >= 0) and whose bias list has at most 64 entries takes a history of any length up to
-                                max_hist; any other row's lists may hold 2048 entries together, else ARCS_ERR_LIST */
+                                max_hist; any other row's lists may hold 1024 entries together, else ARCS_ERR_LIST */
   int32_t id_base;           /* global id of column 0 (vocabulary shards); 0 otherwise */
   int32_t v_global;          /* whole vocabulary size when sharded; 0 means V */
   /* outputs (device pointers; optional ones may be NULL) */
