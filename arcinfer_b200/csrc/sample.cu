@@ -27,7 +27,7 @@ static cudaError_t launch_dependent(K kernel, unsigned grid, unsigned block, siz
 
 constexpr int kMaxRows = 65536;
 constexpr int kItemsPerSm = 1;        // work items per SM that few rows are cut into
-constexpr int kFinishThreads = 128;   // threads of the finish kernel's CTA (one CTA per row)
+constexpr int kFinishThreads = 128;   // threads of the finish kernel's CTA (four rows per CTA; one with an allowed-token mask)
 
 static int table_slots(int max_list) {
   int slots = kGroup;
@@ -107,7 +107,7 @@ static int sample_launch(const arcs_sample_args* g, void* stream, cudaEvent_t* e
     return set_error(ARCS_ERR_WORKSPACE, "sample_batch: workspace too small");
   if ((reinterpret_cast<uintptr_t>(g->workspace) & 15u) != 0) return set_error(ARCS_ERR_WORKSPACE, "sample_batch: workspace must be 16-byte aligned");
 
-  const size_t smem_s = stream_smem_bytes(slots);
+  const size_t smem_s = stream_smem_bytes(masked, slots);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int items = a.nseg * a.B;
   const unsigned grid_s = (unsigned)(items < kSmCount ? items : kSmCount);
@@ -119,7 +119,7 @@ static int sample_launch(const arcs_sample_args* g, void* stream, cudaEvent_t* e
     if (events) cudaEventRecord(events[0], st);                                                                    \
     stream_kernel<T, M><<<grid_s, kThreadsS, smem_s, st>>>(a);                                                     \
     if (events) cudaEventRecord(events[1], st);                                                                    \
-    const cudaError_t e = launch_dependent(finish_kernel<T, M, kFinishThreads>, (unsigned)a.B, kFinishThreads, 0, st, a, events == nullptr); \
+    const cudaError_t e = launch_dependent(finish_kernel<T, M, kFinishThreads>, (unsigned)(M ? a.B : (a.B + 3) / 4), kFinishThreads, 0, st, a, events == nullptr); \
     if (e != cudaSuccess) return set_error(ARCS_ERR_CUDA, cudaGetErrorString(e));                                  \
     if (events) cudaEventRecord(events[2], st);                                                                    \
   } while (0)
@@ -183,12 +183,15 @@ extern "C" int arcs_merge_batch(const arcs_merge_args* g, void* stream) {
   a.merge_id = g->cand_id;
   a.merge_val = g->cand_val;
   a.merge_n = g->n_cand;
-  finish_kernel<float, false, kFinishThreads><<<(unsigned)g->B, kFinishThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  finish_kernel<float, false, kFinishThreads><<<(unsigned)((g->B + 3) / 4), kFinishThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return check_launch("merge_batch");
 }
 
 #ifdef ARCS_DEV_TRACE
 extern "C" int arcs_dev_trace(long long* host_out) {
   return (int)cudaMemcpyFromSymbol(host_out, arcs::g_trace, sizeof(long long) * 148 * 64);
+}
+extern "C" int arcs_dev_ftrace(long long* host_out) {
+  return (int)cudaMemcpyFromSymbol(host_out, arcs::g_ftrace, sizeof(long long) * 64);
 }
 #endif

@@ -69,7 +69,7 @@ constexpr int kShare = 2;                    // scanner warps that split one til
 constexpr int kTeams = kScanW / kShare;      // teams: team x takes the tiles whose running number is x modulo kTeams
 constexpr int kSTile = 8192;                 // bytes per tile (512 chunks of 16 bytes)
 constexpr int kMine = kSTile / 16 / kShare;  // chunks of a tile per scanner warp
-constexpr int kBootTiles = 4;                // first tiles of an item its first threshold is read off
+constexpr int kBootTiles = 2;                // first tiles of an item its first threshold is read off
 constexpr int kBootBytes = kBootTiles * kSTile;
 constexpr int kPrepW = 4;                    // preparing warps of the stream kernel
 constexpr int kPrepG = kPrepW * 32;          // ... threads (named barrier 3)

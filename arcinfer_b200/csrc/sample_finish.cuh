@@ -1,32 +1,25 @@
 // finish_kernel: from an item's survivors to the row's token.
 //
-// One CTA of kGroup threads per row. It runs beside the stream kernel: it waits until that kernel
-// has released every item of its row, then merges what the preparing warps supplied (touched
+// It runs beside the stream kernel: a row is taken when that kernel has released every item of
+// it. The common case of a row is finished by one warp (sample_finish_warp.cuh), four rows to a
+// CTA; what follows here is the general path, which all threads of the CTA walk together for a
+// row the warp path left (an allowed-token mask, many candidates, lists that overflowed): it merges what the preparing warps supplied (touched
 // tokens with their adjusted logits, elements outside the aligned body) with what the scanners
 // kept, for every segment of the row, selects the k best under (value desc, id asc), and then
 // follows tools/sampler.h:54-77 (or :105-143 with an allowed-token mask) to the letter: fp64
 // softmax in candidate order, min-p / top-p cuts, the draw.
 #pragma once
-#include "sample_common.cuh"
+#include "sample_finish_warp.cuh"
 
 namespace arcs {
 
 constexpr int kStage = 1024;   // flagged entries settled together
-constexpr uint32_t kFlagWaitLimit = 1u << 21;  // bounded wait for an item's release (about a second)
-
-__device__ __forceinline__ int32_t ld_acquire_gpu(const int32_t* p) {
-  int32_t v;
-  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
 constexpr int kSortCap = 160;  // a longer buffer is cut to the k best by the radix select before it is ranked by counting
-
 template <typename T, bool MASKED, int G>
-__global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (eight CTAs per SM: a thousand rows are one wave)
+__global__ void __launch_bounds__(G, 5) finish_kernel(const SampleDev a) {  // (at most 96 registers: one CTA fits beside the stream kernel's)
   __shared__ unsigned long long s64[8];
   __shared__ double spr[ARCS_KCAP + 1];
-  __shared__ __align__(8) uint32_t bkey[kCapB];
+  __shared__ __align__(16) uint32_t bkey[kCapB];
   __shared__ int32_t bid[kCapB];
   __shared__ uint32_t akey[MASKED ? kCapA : 1];
   __shared__ int32_t aid[MASKED ? kCapA : 1];
@@ -38,15 +31,45 @@ __global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (
   __shared__ int misc[8];
   __shared__ int sh[12];
   __shared__ int seg_n[4][kMaxSeg];  // per segment: entries of the prepare kernel (+ flagged ones of the stream), survivors B, A, overflowed
-  __shared__ uint32_t fl_key[kStage];   // hot elements the filter flagged, waiting to be settled
-  __shared__ int32_t fl_id[kStage];     // (global id | kOkB)
-  __shared__ uint32_t fl_cnt[kStage];   // occurrences in the history | in the repeat window << 31 | in the bias list << 30
+  __shared__ __align__(16) uint32_t fl_key[kStage];   // hot elements the filter flagged, waiting to be settled
+  __shared__ __align__(16) int32_t fl_id[kStage];     // (global id | kOkB)
+  __shared__ __align__(16) uint32_t fl_cnt[kStage];   // occurrences in the history | in the repeat window << 31 | in the bias list << 30
   enum { L_TAU_B = 0, L_TAU_A, L_PRUNE_MIN, L_TOP, L_LOW };
   enum { S_CNT_B = 0, S_CNT_A, S_FLAGS, S_NCAND, S_BANS, S_NFLAG, S_NLIST, S_NLISTA, S_OVER, S_NPRE };
 
   const int gt = threadIdx.x;
-  const int b = blockIdx.x;
   const int32_t Vg = a.v_global > 0 ? a.v_global : a.V;
+  const bool merging = a.merge_G > 0;
+  // ---- rows of this CTA: the warp path first, every warp its own row
+  constexpr int kRows = MASKED ? 1 : G / 32;
+  static_assert(G == 128 && kStage * 4 >= (int)sizeof(FastScratch) && kCapB * 4 >= (int)sizeof(FastScratch), "the warps' scratch lies in four of the arrays above");
+  __shared__ int row_rc[G / 32];
+  const int b_first = (int)blockIdx.x * kRows;
+  if (!MASKED) {
+    const int w = gt >> 5, bw = b_first + w;
+    int rc = kFastSlow;
+    if (bw >= a.B) rc = kFastDone;
+    else if (!merging) {
+      void* scratch = w == 0 ? (void*)fl_key : w == 1 ? (void*)fl_id : w == 2 ? (void*)fl_cnt : (void*)bkey;
+      rc = finish_row_warp<T>(a, bw, *reinterpret_cast<FastScratch*>(scratch));
+    }
+    if ((gt & 31) == 0) row_rc[w] = rc;
+    __syncthreads();
+  }
+  for (int rr = 0; rr < kRows; ++rr) {
+  const int b = b_first + rr;
+  if (b >= a.B) break;
+  if (!MASKED) {
+    if (row_rc[rr] == kFastDone) continue;
+    if (row_rc[rr] == kFastLate) {
+      if (gt == 0) {
+        raise_status(a.status, ARCS_ERR_TIMEOUT);
+        a.token[b] = -1;
+      }
+      continue;
+    }
+  }
+  __syncthreads();  // (the row before is through with the shared arrays)
   if (gt == 0) {
     sh[S_CNT_B] = 0;
     sh[S_CNT_A] = 0;
@@ -61,7 +84,6 @@ __global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (
     s64[L_TAU_A] = 0ull;
   }
   __syncthreads();
-  const bool merging = a.merge_G > 0;
   // The stream kernel's lists and headers are read from here on. That kernel may still be running
   // (this one is launched behind it with programmatic stream serialization and does not wait for
   // its end): a row is taken when all its items have been released. The wait is bounded.
@@ -83,7 +105,7 @@ __global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (
         raise_status(a.status, ARCS_ERR_TIMEOUT);
         a.token[b] = -1;
       }
-      return;
+      continue;
     }
   }
   // what the segments' headers say (fetched together with the row's settings). Nothing at or
@@ -461,6 +483,7 @@ __global__ void __launch_bounds__(G, 8) finish_kernel(const SampleDev a) {  // (
     if (a.cand_val) a.cand_val[o] = in ? sv[i] : 0.0f;
     if (a.cand_pr) a.cand_pr[o] = in ? (draw ? (float)spr[i] : (i == 0 ? 1.0f : 0.0f)) : 0.0f;
   }
+  }  // (rows of this CTA)
 }
 
 }  // namespace arcs

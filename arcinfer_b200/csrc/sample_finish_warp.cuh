@@ -1,0 +1,324 @@
+// finish_row_warp: the common case of the finish step, one warp per row.
+//
+// A row whose candidates fit a warp's hands - no allowed-token mask, at most 64 candidates kept,
+// at most 128 survivors above the stream's last threshold, at most 32 flagged entries, no list of
+// the stream overflowed - is finished by one warp without a CTA-wide barrier: the survivors at or
+// above the threshold are gathered, the flagged ones settled against the history and bias lists
+// (tools/sampler.h:154-174), the rest ranked by counting, and tools/sampler.h:54-77 followed to
+// the letter (fp64 softmax in candidate order, min-p / top-p cuts, the draw). Four such rows
+// share a CTA of the finish kernel. Any other row is left to the CTA-wide path.
+#pragma once
+#include "sample_common.cuh"
+
+namespace arcs {
+
+#ifdef ARCS_DEV_TRACE
+__device__ long long g_ftrace[4 * 16];
+#define ARCS_FTRACE(slot) do { if (threadIdx.x == 0 && (blockIdx.x == gridDim.x - 1 || blockIdx.x == gridDim.x / 2)) g_ftrace[(blockIdx.x == gridDim.x - 1 ? 0 : 16) + (slot)] = clock64(); } while (0)
+#else
+#define ARCS_FTRACE(slot) do { } while (0)
+#endif
+
+constexpr int kFastK = 64;      // most candidates a row may keep on this path
+constexpr int kFastBuf = 128;   // most survivors above the last threshold
+constexpr int kFastFlag = 32;   // most flagged entries
+constexpr uint32_t kFlagWaitLimit = 1u << 21;  // bounded wait for an item's release (about a second)
+
+__device__ __forceinline__ int32_t ld_acquire_gpu(const int32_t* p) {
+  int32_t v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// exp(x) for a float x <= 0 (a softmax term), evaluated in fp64 and rounded to float: the value
+// tools/sampler.h:60 stores, std::exp of a float argument. x = n ln 2 + r with |r| <= ln 2 / 2;
+// e^r by a degree-11 Taylor polynomial (relative error below 2^-44, so the rounding to float
+// differs from that of the exact value for about one argument in a million); times 2^n. Far
+// fewer instructions than the general fp64 exponential, on a path where they are a row's latency.
+__device__ __forceinline__ float exp_term(float xf) {
+  if (!(xf > -104.0f)) return 0.0f;  // (below the smallest float denormal; also -inf)
+  const double x = (double)xf;
+  const double n = rint(x * 1.4426950408889634);
+  const double r = fma(n, -6.93147180369123816490e-01, x);
+  const double r2 = fma(n, -1.90821492927058770002e-10, r);
+  double p = 2.50521083854417187751e-08;            // 1/11!
+  p = fma(p, r2, 2.75573192239858906526e-07);       // 1/10!
+  p = fma(p, r2, 2.75573192239858906526e-06);       // 1/9!
+  p = fma(p, r2, 2.48015873015873015873e-05);       // 1/8!
+  p = fma(p, r2, 1.98412698412698412698e-04);       // 1/7!
+  p = fma(p, r2, 1.38888888888888888889e-03);       // 1/6!
+  p = fma(p, r2, 8.33333333333333333333e-03);       // 1/5!
+  p = fma(p, r2, 4.16666666666666666667e-02);       // 1/4!
+  p = fma(p, r2, 1.66666666666666666667e-01);       // 1/3!
+  p = fma(p, r2, 0.5);
+  p = fma(p, r2, 1.0);
+  p = fma(p, r2, 1.0);
+  const int ni = (int)n;  // >= -151: the scaling is split so that neither factor underflows
+  const int n1 = ni < -1000 ? -1000 : ni, n2 = ni - n1;
+  double v = p * __longlong_as_double((long long)(1023 + n1) << 52);
+  if (n2 != 0) v *= __longlong_as_double((long long)(1023 + n2) << 52);
+  return (float)v;
+}
+
+// one warp's scratch (carved out of shared memory by the caller, 8-byte aligned)
+struct FastScratch {
+  unsigned long long buf[kFastBuf];  // composites of the survivors above the threshold; later the running sums
+  float sv[kFastK];
+  int32_t sid[kFastK];
+  double spr[kFastK + 1];
+  uint32_t fkey[kFastFlag];
+  int32_t fid[kFastFlag];   // (global id | kOkB)
+};
+static_assert(sizeof(FastScratch) <= 4096, "a warp's scratch fits one of the CTA-wide path's 4 KB arrays");
+
+enum { kFastDone = 0, kFastSlow = 1, kFastLate = 2 };
+template <int N>
+struct IntTag {
+  static constexpr int value = N;
+};
+
+template <typename T>
+__device__ __noinline__ int finish_row_warp(const SampleDev& a, int b, FastScratch& fs) {
+  const int lane = threadIdx.x & 31;
+  ARCS_FTRACE(0);
+  // ---- the row's items: released by the stream kernel (bounded wait), their headers; the row's
+  // settings and, if it is short, its history travel at the same time
+  unsigned long long tau = 0ull;
+  bool bans = false, over = false, late = false;
+  int n0_mine = 0, n1_mine = 0;  // (lane g: the list lengths of segment g, for rows of at most 32 segments)
+  for (int g = lane; g < a.nseg; g += 32) {
+    const ItemHdr* hd = item_ws(a, b * a.nseg + g).hdr;
+    uint32_t spins = 0;
+    while (ld_acquire_gpu(&hd->streamed) == 0) {
+      if (++spins > kFlagWaitLimit) {
+        late = true;
+        break;
+      }
+      __nanosleep(spins < 64 ? 100 : 400);
+    }
+    const int n0 = __ldcg(&hd->n_pre), nt = __ldcg(&hd->n_tch), n1 = __ldcg(&hd->n_candB);
+    over = over || n1 > kListB || nt > item_pre_cap(a.hash_slots) - n0;
+    bans = bans || __ldcg(&hd->bans) != 0;
+    const unsigned long long t = __ldcg(&hd->tauB);
+    tau = t > tau ? t : tau;
+    n0_mine = n0 + nt;
+    n1_mine = n1;
+  }
+  const RowCfg r = row_cfg<false>(a, b);
+  constexpr int HR = 16;
+  int32_t hreg[HR];
+  const bool hist_in_regs = r.pen_on && r.lists_ok && r.H <= 32 * HR;
+#pragma unroll
+  for (int x = 0; x < HR; ++x) hreg[x] = hist_in_regs && x * 32 + lane < r.H ? __ldg(&a.hist_ids[r.h0 + x * 32 + lane]) : -1;
+  __syncwarp();  // (the lanes that waited have acquired the items' lists for the whole warp)
+  ARCS_FTRACE(1);
+  if (r.kB > kFastK || a.nseg > 32) return kFastSlow;
+  if (__any_sync(0xFFFFFFFFu, late)) return kFastLate;
+  if (__any_sync(0xFFFFFFFFu, over)) return kFastSlow;
+  tau = warp_max_u64(tau);
+  bans = __any_sync(0xFFFFFFFFu, bans);
+  // ---- gather: survivors above the threshold to the buffer, flagged entries to their stage
+  int m = 0, nf = 0;  // (warp-uniform counts)
+  bool spill = false;
+  auto gather = [&](const unsigned long long* list, int n) {
+    constexpr int R = 8;  // entries a lane fetches together: one trip to memory for 256 entries
+    for (int i0 = 0; i0 < n && !spill; i0 += R * 32) {
+      unsigned long long e[R];
+#pragma unroll
+      for (int x = 0; x < R; ++x) e[x] = i0 + x * 32 + lane < n ? __ldcg(&list[i0 + x * 32 + lane]) : 0ull;
+#pragma unroll
+      for (int x = 0; x < R; ++x) {
+        if (i0 + x * 32 >= n) break;
+        const bool p = i0 + x * 32 + lane < n;
+        const uint32_t ky = (uint32_t)e[x], y = (uint32_t)(e[x] >> 32);
+        const int32_t id = (int32_t)(y & kIdMask);
+        const bool fl = p && (y & kTch);
+        const uint64_t cm = comp_of(ky, id);
+        const bool keep = p && !fl && (y & kOkB) && cm > tau;
+        const unsigned bk = __ballot_sync(0xFFFFFFFFu, keep), bf = __ballot_sync(0xFFFFFFFFu, fl);
+        if (m + __popc(bk) > kFastBuf || nf + __popc(bf) > kFastFlag) {
+          spill = true;
+          break;
+        }
+        if (keep) fs.buf[m + __popc(bk & ((1u << lane) - 1u))] = cm;
+        if (fl) {
+          const int pos = nf + __popc(bf & ((1u << lane) - 1u));
+          fs.fkey[pos] = ky;
+          fs.fid[pos] = (int32_t)(y & (kIdMask | kOkB));
+        }
+        m += __popc(bk);
+        nf += __popc(bf);
+      }
+    }
+  };
+  for (int g = 0; g < a.nseg && !spill; ++g) {
+    const ItemWs w = item_ws(a, b * a.nseg + g);
+    gather(w.pre, __shfl_sync(0xFFFFFFFFu, n0_mine, g));
+    gather(w.candB, __shfl_sync(0xFFFFFFFFu, n1_mine, g));
+  }
+  if (spill) return kFastSlow;
+  __syncwarp();
+  ARCS_FTRACE(2);
+  // ---- settle the flagged entries (tools/sampler.h:154-174 for them): one in the bias list was
+  // evaluated by the preparing warps and is dropped here; one in the history is dropped too when
+  // they evaluated the history (table mode), else penalised here; one the filter flagged by
+  // accident is an ordinary element.
+  if (nf > 0) {
+    const int32_t w0 = window_start(r);
+    for (int f = 0; f < nf; ++f) {
+      const int32_t idf = fs.fid[f] & (int32_t)kIdMask;
+      int cnt = 0;
+      bool win = false, inbias = false;
+      for (int i = lane; i < r.NB; i += 32) inbias = inbias || a.bias_ids[r.q0 + i] == idf;
+      if (r.pen_on) {
+        if (hist_in_regs) {
+#pragma unroll
+          for (int x = 0; x < HR; ++x)
+            if (hreg[x] == idf) {
+              ++cnt;
+              win = win || x * 32 + lane >= w0;
+            }
+        } else {
+          for (int i = lane; i < r.H; i += 32)
+            if (__ldg(&a.hist_ids[r.h0 + i]) == idf) {
+              ++cnt;
+              win = win || i >= w0;
+            }
+        }
+      }
+      cnt = (int)__reduce_add_sync(0xFFFFFFFFu, (unsigned)cnt);
+      win = __any_sync(0xFFFFFFFFu, win);
+      inbias = __any_sync(0xFFFFFFFFu, inbias);
+      uint32_t ky = fs.fkey[f];
+      bool p = !inbias && (fs.fid[f] & (int32_t)kOkB) != 0;
+      if (p && cnt > 0) {
+        if (r.touch == kTouchTable) {
+          p = false;
+        } else {
+          ky = key_of(penalise(r, value_of(ky), (uint32_t)cnt, w0 == 0 || win));
+          p = ky != 0u;
+        }
+      }
+      const uint64_t cm = comp_of(ky, idf);
+      p = p && cm > tau;
+      if (p) {
+        if (m >= kFastBuf) return kFastSlow;  // (warp-uniform: every lane computed the same)
+        if (lane == 0) fs.buf[m] = cm;
+        ++m;
+      }
+    }
+    __syncwarp();
+  }
+  ARCS_FTRACE(3);
+  // ---- candidates best first: ranked by counting (composites are unique)
+  const int nB = min(m, r.kB);
+  auto rank_all = [&](auto per_tag) {
+    constexpr int PER = decltype(per_tag)::value;
+    unsigned long long mine[PER];
+    int rank[PER];
+#pragma unroll
+    for (int x = 0; x < PER; ++x) {
+      mine[x] = x * 32 + lane < m ? fs.buf[x * 32 + lane] : 0ull;
+      rank[x] = 0;
+    }
+#pragma unroll 4
+    for (int i = 0; i < m; ++i) {
+      const unsigned long long c = fs.buf[i];
+#pragma unroll
+      for (int x = 0; x < PER; ++x) rank[x] += c > mine[x];
+    }
+#pragma unroll
+    for (int x = 0; x < PER; ++x)
+      if (x * 32 + lane < m && rank[x] < nB) {
+        fs.sv[rank[x]] = value_of(comp_key(mine[x]));
+        fs.sid[rank[x]] = comp_id(mine[x]);
+      }
+  };
+  if (m <= 64) rank_all(IntTag<2>{});
+  else rank_all(IntTag<kFastBuf / 32>{});
+  __syncwarp();
+  ARCS_FTRACE(4);
+  // ---- tools/sampler.h:54-77
+  int nc = nB;
+  if (bans)  // :54-55 (every lane walks the same few steps)
+    while (nc > 1 && fs.sv[nc - 1] <= ARCS_BANNED) --nc;
+  bool tie = false;  // equal logits among the candidates kept: the reference's order there is not defined
+  for (int i = lane; i + 1 < nc; i += 32) tie = tie || fs.sv[i] == fs.sv[i + 1];
+  const int flags = __any_sync(0xFFFFFFFFu, tie) ? ARCS_FLAG_TIE_TOPK : 0;
+  const bool draw = !r.greedy && nc >= 1;
+  int token = nc > 0 ? fs.sid[0] : -1, n = nc > 0 ? 1 : 0;
+  double* cum = reinterpret_cast<double*>(fs.buf);  // (the buffer is no longer needed)
+  if (draw) {
+    const float mx = fs.sv[0];
+    for (int i = lane; i < nc; i += 32) {
+      const float x = __fdiv_rn(__fsub_rn(fs.sv[i], mx), r.prm.temperature);  // :60 float arithmetic
+      fs.spr[i] = (double)exp_term(x);                                        // float exp, widened
+    }
+    __syncwarp();
+    ARCS_FTRACE(5);
+    double z = 0.0;  // :58-60 in candidate order (every lane adds the same chain)
+#pragma unroll 8
+    for (int i = 0; i < nc; ++i) z = __dadd_rn(z, fs.spr[i]);
+    __syncwarp();
+    for (int i = lane; i < nc; i += 32) fs.spr[i] = __ddiv_rn(fs.spr[i], z);  // :64, the same quotients in any order
+    __syncwarp();
+    // :65-72. The running sums are a chain of roundings in candidate order; where the chain is
+    // cut is then found by all lanes.
+    if (lane == 0) {
+      double c = 0.0;
+#pragma unroll 8
+      for (int i = 0; i < nc; ++i) {
+        c = __dadd_rn(c, fs.spr[i]);
+        cum[i] = c;
+      }
+    }
+    __syncwarp();
+    const double mp = __dmul_rn((double)r.prm.min_p, fs.spr[0]);
+    int n_i = nc;
+    for (int i = lane; i < nc; i += 32) {
+      int c = 0x7FFFFFFF;
+      if (r.prm.min_p > 0.0f && fs.spr[i] < mp) c = max(1, i);   // :65 (tested before the candidate is added)
+      else if (cum[i] >= (double)r.prm.top_p) c = i + 1;         // :67
+      n_i = min(n_i, c);
+    }
+    n = (int)__reduce_min_sync(0xFFFFFFFFu, (unsigned)n_i);
+    ARCS_FTRACE(6);
+    if (lane == 0) {
+      const double tot = cum[n - 1];             // the same sum, in the same order, as :70
+      double rr = __dmul_rn(a.u[b], tot);        // :71-72
+      int pick = -1;
+      for (int i = 0; i < n && pick < 0; i += 4) {  // (four steps of the chain at a time: the loads run ahead of it)
+        const double p0 = fs.spr[i], p1 = i + 1 < n ? fs.spr[i + 1] : 0.0, p2 = i + 2 < n ? fs.spr[i + 2] : 0.0, p3 = i + 3 < n ? fs.spr[i + 3] : 0.0;
+        const double r0 = __dsub_rn(rr, p0), r1 = __dsub_rn(r0, p1), r2 = __dsub_rn(r1, p2), r3 = __dsub_rn(r2, p3);
+        if (r0 <= 0.0) pick = i;
+        else if (i + 1 < n && r1 <= 0.0) pick = i + 1;
+        else if (i + 2 < n && r2 <= 0.0) pick = i + 2;
+        else if (i + 3 < n && r3 <= 0.0) pick = i + 3;
+        rr = r3;
+      }
+      if (pick < 0) pick = n - 1;
+      token = fs.sid[pick];
+    }
+  }
+  ARCS_FTRACE(7);
+  if (lane == 0) {
+    if (r.k_bad || !r.lists_ok) token = -1;
+    a.token[b] = token;
+    if (a.n_cand) a.n_cand[b] = nc;
+    if (a.n_kept) a.n_kept[b] = n;
+    if (a.flags) a.flags[b] = flags;
+  }
+  if (a.cand_id || a.cand_val || a.cand_pr) {
+    for (int i = lane; i < a.cand_stride; i += 32) {
+      const size_t o = (size_t)b * a.cand_stride + i;
+      const bool in = i < nc;
+      if (a.cand_id) a.cand_id[o] = in ? fs.sid[i] : -1;
+      if (a.cand_val) a.cand_val[o] = in ? fs.sv[i] : 0.0f;
+      if (a.cand_pr) a.cand_pr[o] = in ? (draw ? (float)fs.spr[i] : (i == 0 ? 1.0f : 0.0f)) : 0.0f;
+    }
+  }
+  ARCS_FTRACE(8);
+  return kFastDone;
+}
+
+}  // namespace arcs

@@ -259,9 +259,10 @@ __device__ __forceinline__ void boot_item(const SampleDev& a, const Item<T>& it,
   group_sync<3, G>();
 }
 
-static size_t stream_smem_bytes(int hash_slots) {
+static size_t stream_smem_bytes(bool masked, int hash_slots) {
+  const size_t boot_tm_words = masked ? 8 * kPrepG : 2 * kPrepG;
   return (size_t)kRing * kSTile + kBootBytes + 3 * ((size_t)item_tab_bytes(hash_slots) + kBootSkipWords * 4) + (size_t)kScanW * kStash * 20 + (2 * kRing + 8) * 8 +
-         L_END * 8 + 6 * 256 * 4 + 8 * kPrepG * 4 + (size_t)hash_slots * 8 + S_END * 4 + P_END * 4 + 128;
+         L_END * 8 + 6 * 256 * 4 + boot_tm_words * 4 + (size_t)hash_slots * 8 + S_END * 4 + P_END * 4 + 128;
 }
 
 template <typename T, bool MASKED>
@@ -281,8 +282,8 @@ __global__ void __launch_bounds__(kRegBoundThreads, 1) stream_kernel(const Sampl
   unsigned long long* s64 = reinterpret_cast<unsigned long long*>(bootok_bar + 3);  // [L_END]
   int32_t* stash_c = reinterpret_cast<int32_t*>(s64 + L_END);                 // [kScanW][kStash]
   uint32_t* xh = reinterpret_cast<uint32_t*>(stash_c + kScanW * kStash);      // [3 sets][B, A][256] coarse histograms
-  uint32_t* boot_tm = xh + 6 * 256;                                           // [2][4 * kPrepG] the preparing threads' largest chunk maxima
-  uint32_t* hk = boot_tm + 8 * kPrepG;                                       // [hash_slots] the preparing warps' table: columns
+  uint32_t* boot_tm = xh + 6 * 256;                                           // [1 or 2][2 or 4][kPrepG] the preparing threads' largest chunk maxima
+  uint32_t* hk = boot_tm + (MASKED ? 8 : 2) * kPrepG;                                       // [hash_slots] the preparing warps' table: columns
   uint32_t* hi_ = hk + a.hash_slots;                                          // [hash_slots] ... what applies to them
   int* sh = reinterpret_cast<int*>(hi_ + a.hash_slots);                       // [S_END]
   int* pmisc = sh + S_END;                                                    // [P_END]
