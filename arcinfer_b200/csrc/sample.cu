@@ -186,12 +186,3 @@ extern "C" int arcs_merge_batch(const arcs_merge_args* g, void* stream) {
   finish_kernel<float, false, kFinishThreads><<<(unsigned)((g->B + 3) / 4), kFinishThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return check_launch("merge_batch");
 }
-
-#ifdef ARCS_DEV_TRACE
-extern "C" int arcs_dev_trace(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, arcs::g_trace, sizeof(long long) * 148 * 64);
-}
-extern "C" int arcs_dev_ftrace(long long* host_out) {
-  return (int)cudaMemcpyFromSymbol(host_out, arcs::g_ftrace, sizeof(long long) * 64);
-}
-#endif

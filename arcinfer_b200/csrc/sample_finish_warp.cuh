@@ -12,12 +12,6 @@
 
 namespace arcs {
 
-#ifdef ARCS_DEV_TRACE
-__device__ long long g_ftrace[4 * 16];
-#define ARCS_FTRACE(slot) do { if (threadIdx.x == 0 && (blockIdx.x == gridDim.x - 1 || blockIdx.x == gridDim.x / 2)) g_ftrace[(blockIdx.x == gridDim.x - 1 ? 0 : 16) + (slot)] = clock64(); } while (0)
-#else
-#define ARCS_FTRACE(slot) do { } while (0)
-#endif
 
 constexpr int kFastK = 64;      // most candidates a row may keep on this path
 constexpr int kFastBuf = 128;   // most survivors above the last threshold
@@ -80,9 +74,15 @@ struct IntTag {
 template <typename T>
 __device__ __noinline__ int finish_row_warp(const SampleDev& a, int b, FastScratch& fs) {
   const int lane = threadIdx.x & 31;
-  ARCS_FTRACE(0);
-  // ---- the row's items: released by the stream kernel (bounded wait), their headers; the row's
-  // settings and, if it is short, its history travel at the same time
+  // ---- the row's settings and, if it is short, its history: fetched before the row's items are
+  // waited for (a CTA of the last rows sits here while the stream kernel runs)
+  const RowCfg r = row_cfg<false>(a, b);
+  constexpr int HR = 16;
+  int32_t hreg[HR];
+  const bool hist_in_regs = r.pen_on && r.lists_ok && r.H <= 32 * HR;
+#pragma unroll
+  for (int x = 0; x < HR; ++x) hreg[x] = hist_in_regs && x * 32 + lane < r.H ? __ldg(&a.hist_ids[r.h0 + x * 32 + lane]) : -1;
+  // ---- the row's items: released by the stream kernel (bounded wait), their headers
   unsigned long long tau = 0ull;
   bool bans = false, over = false, late = false;
   int n0_mine = 0, n1_mine = 0;  // (lane g: the list lengths of segment g, for rows of at most 32 segments)
@@ -104,14 +104,7 @@ __device__ __noinline__ int finish_row_warp(const SampleDev& a, int b, FastScrat
     n0_mine = n0 + nt;
     n1_mine = n1;
   }
-  const RowCfg r = row_cfg<false>(a, b);
-  constexpr int HR = 16;
-  int32_t hreg[HR];
-  const bool hist_in_regs = r.pen_on && r.lists_ok && r.H <= 32 * HR;
-#pragma unroll
-  for (int x = 0; x < HR; ++x) hreg[x] = hist_in_regs && x * 32 + lane < r.H ? __ldg(&a.hist_ids[r.h0 + x * 32 + lane]) : -1;
   __syncwarp();  // (the lanes that waited have acquired the items' lists for the whole warp)
-  ARCS_FTRACE(1);
   if (r.kB > kFastK || a.nseg > 32) return kFastSlow;
   if (__any_sync(0xFFFFFFFFu, late)) return kFastLate;
   if (__any_sync(0xFFFFFFFFu, over)) return kFastSlow;
@@ -158,7 +151,6 @@ __device__ __noinline__ int finish_row_warp(const SampleDev& a, int b, FastScrat
   }
   if (spill) return kFastSlow;
   __syncwarp();
-  ARCS_FTRACE(2);
   // ---- settle the flagged entries (tools/sampler.h:154-174 for them): one in the bias list was
   // evaluated by the preparing warps and is dropped here; one in the history is dropped too when
   // they evaluated the history (table mode), else penalised here; one the filter flagged by
@@ -209,7 +201,6 @@ __device__ __noinline__ int finish_row_warp(const SampleDev& a, int b, FastScrat
     }
     __syncwarp();
   }
-  ARCS_FTRACE(3);
   // ---- candidates best first: ranked by counting (composites are unique)
   const int nB = min(m, r.kB);
   auto rank_all = [&](auto per_tag) {
@@ -237,7 +228,6 @@ __device__ __noinline__ int finish_row_warp(const SampleDev& a, int b, FastScrat
   if (m <= 64) rank_all(IntTag<2>{});
   else rank_all(IntTag<kFastBuf / 32>{});
   __syncwarp();
-  ARCS_FTRACE(4);
   // ---- tools/sampler.h:54-77
   int nc = nB;
   if (bans)  // :54-55 (every lane walks the same few steps)
@@ -255,7 +245,6 @@ __device__ __noinline__ int finish_row_warp(const SampleDev& a, int b, FastScrat
       fs.spr[i] = (double)exp_term(x);                                        // float exp, widened
     }
     __syncwarp();
-    ARCS_FTRACE(5);
     double z = 0.0;  // :58-60 in candidate order (every lane adds the same chain)
 #pragma unroll 8
     for (int i = 0; i < nc; ++i) z = __dadd_rn(z, fs.spr[i]);
@@ -282,7 +271,6 @@ __device__ __noinline__ int finish_row_warp(const SampleDev& a, int b, FastScrat
       n_i = min(n_i, c);
     }
     n = (int)__reduce_min_sync(0xFFFFFFFFu, (unsigned)n_i);
-    ARCS_FTRACE(6);
     if (lane == 0) {
       const double tot = cum[n - 1];             // the same sum, in the same order, as :70
       double rr = __dmul_rn(a.u[b], tot);        // :71-72
@@ -300,7 +288,6 @@ __device__ __noinline__ int finish_row_warp(const SampleDev& a, int b, FastScrat
       token = fs.sid[pick];
     }
   }
-  ARCS_FTRACE(7);
   if (lane == 0) {
     if (r.k_bad || !r.lists_ok) token = -1;
     a.token[b] = token;
@@ -317,7 +304,6 @@ __device__ __noinline__ int finish_row_warp(const SampleDev& a, int b, FastScrat
       if (a.cand_pr) a.cand_pr[o] = in ? (draw ? (float)fs.spr[i] : (i == 0 ? 1.0f : 0.0f)) : 0.0f;
     }
   }
-  ARCS_FTRACE(8);
   return kFastDone;
 }
 

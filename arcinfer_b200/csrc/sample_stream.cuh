@@ -24,16 +24,6 @@
 
 namespace arcs {
 
-#ifdef ARCS_DEV_TRACE
-__device__ long long g_trace[148 * 64];
-#define ARCS_TRACE(slot) do { if ((slot) < 64) g_trace[blockIdx.x * 64 + (slot)] = clock64(); } while (0)
-#define ARCS_TACC_BEGIN long long tacc0_ = clock64()
-#define ARCS_TACC_END(slot) do { if ((threadIdx.x & 31) == 0 && (threadIdx.x >> 5) == 3) { g_trace[blockIdx.x * 64 + (slot)] += clock64() - tacc0_; g_trace[blockIdx.x * 64 + (slot) + 1] += 1; } } while (0)
-#else
-#define ARCS_TACC_BEGIN do { } while (0)
-#define ARCS_TACC_END(slot) do { } while (0)
-#define ARCS_TRACE(slot) do { } while (0)
-#endif
 
 constexpr int kProdWarp = kScanW;                          // producer warp (its first lanes work)
 constexpr int kTauWarp = kScanW + 1;                       // threshold warp
@@ -49,7 +39,7 @@ constexpr int kRing = 16;                                  // tiles in the ring 
 constexpr int kPend = 2;                                   // chunks each lane of a scanner can set aside
 constexpr int kStash = kPend * 32;                         // ... per warp
 constexpr int kFlushEvery = 2;                             // visits after which a warp examines what it has set aside even if its next tile is there
-constexpr int kU = 4;                                      // chunks per lane per step of the scan
+constexpr int kU = 2;                                      // chunks per lane per step of the scan (a step that meets a hot chunk takes the slow way as a whole: short steps)
 constexpr int kBootLead = 72;                              // tiles the producer is short of an item when that item's first tiles are fetched for its first threshold
 static_assert(kRing % kTeams == 0, "a team always meets its tiles in the same slots");
 static_assert(kMine % (32 * kU) == 0 && kMine / 32 <= 8, "a warp's share of a tile: whole steps, at most 8 chunks per lane");
@@ -318,10 +308,6 @@ __global__ void __launch_bounds__(kRegBoundThreads, 1) stream_kernel(const Sampl
   for (int j = tid; j < my_n; j += kThreadsS) item_ws(a, (int)blockIdx.x + j * (int)gridDim.x).hdr->streamed = 0;
   __threadfence();
   __syncthreads();  // the only CTA-wide barrier
-#ifdef ARCS_DEV_TRACE
-  if (tid < 24) g_trace[blockIdx.x * 64 + 40 + tid] = 0;
-#endif
-  if (tid == 0) ARCS_TRACE(0);
   if (tid == 0) pdl_trigger();  // the finish kernel's CTAs may take their places beside this kernel: each waits for its row's items
 
   auto abort_now = [&]() {
@@ -380,10 +366,8 @@ __global__ void __launch_bounds__(kRegBoundThreads, 1) stream_kernel(const Sampl
       const Item<T> it = item_of<T>(a, (int)blockIdx.x + j * (int)gridDim.x);
       const int T_ = s_tiles(it.p);
       {  // the item's filter, header and first thresholds must be there
-        ARCS_TACC_BEGIN;
         if (!mbar_wait_warp(&prep_bar[st], (uint32_t)(j / 3) & 1u) || !mbar_wait_warp(&bootok_bar[st], (uint32_t)(j / 3) & 1u)) abort_now();
         __threadfence_block();
-        ARCS_TACC_END(46);
       }
       if (vsh[S_ABORT]) break;
       const ItemHdr* hd = tab_hdr(st);
@@ -410,7 +394,6 @@ __global__ void __launch_bounds__(kRegBoundThreads, 1) stream_kernel(const Sampl
       const uint32_t* mrow = ctx.mrow;
       // examine everything the warp has set aside, against the thresholds of this moment
       auto flush = [&]() {
-        ARCS_TACC_BEGIN;
         ctx.tcB = v64[L_TAU_B + st];
         ctx.tcA = MASKED ? v64[L_TAU_A + st] : 0xFFFFFFFFFFFFFFFFull;
 #pragma unroll 1
@@ -421,7 +404,6 @@ __global__ void __launch_bounds__(kRegBoundThreads, 1) stream_kernel(const Sampl
         }
         have = 0;
         __syncwarp();
-        ARCS_TACC_END(40);
       };
       const int t_first = (int)(((uint32_t)(warp / kShare) - G0) % kTeams);
       const int c_lo = (warp % kShare) * kMine;
@@ -445,12 +427,10 @@ __global__ void __launch_bounds__(kRegBoundThreads, 1) stream_kernel(const Sampl
           }
         }
         {
-          ARCS_TACC_BEGIN;
           if (!mbar_wait_warp(&full[slot], (g / kRing) & 1u)) {
             abort_now();
             break;
           }
-          ARCS_TACC_END(42);
         }
         const int nchunk = (int)(s_tile_bytes(it.p, t) / 16u);
         const int32_t col0 = it.p.body_first + t * (kSTile / (int)sizeof(T)) + a.id_base;  // global id of the tile's first element
@@ -576,7 +556,6 @@ __global__ void __launch_bounds__(kRegBoundThreads, 1) stream_kernel(const Sampl
         __nanosleep(100);
       }
       if (vsh[S_ABORT]) break;
-      if (lane == 0) ARCS_TRACE(3 + 4 * j);
       __threadfence_block();
       const ItemHdr* hd = tab_hdr(st);
       const ItemWs w = item_ws(a, (int)blockIdx.x + j * (int)gridDim.x);
@@ -624,7 +603,6 @@ __global__ void __launch_bounds__(kRegBoundThreads, 1) stream_kernel(const Sampl
         // (gpu scope: the scanners' list entries, ordered before their arrival at CTA scope, and
         //  the header are read by another kernel once the item is released)
         st_release_gpu(&w.hdr->streamed, 1);
-        ARCS_TRACE(4 + 4 * j);
       }
       __syncwarp();
     }
@@ -659,11 +637,7 @@ __global__ void __launch_bounds__(kRegBoundThreads, 1) stream_kernel(const Sampl
           abort_now();
           break;
         }
-#ifdef ARCS_DEV_TRACE
-        { long long t0_ = clock64(); __nanosleep(200); if (gt == 0) { g_trace[blockIdx.x * 64 + 48] += clock64() - t0_; g_trace[blockIdx.x * 64 + 49] += 1; } }
-#else
         __nanosleep(200);
-#endif
         continue;
       }
       idle = 0;
@@ -689,20 +663,13 @@ __global__ void __launch_bounds__(kRegBoundThreads, 1) stream_kernel(const Sampl
         const Item<T> it = item_of<T>(a, (int)blockIdx.x + jb * (int)gridDim.x);
         const int nb = min(it.p.body_bytes, kBootBytes);
         const ItemHdr* hb = tab_hdr(st);
-#ifdef ARCS_DEV_TRACE
-        long long tb0_ = clock64();
-#endif
         unsigned long long* tB = &s64[L_TAU_B + st];
         unsigned long long* tA = &s64[L_TAU_A + st];
         boot_item<T, MASKED>(a, it, hb, bootbuf, nb, tab_skip(st), boot_tm, tB, tA, &sh[S_BASEB + st], &sh[S_BASEA + st], gt);
-#ifdef ARCS_DEV_TRACE
-        if (gt == 0) { g_trace[blockIdx.x * 64 + 52] += clock64() - tb0_; g_trace[blockIdx.x * 64 + 53] += 1; }
-#endif
         if (gt == 0) {
           __threadfence_block();
           vsh[S_BOOTOK + st] = jb + 1;
           mbar_arrive(&bootok_bar[st]);
-          ARCS_TRACE(2 + 4 * jb);
         }
         ++boot_done;
       } else {
@@ -713,18 +680,11 @@ __global__ void __launch_bounds__(kRegBoundThreads, 1) stream_kernel(const Sampl
           s64[L_TAU_B + st] = 0ull;
           s64[L_TAU_A + st] = 0ull;
         }
-#ifdef ARCS_DEV_TRACE
-        long long tp0_ = clock64();
-#endif
         prep_item<T, MASKED>(a, (int)blockIdx.x + j * (int)gridDim.x, tab_hdr(st), tab_bloom(st), tab_skip(st), hk, hi_, pmisc, gt);
-#ifdef ARCS_DEV_TRACE
-        if (gt == 0) { g_trace[blockIdx.x * 64 + 50] += clock64() - tp0_; g_trace[blockIdx.x * 64 + 51] += 1; }
-#endif
         if (gt == 0) {
           __threadfence();  // (gpu scope as well: the entries written to the workspace are read by the finish kernel)
           vsh[S_PREPARED] = j + 1;
           mbar_arrive(&prep_bar[st]);
-          ARCS_TRACE(1 + 4 * j);
         }
         ++next_prep;
       }
