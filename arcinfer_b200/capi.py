@@ -44,6 +44,7 @@ class SampleArgs(C.Structure):
         ("token", C.c_void_p), ("n_cand", C.c_void_p), ("n_kept", C.c_void_p), ("flags", C.c_void_p),
         ("cand_id", C.c_void_p), ("cand_val", C.c_void_p), ("cand_pr", C.c_void_p), ("cand_stride", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
+        ("head_id", C.c_void_p), ("head_val", C.c_void_p), ("n_head", C.c_void_p),
     ]  # fmt: skip
 
 
@@ -142,7 +143,7 @@ def reset_workspaces():
 
 def sample_batch(logits, params, u, hist_off=None, hist_ids=None, bias_off=None, bias_ids=None, bias_vals=None,
                  mask=None, mask_row=None, max_hist=0, max_bias=0, id_base=0, v_global=0, V=None,
-                 want_cands=False, status=None):
+                 want_cands=False, want_head=False, status=None):
     """arcs_sample_batch on device tensors. logits: [B, >=V] float32/bfloat16 (row stride =
     logits.stride(0)); params: uint8 tensor holding B arcs_row_params; u: float64 [B]."""
     assert logits.is_cuda and logits.dim() == 2 and logits.stride(1) == 1
@@ -179,6 +180,11 @@ def sample_batch(logits, params, u, hist_off=None, hist_ids=None, bias_off=None,
     if want_cands:
         a.cand_id, a.cand_val, a.cand_pr = out["cand_id"].data_ptr(), out["cand_val"].data_ptr(), out["cand_pr"].data_ptr()
     a.cand_stride = KCAP
+    if want_head:  # (constrained rows only) the 512 most likely tokens in the order the reference calls its predicate
+        out["head_id"] = torch.empty(B, HEAD, dtype=torch.int32, device=dev)
+        out["head_val"] = torch.empty(B, HEAD, dtype=torch.float32, device=dev)
+        out["n_head"] = torch.empty(B, dtype=torch.int32, device=dev)
+        a.head_id, a.head_val, a.n_head = out["head_id"].data_ptr(), out["head_val"].data_ptr(), out["n_head"].data_ptr()
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
     a.status = status.data_ptr()
     _check(lib.arcs_sample_batch(C.byref(a), _stream(dev)), "arcs_sample_batch")
@@ -230,6 +236,35 @@ def dfa_mask(table, dead, states, byte_off, bytes_, special=None, special_ok=Fal
                           bytes_.data_ptr(), _ptr(special), int(special_ok), V, out.data_ptr(), W, _stream(dev)),
         "arcs_dfa_mask",
     )
+    return out
+
+
+class AdjustedArgs(C.Structure):
+    _fields_ = [
+        ("logits", C.c_void_p), ("dtype", C.c_int32), ("B", C.c_int32), ("V", C.c_int32), ("row_stride", C.c_int64),
+        ("params", C.c_void_p), ("hist_off", C.c_void_p), ("hist_ids", C.c_void_p),
+        ("bias_off", C.c_void_p), ("bias_ids", C.c_void_p), ("bias_vals", C.c_void_p),
+        ("out", C.c_void_p), ("out_stride", C.c_int64),
+    ]  # fmt: skip
+
+
+lib.arcs_adjusted_batch.restype = C.c_int
+lib.arcs_adjusted_batch.argtypes = [C.POINTER(AdjustedArgs), C.c_void_p]
+
+
+def adjusted_batch(logits, params, hist_off=None, hist_ids=None, bias_off=None, bias_ids=None, bias_vals=None, V=None):
+    """arcs_adjusted_batch: the penalised logits of whole rows (Sampler::adjusted) as float32 [B, V]."""
+    dev = logits.device
+    B = logits.shape[0]
+    V = logits.shape[1] if V is None else V
+    out = torch.empty(B, V, dtype=torch.float32, device=dev)
+    a = AdjustedArgs()
+    a.logits, a.dtype, a.B, a.V, a.row_stride = logits.data_ptr(), _dtype_code(logits), B, V, logits.stride(0)
+    a.params = params.data_ptr()
+    a.hist_off, a.hist_ids = _ptr(hist_off), _ptr(hist_ids)
+    a.bias_off, a.bias_ids, a.bias_vals = _ptr(bias_off), _ptr(bias_ids), _ptr(bias_vals)
+    a.out, a.out_stride = out.data_ptr(), V
+    _check(lib.arcs_adjusted_batch(C.byref(a), _stream(dev)), "arcs_adjusted_batch")
     return out
 
 

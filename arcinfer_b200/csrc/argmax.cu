@@ -236,7 +236,8 @@ extern "C" int arcs_argmax_batch(const arcs_argmax_args* g, void* stream) {
   constexpr int smem = kStages * kTileBytes;
 #define ARCS_LAUNCH(T, L)                                                                                  \
   do {                                                                                                     \
-    cudaError_t e = cudaFuncSetAttribute(argmax_kernel<T, L>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+    static std::atomic<unsigned long long> attr_done{0};                                                   \
+    cudaError_t e = ensure_dynamic_smem(argmax_kernel<T, L>, smem, attr_done);                             \
     if (e != cudaSuccess) return set_error(ARCS_ERR_CUDA, cudaGetErrorString(e));                          \
     argmax_kernel<T, L><<<grid, kThreads, smem, st>>>(a);                                                  \
   } while (0)

@@ -30,6 +30,13 @@ struct arcs_host_ctx {
   size_t ws_bytes = 0;               // argmax scratch
   int32_t* status = nullptr;
   int32_t last_status = 0;
+  // grown on first use
+  int32_t *head_id = nullptr, *n_head = nullptr;  // [max_B][ARCS_HEAD], [max_B]
+  float* head_val = nullptr;
+  float* adj_out = nullptr;                       // [max_B][max_V]
+  int32_t* draw_id = nullptr;                     // [ARCS_KCAP] candidates handed in by the host
+  float* draw_val = nullptr;
+  int32_t* draw_n = nullptr;
 };
 
 #define CU(x)                                                                  \
@@ -51,7 +58,8 @@ extern "C" void arcs_host_destroy(arcs_host_ctx* c) {
                   (void*)c->token, (void*)c->n_cand, (void*)c->n_kept, (void*)c->flags, (void*)c->cand_id,
                   (void*)c->cand_val, (void*)c->cand_pr, (void*)c->argmax, (void*)c->row_off, (void*)c->draft,
                   (void*)c->draft_off, (void*)c->accepted, (void*)c->next, (void*)c->max_sumexp, c->ws[0], c->ws[1], c->ws_argmax,
-                  (void*)c->status})
+                  (void*)c->status, (void*)c->head_id, (void*)c->n_head, (void*)c->head_val, (void*)c->adj_out, (void*)c->draw_id,
+                  (void*)c->draw_val, (void*)c->draw_n})
     if (p) cudaFree(p);
   if (c->small_ready) cudaEventDestroy(c->small_ready);
   for (auto s : c->st)
@@ -201,6 +209,14 @@ extern "C" int arcs_sample_batch_host(arcs_host_ctx* c, const arcs_sample_args* 
     }
   }
   const bool cands = h->cand_id || h->cand_val || h->cand_pr;
+  const bool head = h->head_id || h->head_val || h->n_head;
+  if (head && !(masked && h->head_id && h->head_val && h->n_head))
+    return set_error(ARCS_ERR_ARG, "sample_batch_host: the ranked head needs a mask and all three of head_id, head_val, n_head");
+  if (head && !c->head_id) {
+    CU(dalloc(&c->head_id, (size_t)c->max_B * ARCS_HEAD));
+    CU(dalloc(&c->head_val, (size_t)c->max_B * ARCS_HEAD));
+    CU(dalloc(&c->n_head, (size_t)c->max_B));
+  }
   int k = 0;
   for (int32_t r0 = 0; r0 < B; r0 += R, ++k) {
     const int32_t rows = std::min(R, B - r0);
@@ -234,6 +250,9 @@ extern "C" int arcs_sample_batch_host(arcs_host_ctx* c, const arcs_sample_args* 
     d.cand_val = cands ? c->cand_val + (size_t)r0 * ARCS_KCAP : nullptr;
     d.cand_pr = cands ? c->cand_pr + (size_t)r0 * ARCS_KCAP : nullptr;
     d.cand_stride = ARCS_KCAP;
+    d.head_id = head ? c->head_id + (size_t)r0 * ARCS_HEAD : nullptr;
+    d.head_val = head ? c->head_val + (size_t)r0 * ARCS_HEAD : nullptr;
+    d.n_head = head ? c->n_head + r0 : nullptr;
     d.workspace = c->ws[k & 1];
     d.workspace_bytes = c->ws_sample_bytes;
     d.status = c->status;
@@ -254,7 +273,100 @@ extern "C" int arcs_sample_batch_host(arcs_host_ctx* c, const arcs_sample_args* 
     if (h->cand_id) CU(back2d(h->cand_id, d.cand_id, 4));
     if (h->cand_val) CU(back2d(h->cand_val, d.cand_val, 4));
     if (h->cand_pr) CU(back2d(h->cand_pr, d.cand_pr, 4));
+    if (head) {
+      CU(cudaMemcpyAsync(h->head_id + (size_t)r0 * ARCS_HEAD, d.head_id, sizeof(int32_t) * ARCS_HEAD * rows, cudaMemcpyDeviceToHost, st));
+      CU(cudaMemcpyAsync(h->head_val + (size_t)r0 * ARCS_HEAD, d.head_val, sizeof(float) * ARCS_HEAD * rows, cudaMemcpyDeviceToHost, st));
+      CU(cudaMemcpyAsync(h->n_head + r0, d.n_head, sizeof(int32_t) * rows, cudaMemcpyDeviceToHost, st));
+    }
   }
+  return finish(c);
+}
+
+// Sampler::adjusted with host buffers: all pointers of `h` are host pointers.
+extern "C" int arcs_adjusted_batch_host(arcs_host_ctx* c, const arcs_adjusted_args* h) {
+  if (!c || !h || !h->logits || !h->params || !h->out || h->B <= 0 || h->V <= 0 || h->row_stride < h->V || h->out_stride < h->V)
+    return set_error(ARCS_ERR_ARG, "adjusted_batch_host: bad argument");
+  if (h->B > c->max_B || h->V > c->max_V || h->dtype != c->dtype)
+    return set_error(ARCS_ERR_ARG, "adjusted_batch_host: batch larger than the context was created for");
+  CU(cudaSetDevice(c->device));
+  const int32_t B = h->B, V = h->V;
+  const size_t es = c->dtype == ARCS_F32 ? 4 : 2;
+  const int64_t nh = h->hist_off ? h->hist_off[B] : 0, nb = h->bias_off ? h->bias_off[B] : 0;
+  if (nh > c->max_hist || nb > c->max_bias) return set_error(ARCS_ERR_ARG, "adjusted_batch_host: lists larger than the context was created for");
+  if (!c->adj_out) CU(dalloc(&c->adj_out, (size_t)c->max_B * c->max_V));
+  cudaStream_t st = c->st[0];
+  CU(cudaMemcpyAsync(c->params, h->params, sizeof(arcs_row_params) * B, cudaMemcpyHostToDevice, st));
+  if (h->hist_off) {
+    CU(cudaMemcpyAsync(c->hist_off, h->hist_off, sizeof(int32_t) * (B + 1), cudaMemcpyHostToDevice, st));
+    if (nh) CU(cudaMemcpyAsync(c->hist_ids, h->hist_ids, sizeof(int32_t) * nh, cudaMemcpyHostToDevice, st));
+  }
+  if (h->bias_off) {
+    CU(cudaMemcpyAsync(c->bias_off, h->bias_off, sizeof(int32_t) * (B + 1), cudaMemcpyHostToDevice, st));
+    if (nb) {
+      CU(cudaMemcpyAsync(c->bias_ids, h->bias_ids, sizeof(int32_t) * nb, cudaMemcpyHostToDevice, st));
+      CU(cudaMemcpyAsync(c->bias_vals, h->bias_vals, sizeof(float) * nb, cudaMemcpyHostToDevice, st));
+    }
+  }
+  CU(cudaMemcpy2DAsync(c->logits, (size_t)V * es, h->logits, (size_t)h->row_stride * es, (size_t)V * es, B, cudaMemcpyHostToDevice, st));
+  arcs_adjusted_args d = *h;
+  d.logits = c->logits;
+  d.row_stride = V;
+  d.params = c->params;
+  d.hist_off = h->hist_off ? c->hist_off : nullptr;
+  d.hist_ids = c->hist_ids;
+  d.bias_off = h->bias_off ? c->bias_off : nullptr;
+  d.bias_ids = c->bias_ids;
+  d.bias_vals = c->bias_vals;
+  d.out = c->adj_out;
+  d.out_stride = V;
+  const int rc = arcs_adjusted_batch(&d, st);
+  if (rc != ARCS_OK) return rc;
+  CU(cudaMemcpy2DAsync(h->out, (size_t)h->out_stride * 4, c->adj_out, (size_t)V * 4, (size_t)V * 4, B, cudaMemcpyDeviceToHost, st));
+  return finish(c);
+}
+
+// The last step of Sampler::sample_allowed (tools/sampler.h:121-143) for a host that called its
+// predicate itself: n candidates in the order they were found (ids, adjusted logits; host
+// pointers), the row's settings, the uniform draw; softmax, min-p / top-p cuts and the draw on the
+// device. *token = -1 when n == 0.
+extern "C" int arcs_draw_candidates_host(arcs_host_ctx* c, const int32_t* ids, const float* vals, int32_t n, const arcs_row_params* p,
+                                         double u, int32_t v_global, int32_t* token, int32_t* n_kept) {
+  if (!c || !p || !token || n < 0 || n > ARCS_KCAP || (n > 0 && (!ids || !vals)) || v_global <= 0)
+    return set_error(ARCS_ERR_ARG, "draw_candidates_host: bad argument");
+  if (n == 0) {
+    *token = -1;
+    if (n_kept) *n_kept = 0;
+    return ARCS_OK;
+  }
+  CU(cudaSetDevice(c->device));
+  if (!c->draw_id) {
+    CU(dalloc(&c->draw_id, (size_t)ARCS_KCAP));
+    CU(dalloc(&c->draw_val, (size_t)ARCS_KCAP));
+    CU(dalloc(&c->draw_n, (size_t)1));
+  }
+  cudaStream_t st = c->st[0];
+  CU(cudaMemcpyAsync(c->draw_id, ids, sizeof(int32_t) * n, cudaMemcpyHostToDevice, st));
+  CU(cudaMemcpyAsync(c->draw_val, vals, sizeof(float) * n, cudaMemcpyHostToDevice, st));
+  CU(cudaMemcpyAsync(c->draw_n, &n, sizeof(int32_t), cudaMemcpyHostToDevice, st));
+  CU(cudaMemcpyAsync(c->params, p, sizeof(arcs_row_params), cudaMemcpyHostToDevice, st));
+  CU(cudaMemcpyAsync(c->u, &u, sizeof(double), cudaMemcpyHostToDevice, st));
+  arcs_merge_args m = {};
+  m.G = 1;
+  m.B = 1;
+  m.cand_stride = ARCS_KCAP;
+  m.cand_id = c->draw_id;
+  m.cand_val = c->draw_val;
+  m.n_cand = c->draw_n;
+  m.params = c->params;
+  m.u = c->u;
+  m.v_global = v_global;
+  m.token = c->token;
+  m.n_kept = c->n_kept;
+  m.status = c->status;
+  const int rc = arcs_merge_batch(&m, st);
+  if (rc != ARCS_OK) return rc;
+  CU(cudaMemcpyAsync(token, c->token, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
+  if (n_kept) CU(cudaMemcpyAsync(n_kept, c->n_kept, sizeof(int32_t), cudaMemcpyDeviceToHost, st));
   return finish(c);
 }
 

@@ -522,7 +522,8 @@ extern "C" int arcs_logprobs_batch(const arcs_logprob_args* g, void* stream) {
   const unsigned grid = (unsigned)g->B * (unsigned)a.nseg;
 #define ARCS_LAUNCH(T)                                                                                               \
   do {                                                                                                               \
-    cudaError_t e = cudaFuncSetAttribute(logprob_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kLpSmem); \
+    static std::atomic<unsigned long long> attr_done{0};                                                   \
+    cudaError_t e = ensure_dynamic_smem(logprob_kernel<T>, (int)kLpSmem, attr_done);                       \
     if (e != cudaSuccess) return set_error(ARCS_ERR_CUDA, cudaGetErrorString(e));                                    \
     logprob_kernel<T><<<grid, kThreads, kLpSmem, st>>>(a);                                                           \
   } while (0)

@@ -1,5 +1,7 @@
 // Host-side helpers shared by the entry points: launch geometry, error text, fault injection.
 #pragma once
+#include <atomic>
+
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
@@ -40,6 +42,21 @@ inline int check_launch(const char* what) {
   snprintf(error_buffer(), 256, "%s: %s", what, cudaGetErrorString(e));
   return ARCS_ERR_CUDA;
 }
+// Raises a kernel's dynamic shared-memory limit once per device and process (the attribute belongs
+// to the device's context; setting it costs microseconds, which a small batch notices on every
+// call). `done`: one bit per device, owned by the call site.
+template <typename K>
+inline cudaError_t ensure_dynamic_smem(K kernel, int bytes, std::atomic<unsigned long long>& done) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  const unsigned long long bit = 1ull << (dev & 63);
+  if (done.load(std::memory_order_acquire) & bit) return cudaSuccess;
+  e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e == cudaSuccess) done.fetch_or(bit, std::memory_order_release);
+  return e;
+}
+
 // Host-side fault injection (no device is ever faulted): with ARCS_FAIL_CALL=N in the
 // environment the N-th entry-point call of the process returns ARCS_ERR_INJECTED before
 // anything is launched. Returns 0 when the call should proceed.

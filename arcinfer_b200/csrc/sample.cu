@@ -59,6 +59,8 @@ static int sample_launch(const arcs_sample_args* g, void* stream, cudaEvent_t* e
   if (masked && g->mask_stride < (g->V + 31) / 32) return set_error(ARCS_ERR_ARG, "sample_batch: mask_stride too small");
   if (masked && (g->id_base != 0 || (g->v_global != 0 && g->v_global != g->V)))
     return set_error(ARCS_ERR_ARG, "sample_batch: a mask cannot be combined with a vocabulary shard");
+  if ((g->head_id || g->head_val || g->n_head) && !(masked && g->head_id && g->head_val && g->n_head))
+    return set_error(ARCS_ERR_ARG, "sample_batch: the ranked head needs a mask and all three of head_id, head_val, n_head");
   if ((g->cand_id || g->cand_val || g->cand_pr) && g->cand_stride < ARCS_KCAP)
     return set_error(ARCS_ERR_ARG, "sample_batch: cand_stride must be at least ARCS_KCAP");
 
@@ -95,6 +97,9 @@ static int sample_launch(const arcs_sample_args* g, void* stream, cudaEvent_t* e
   a.cand_val = g->cand_val;
   a.cand_pr = g->cand_pr;
   a.cand_stride = g->cand_stride;
+  a.head_id = g->head_id;
+  a.head_val = g->head_val;
+  a.n_head = g->n_head;
   a.ws_items = static_cast<char*>(g->workspace);
   a.item_block = item_block_bytes(masked, slots);
   a.status = g->status;
@@ -113,8 +118,8 @@ static int sample_launch(const arcs_sample_args* g, void* stream, cudaEvent_t* e
   const unsigned grid_s = (unsigned)(items < kSmCount ? items : kSmCount);
 #define ARCS_LAUNCH(T, M)                                                                                          \
   do {                                                                                                             \
-    static const cudaError_t attr_rc =                                                                             \
-        cudaFuncSetAttribute(stream_kernel<T, M>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);        \
+    static std::atomic<unsigned long long> attr_done{0};                                                           \
+    const cudaError_t attr_rc = ensure_dynamic_smem(stream_kernel<T, M>, 227 * 1024, attr_done);                   \
     if (attr_rc != cudaSuccess) return set_error(ARCS_ERR_CUDA, cudaGetErrorString(attr_rc));                      \
     if (events) cudaEventRecord(events[0], st);                                                                    \
     stream_kernel<T, M><<<grid_s, kThreadsS, smem_s, st>>>(a);                                                     \

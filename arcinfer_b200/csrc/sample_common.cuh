@@ -52,6 +52,9 @@ struct SampleDev {
   float* cand_val;
   float* cand_pr;
   int32_t cand_stride;
+  int32_t* head_id;         // [B][ARCS_HEAD] ranked head of a constrained row (optional)
+  float* head_val;
+  int32_t* n_head;
   char* ws_items;           // [B * nseg] blocks of item_block bytes
   int64_t item_block;
   int32_t* status;

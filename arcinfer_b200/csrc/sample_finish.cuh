@@ -337,6 +337,24 @@ __global__ void __launch_bounds__(G, 5) finish_kernel(const SampleDev a) {  // (
   settle();
   group_sync<2, G>();
   if (MASKED) sel_prune<2, G>(selA, selA.k, psF, gt);
+  if (MASKED && a.head_id) {
+    // the ranked head: the (at most) 512 best of all tokens, banned ones included, best first
+    // (composites are unique, so counting the larger ones ranks them)
+    const int nA = min(*selA.cnt, ARCS_HEAD);
+    for (int i = gt; i < ARCS_HEAD; i += G) {
+      if (i < nA) {
+        const uint64_t c = comp_of(selA.key[i], selA.id[i]);
+        int rank = 0;
+        for (int x = 0; x < nA; ++x) rank += comp_of(selA.key[x], selA.id[x]) > c;
+        a.head_id[(size_t)b * ARCS_HEAD + rank] = selA.id[i];
+        a.head_val[(size_t)b * ARCS_HEAD + rank] = value_of(selA.key[i]);
+      } else {
+        a.head_id[(size_t)b * ARCS_HEAD + i] = -1;
+        a.head_val[(size_t)b * ARCS_HEAD + i] = 0.0f;
+      }
+    }
+    if (gt == 0) a.n_head[b] = nA;
+  }
 
   // ---- candidates best first. A short buffer is ranked by counting, which selects the k best
   // and sorts them in one step; a longer one is cut to the k best by the radix select first.

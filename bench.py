@@ -180,6 +180,169 @@ def bench_logprobs(args):
     print(json.dumps(line), flush=True)
 
 
+def bench_small(args):
+    """The four latency workloads (--workload single-row | multi-slot | spec-verify | constrained, one
+    GPU): the shapes the reference itself runs (at most 16 rows a pass, zero/engine.h:2910, scaled as
+    the measured configurations say). One step = one call on device-resident inputs; `e2e` = the same
+    call through the host-buffer entry point; every row's result is compared with the CPU checker;
+    `cpu_baseline` = the reference's own code on one host thread, which is how the reference runs it."""
+    import ctypes as C
+
+    import numpy as np
+    import torch
+
+    import arcinfer_b200 as ab
+    from arcinfer_b200 import synth
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import orc
+
+    torch.cuda.set_device(0)
+    dev = "cuda"
+    wl = args.workload
+    c = {"single-row": synth.config1, "multi-slot": synth.config2, "spec-verify": synth.config3, "constrained": synth.config4}[wl]()
+    x = c["logits"]
+    bf16 = c["bf16"]
+    B, V = x.shape
+    lg = torch.from_numpy(x.view(np.int16)).to(dev).view(torch.bfloat16) if bf16 else torch.from_numpy(x).to(dev)
+    xf = synth.bf16_bits_to_f32(x) if bf16 else x
+    elt = 2 if bf16 else 4
+    launches_per_step, extra_bytes = 2, 0
+    if wl == "spec-verify":
+        kw = dict(row_off=torch.from_numpy(c["row_off"]).to(dev), draft=torch.from_numpy(c["draft"]).to(dev), draft_off=torch.from_numpy(c["draft_off"]).to(dev))
+        step = lambda: ab.argmax_batch(lg, **kw)
+        launches_per_step, extra_bytes = 1, c["draft"].nbytes
+        kernel = "argmax_kernel"
+    else:
+        p_dev = ab.capi.params_to_device(c["params"], dev)
+        u = torch.from_numpy(np.ascontiguousarray(c["u"])).to(dev)
+        ho, hi = synth.csr(c["hist"])
+        H = int(max(len(h) for h in c["hist"]))
+        kw = {}
+        if H:
+            kw = dict(hist_off=torch.from_numpy(ho).to(dev), hist_ids=torch.from_numpy(hi).to(dev), max_hist=H)
+            extra_bytes += hi.nbytes
+        if wl == "constrained":
+            states, inv = np.unique(c["states"], return_inverse=True)
+            tab = torch.from_numpy(c["table"].view(np.int16)).to(dev)
+            st_dev = torch.from_numpy(states.astype(np.int32)).to(dev)
+            off_dev, by_dev = torch.from_numpy(c["byte_off"].view(np.int32)).to(dev), torch.from_numpy(c["bytes"]).to(dev)
+            mrow = torch.from_numpy(inv.astype(np.int32)).to(dev)
+            launches_per_step = 3
+            extra_bytes += c["bytes"].nbytes + c["byte_off"].nbytes + c["table"].nbytes + len(states) * ((V + 31) // 32) * 4
+
+            def step():  # the mask of every distinct automaton state, then the constrained selection
+                m = ab.dfa_mask(tab, c["dead"], st_dev, off_dev, by_dev, V=V)
+                return ab.sample_batch(lg, p_dev, u, mask=m, mask_row=mrow, **kw)
+        else:
+            step = lambda: ab.sample_batch(lg, p_dev, u, **kw)
+        kernel = "stream_kernel"
+    for _ in range(max(args.warmup, 5)):
+        out = step()
+    torch.cuda.synchronize()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)  # larger than L2: written between timed calls
+    clocks = ClockSampler(0)
+    times = []
+    for _ in range(args.steps):
+        flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = step()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    t_end = time.perf_counter() + 0.5
+    while time.perf_counter() < t_end:
+        step()
+        torch.cuda.synchronize()
+    clk = clocks.stop()
+    ms = float(np.median(times))
+    assert int(out["status"].item()) == 0
+    # ---- every row against the CPU checker
+    bad = 0
+    masks_h = None
+    if wl == "spec-verify":
+        sel = np.array([orc.argmax(r) for r in xf], np.int32)
+        acc, nxt = orc.verify_greedy(sel, c["row_off"], c["draft"], c["draft_off"])
+        bad = int((out["argmax"].cpu().numpy() != sel).sum() + (out["accepted"].cpu().numpy() != acc).sum() + (out["next"].cpu().numpy() != nxt).sum())
+    else:
+        if wl == "constrained":
+            masks_h = ab.dfa_mask(tab, c["dead"], st_dev, off_dev, by_dev, V=V).cpu().numpy().view(np.uint32)
+            for i, sidx in enumerate(states):
+                bad += int(not np.array_equal(masks_h[i], orc.dfa_mask(c["table"], c["dead"], int(sidx), c["byte_off"], c["bytes"])))
+        tok = out["token"].cpu().numpy()
+        for b in range(B):
+            m = None if masks_h is None else masks_h[inv[b]]
+            bad += int(tok[b] != orc.sample(xf[b], c["params"][b:b + 1], c["hist"][b], float(c["u"][b]), None, m)["token"])
+    parity = {"rows_checked": B, "mismatches": bad, "against": "oracle/arcs_oracle.c on the same inputs"}
+    if bad:
+        print(json.dumps({"parity": parity}), flush=True)
+        sys.exit(3)
+    # ---- end to end: host buffers in, results out
+    ctx = ab.capi.HostContext(0, B, V, bf16, max_hist_total=max(1, extra_bytes), max_mask_words=(B * ((V + 31) // 32)) if wl == "constrained" else 0)
+    h_x = torch.from_numpy(x.view(np.int16) if bf16 else x).pin_memory().numpy()
+    if bf16:
+        h_x = h_x.view(np.uint16)
+    if wl == "spec-verify":
+        am, ac, nx = np.zeros(B, np.int32), np.zeros(len(c["row_off"]) - 1, np.int32), np.zeros(len(c["row_off"]) - 1, np.int32)
+        host_step = lambda: ctx.argmax(h_x, am, row_off=c["row_off"], draft=c["draft"], draft_off=c["draft_off"], accepted=ac, next_=nx)
+        d2h = am.nbytes + ac.nbytes + nx.nbytes
+    else:
+        tk = np.zeros(B, np.int32)
+        hkw = dict(hist_off=ho, hist_ids=hi, max_hist=H) if H else {}
+        if wl == "constrained":
+            hkw.update(mask=np.ascontiguousarray(masks_h), mask_row=inv.astype(np.int32))
+        us = np.ascontiguousarray(c["u"])
+        host_step = lambda: ctx.sample(h_x, c["params"], us, tk, **hkw)
+        d2h = tk.nbytes + 4
+    for _ in range(3):
+        host_step()
+    t0 = time.perf_counter()
+    esteps = max(5, min(args.steps, 20))
+    for _ in range(esteps):
+        host_step()
+    e_ms = 1e3 * (time.perf_counter() - t0) / esteps
+    ctx.close()
+    # ---- the reference's own code, one host thread
+    cpu = None
+    if not args.no_cpu:
+        t0 = time.perf_counter()
+        reps = 0
+        while reps == 0 or time.perf_counter() - t0 < 3.0:
+            if wl == "spec-verify":
+                sel = np.array([orc.argmax(r) for r in xf], np.int32)
+                orc.verify_greedy(sel, c["row_off"], c["draft"], c["draft_off"])
+            elif orc.ref is not None:
+                seeds = np.arange(1, B + 1, dtype=np.uint64)
+                outc = np.zeros(B, np.int32)
+                mk = None if masks_h is None else np.ascontiguousarray(masks_h[inv])
+                orc.ref.ref_sample_batch(c["params"].ctypes.data_as(C.c_void_p), seeds.ctypes.data_as(C.c_void_p), np.ascontiguousarray(xf).ctypes.data_as(C.c_void_p),
+                                         C.c_int64(B), V, ho.ctypes.data_as(C.c_void_p), (hi if len(hi) else np.zeros(1, np.int32)).ctypes.data_as(C.c_void_p),
+                                         None if mk is None else mk.ctypes.data_as(C.c_void_p), C.c_int64(0 if mk is None else mk.shape[1]), 1,
+                                         outc.ctypes.data_as(C.c_void_p))
+            else:
+                for b in range(B):
+                    orc.sample(xf[b], c["params"][b:b + 1], c["hist"][b], float(c["u"][b]), None, None if masks_h is None else masks_h[inv[b]])
+            reps += 1
+        dt = (time.perf_counter() - t0) / reps
+        kind = "reference" if (orc.ref is not None and wl != "spec-verify") else "port"
+        cpu = {"value": B / dt, "unit": UNIT, "cores": 1, "kind": kind, "sample": f"the whole workload ({B} rows), repeated for >= 3 s, one thread"}
+    peak, which = measured_peak()
+    abytes = B * V * elt + extra_bytes
+    line = {
+        "metric": METRIC, "value": B / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 5),
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16" if bf16 else "f32",
+        "data": "synthetic", "config": {"workload": wl, "rows": B, "vocab": V, "l2": "L2 flushed (256 MiB written) between timed calls; median of the calls"},
+        "gpu_launches": launches_per_step * args.steps, "clocks": clk,
+        "e2e": {"value": B / (e_ms * 1e-3), "unit": UNIT, "h2d_bytes_per_step": B * V * elt + extra_bytes, "d2h_bytes_per_step": d2h, "ms_per_step": e_ms},
+        "roofline": {"bound": "hbm", "kernel": kernel, "achieved": abytes / (ms * 1e-3) / 1e9, "peak": peak, "peak_source": f"of {which}", "unit": "GB/s",
+                     "frac": abytes / (ms * 1e-3) / 1e9 / peak, "traffic": None, "algorithmic_bytes_per_launch": abytes,
+                     "note": "a latency case: launch and per-row dependency chains, not HBM, bound it"},
+        "cpu_baseline": cpu, "parity": parity,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -190,8 +353,9 @@ def main():
     ap.add_argument("--vocab", type=int, default=VOCAB)
     ap.add_argument("--shard", default="rows", choices=["rows", "vocab"],
                     help="how N GPUs split the work: rows (default, no collective) or vocabulary columns (one all-gather)")
-    ap.add_argument("--workload", default="wide-batch", choices=["wide-batch", "logprobs"],
-                    help="wide-batch: the sampling step (the headline); logprobs: arcs_logprobs_batch on the same logits, one GPU")
+    ap.add_argument("--workload", default="wide-batch", choices=["wide-batch", "logprobs", "single-row", "multi-slot", "spec-verify", "constrained"],
+                    help="wide-batch: the sampling step (the headline); logprobs: arcs_logprobs_batch on the same logits; the other four: "
+                         "the latency workloads of the measured configurations 1-4 (one GPU)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-parity", action="store_true", help="skip the oracle check of the timed launch's tokens")
@@ -201,6 +365,10 @@ def main():
     if args.workload == "logprobs" and args.impl == "ours":
         if int(os.environ.get("RANK", "0")) == 0:
             bench_logprobs(args)
+        return
+    if args.workload in ("single-row", "multi-slot", "spec-verify", "constrained") and args.impl == "ours":
+        if int(os.environ.get("RANK", "0")) == 0:
+            bench_small(args)
         return
 
     import numpy as np

@@ -100,6 +100,14 @@ typedef struct {
   void* workspace;           /* arcs_sample_workspace_bytes() bytes, 16-byte aligned; needs no initialisation */
   size_t workspace_bytes;
   int32_t* status;           /* optional device word: 0 or an arcs_status set by the kernels */
+  /* The ranked head of a constrained row (only with a mask; all three or none): the ARCS_HEAD most
+   * likely tokens by adjusted logit, banned ones included, in (logit descending, id ascending)
+   * order - the order in which Sampler::sample_allowed calls its predicate (tools/sampler.h:93-120).
+   * A host whose predicate cannot be written as a mask calls with an all-zero mask, reads the head,
+   * and calls the predicate itself in that order. */
+  int32_t* head_id;          /* [B][ARCS_HEAD] optional; entries past n_head are -1 */
+  float* head_val;           /* [B][ARCS_HEAD] their adjusted logits */
+  int32_t* n_head;           /* [B] min(V, ARCS_HEAD) less the NaN logits among them */
 } arcs_sample_args;
 
 /* max_list: max_hist + max_bias of the call (0 without lists) */
@@ -109,6 +117,24 @@ int arcs_sample_batch(const arcs_sample_args* args, void* stream);
  * beside the stream kernel here), with CUDA events between them on `stream`; waits for them and
  * returns the device time of the stream and finish kernels in ms2[0..1]. */
 int arcs_sample_batch_timed(const arcs_sample_args* args, void* stream, float* ms2);
+
+/* adjusted_batch: Sampler::adjusted (tools/sampler.h:147-176) for whole rows: the logits after
+ * logit_bias, the frequency / repeat / presence penalties and the bans, as fp32 (bit for bit the
+ * reference's values: every operation a separate fp32 rounding in its order). Device pointers. */
+typedef struct {
+  const void* logits;        /* [B][row_stride] of dtype */
+  int32_t dtype, B, V;
+  int64_t row_stride;
+  const arcs_row_params* params;
+  const int32_t* hist_off;   /* as in arcs_sample_args; lists of any length */
+  const int32_t* hist_ids;
+  const int32_t* bias_off;
+  const int32_t* bias_ids;
+  const float* bias_vals;
+  float* out;                /* [B][out_stride] */
+  int64_t out_stride;        /* >= V */
+} arcs_adjusted_args;
+int arcs_adjusted_batch(const arcs_adjusted_args* args, void* stream);
 
 /* Vocabulary shards (no counterpart in the reference, which has one device): every GPU runs
  * arcs_sample_batch on its columns of all rows (`id_base`, `v_global`; lists are filtered by range)
@@ -245,6 +271,14 @@ int arcs_host_create(arcs_host_ctx** out, int32_t device, int32_t max_B, int32_t
                      int64_t max_hist_total, int64_t max_bias_total, int64_t max_mask_words);
 void arcs_host_destroy(arcs_host_ctx* ctx);
 int arcs_sample_batch_host(arcs_host_ctx* ctx, const arcs_sample_args* host_args);
+/* Sampler::adjusted with host buffers (tools/sampler.h:147-176); all pointers of host_args are host pointers */
+int arcs_adjusted_batch_host(arcs_host_ctx* ctx, const arcs_adjusted_args* host_args);
+/* The last step of Sampler::sample_allowed (tools/sampler.h:121-143) for a host that has called its
+ * predicate itself, in the order of the ranked head: n <= ARCS_KCAP candidates in the order they
+ * were found (ids, adjusted logits: host pointers), the row's settings, the uniform draw;
+ * softmax, min-p / top-p cuts and the draw on the device. *token = -1 when n == 0. */
+int arcs_draw_candidates_host(arcs_host_ctx* ctx, const int32_t* ids, const float* vals, int32_t n, const arcs_row_params* params,
+                              double u, int32_t v_global, int32_t* token, int32_t* n_kept);
 /* greedy selection + acceptance with host buffers (zero/runz.cpp:683-715) */
 int arcs_argmax_batch_host(arcs_host_ctx* ctx, const arcs_argmax_args* host_args);
 /* device status word of the last host call (0 = fine) */

@@ -17,6 +17,14 @@ def test_wrapper_compiles_without_cuda_headers():
     subprocess.run(["g++", "-std=c++17", "-fsyntax-only", "-Wall", SRC], check=True, cwd=ROOT)
 
 
+def orc_default_params():
+    import orc
+
+    p = np.zeros(1, orc.PARAMS_DTYPE)
+    p["temperature"], p["top_p"], p["repeat_penalty"], p["repeat_last_n"], p["top_k"] = 1.0, 0.95, 1.0, 64, 20
+    return p
+
+
 def _write_case(path, logits, p, recent, bias, mask, seed, n_calls, append):
     with open(path, "wb") as f:
         f.write(struct.pack("<6i", len(logits), len(recent), len(bias), n_calls, int(mask is not None), int(append)))
@@ -41,12 +49,19 @@ def test_wrapper_replays_like_the_oracle(tmp_path):
     subprocess.run(["g++", "-std=c++17", "-O1", SRC, "-o", exe, "-L" + libdir, "-larcsample", "-Wl,-rpath," + libdir],
                    check=True, cwd=ROOT)
     g = np.random.default_rng(77)
-    for case in range(10):
+    for case in range(12):
         V = int(g.choice([300, 5000, 40000]))
         masked = case % 3 == 2
         logits = rand_logits(g, V, 0)
         p, bias = rand_params(g, V, True, allow_k0=not masked)
         recent = rand_recent(g, V)
+        if case == 10:  # a long answer with default parameters: the history is never read (tools/sampler.h:151)
+            p, bias = orc_default_params(), []
+            recent = g.integers(0, V, 5000).astype(np.int32)
+        if case == 11:  # ... and with the repeat penalty alone, which reads the last 64 ids
+            p, bias = orc_default_params(), []
+            p["repeat_penalty"] = 1.3
+            recent = g.integers(0, V, 70000).astype(np.int32)
         mask = rand_mask(g, V, 0.3) if masked else None
         seed, n_calls, append = int(g.integers(1, 1 << 40)), 5, case % 2 == 0
         path = str(tmp_path / f"case{case}.bin")
