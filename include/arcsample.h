@@ -34,7 +34,8 @@ typedef enum {
   ARCS_ERR_CUDA = 4,       /* a CUDA call failed; arcs_last_error() has the text */
   ARCS_ERR_LIST = 5,       /* a row's history / bias list is longer than max_hist / max_bias */
   ARCS_ERR_TIMEOUT = 6,    /* device side: a bounded wait ran out (status word only) */
-  ARCS_ERR_INJECTED = 7    /* host-side fault injection (ARCS_FAIL_CALL=N environment variable) */
+  ARCS_ERR_INJECTED = 7,   /* host-side fault injection (ARCS_FAIL_CALL=N environment variable) */
+  ARCS_ERR_UNSUPPORTED = 8 /* jcon: the schema (or this step's table) is outside what the automaton expresses */
 } arcs_status;
 
 typedef enum { ARCS_F32 = 0, ARCS_BF16 = 1 } arcs_dtype;
@@ -220,6 +221,42 @@ int arcs_argmax_batch_static(const arcs_argmax_args* args, void* stream);
 int arcs_dfa_mask(const uint16_t* table, int32_t n_table_states, int32_t dead, const int32_t* states,
                   int32_t n_states, const uint32_t* byte_off, const uint8_t* bytes, const uint8_t* special,
                   int32_t special_ok, int32_t V, uint32_t* out, int64_t out_stride, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * jcon: the constrained-JSON prefix checker (jcon::Checker, tools/json_constraint.h:30-281) as an
+ * incremental byte automaton, and the bridge from it to arcs_dfa_mask. HOST code, no GPU work.
+ * The reference asks check(answer + piece(t)) != FAIL per candidate token, each call parsing the
+ * whole answer again (tools/server_chat.h:553-557); here the answer is walked once per step and
+ * the transitions that the vocabulary's tokens can take from there are written out as a table.
+ *   arcs_jcon_create: schema_json is the schema's JSON text ("{}" = any value), object_only the
+ *     json_object mode (tools/server_chat.h:30-31); the vocabulary (byte_off[V+1], bytes; host
+ *     memory, copied) is the one later given to arcs_dfa_mask. Returns ARCS_ERR_UNSUPPORTED, with
+ *     the handle still created so that arcs_jcon_why() names the construct, for the two schema
+ *     forms without a finite automaton: anyOf / oneOf whose branches can begin with the same
+ *     character, and an enum with one option's text a proper prefix of another's. The caller
+ *     then keeps the reference's per-candidate predicate (arcs_sample_batch's ranked head).
+ *   arcs_jcon_check: jcon::Checker::check(text): 0 FAIL, 1 PARTIAL, 2 DONE (-1: bad handle).
+ *   arcs_jcon_table: the table for the step after `text`: state 0 is the configuration after
+ *     text; token t is allowed iff walking its bytes from state 0 never reaches *dead, i.e. iff
+ *     check(text + piece(t)) != FAIL. done[s] != 0: the answer is complete in state s
+ *     (tools/server_chat.h:550: the server then ends the answer). text_state receives
+ *     check(text). Only transitions some token takes are filled in; the rest lead to *dead. The
+ *     pointers are host memory owned by the handle and stay valid until the next call on it;
+ *     tables are cached by configuration. ARCS_ERR_ARG when text itself already fails;
+ *     ARCS_ERR_UNSUPPORTED when the step needs more than 8192 states.
+ *   One corner differs from the reference inside a single token: a token that closes TWO keys
+ *   the schema does not name, in one object that allows other keys, is refused even if the two
+ *   keys differ (the table does not remember such keys' text).
+ * ---------------------------------------------------------------------------------------- */
+typedef struct arcs_jcon arcs_jcon;
+int arcs_jcon_create(const char* schema_json, int32_t object_only, const uint32_t* byte_off, const uint8_t* bytes,
+                     int32_t V, arcs_jcon** out);
+const char* arcs_jcon_why(const arcs_jcon* h);
+int arcs_jcon_check(const arcs_jcon* h, const char* text, int64_t len);
+int arcs_jcon_table(arcs_jcon* h, const char* text, int64_t len, const uint16_t** table, int32_t* n_states,
+                    int32_t* dead, const uint8_t** done, int32_t* text_state);
+void arcs_jcon_cache_stats(const arcs_jcon* h, int64_t* hits, int64_t* misses);
+void arcs_jcon_destroy(arcs_jcon* h);
 
 /* ------------------------------------------------------------------------------------------
  * logprobs_batch: per row, the log probability of one token and the top_n most likely
