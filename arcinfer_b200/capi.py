@@ -223,14 +223,17 @@ def argmax_batch(logits, V=None, want_lse=False, row_off=None, draft=None, draft
     return out
 
 
-def dfa_mask(table, dead, states, byte_off, bytes_, special=None, special_ok=False, V=None, out_stride=None):
+def dfa_mask(table, dead, states, byte_off, bytes_, special=None, special_ok=False, V=None, out_stride=None, out=None):
     """arcs_dfa_mask: table [S,256] uint16-as-int16 tensor, states int32 [n], byte_off
     uint32-as-int32 [V+1], bytes_ uint8. Returns int32 [n, out_stride] packed bits (out_stride
-    defaults to ceil(V/32); words past that are left zero)."""
+    defaults to ceil(V/32); words past that are left zero). out: a tensor of that shape to write
+    into instead of a new one (its words past ceil(V/32) are left as they are)."""
     dev = table.device
     V = byte_off.numel() - 1 if V is None else V
     W = (V + 31) // 32 if out_stride is None else out_stride
-    out = torch.zeros(states.numel(), W, dtype=torch.int32, device=dev)
+    if out is None:
+        out = torch.zeros(states.numel(), W, dtype=torch.int32, device=dev)
+    assert out.shape == (states.numel(), W) and out.dtype == torch.int32 and out.is_contiguous()
     _check(
         lib.arcs_dfa_mask(table.data_ptr(), table.shape[0], dead, states.data_ptr(), states.numel(), byte_off.data_ptr(),
                           bytes_.data_ptr(), _ptr(special), int(special_ok), V, out.data_ptr(), W, _stream(dev)),
@@ -422,6 +425,7 @@ class SamplePlan:
         self.keep = (logits, params, u, hist_off, hist_ids, mask, mask_row)
         self.out = {k: torch.empty(B, dtype=torch.int32, device=dev) for k in ("token", "n_cand", "n_kept", "flags")}
         self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.out["status"] = self.status
         masked = mask is not None
         max_list = max_hist if hist_off is not None else 0
         self.ws = _workspace("sample", dev, lib.arcs_sample_workspace_bytes(B, V, int(masked), max_list))

@@ -29,6 +29,18 @@ constexpr int kMaxRows = 65536;
 constexpr int kItemsPerSm = 1;        // work items per SM that few rows are cut into
 constexpr int kFinishThreads = 128;   // threads of the finish kernel's CTA (four rows per CTA; one with an allowed-token mask)
 
+// Rows with an allowed-token mask are not cut: the ranked head needs the 512 best of the whole
+// row, and every segment would have to keep 512 of its own (a list that a short segment cannot
+// prune before it ends).
+static void plan_items(int B, int V, bool masked, int* nseg, int* seg_len) {
+  if (!masked) return plan_segments(B, V, nseg, seg_len, kItemsPerSm);
+  *nseg = 1;
+  *seg_len = ((V + 2047) / 2048) * 2048;
+}
+// Few rows: a CTA of the finish kernel takes one row, so that a row the warp path leaves does not
+// wait for its neighbours.
+static int finish_rows_per_cta(int B) { return B > 2 * kSmCount ? 4 : 1; }
+
 static int table_slots(int max_list) {
   int slots = kGroup;
   while (slots < 2 * max_list && slots < kMaxTableSlots) slots <<= 1;
@@ -38,7 +50,7 @@ static int table_slots(int max_list) {
 extern "C" size_t arcs_sample_workspace_bytes(int32_t B, int32_t V, int32_t masked, int32_t max_list) {
   if (B <= 0 || V <= 0 || max_list < 0) return 0;
   int nseg, seg_len;
-  plan_segments(B, V, &nseg, &seg_len, kItemsPerSm);
+  plan_items(B, V, masked != 0, &nseg, &seg_len);
   return (size_t)B * nseg * (size_t)item_block_bytes(masked != 0, table_slots(max_list));
 }
 
@@ -65,11 +77,12 @@ static int sample_launch(const arcs_sample_args* g, void* stream, cudaEvent_t* e
     return set_error(ARCS_ERR_ARG, "sample_batch: cand_stride must be at least ARCS_KCAP");
 
   SampleDev a;
+  plan_items(g->B, g->V, masked, &a.nseg, &a.seg_len);
+  a.rows_per_cta = finish_rows_per_cta(g->B);
   a.logits = g->logits;
   a.row_stride = g->row_stride;
   a.B = g->B;
   a.V = g->V;
-  plan_segments(g->B, g->V, &a.nseg, &a.seg_len, kItemsPerSm);
   a.params = g->params;
   a.hist_off = g->hist_off;
   a.hist_ids = g->hist_ids;
@@ -124,7 +137,7 @@ static int sample_launch(const arcs_sample_args* g, void* stream, cudaEvent_t* e
     if (events) cudaEventRecord(events[0], st);                                                                    \
     stream_kernel<T, M><<<grid_s, kThreadsS, smem_s, st>>>(a);                                                     \
     if (events) cudaEventRecord(events[1], st);                                                                    \
-    const cudaError_t e = launch_dependent(finish_kernel<T, M, kFinishThreads>, (unsigned)(M ? a.B : (a.B + 3) / 4), kFinishThreads, 0, st, a, events == nullptr); \
+    const cudaError_t e = launch_dependent(finish_kernel<T, M, kFinishThreads>, (unsigned)(M ? a.B : (a.B + a.rows_per_cta - 1) / a.rows_per_cta), kFinishThreads, 0, st, a, events == nullptr); \
     if (e != cudaSuccess) return set_error(ARCS_ERR_CUDA, cudaGetErrorString(e));                                  \
     if (events) cudaEventRecord(events[2], st);                                                                    \
   } while (0)
@@ -188,6 +201,7 @@ extern "C" int arcs_merge_batch(const arcs_merge_args* g, void* stream) {
   a.merge_id = g->cand_id;
   a.merge_val = g->cand_val;
   a.merge_n = g->n_cand;
+  a.rows_per_cta = 4;
   finish_kernel<float, false, kFinishThreads><<<(unsigned)((g->B + 3) / 4), kFinishThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return check_launch("merge_batch");
 }

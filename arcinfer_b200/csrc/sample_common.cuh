@@ -21,7 +21,7 @@ constexpr uint32_t kTch = 1u << 29, kOkB = 1u << 30;
 constexpr int kCapB = 1024;   // finish kernel's candidate buffer: prune trigger + one round of pushes
 constexpr int kCapA = 1280;   // ... for the constrained head select (k = 512): trigger 768 + four rounds of 128
 constexpr int kListB = 4096;  // survivors of the stream an item's block holds: selection proper (typically k * (1 + ln(V / 4096)))
-constexpr int kListA = 4096;  // ... constrained head ranking
+constexpr int kListA = 8192;  // ... constrained head ranking
 constexpr uint32_t kEmpty = 0xFFFFFFFFu;
 // per touched token: occurrences in the history (low 20 bits) and what applies to it
 constexpr uint32_t kInfoCount = 0xFFFFFu, kInfoWindow = 1u << 31, kInfoBias = 1u << 30, kInfoBan = 1u << 29;
@@ -63,6 +63,7 @@ struct SampleDev {
   const int32_t* merge_id;   // [G][B][merge_stride] global ids, best first
   const float* merge_val;    // [G][B][merge_stride] adjusted logits
   const int32_t* merge_n;    // [G][B] entries per list
+  int32_t rows_per_cta;      // finish kernel without a mask: rows a CTA takes, one a warp (4; 1 when the rows are few)
 };
 
 // ---- geometry of the stream (shared with the preparing warps, which count the listed columns

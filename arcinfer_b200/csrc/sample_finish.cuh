@@ -2,7 +2,8 @@
 //
 // It runs beside the stream kernel: a row is taken when that kernel has released every item of
 // it. The common case of a row is finished by one warp (sample_finish_warp.cuh), four rows to a
-// CTA; what follows here is the general path, which all threads of the CTA walk together for a
+// CTA, or by all warps of a CTA together when the rows are few (a row is then cut into many
+// segments, whose lists all have to be merged); what follows here is the general path, which all threads of the CTA walk together for a
 // row the warp path left (an allowed-token mask, many candidates, lists that overflowed): it merges what the preparing warps supplied (touched
 // tokens with their adjusted logits, elements outside the aligned body) with what the scanners
 // kept, for every segment of the row, selects the k best under (value desc, id asc), and then
@@ -41,17 +42,21 @@ __global__ void __launch_bounds__(G, 5) finish_kernel(const SampleDev a) {  // (
   const int32_t Vg = a.v_global > 0 ? a.v_global : a.V;
   const bool merging = a.merge_G > 0;
   // ---- rows of this CTA: the warp path first, every warp its own row
-  constexpr int kRows = MASKED ? 1 : G / 32;
+  const int kRows = MASKED ? 1 : a.rows_per_cta;  // (at most G / 32)
   static_assert(G == 128 && kStage * 4 >= (int)sizeof(FastScratch) && kCapB * 4 >= (int)sizeof(FastScratch), "the warps' scratch lies in four of the arrays above");
   __shared__ int row_rc[G / 32];
   const int b_first = (int)blockIdx.x * kRows;
   if (!MASKED) {
     const int w = gt >> 5, bw = b_first + w;
     int rc = kFastSlow;
-    if (bw >= a.B) rc = kFastDone;
-    else if (!merging) {
+    if (kRows == 1) {  // few rows: the whole CTA on one
+      if (!merging) rc = finish_row_fast<T, G>(a, b_first, *reinterpret_cast<FastScratch*>(fl_key), hist);
+      if (w > 0) rc = kFastDone;
+    } else if (w >= kRows || bw >= a.B) {
+      rc = kFastDone;
+    } else if (!merging) {
       void* scratch = w == 0 ? (void*)fl_key : w == 1 ? (void*)fl_id : w == 2 ? (void*)fl_cnt : (void*)bkey;
-      rc = finish_row_warp<T>(a, bw, *reinterpret_cast<FastScratch*>(scratch));
+      rc = finish_row_fast<T, 32>(a, bw, *reinterpret_cast<FastScratch*>(scratch), nullptr);
     }
     if ((gt & 31) == 0) row_rc[w] = rc;
     __syncthreads();

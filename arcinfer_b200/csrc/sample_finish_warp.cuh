@@ -1,12 +1,13 @@
-// finish_row_warp: the common case of the finish step, one warp per row.
+// finish_row_fast: the common case of the finish step, one warp per row (or, when the rows are
+// few, one CTA per row).
 //
 // A row whose candidates fit a warp's hands - no allowed-token mask, at most 64 candidates kept,
-// at most 128 survivors above the stream's last threshold, at most 32 flagged entries, no list of
-// the stream overflowed - is finished by one warp without a CTA-wide barrier: the survivors at or
-// above the threshold are gathered, the flagged ones settled against the history and bias lists
-// (tools/sampler.h:154-174), the rest ranked by counting, and tools/sampler.h:54-77 followed to
-// the letter (fp64 softmax in candidate order, min-p / top-p cuts, the draw). Four such rows
-// share a CTA of the finish kernel. Any other row is left to the CTA-wide path.
+// at most 256 survivors above the last threshold, at most 32 flagged entries, at most 32
+// segments, no list of the stream overflowed - is finished without the CTA-wide selection: the
+// survivors above the threshold are gathered, the flagged ones settled against the history and
+// bias lists (tools/sampler.h:154-174), the rest ranked by counting, and tools/sampler.h:54-77
+// followed to the letter (fp64 softmax in candidate order, min-p / top-p cuts, the draw). Any
+// other row is left to the CTA-wide path of the finish kernel.
 #pragma once
 #include "sample_common.cuh"
 
@@ -14,7 +15,7 @@ namespace arcs {
 
 
 constexpr int kFastK = 64;      // most candidates a row may keep on this path
-constexpr int kFastBuf = 128;   // most survivors above the last threshold
+constexpr int kFastBuf = 256;   // most survivors above the last threshold
 constexpr int kFastFlag = 32;   // most flagged entries
 constexpr uint32_t kFlagWaitLimit = 1u << 21;  // bounded wait for an item's release (about a second)
 
@@ -62,6 +63,9 @@ struct FastScratch {
   double spr[kFastK + 1];
   uint32_t fkey[kFastFlag];
   int32_t fid[kFastFlag];   // (global id | kOkB)
+  int32_t loff[66];         // where each of the row's lists (two a segment) begins in the row's run of entries
+  unsigned long long tau;   // the threshold the survivors must exceed
+  int32_t rc, m, nf, spill, kB;
 };
 static_assert(sizeof(FastScratch) <= 4096, "a warp's scratch fits one of the CTA-wide path's 4 KB arrays");
 
@@ -71,145 +75,267 @@ struct IntTag {
   static constexpr int value = N;
 };
 
-template <typename T>
-__device__ __noinline__ int finish_row_warp(const SampleDev& a, int b, FastScratch& fs) {
+// NT threads finish row b: one warp (NT == 32, four rows to a CTA), or the whole CTA (NT == 128)
+// when the rows are few, which are then cut into many segments with as many loose thresholds:
+// the entries are read by all threads, the threshold is tightened from a count of the entries by
+// the upper 16 bits of their keys (bins: 256 counters, NT == 128 only) before the survivors are
+// kept, and the survivors are ranked by all threads. What one warp can do (settings, headers,
+// flagged entries, softmax, cuts, draw) the first warp does. Every thread returns the same code
+// up to the last barrier.
+template <typename T, int NT>
+__device__ __noinline__ int finish_row_fast(const SampleDev& a, int b, FastScratch& fs, uint32_t* bins) {
+  static_assert(NT == 32 || NT == 128, "one warp or the CTA");
   const int lane = threadIdx.x & 31;
+  const int tid = NT == 32 ? lane : (int)threadIdx.x;
+  const bool lead = NT == 32 || threadIdx.x < 32;
+  auto bar = [&]() {
+    if (NT == 32) __syncwarp();
+    else __syncthreads();
+  };
   // ---- the row's settings and, if it is short, its history: fetched before the row's items are
   // waited for (a CTA of the last rows sits here while the stream kernel runs)
-  const RowCfg r = row_cfg<false>(a, b);
+  RowCfg r;
   constexpr int HR = 16;
   int32_t hreg[HR];
-  const bool hist_in_regs = r.pen_on && r.lists_ok && r.H <= 32 * HR;
+  bool hist_in_regs = false, bans = false;
+  if (lead) {
+    r = row_cfg<false>(a, b);
+    hist_in_regs = r.pen_on && r.lists_ok && r.H <= 32 * HR;
 #pragma unroll
-  for (int x = 0; x < HR; ++x) hreg[x] = hist_in_regs && x * 32 + lane < r.H ? __ldg(&a.hist_ids[r.h0 + x * 32 + lane]) : -1;
-  // ---- the row's items: released by the stream kernel (bounded wait), their headers
-  unsigned long long tau = 0ull;
-  bool bans = false, over = false, late = false;
-  int n0_mine = 0, n1_mine = 0;  // (lane g: the list lengths of segment g, for rows of at most 32 segments)
-  for (int g = lane; g < a.nseg; g += 32) {
-    const ItemHdr* hd = item_ws(a, b * a.nseg + g).hdr;
-    uint32_t spins = 0;
-    while (ld_acquire_gpu(&hd->streamed) == 0) {
-      if (++spins > kFlagWaitLimit) {
-        late = true;
-        break;
+    for (int x = 0; x < HR; ++x) hreg[x] = hist_in_regs && x * 32 + lane < r.H ? __ldg(&a.hist_ids[r.h0 + x * 32 + lane]) : -1;
+    // ---- the row's items: released by the stream kernel (bounded wait), their headers
+    unsigned long long tau = 0ull;
+    bool over = false, late = false;
+    int c0 = 0, c1 = 0;  // (lane g: the list lengths of segment g, for rows of at most 32 segments)
+    for (int g = lane; g < a.nseg; g += 32) {
+      const ItemHdr* hd = item_ws(a, b * a.nseg + g).hdr;
+      uint32_t spins = 0;
+      while (ld_acquire_gpu(&hd->streamed) == 0) {
+        if (++spins > kFlagWaitLimit) {
+          late = true;
+          break;
+        }
+        __nanosleep(spins < 64 ? 100 : 400);
       }
-      __nanosleep(spins < 64 ? 100 : 400);
+      const int n0 = __ldcg(&hd->n_pre), nt = __ldcg(&hd->n_tch), n1 = __ldcg(&hd->n_candB);
+      over = over || n1 > kListB || nt > item_pre_cap(a.hash_slots) - n0;
+      bans = bans || __ldcg(&hd->bans) != 0;
+      const unsigned long long t = __ldcg(&hd->tauB);
+      tau = t > tau ? t : tau;
+      c0 = n0 + nt;
+      c1 = n1;
     }
-    const int n0 = __ldcg(&hd->n_pre), nt = __ldcg(&hd->n_tch), n1 = __ldcg(&hd->n_candB);
-    over = over || n1 > kListB || nt > item_pre_cap(a.hash_slots) - n0;
-    bans = bans || __ldcg(&hd->bans) != 0;
-    const unsigned long long t = __ldcg(&hd->tauB);
-    tau = t > tau ? t : tau;
-    n0_mine = n0 + nt;
-    n1_mine = n1;
+    __syncwarp();  // (the lanes that waited have acquired the items' lists for the whole warp)
+    int rc = kFastDone;
+    if (r.kB > kFastK || a.nseg > 32) rc = kFastSlow;
+    else if (__any_sync(0xFFFFFFFFu, late)) rc = kFastLate;
+    else if (__any_sync(0xFFFFFFFFu, over)) rc = kFastSlow;
+    tau = warp_max_u64(tau);
+    bans = __any_sync(0xFFFFFFFFu, bans);
+    // The row's lists (two a segment: what the preparing warps supplied with the flagged entries
+    // behind it, and the scanners' survivors) are read as one run of entries: where each begins
+    if (a.nseg > 32) c0 = c1 = 0;
+    int inc = c0 + c1;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int t = __shfl_up_sync(0xFFFFFFFFu, inc, d);
+      if (lane >= d) inc += t;
+    }
+    if (lane < a.nseg) {
+      fs.loff[2 * lane] = inc - c0 - c1;
+      fs.loff[2 * lane + 1] = inc - c1;
+    }
+    if (lane == 31) fs.loff[2 * min(a.nseg, 32)] = inc;
+    if (lane == 0) {
+      fs.rc = rc;
+      fs.tau = tau;
+      fs.m = 0;
+      fs.nf = 0;
+      fs.spill = 0;
+      fs.kB = r.kB;
+    }
   }
-  __syncwarp();  // (the lanes that waited have acquired the items' lists for the whole warp)
-  if (r.kB > kFastK || a.nseg > 32) return kFastSlow;
-  if (__any_sync(0xFFFFFFFFu, late)) return kFastLate;
-  if (__any_sync(0xFFFFFFFFu, over)) return kFastSlow;
-  tau = warp_max_u64(tau);
-  bans = __any_sync(0xFFFFFFFFu, bans);
-  // ---- gather: survivors above the threshold to the buffer, flagged entries to their stage
-  int m = 0, nf = 0;  // (warp-uniform counts)
-  bool spill = false;
-  auto gather = [&](const unsigned long long* list, int n) {
-    constexpr int R = 8;  // entries a lane fetches together: one trip to memory for 256 entries
-    for (int i0 = 0; i0 < n && !spill; i0 += R * 32) {
+  bar();
+  if (fs.rc != kFastDone) return fs.rc;
+  const int nl = 2 * a.nseg, total = fs.loff[nl];
+  // entry f of the run. A thread's entries come in rising order: the list it stands in (its
+  // entries as if the run began at base[0]) is kept from one entry to the next.
+  struct Cursor {
+    const unsigned long long* base = nullptr;
+    int end = 0, lst = -1;
+  };
+  auto entry = [&](int f, Cursor& c) {
+    while (f >= c.end) {  // (f < total == loff[nl]: the walk ends inside the table)
+      ++c.lst;
+      c.end = fs.loff[c.lst + 1];
+      const ItemWs w = item_ws(a, b * a.nseg + (c.lst >> 1));
+      c.base = ((c.lst & 1) ? w.candB : w.pre) - fs.loff[c.lst];
+    }
+    return __ldcg(c.base + f);
+  };
+  constexpr int R = 8;  // entries a thread fetches together: one trip to memory for R * NT entries
+  // ---- many entries (NT == 128): a tighter threshold first, read off the counts of the entries by
+  // the upper 16 bits of their keys, as the stream kernel does for its own (flagged entries count
+  // for nothing: what they are worth is not known yet)
+  if (NT == 128 && total > kFastBuf) {
+    for (int i = tid; i < 256; i += NT) bins[i] = 0u;
+    bar();
+    const unsigned long long tau0 = fs.tau;
+    const uint32_t base = (uint32_t)(tau0 >> 48);
+    Cursor lst;
+    for (int i0 = 0; i0 < total; i0 += R * NT) {
       unsigned long long e[R];
 #pragma unroll
-      for (int x = 0; x < R; ++x) e[x] = i0 + x * 32 + lane < n ? __ldcg(&list[i0 + x * 32 + lane]) : 0ull;
+      for (int x = 0; x < R; ++x) {
+        const int f = i0 + x * NT + tid;
+        e[x] = f < total ? entry(f, lst) : 0ull;
+      }
 #pragma unroll
       for (int x = 0; x < R; ++x) {
-        if (i0 + x * 32 >= n) break;
-        const bool p = i0 + x * 32 + lane < n;
+        const uint32_t ky = (uint32_t)e[x], y = (uint32_t)(e[x] >> 32);
+        if (i0 + x * NT + tid < total && !(y & kTch) && (y & kOkB) && comp_of(ky, (int32_t)(y & kIdMask)) > tau0)
+          sm_red_add(&bins[min((ky >> 16) - base, 255u)], 1u);
+      }
+    }
+    bar();
+    if (lead) {
+      int d, kr;
+      bool ex;
+      find_bin(bins, fs.kB, d, kr, ex);
+      if (d > 0 && lane == 0) {
+        const unsigned long long t = (unsigned long long)((base + (uint32_t)d) << 16) << 32;
+        if (t > fs.tau) fs.tau = t;
+      }
+    }
+    bar();
+  }
+  // ---- gather: survivors above the threshold to the buffer, flagged entries to their stage (in
+  // any order: the ranking below does not depend on it)
+  {
+    const unsigned long long tau = fs.tau;
+    Cursor lst;
+    int m_w = 0, nf_w = 0;
+    for (int i0 = 0; i0 < total; i0 += R * NT) {
+      unsigned long long e[R];
+#pragma unroll
+      for (int x = 0; x < R; ++x) {
+        const int f = i0 + x * NT + tid;
+        e[x] = f < total ? entry(f, lst) : 0ull;
+      }
+#pragma unroll
+      for (int x = 0; x < R; ++x) {
+        if (i0 + x * NT >= total) break;
+        const bool p = i0 + x * NT + tid < total;
         const uint32_t ky = (uint32_t)e[x], y = (uint32_t)(e[x] >> 32);
         const int32_t id = (int32_t)(y & kIdMask);
         const bool fl = p && (y & kTch);
         const uint64_t cm = comp_of(ky, id);
         const bool keep = p && !fl && (y & kOkB) && cm > tau;
         const unsigned bk = __ballot_sync(0xFFFFFFFFu, keep), bf = __ballot_sync(0xFFFFFFFFu, fl);
-        if (m + __popc(bk) > kFastBuf || nf + __popc(bf) > kFastFlag) {
-          spill = true;
-          break;
+        // (one warp counts in registers; the warps of a CTA draw their places from the shared counters)
+        int atk = m_w + __popc(bk & ((1u << lane) - 1u)), atf = nf_w + __popc(bf & ((1u << lane) - 1u));
+        if (NT != 32) {
+          const int lk = __ffs(bk) - 1, lf = __ffs(bf) - 1;
+          int bk0 = 0, bf0 = 0;
+          if (bk && lane == lk) bk0 = (int)sm_atomic_add(&fs.m, (uint32_t)__popc(bk));
+          if (bf && lane == lf) bf0 = (int)sm_atomic_add(&fs.nf, (uint32_t)__popc(bf));
+          if (bk) atk += __shfl_sync(0xFFFFFFFFu, bk0, lk);
+          if (bf) atf += __shfl_sync(0xFFFFFFFFu, bf0, lf);
+        } else {
+          m_w += __popc(bk);
+          nf_w += __popc(bf);
         }
-        if (keep) fs.buf[m + __popc(bk & ((1u << lane) - 1u))] = cm;
+        if (keep) {
+          if (atk < kFastBuf) fs.buf[atk] = cm;
+          else fs.spill = 1;
+        }
         if (fl) {
-          const int pos = nf + __popc(bf & ((1u << lane) - 1u));
-          fs.fkey[pos] = ky;
-          fs.fid[pos] = (int32_t)(y & (kIdMask | kOkB));
+          if (atf < kFastFlag) {
+            fs.fkey[atf] = ky;
+            fs.fid[atf] = (int32_t)(y & (kIdMask | kOkB));
+          } else {
+            fs.spill = 1;
+          }
         }
-        m += __popc(bk);
-        nf += __popc(bf);
       }
     }
-  };
-  for (int g = 0; g < a.nseg && !spill; ++g) {
-    const ItemWs w = item_ws(a, b * a.nseg + g);
-    gather(w.pre, __shfl_sync(0xFFFFFFFFu, n0_mine, g));
-    gather(w.candB, __shfl_sync(0xFFFFFFFFu, n1_mine, g));
+    if (NT == 32 && lane == 0) {
+      fs.m = m_w;
+      fs.nf = nf_w;
+    }
   }
-  if (spill) return kFastSlow;
-  __syncwarp();
+  bar();
+  if (fs.spill) return kFastSlow;
   // ---- settle the flagged entries (tools/sampler.h:154-174 for them): one in the bias list was
   // evaluated by the preparing warps and is dropped here; one in the history is dropped too when
   // they evaluated the history (table mode), else penalised here; one the filter flagged by
   // accident is an ordinary element.
-  if (nf > 0) {
-    const int32_t w0 = window_start(r);
-    for (int f = 0; f < nf; ++f) {
-      const int32_t idf = fs.fid[f] & (int32_t)kIdMask;
-      int cnt = 0;
-      bool win = false, inbias = false;
-      for (int i = lane; i < r.NB; i += 32) inbias = inbias || a.bias_ids[r.q0 + i] == idf;
-      if (r.pen_on) {
-        if (hist_in_regs) {
+  if (fs.nf > 0) {
+    if (lead) {
+      const unsigned long long tau = fs.tau;
+      const int nf = fs.nf;
+      int m = fs.m;
+      const int32_t w0 = window_start(r);
+      for (int f = 0; f < nf; ++f) {
+        const int32_t idf = fs.fid[f] & (int32_t)kIdMask;
+        int cnt = 0;
+        bool win = false, inbias = false;
+        for (int i = lane; i < r.NB; i += 32) inbias = inbias || a.bias_ids[r.q0 + i] == idf;
+        if (r.pen_on) {
+          if (hist_in_regs) {
 #pragma unroll
-          for (int x = 0; x < HR; ++x)
-            if (hreg[x] == idf) {
-              ++cnt;
-              win = win || x * 32 + lane >= w0;
-            }
-        } else {
-          for (int i = lane; i < r.H; i += 32)
-            if (__ldg(&a.hist_ids[r.h0 + i]) == idf) {
-              ++cnt;
-              win = win || i >= w0;
-            }
+            for (int x = 0; x < HR; ++x)
+              if (hreg[x] == idf) {
+                ++cnt;
+                win = win || x * 32 + lane >= w0;
+              }
+          } else {
+            for (int i = lane; i < r.H; i += 32)
+              if (__ldg(&a.hist_ids[r.h0 + i]) == idf) {
+                ++cnt;
+                win = win || i >= w0;
+              }
+          }
+        }
+        cnt = (int)__reduce_add_sync(0xFFFFFFFFu, (unsigned)cnt);
+        win = __any_sync(0xFFFFFFFFu, win);
+        inbias = __any_sync(0xFFFFFFFFu, inbias);
+        uint32_t ky = fs.fkey[f];
+        bool p = !inbias && (fs.fid[f] & (int32_t)kOkB) != 0;
+        if (p && cnt > 0) {
+          if (r.touch == kTouchTable) {
+            p = false;
+          } else {
+            ky = key_of(penalise(r, value_of(ky), (uint32_t)cnt, w0 == 0 || win));
+            p = ky != 0u;
+          }
+        }
+        const uint64_t cm = comp_of(ky, idf);
+        p = p && cm > tau;
+        if (p) {  // (warp-uniform: every lane computed the same)
+          if (m >= kFastBuf) {
+            if (lane == 0) fs.spill = 1;
+            break;
+          }
+          if (lane == 0) fs.buf[m] = cm;
+          ++m;
         }
       }
-      cnt = (int)__reduce_add_sync(0xFFFFFFFFu, (unsigned)cnt);
-      win = __any_sync(0xFFFFFFFFu, win);
-      inbias = __any_sync(0xFFFFFFFFu, inbias);
-      uint32_t ky = fs.fkey[f];
-      bool p = !inbias && (fs.fid[f] & (int32_t)kOkB) != 0;
-      if (p && cnt > 0) {
-        if (r.touch == kTouchTable) {
-          p = false;
-        } else {
-          ky = key_of(penalise(r, value_of(ky), (uint32_t)cnt, w0 == 0 || win));
-          p = ky != 0u;
-        }
-      }
-      const uint64_t cm = comp_of(ky, idf);
-      p = p && cm > tau;
-      if (p) {
-        if (m >= kFastBuf) return kFastSlow;  // (warp-uniform: every lane computed the same)
-        if (lane == 0) fs.buf[m] = cm;
-        ++m;
-      }
+      if (lane == 0) fs.m = m;
     }
-    __syncwarp();
+    bar();
+    if (fs.spill) return kFastSlow;
   }
   // ---- candidates best first: ranked by counting (composites are unique)
-  const int nB = min(m, r.kB);
+  const int m = fs.m;
+  const int nB = min(m, fs.kB);
   auto rank_all = [&](auto per_tag) {
     constexpr int PER = decltype(per_tag)::value;
     unsigned long long mine[PER];
     int rank[PER];
 #pragma unroll
     for (int x = 0; x < PER; ++x) {
-      mine[x] = x * 32 + lane < m ? fs.buf[x * 32 + lane] : 0ull;
+      mine[x] = x * NT + tid < m ? fs.buf[x * NT + tid] : 0ull;
       rank[x] = 0;
     }
 #pragma unroll 4
@@ -220,14 +346,17 @@ __device__ __noinline__ int finish_row_warp(const SampleDev& a, int b, FastScrat
     }
 #pragma unroll
     for (int x = 0; x < PER; ++x)
-      if (x * 32 + lane < m && rank[x] < nB) {
+      if (x * NT + tid < m && rank[x] < nB) {
         fs.sv[rank[x]] = value_of(comp_key(mine[x]));
         fs.sid[rank[x]] = comp_id(mine[x]);
       }
   };
-  if (m <= 64) rank_all(IntTag<2>{});
+  if (NT == 128) rank_all(IntTag<kFastBuf / 128>{});
+  else if (m <= 64) rank_all(IntTag<2>{});
+  else if (m <= 128) rank_all(IntTag<4>{});
   else rank_all(IntTag<kFastBuf / 32>{});
-  __syncwarp();
+  bar();
+  if (!lead) return kFastDone;  // (the rest is one warp's work)
   // ---- tools/sampler.h:54-77
   int nc = nB;
   if (bans)  // :54-55 (every lane walks the same few steps)

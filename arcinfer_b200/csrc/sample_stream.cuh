@@ -99,6 +99,16 @@ struct ScanCtx {
 // The chunks a scanner warp has set aside are examined one per lane (q: the lane's chunk, g0: global
 // id of its first element, have: the lane has one): a float compare finds the (usually single)
 // element that reaches the threshold, then those elements go through the exact test together.
+// The threshold of the constrained head ranking as the scanners apply it. The head (the 512 best
+// of all tokens, tools/sampler.h:93-103) decides two things: whether the best token was refused,
+// and, when fewer than k allowed tokens lie inside it, where rank 512 is (:106-116). Both are
+// settled by the elements above the k-th best ALLOWED token, and the selection's own threshold
+// never exceeds that token: nothing at or below it need be listed, unless the caller wants the
+// head itself.
+__device__ __forceinline__ uint64_t tau_a_of(uint64_t tauA, uint64_t tauB, bool full_head) {
+  return full_head || tauA > tauB ? tauA : tauB;
+}
+
 template <typename T, bool MASKED>
 __device__ __forceinline__ void scan_examine(const ScanCtx& c, bool have, uint4 q, int32_t g0) {
   constexpr int E = Elem<T>::kPerChunk;
@@ -285,6 +295,7 @@ __global__ void __launch_bounds__(kRegBoundThreads, 1) stream_kernel(const Sampl
 
   constexpr int E = Elem<T>::kPerChunk;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const bool full_head = MASKED && a.head_id != nullptr;  // (the caller wants the ranked head itself: every one of its 512 entries is listed)
   const int n_items = a.B * a.nseg;
   const int my_n = (n_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
 
@@ -395,7 +406,7 @@ __global__ void __launch_bounds__(kRegBoundThreads, 1) stream_kernel(const Sampl
       // examine everything the warp has set aside, against the thresholds of this moment
       auto flush = [&]() {
         ctx.tcB = v64[L_TAU_B + st];
-        ctx.tcA = MASKED ? v64[L_TAU_A + st] : 0xFFFFFFFFFFFFFFFFull;
+        ctx.tcA = MASKED ? tau_a_of(v64[L_TAU_A + st], ctx.tcB, full_head) : 0xFFFFFFFFFFFFFFFFull;
 #pragma unroll 1
         for (int sl = 0; sl < kPend; ++sl) {
           const bool mine = have > sl;
@@ -438,7 +449,7 @@ __global__ void __launch_bounds__(kRegBoundThreads, 1) stream_kernel(const Sampl
         typename Elem<T>::Thr thB, thA;
         auto refresh = [&]() {
           tcB = v64[L_TAU_B + st];
-          tcA = MASKED ? v64[L_TAU_A + st] : 0xFFFFFFFFFFFFFFFFull;
+          tcA = MASKED ? tau_a_of(v64[L_TAU_A + st], tcB, full_head) : 0xFFFFFFFFFFFFFFFFull;
           // chunk-level test on values: inclusive on the threshold's value (ids are settled per element)
           const uint32_t kB32 = (uint32_t)(tcB >> 32), kA32 = (uint32_t)(tcA >> 32);
           thB = Elem<T>::make_thr(value_of(kB32 < 0x007FFFFFu ? 0x007FFFFFu : kB32));
@@ -570,8 +581,32 @@ __global__ void __launch_bounds__(kRegBoundThreads, 1) stream_kernel(const Sampl
         if (booted && d > 0 && lane == 0) sm_red_max_u64(&s64[L_TAU_A + st], (unsigned long long)((baseA + (uint32_t)d) << 16) << 32);
       }
       __syncwarp();
-      const int nB = vsh[S_CNT + 4 * st + 0], nA = vsh[S_CNT + 4 * st + 1], nT = vsh[S_CNT + 4 * st + 2];
+      int nB = vsh[S_CNT + 4 * st + 0];
+      const int nA = vsh[S_CNT + 4 * st + 1], nT = vsh[S_CNT + 4 * st + 2];
       const int n_pre = hd->n_pre;
+      if (!MASKED && a.nseg > 1 && nB <= kListB) {
+        // A row cut into segments: the finish kernel has to merge every segment's list, most of
+        // which was written under the item's first, loose thresholds. The list is cut here to
+        // the entries above the item's last threshold (in place: a round's entries are all read
+        // before any is written, to places at or before the round's first).
+        const unsigned long long tau = v64[L_TAU_B + st];
+        int kept = 0;
+        for (int i0 = 0; i0 < nB; i0 += 8 * 32) {
+          unsigned long long e[8];
+#pragma unroll
+          for (int x = 0; x < 8; ++x) e[x] = i0 + x * 32 + lane < nB ? __ldcg(&w.candB[i0 + x * 32 + lane]) : 0ull;
+#pragma unroll
+          for (int x = 0; x < 8; ++x) {
+            const uint32_t ky = (uint32_t)e[x], y = (uint32_t)(e[x] >> 32);
+            const bool keep = i0 + x * 32 + lane < nB && comp_of(ky, (int32_t)(y & kIdMask)) > tau;
+            const unsigned bk = __ballot_sync(0xFFFFFFFFu, keep);
+            if (keep) w.candB[kept + __popc(bk & ((1u << lane) - 1u))] = e[x];
+            kept += __popc(bk);
+          }
+        }
+        nB = kept;
+        __syncwarp();
+      }
       if (nB > kListB || nA > kListA || nT > item_pre_cap(a.hash_slots) - n_pre) {
         // a list overflowed: the finish kernel will read the item again and needs its filter
         const uint32_t* bl = tab_bloom(st);

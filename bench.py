@@ -231,11 +231,16 @@ def bench_small(args):
             launches_per_step = 3
             extra_bytes += c["bytes"].nbytes + c["byte_off"].nbytes + c["table"].nbytes + len(states) * ((V + 31) // 32) * 4
 
+            # the argument blocks are built once (a caller that decodes step after step does the same)
+            m_dev = ab.dfa_mask(tab, c["dead"], st_dev, off_dev, by_dev, V=V)
+            plan = ab.capi.SamplePlan(lg, p_dev, u, mask=m_dev, mask_row=mrow, **kw)
+
             def step():  # the mask of every distinct automaton state, then the constrained selection
-                m = ab.dfa_mask(tab, c["dead"], st_dev, off_dev, by_dev, V=V)
-                return ab.sample_batch(lg, p_dev, u, mask=m, mask_row=mrow, **kw)
+                ab.dfa_mask(tab, c["dead"], st_dev, off_dev, by_dev, V=V, out=m_dev)
+                return plan.launch()
         else:
-            step = lambda: ab.sample_batch(lg, p_dev, u, **kw)
+            plan = ab.capi.SamplePlan(lg, p_dev, u, **kw)
+            step = plan.launch
         kernel = "stream_kernel"
     for _ in range(max(args.warmup, 5)):
         out = step()

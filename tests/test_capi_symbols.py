@@ -30,7 +30,8 @@ def test_argument_checks_need_no_device():
     lp = ab.capi.LogprobArgs()
     assert ab.lib.arcs_logprobs_batch(C.byref(lp), None) == 1
     assert ab.lib.arcs_sample_workspace_bytes(1024, 262144, 0, 0) >= 1024 * 4
-    assert ab.lib.arcs_sample_workspace_bytes(8, 262144, 1, 0) > ab.lib.arcs_sample_workspace_bytes(8, 262144, 0, 0)
+    # (many rows: one block a row either way, a masked one with the head ranking's list on top)
+    assert ab.lib.arcs_sample_workspace_bytes(1024, 262144, 1, 0) > ab.lib.arcs_sample_workspace_bytes(1024, 262144, 0, 0)
     assert ab.lib.arcs_sample_workspace_bytes(8, 262144, 0, 512) > ab.lib.arcs_sample_workspace_bytes(8, 262144, 0, 0)
 
 
