@@ -402,7 +402,6 @@ __global__ void __launch_bounds__(kRegBoundThreads, 1) stream_kernel(const Sampl
       ctx.listT = w.pre + hd->n_pre;  // (right behind the preparing warps' entries)
       ctx.roomT = item_pre_cap(a.hash_slots) - hd->n_pre;
       ctx.id_base = a.id_base;
-      const uint32_t* mrow = ctx.mrow;
       // examine everything the warp has set aside, against the thresholds of this moment
       auto flush = [&]() {
         ctx.tcB = v64[L_TAU_B + st];
@@ -465,12 +464,11 @@ __global__ void __launch_bounds__(kRegBoundThreads, 1) stream_kernel(const Sampl
 #pragma unroll
           for (int u = 0; u < kU; ++u) {
             const int ci = c0 + u * 32 + lane;
+            // (with a mask, whether the chunk's hot element is an allowed one is asked when the
+            //  chunk is examined, for all the chunks a warp has set aside at once: a look at the
+            //  mask here would stall the scan for a trip to memory at every hot chunk)
             bool h = Elem<T>::chunk_reaches(q[u], thB);
-            if (MASKED) {
-              bool hb = h && ci < nchunk;
-              if (hb) hb = mask_bits_of<E>(mrow, col0 + ci * E) != 0u;
-              h = hb || Elem<T>::chunk_reaches(q[u], thA);
-            }
+            if (MASKED) h = h || Elem<T>::chunk_reaches(q[u], thA);
             if (!whole) h = h && ci < nchunk;
             m |= (h ? 1u : 0u) << u;
           }
