@@ -45,6 +45,7 @@ class SampleArgs(C.Structure):
         ("cand_id", C.c_void_p), ("cand_val", C.c_void_p), ("cand_pr", C.c_void_p), ("cand_stride", C.c_int32),
         ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
         ("head_id", C.c_void_p), ("head_val", C.c_void_p), ("n_head", C.c_void_p),
+        ("cand_width", C.c_int32),
     ]  # fmt: skip
 
 
@@ -75,6 +76,7 @@ class MergeArgs(C.Structure):
         ("token", C.c_void_p), ("n_cand_out", C.c_void_p), ("n_kept", C.c_void_p), ("flags", C.c_void_p),
         ("out_id", C.c_void_p), ("out_val", C.c_void_p), ("out_pr", C.c_void_p), ("out_stride", C.c_int32),
         ("status", C.c_void_p),
+        ("cand_width", C.c_int32), ("shard_mz", C.c_void_p), ("mz_stride", C.c_int32), ("mz_out", C.c_void_p),
     ]
 
 
@@ -143,9 +145,11 @@ def reset_workspaces():
 
 def sample_batch(logits, params, u, hist_off=None, hist_ids=None, bias_off=None, bias_ids=None, bias_vals=None,
                  mask=None, mask_row=None, max_hist=0, max_bias=0, id_base=0, v_global=0, V=None,
-                 want_cands=False, want_head=False, status=None):
+                 want_cands=False, want_head=False, status=None, records=None):
     """arcs_sample_batch on device tensors. logits: [B, >=V] float32/bfloat16 (row stride =
-    logits.stride(0)); params: uint8 tensor holding B arcs_row_params; u: float64 [B]."""
+    logits.stride(0)); params: uint8 tensor holding B arcs_row_params; u: float64 [B].
+    records: an int32 tensor [B, 2k + 2] that receives each row's candidates as a packed record
+    (k ids, k values as bit patterns; the last two words are left to the caller), see pack_width."""
     assert logits.is_cuda and logits.dim() == 2 and logits.stride(1) == 1
     dev = logits.device
     B = logits.shape[0]
@@ -180,6 +184,8 @@ def sample_batch(logits, params, u, hist_off=None, hist_ids=None, bias_off=None,
     if want_cands:
         a.cand_id, a.cand_val, a.cand_pr = out["cand_id"].data_ptr(), out["cand_val"].data_ptr(), out["cand_pr"].data_ptr()
     a.cand_stride = KCAP
+    if records is not None:
+        _point_at_records(a, records)
     if want_head:  # (constrained rows only) the 512 most likely tokens in the order the reference calls its predicate
         out["head_id"] = torch.empty(B, HEAD, dtype=torch.int32, device=dev)
         out["head_val"] = torch.empty(B, HEAD, dtype=torch.float32, device=dev)
@@ -189,6 +195,18 @@ def sample_batch(logits, params, u, hist_off=None, hist_ids=None, bias_off=None,
     a.status = status.data_ptr()
     _check(lib.arcs_sample_batch(C.byref(a), _stream(dev)), "arcs_sample_batch")
     return out
+
+
+def pack_width(records):
+    """k of a record tensor [.., 2k + 2]: k ids, k values, (max, sum exp)."""
+    assert records.dtype == torch.int32 and records.shape[-1] % 2 == 0 and records.is_contiguous()
+    return (records.shape[-1] - 2) // 2
+
+
+def _point_at_records(a, records):
+    k = pack_width(records)
+    a.cand_id, a.cand_val, a.cand_pr = records.data_ptr(), records.data_ptr() + 4 * k, None
+    a.cand_stride, a.cand_width = records.shape[-1], k
 
 
 def argmax_batch(logits, V=None, want_lse=False, row_off=None, draft=None, draft_off=None, status=None, static_scratch=False):
@@ -389,14 +407,31 @@ def merge_batch(cand_id, cand_val, n_cand, params, u, v_global, bias_off=None, b
     """arcs_merge_batch: the global choice from the shards' gathered candidate lists.
     cand_id / cand_val: [G, B, stride] int32 / float32; n_cand: [G, B] int32 (device tensors)."""
     G, B, stride = cand_id.shape
-    dev = cand_id.device
+    return _merge(G, B, stride, cand_id.data_ptr(), cand_val.data_ptr(), n_cand.data_ptr(), 0, None, cand_id.device, params, u, v_global,
+                  bias_off, bias_vals, want_cands, status)
+
+
+def merge_records(records, params, u, v_global, bias_off=None, bias_vals=None, want_cands=False, want_mz=False, status=None):
+    """arcs_merge_batch on gathered packed records [G, B, 2k + 2] (int32), read in place: k ids,
+    k values, (max, sum exp) of every shard and row. want_mz: also combine the pairs into out["mz"]."""
+    G, B, stride = records.shape
+    k = pack_width(records)
+    return _merge(G, B, stride, records.data_ptr(), records.data_ptr() + 4 * k, None, k, records.data_ptr() + 8 * k if want_mz else None,
+                  records.device, params, u, v_global, bias_off, bias_vals, want_cands, status)
+
+
+def _merge(G, B, stride, p_id, p_val, p_n, width, p_mz, dev, params, u, v_global, bias_off, bias_vals, want_cands, status):
     out = {k: torch.empty(B, dtype=torch.int32, device=dev) for k in ("token", "n_cand", "n_kept", "flags")}
     if status is None:
         status = torch.zeros(1, dtype=torch.int32, device=dev)
     out["status"] = status
     a = MergeArgs()
     a.G, a.B, a.cand_stride = G, B, stride
-    a.cand_id, a.cand_val, a.n_cand = cand_id.data_ptr(), cand_val.data_ptr(), n_cand.data_ptr()
+    a.cand_id, a.cand_val, a.n_cand = p_id, p_val, p_n
+    a.cand_width = width
+    if p_mz is not None:
+        out["mz"] = torch.empty(B, 2, dtype=torch.float32, device=dev)
+        a.shard_mz, a.mz_stride, a.mz_out = p_mz, stride, out["mz"].data_ptr()
     a.params, a.u = params.data_ptr(), u.data_ptr()
     a.bias_off, a.bias_vals = _ptr(bias_off), _ptr(bias_vals)
     a.v_global = v_global
@@ -417,7 +452,7 @@ class SamplePlan:
     once, launch() only enqueues the kernel (what a serving loop does every step)."""
 
     def __init__(self, logits, params, u, hist_off=None, hist_ids=None, max_hist=0, mask=None, mask_row=None, V=None,
-                 id_base=0, v_global=0, want_cands=False):
+                 id_base=0, v_global=0, want_cands=False, records=None):
         dev = logits.device
         B = logits.shape[0]
         V = logits.shape[1] if V is None else V
@@ -442,6 +477,9 @@ class SamplePlan:
                 self.out[k] = torch.empty(B, KCAP, dtype=dt, device=dev)
             a.cand_id, a.cand_val, a.cand_pr = (self.out[k].data_ptr() for k in ("cand_id", "cand_val", "cand_pr"))
         a.cand_stride = KCAP
+        if records is not None:  # candidates straight into packed records (see sample_batch)
+            _point_at_records(a, records)
+            self.keep += (records,)
         a.workspace, a.workspace_bytes, a.status = self.ws.data_ptr(), self.ws.numel(), self.status.data_ptr()
         self.args = a
 

@@ -73,8 +73,9 @@ static int sample_launch(const arcs_sample_args* g, void* stream, cudaEvent_t* e
     return set_error(ARCS_ERR_ARG, "sample_batch: a mask cannot be combined with a vocabulary shard");
   if ((g->head_id || g->head_val || g->n_head) && !(masked && g->head_id && g->head_val && g->n_head))
     return set_error(ARCS_ERR_ARG, "sample_batch: the ranked head needs a mask and all three of head_id, head_val, n_head");
-  if ((g->cand_id || g->cand_val || g->cand_pr) && g->cand_stride < ARCS_KCAP)
-    return set_error(ARCS_ERR_ARG, "sample_batch: cand_stride must be at least ARCS_KCAP");
+  if ((g->cand_id || g->cand_val || g->cand_pr) &&
+      (g->cand_width < 0 || g->cand_width > ARCS_KCAP || g->cand_stride < (g->cand_width > 0 ? g->cand_width : ARCS_KCAP)))
+    return set_error(ARCS_ERR_ARG, "sample_batch: cand_stride must be at least cand_width (ARCS_KCAP when that is 0)");
 
   SampleDev a;
   plan_items(g->B, g->V, masked, &a.nseg, &a.seg_len);
@@ -110,6 +111,7 @@ static int sample_launch(const arcs_sample_args* g, void* stream, cudaEvent_t* e
   a.cand_val = g->cand_val;
   a.cand_pr = g->cand_pr;
   a.cand_stride = g->cand_stride;
+  a.cand_width = g->cand_width > 0 ? g->cand_width : g->cand_stride;
   a.head_id = g->head_id;
   a.head_val = g->head_val;
   a.n_head = g->n_head;
@@ -121,6 +123,10 @@ static int sample_launch(const arcs_sample_args* g, void* stream, cudaEvent_t* e
   a.merge_id = nullptr;
   a.merge_val = nullptr;
   a.merge_n = nullptr;
+  a.merge_width = 0;
+  a.merge_mz = nullptr;
+  a.merge_mz_stride = 0;
+  a.mz_out = nullptr;
   if (!g->workspace || g->workspace_bytes < arcs_sample_workspace_bytes(g->B, g->V, masked, max_list))
     return set_error(ARCS_ERR_WORKSPACE, "sample_batch: workspace too small");
   if ((reinterpret_cast<uintptr_t>(g->workspace) & 15u) != 0) return set_error(ARCS_ERR_WORKSPACE, "sample_batch: workspace must be 16-byte aligned");
@@ -170,7 +176,8 @@ extern "C" int arcs_sample_batch_timed(const arcs_sample_args* g, void* stream, 
 // ---- vocabulary shards: the global choice from the shards' gathered candidate lists
 extern "C" int arcs_merge_batch(const arcs_merge_args* g, void* stream) {
   if (int inj = fault_injected()) return inj;
-  if (!g || g->G <= 0 || g->G > 64 || g->B <= 0 || g->B > kMaxRows || g->cand_stride <= 0 || !g->cand_id || !g->cand_val || !g->n_cand ||
+  if (!g || g->G <= 0 || g->G > 64 || g->B <= 0 || g->B > kMaxRows || g->cand_stride <= 0 || !g->cand_id || !g->cand_val ||
+      g->cand_width < 0 || g->cand_width > g->cand_stride || (!g->n_cand && g->cand_width == 0) || (g->mz_out && (!g->shard_mz || g->mz_stride < 2)) ||
       !g->params || !g->u || !g->token || g->v_global <= 0 || g->v_global >= (int32_t)kIdMask)
     return set_error(ARCS_ERR_ARG, "merge_batch: bad argument");
   if (g->bias_off && !g->bias_vals) return set_error(ARCS_ERR_ARG, "merge_batch: bias offsets without the values");
@@ -195,12 +202,17 @@ extern "C" int arcs_merge_batch(const arcs_merge_args* g, void* stream) {
   a.cand_val = g->out_val;
   a.cand_pr = g->out_pr;
   a.cand_stride = g->out_stride;
+  a.cand_width = g->out_stride;
   a.status = g->status;
   a.merge_G = g->G;
   a.merge_stride = g->cand_stride;
   a.merge_id = g->cand_id;
   a.merge_val = g->cand_val;
   a.merge_n = g->n_cand;
+  a.merge_width = g->cand_width > 0 ? g->cand_width : g->cand_stride;
+  a.merge_mz = g->shard_mz;
+  a.merge_mz_stride = g->mz_stride;
+  a.mz_out = g->mz_out;
   a.rows_per_cta = 4;
   finish_kernel<float, false, kFinishThreads><<<(unsigned)((g->B + 3) / 4), kFinishThreads, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return check_launch("merge_batch");

@@ -52,6 +52,7 @@ struct SampleDev {
   float* cand_val;
   float* cand_pr;
   int32_t cand_stride;
+  int32_t cand_width;       // entries written per row of the candidate outputs (<= cand_stride)
   int32_t* head_id;         // [B][ARCS_HEAD] ranked head of a constrained row (optional)
   float* head_val;
   int32_t* n_head;
@@ -63,6 +64,10 @@ struct SampleDev {
   const int32_t* merge_id;   // [G][B][merge_stride] global ids, best first
   const float* merge_val;    // [G][B][merge_stride] adjusted logits
   const int32_t* merge_n;    // [G][B] entries per list
+  int32_t merge_width;       // entries per gathered list (<= merge_stride)
+  const float* merge_mz;     // [G][B] (max, sum exp) pairs of the shards, merge_mz_stride floats apart (optional)
+  int32_t merge_mz_stride;
+  float* mz_out;             // [B][2] the pairs combined (optional)
   int32_t rows_per_cta;      // finish kernel without a mask: rows a CTA takes, one a warp (4; 1 when the rows are few)
 };
 

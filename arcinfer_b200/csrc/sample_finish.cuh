@@ -50,11 +50,11 @@ __global__ void __launch_bounds__(G, 5) finish_kernel(const SampleDev a) {  // (
     const int w = gt >> 5, bw = b_first + w;
     int rc = kFastSlow;
     if (kRows == 1) {  // few rows: the whole CTA on one
-      if (!merging) rc = finish_row_fast<T, G>(a, b_first, *reinterpret_cast<FastScratch*>(fl_key), hist);
+      rc = finish_row_fast<T, G>(a, b_first, *reinterpret_cast<FastScratch*>(fl_key), hist);
       if (w > 0) rc = kFastDone;
     } else if (w >= kRows || bw >= a.B) {
       rc = kFastDone;
-    } else if (!merging) {
+    } else {
       void* scratch = w == 0 ? (void*)fl_key : w == 1 ? (void*)fl_id : w == 2 ? (void*)fl_cnt : (void*)bkey;
       rc = finish_row_fast<T, 32>(a, bw, *reinterpret_cast<FastScratch*>(scratch), nullptr);
     }
@@ -117,6 +117,7 @@ __global__ void __launch_bounds__(G, 5) finish_kernel(const SampleDev a) {  // (
   // below the largest threshold a segment's stream ended on can be among the k best: that
   // segment alone holds k above it.
   const RowCfg r = row_cfg<MASKED>(a, b);  // (its loads travel together with the headers')
+  if (merging && gt < 32) combine_mz(a, b);
   if (merging) {  // the banned-tail rule needs to know whether the row's bias list bans anything (tools/sampler.h:34)
     bool any = false;
     for (int i = gt; i < r.NB; i += G) any = any || a.bias_vals[r.q0 + i] <= -100.0f;
@@ -327,14 +328,14 @@ __global__ void __launch_bounds__(G, 5) finish_kernel(const SampleDev a) {  // (
     // the shards' lists: each already holds that shard's k best under the same order
     for (int g = 0; g < a.merge_G; ++g) {
       const size_t row = (size_t)g * a.B + b;
-      const int n = min(__ldg(&a.merge_n[row]), a.merge_stride);
+      const int n = a.merge_n ? min(__ldg(&a.merge_n[row]), a.merge_width) : a.merge_width;  // (without lengths a list ends at its first negative id)
       for (int i0 = 0; i0 < n; i0 += G) {
         const int i = i0 + gt;
         const bool p = i < n;
         const float v = p ? __ldg(&a.merge_val[row * a.merge_stride + i]) : 0.0f;
         const int32_t id = p ? __ldg(&a.merge_id[row * a.merge_stride + i]) : 0;
         const uint32_t ky = key_of(v);
-        sel_push(selB, p && ky != 0u && comp_of(ky, id) > *selB.tau, ky, id, hot, a.status);
+        sel_push(selB, p && id >= 0 && ky != 0u && comp_of(ky, id) > *selB.tau, ky, id, hot, a.status);
         if (careful) after_push();
       }
     }
@@ -499,7 +500,8 @@ __global__ void __launch_bounds__(G, 5) finish_kernel(const SampleDev a) {  // (
   }
   group_sync<2, G>();
   if (gt == 0 && a.flags) a.flags[b] = sh[S_FLAGS];
-  for (int i = gt; i < a.cand_stride && (a.cand_id || a.cand_val || a.cand_pr); i += G) {
+  if (gt == 0 && nc > a.cand_width && (a.cand_id || a.cand_val || a.cand_pr)) raise_status(a.status, ARCS_ERR_TOPK);
+  for (int i = gt; i < a.cand_width && (a.cand_id || a.cand_val || a.cand_pr); i += G) {
     const size_t o = (size_t)b * a.cand_stride + i;
     const bool in = i < nc;
     if (a.cand_id) a.cand_id[o] = in ? sid[i] : -1;

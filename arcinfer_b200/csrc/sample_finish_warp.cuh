@@ -75,6 +75,29 @@ struct IntTag {
   static constexpr int value = N;
 };
 
+// Vocabulary shards: the shards' (max, sum of exp(l - max)) pairs of row b combined by one warp:
+// M = max m_g, Z = sum z_g exp(m_g - M).
+__device__ __forceinline__ void combine_mz(const SampleDev& a, int b) {
+  if (!a.mz_out || !a.merge_mz) return;
+  const int lane = threadIdx.x & 31;
+  float M = -INFINITY;
+  for (int g = lane; g < a.merge_G; g += 32) M = fmaxf(M, __ldg(&a.merge_mz[((size_t)g * a.B + b) * a.merge_mz_stride]));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xFFFFFFFFu, M, o));
+  double Z = 0.0;
+  for (int g = lane; g < a.merge_G; g += 32) {
+    const float* mz = &a.merge_mz[((size_t)g * a.B + b) * a.merge_mz_stride];
+    const float m = __ldg(&mz[0]), z = __ldg(&mz[1]);
+    if (m > -INFINITY) Z += (double)z * exp((double)m - (double)M);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) Z += __shfl_xor_sync(0xFFFFFFFFu, Z, o);
+  if (lane == 0) {
+    a.mz_out[2 * (size_t)b] = M;
+    a.mz_out[2 * (size_t)b + 1] = (float)Z;
+  }
+}
+
 // NT threads finish row b: one warp (NT == 32, four rows to a CTA), or the whole CTA (NT == 128)
 // when the rows are few, which are then cut into many segments with as many loose thresholds:
 // the entries are read by all threads, the threshold is tightened from a count of the entries by
@@ -88,6 +111,7 @@ __device__ __noinline__ int finish_row_fast(const SampleDev& a, int b, FastScrat
   const int lane = threadIdx.x & 31;
   const int tid = NT == 32 ? lane : (int)threadIdx.x;
   const bool lead = NT == 32 || threadIdx.x < 32;
+  const bool merging = a.merge_G > 0;
   auto bar = [&]() {
     if (NT == 32) __syncwarp();
     else __syncthreads();
@@ -107,7 +131,21 @@ __device__ __noinline__ int finish_row_fast(const SampleDev& a, int b, FastScrat
     unsigned long long tau = 0ull;
     bool over = false, late = false;
     int c0 = 0, c1 = 0;  // (lane g: the list lengths of segment g, for rows of at most 32 segments)
-    for (int g = lane; g < a.nseg; g += 32) {
+    if (merging) {
+      // Vocabulary shards: the row's lists are the shards' candidates, each best first. A shard
+      // that sent k entries has k at or above its k-th: nothing below the largest such entry can
+      // be among the k best of all.
+      combine_mz(a, b);
+      for (int i = lane; i < r.NB; i += 32) bans = bans || __ldg(&a.bias_vals[r.q0 + i]) <= ARCS_BANNED;
+      const int kth = r.kB - 1;
+      if (lane < a.merge_G && kth >= 0 && kth < a.merge_width) {
+        const size_t row = ((size_t)lane * a.B + b) * a.merge_stride;
+        const int32_t id = (!a.merge_n || kth < __ldg(&a.merge_n[(size_t)lane * a.B + b])) ? __ldg(&a.merge_id[row + kth]) : -1;
+        const uint32_t ky = key_of(__ldg(&a.merge_val[row + kth]));
+        if (id >= 0 && ky != 0u) tau = comp_of(ky, id) - 1ull;  // (composites are unique: "above tau" keeps the k-th itself)
+      }
+    }
+    for (int g = lane; g < a.nseg && !merging; g += 32) {
       const ItemHdr* hd = item_ws(a, b * a.nseg + g).hdr;
       uint32_t spins = 0;
       while (ld_acquire_gpu(&hd->streamed) == 0) {
@@ -127,7 +165,7 @@ __device__ __noinline__ int finish_row_fast(const SampleDev& a, int b, FastScrat
     }
     __syncwarp();  // (the lanes that waited have acquired the items' lists for the whole warp)
     int rc = kFastDone;
-    if (r.kB > kFastK || a.nseg > 32) rc = kFastSlow;
+    if (r.kB > kFastK || a.nseg > 32 || a.merge_G > 32) rc = kFastSlow;
     else if (__any_sync(0xFFFFFFFFu, late)) rc = kFastLate;
     else if (__any_sync(0xFFFFFFFFu, over)) rc = kFastSlow;
     tau = warp_max_u64(tau);
@@ -157,14 +195,23 @@ __device__ __noinline__ int finish_row_fast(const SampleDev& a, int b, FastScrat
   }
   bar();
   if (fs.rc != kFastDone) return fs.rc;
-  const int nl = 2 * a.nseg, total = fs.loff[nl];
+  const int nl = 2 * a.nseg, total = merging ? a.merge_G * a.merge_width : fs.loff[nl];
   // entry f of the run. A thread's entries come in rising order: the list it stands in (its
   // entries as if the run began at base[0]) is kept from one entry to the next.
   struct Cursor {
     const unsigned long long* base = nullptr;
     int end = 0, lst = -1;
   };
-  auto entry = [&](int f, Cursor& c) {
+  auto entry = [&](int f, Cursor& c) -> unsigned long long {
+    if (merging) {  // entry i of shard g's list, in the lists' own form
+      const int g = f / a.merge_width, i = f - g * a.merge_width;
+      const size_t row = (size_t)g * a.B + b;
+      if (a.merge_n && i >= __ldg(&a.merge_n[row])) return 0ull;
+      const int32_t id = __ldg(&a.merge_id[row * a.merge_stride + i]);
+      const uint32_t ky = key_of(__ldg(&a.merge_val[row * a.merge_stride + i]));
+      if (id < 0 || ky == 0u) return 0ull;
+      return (unsigned long long)ky | ((unsigned long long)((uint32_t)id | kOkB) << 32);
+    }
     while (f >= c.end) {  // (f < total == loff[nl]: the walk ends inside the table)
       ++c.lst;
       c.end = fs.loff[c.lst + 1];
@@ -425,7 +472,8 @@ __device__ __noinline__ int finish_row_fast(const SampleDev& a, int b, FastScrat
     if (a.flags) a.flags[b] = flags;
   }
   if (a.cand_id || a.cand_val || a.cand_pr) {
-    for (int i = lane; i < a.cand_stride; i += 32) {
+    if (lane == 0 && nc > a.cand_width) raise_status(a.status, ARCS_ERR_TOPK);
+    for (int i = lane; i < a.cand_width; i += 32) {
       const size_t o = (size_t)b * a.cand_stride + i;
       const bool in = i < nc;
       if (a.cand_id) a.cand_id[o] = in ? fs.sid[i] : -1;

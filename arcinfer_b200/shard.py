@@ -32,23 +32,56 @@ def gather_tokens(local_tokens, n_rows, world, all_gather):
     return torch.cat([p[: hi - lo] for p, (lo, hi) in zip(parts, sizes)])
 
 
-def vocab_sharded_sample(local_logits, lo, v_global, params, u, all_gather, world, sample_batch, merge_batch, **lists):
+def record_words(k):
+    """int32 words of a packed per-row record: k ids, k values (bit patterns), (max, sum exp)."""
+    return 2 * k + 2
+
+
+def vocab_sharded_sample(local_logits, lo, v_global, params, u, all_gather_into, world, sample_batch, merge_records, k, **lists):
     """The vocabulary-sharded step on one rank: this rank's columns [lo, lo + local V) of every row
-    go through sample_batch under global ids, the per-row candidate lists of all ranks are gathered
-    (`all_gather(list_of_tensors, tensor)`: torch.distributed.all_gather over NCCL, or a stand-in),
-    and merge_batch takes the global choice. The one collective on the data path carries
-    B * (k * 8 + 4) bytes per rank."""
+    go through sample_batch under global ids, which writes each row's candidates straight into a
+    packed record of k * 8 + 8 bytes; the records of all ranks are gathered into one preallocated
+    buffer (`all_gather_into(out, inp)`: torch.distributed.all_gather_into_tensor over NCCL, or a
+    stand-in) that merge_records reads in place for the global choice. The one collective on the
+    data path carries B * (k * 8 + 8) bytes per rank. k: at least the largest top_k of the rows."""
     import torch
 
-    out = sample_batch(local_logits, params, u, id_base=lo, v_global=v_global, want_cands=True, **lists)
-    # one message per rank: ids, values (bit patterns) and list lengths side by side
-    k = out["cand_id"].shape[1]
-    mine = torch.cat([out["cand_id"], out["cand_val"].view(torch.int32), out["n_cand"][:, None]], dim=1).contiguous()
-    got = [torch.empty_like(mine) for _ in range(world)]
-    all_gather(got, mine)
-    allp = torch.stack(got)
-    cand_id = allp[:, :, :k].contiguous()
-    cand_val = allp[:, :, k : 2 * k].contiguous().view(torch.float32)
-    n_cand = allp[:, :, 2 * k].contiguous()
-    return merge_batch(cand_id, cand_val, n_cand, params, u, v_global,
-                       bias_off=lists.get("bias_off"), bias_vals=lists.get("bias_vals"), want_cands=True)
+    B = local_logits.shape[0]
+    rec = torch.full((B, record_words(k)), -1, dtype=torch.int32, device=local_logits.device)
+    sample_batch(local_logits, params, u, id_base=lo, v_global=v_global, records=rec, **lists)
+    gathered = torch.empty((world, B, record_words(k)), dtype=torch.int32, device=local_logits.device)
+    all_gather_into(gathered.view(world * B, -1), rec)  # (rank r's rows land at [r * B, (r + 1) * B))
+    return merge_records(gathered, params, u, v_global, bias_off=lists.get("bias_off"), bias_vals=lists.get("bias_vals"), want_cands=True)
+
+
+class VocabShardStep:
+    """The same step with everything allocated once: the argument block of the local pass, the
+    record buffer it writes, the gathered buffer the merge reads. step() enqueues three pieces of
+    work on the current stream: local pass, all-gather, merge. want_mz: every rank also reduces its
+    columns to (max, sum exp) per row (arcs_argmax_batch), the pairs travel in the records and the
+    merge combines them (out["mz"]): the normaliser of log-probabilities over the whole vocabulary."""
+
+    def __init__(self, local_logits, lo, v_global, params, u, world, k, want_mz=False, **lists):
+        import torch
+
+        from . import capi
+
+        self.capi, self.world, self.k, self.want_mz = capi, world, k, want_mz
+        self.logits, self.params, self.u, self.v_global, self.lists = local_logits, params, u, v_global, lists
+        B = local_logits.shape[0]
+        dev = local_logits.device
+        self.rec = torch.full((B, record_words(k)), -1, dtype=torch.int32, device=dev)
+        self.rec[:, 2 * k :] = 0
+        self.gathered = torch.empty((world, B, record_words(k)), dtype=torch.int32, device=dev)
+        self.plan = capi.SamplePlan(local_logits, params, u, id_base=lo, v_global=v_global, records=self.rec,
+                                    hist_off=lists.get("hist_off"), hist_ids=lists.get("hist_ids"), max_hist=lists.get("max_hist", 0))
+        self.collective_bytes_per_rank = B * record_words(k) * 4
+
+    def step(self, all_gather_into):
+        self.plan.launch()
+        if self.want_mz:
+            ms = self.capi.argmax_batch(self.logits, want_lse=True)["max_sumexp"]
+            self.rec[:, 2 * self.k :] = ms.view(self.rec.dtype)
+        all_gather_into(self.gathered.view(-1, self.rec.shape[1]), self.rec)
+        return self.capi.merge_records(self.gathered, self.params, self.u, self.v_global, bias_off=self.lists.get("bias_off"),
+                                       bias_vals=self.lists.get("bias_vals"), want_mz=self.want_mz)

@@ -109,6 +109,12 @@ typedef struct {
   int32_t* head_id;          /* [B][ARCS_HEAD] optional; entries past n_head are -1 */
   float* head_val;           /* [B][ARCS_HEAD] their adjusted logits */
   int32_t* n_head;           /* [B] min(V, ARCS_HEAD) less the NaN logits among them */
+  /* Entries written per row of cand_id / cand_val / cand_pr: 0 means cand_stride (which must then be
+   * >= ARCS_KCAP). A smaller width lets the lists be written straight into packed per-row records
+   * (ids, values and whatever else the record carries, cand_stride apart): what a vocabulary shard
+   * sends to the others. A row that keeps more candidates than cand_width raises ARCS_ERR_TOPK in
+   * the status word and writes the first cand_width. */
+  int32_t cand_width;
 } arcs_sample_args;
 
 /* max_list: max_hist + max_bias of the call (0 without lists) */
@@ -145,7 +151,7 @@ typedef struct arcs_merge_args {
   int32_t G, B, cand_stride;   /* shards, rows, stride of the gathered lists */
   const int32_t* cand_id;      /* [G][B][cand_stride] global ids, best first (device) */
   const float* cand_val;       /* [G][B][cand_stride] their adjusted logits */
-  const int32_t* n_cand;       /* [G][B] entries per list */
+  const int32_t* n_cand;       /* [G][B] entries per list (may be NULL with packed records, below) */
   const arcs_row_params* params;
   const double* u;
   const int32_t* bias_off;     /* optional: only "does the row ban anything" is read from the bias list */
@@ -160,6 +166,17 @@ typedef struct arcs_merge_args {
   float* out_pr;
   int32_t out_stride;
   int32_t* status;
+  /* Packed records. cand_width: entries per gathered list (0: cand_stride); n_cand may then be NULL:
+   * a list ends at its first negative id. shard_mz: [G][B] pairs (max, sum of exp(l - max)) of every
+   * shard's raw logits, mz_stride floats apart (optional, e.g. from arcs_argmax_batch's max_sumexp),
+   * combined into mz_out [B][2]: M = max m_g, Z = sum z_g exp(m_g - M), so that
+   * log-probabilities over the whole vocabulary are M + log Z away from a raw logit. With
+   * cand_id = rec, cand_val = rec + k, shard_mz = rec + 2k, cand_stride = mz_stride = 2k + 2 the
+   * call reads a gathered buffer of [G][B] records of k * 8 + 8 bytes in place. */
+  int32_t cand_width;
+  const float* shard_mz;
+  int32_t mz_stride;
+  float* mz_out;
 } arcs_merge_args;
 int arcs_merge_batch(const arcs_merge_args* args, void* stream);
 

@@ -71,6 +71,54 @@ def test_shards_on_one_gpu_match_the_oracle(bf16):
         check_rows(out, xb, bf16, params, hists, us, biases, tag=f"G={G}")
 
 
+def test_packed_records_read_in_place():
+    """The layout the shards exchange: every shard writes k ids and k values per row straight into
+    a record of k * 8 + 8 bytes whose last two words carry (max, sum exp) of its raw columns; the
+    merge reads the gathered records where they lie, without list lengths, and combines the pairs."""
+    import torch
+
+    import arcinfer_b200 as ab
+    from gpuutil import check_rows, to_dev_logits
+
+    g = np.random.default_rng(540)
+    for V, B, G, k in [(40000, 7, 4, 64), (262144, 130, 2, 50), (151936, 5, 8, 20)]:
+        x = np.stack([rand_logits(g, V, b % 3) for b in range(B)])
+        params = synth.make_params(B, top_k=k, top_p=0.9, min_p=0.02, repeat_penalty=1.2, presence_penalty=0.3, temperature=0.8)
+        params["top_k"][::3] = max(1, k // 2)
+        hists = [rand_recent(g, V) for _ in range(B)]
+        biases = [[] for _ in range(B)]
+        us = g.random(B)
+        xb = synth.f32_to_bf16_bits(x)
+        p_dev = ab.capi.params_to_device(params, "cuda")
+        u_dev = torch.from_numpy(us).cuda()
+        gathered = torch.empty(G, B, shard.record_words(k), dtype=torch.int32, device="cuda")
+        for r in range(G):
+            lo, hi = shard.vocab_range(V, r, G)
+            lg, Vl = to_dev_logits(np.ascontiguousarray(xb[:, lo:hi]), True)
+            kw = _lists(hists, biases, lo, hi)
+            o = ab.sample_batch(lg, p_dev, u_dev, V=Vl, id_base=lo, v_global=V, records=gathered[r],
+                                hist_off=kw["hist_off"], hist_ids=kw["hist_ids"], max_hist=kw["max_hist"])
+            assert int(o["status"].item()) == 0
+            gathered[r, :, 2 * k :] = ab.argmax_batch(lg, V=Vl, want_lse=True)["max_sumexp"].view(torch.int32)
+        out = ab.merge_records(gathered, p_dev, u_dev, V, want_cands=True, want_mz=True)
+        torch.cuda.synchronize()
+        assert int(out["status"].item()) == 0
+        mz = out.pop("mz").cpu().numpy().astype(np.float64)
+        out = {kk: v.cpu().numpy() for kk, v in out.items()}
+        check_rows(out, xb, True, params, hists, us, biases, tag=f"packed G={G}")
+        xf = synth.bf16_bits_to_f32(xb).astype(np.float64)
+        m = xf.max(axis=1)
+        lse = m + np.log(np.exp(xf - m[:, None]).sum(axis=1))
+        assert np.array_equal(mz[:, 0], m)
+        assert np.abs(mz[:, 0] + np.log(mz[:, 1]) - lse).max() < 1e-5  # (fp32 sums of exponentials per shard)
+    # a row that keeps more candidates than the record holds is reported, not written past the record
+    lg, Vl = to_dev_logits(np.ascontiguousarray(xb[:, :4096]), True)
+    small = torch.empty(B, shard.record_words(4), dtype=torch.int32, device="cuda")
+    o = ab.sample_batch(lg, p_dev, u_dev, V=Vl, records=small)
+    torch.cuda.synchronize()
+    assert int(o["status"].item()) == 2  # ARCS_ERR_TOPK
+
+
 def test_two_ranks_over_nccl():
     import torch
 

@@ -76,30 +76,27 @@ def test_two_ranks_equal_one_process():
 # ---- the vocabulary-sharded step (shard.vocab_sharded_sample) with stand-ins for the two kernels:
 # every rank ranks its own columns with the CPU oracle, the lists travel through one gloo
 # all-gather in the packed layout the real path uses, and the merge picks from the gathered lists.
-KCAP = 256
+K = 64  # entries per packed record
 
 
 def _fake_sample(x_rows, hist, p_rows):
-    def f(local_logits, params, u, id_base=0, v_global=0, want_cands=True, **_):
+    def f(local_logits, params, u, id_base=0, v_global=0, records=None, **_):
         B, Vl = local_logits.shape
-        ids = torch.full((B, KCAP), -1, dtype=torch.int32)
-        vals = torch.zeros(B, KCAP, dtype=torch.float32)
-        n = torch.zeros(B, dtype=torch.int32)
         for b in range(B):
             adj = orc.adjusted(x_rows[b], p_rows[b : b + 1], hist[b])[id_base : id_base + Vl]
             k = min(int(p_rows[b]["top_k"]), Vl)
             order = np.lexsort((np.arange(Vl), -adj.astype(np.float64)))[:k]  # value desc, id asc
-            ids[b, :k] = torch.from_numpy((order + id_base).astype(np.int32))
-            vals[b, :k] = torch.from_numpy(adj[order])
-            n[b] = k
-        return {"cand_id": ids, "cand_val": vals, "n_cand": n}
+            records[b, :K] = -1
+            records[b, :k] = torch.from_numpy((order + id_base).astype(np.int32))
+            records[b, K : K + k] = torch.from_numpy(adj[order].view(np.int32))
+        return {}
 
     return f
 
 
 def _fake_merge(p_rows, V):
-    def f(cand_id, cand_val, n_cand, params, u, v_global, **_):
-        G, B, _ = cand_id.shape
+    def f(records, params, u, v_global, **_):
+        G, B, _ = records.shape
         tok = torch.zeros(B, dtype=torch.int32)
         plain = p_rows.copy()
         for name in ("presence_penalty", "frequency_penalty"):
@@ -108,8 +105,9 @@ def _fake_merge(p_rows, V):
         for b in range(B):
             row = np.full(V, -3.0e38, np.float32)
             for g in range(G):
-                k = int(n_cand[g, b])
-                row[cand_id[g, b, :k].numpy()] = cand_val[g, b, :k].numpy()
+                ids = records[g, b, :K].numpy()
+                k = int((ids >= 0).sum())  # (a list ends at its first negative id)
+                row[ids[:k]] = records[g, b, K : K + k].numpy().view(np.float32)
             tok[b] = orc.sample(row, plain[b : b + 1], np.zeros(0, np.int32), float(u[b]))["token"]
         return {"token": tok}
 
@@ -122,7 +120,7 @@ def _vocab_worker(rank, world, port, B, V, out):
     x, p, hist, u = _rows(6, B, V)
     lo, hi = shard.vocab_range(V, rank, world, align=256)
     local = torch.from_numpy(np.ascontiguousarray(x[:, lo:hi]))
-    res = shard.vocab_sharded_sample(local, lo, V, p, torch.from_numpy(u), dist.all_gather, world, _fake_sample(x, hist, p), _fake_merge(p, V))
+    res = shard.vocab_sharded_sample(local, lo, V, p, torch.from_numpy(u), dist.all_gather_into_tensor, world, _fake_sample(x, hist, p), _fake_merge(p, V), K)
     if rank == 0:
         out.put(res["token"].numpy())
     dist.barrier()

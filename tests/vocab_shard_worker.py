@@ -1,5 +1,5 @@
 """Worker of tests/test_gpu_vocab_shard.py::test_two_ranks_over_nccl (one process per GPU under
-torchrun): every rank samples its columns, the candidate lists travel through one NCCL all-gather,
+torchrun): every rank samples its columns, the packed records travel through one NCCL all-gather,
 every rank merges, and rank 0 compares with the CPU oracle."""
 import os
 import sys
@@ -32,9 +32,15 @@ def main():
     lists = dict(hist_off=torch.from_numpy(ho).cuda(), hist_ids=torch.from_numpy(hi_).cuda(), max_hist=H)
     p_dev = ab.capi.params_to_device(params, "cuda")
     u_dev = torch.from_numpy(us).cuda()
-    out = shard.vocab_sharded_sample(local_logits, lo, V, p_dev, u_dev, dist.all_gather, world, ab.sample_batch, ab.merge_batch, **lists)
+    out = shard.vocab_sharded_sample(local_logits, lo, V, p_dev, u_dev, dist.all_gather_into_tensor, world, ab.sample_batch, ab.merge_records, 50, **lists)
     torch.cuda.synchronize()
     tok = out["token"].cpu().numpy()
+    step = shard.VocabShardStep(local_logits, lo, V, p_dev, u_dev, world, 50, want_mz=True, **lists)  # the prebuilt form, with the normaliser
+    for _ in range(2):
+        out2 = step.step(dist.all_gather_into_tensor)
+    torch.cuda.synchronize()
+    assert np.array_equal(out2["token"].cpu().numpy(), tok)
+    mz = out2["mz"].cpu().numpy().astype(np.float64)
     if rank == 0:
         import orc
 
@@ -42,6 +48,9 @@ def main():
         for b in range(B):
             want = orc.sample(xf[b], params[b : b + 1], hists[b], float(us[b]))
             assert tok[b] == want["token"], (b, tok[b], want["token"])
+        xd = xf.astype(np.float64)
+        m = xd.max(axis=1)
+        assert np.abs(mz[:, 0] + np.log(mz[:, 1]) - (m + np.log(np.exp(xd - m[:, None]).sum(axis=1)))).max() < 1e-5
         print("VOCAB_SHARD_OK")
     dist.barrier()
     dist.destroy_process_group()
