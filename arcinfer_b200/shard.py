@@ -85,3 +85,20 @@ class VocabShardStep:
         all_gather_into(self.gathered.view(-1, self.rec.shape[1]), self.rec)
         return self.capi.merge_records(self.gathered, self.params, self.u, self.v_global, bias_off=self.lists.get("bias_off"),
                                        bias_vals=self.lists.get("bias_vals"), want_mz=self.want_mz)
+
+    def capture(self, all_gather_into):
+        """The three pieces of work of a step as one CUDA graph (call step() at least once before, so
+        that the communicator exists). replay() of the returned graph runs the step on the current
+        stream without the host between its launches; the outputs are self.out."""
+        import torch
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.step(all_gather_into)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                self.out = self.step(all_gather_into)
+        torch.cuda.current_stream().wait_stream(side)
+        return graph
