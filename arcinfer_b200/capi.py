@@ -126,20 +126,23 @@ def params_to_device(p, device):
 _workspaces = {}
 
 
-def _workspace(kind, device, nbytes):
+def _workspace(kind, device, nbytes, shape=None):
     """One zero-initialised scratch buffer per (kind, device), grown on demand. The kernels leave
-    it zeroed again, so it is cleared only when (re)allocated."""
+    their counters zeroed again, but where the counters lie depends on the call's shape: the buffer
+    is cleared when it is (re)allocated and when a call of another shape takes it over."""
     key = (kind, str(device))
-    w = _workspaces.get(key)
+    w, last = _workspaces.get(key, (None, None))
     if w is None or w.numel() < nbytes:
         w = torch.zeros(max(nbytes, 1024), dtype=torch.uint8, device=device)
-        _workspaces[key] = w
+    elif shape != last:
+        w.zero_()
+    _workspaces[key] = (w, shape)
     return w
 
 
 def reset_workspaces():
     """Zero every cached scratch buffer (needed after a launch that reported a device status)."""
-    for w in _workspaces.values():
+    for w, _ in _workspaces.values():
         w.zero_()
 
 
@@ -226,7 +229,7 @@ def argmax_batch(logits, V=None, want_lse=False, row_off=None, draft=None, draft
     if status is None:
         status = torch.zeros(1, dtype=torch.int32, device=dev)
     out["status"] = status
-    ws = None if static_scratch else _workspace("argmax", dev, lib.arcs_argmax_workspace_bytes(R, V))
+    ws = None if static_scratch else _workspace("argmax", dev, lib.arcs_argmax_workspace_bytes(R, V), (R, V))
     a = ArgmaxArgs()
     a.logits, a.dtype, a.R, a.V, a.row_stride = logits.data_ptr(), _dtype_code(logits), R, V, logits.stride(0)
     a.argmax, a.max_sumexp = out["argmax"].data_ptr(), _ptr(out.get("max_sumexp"))
@@ -325,10 +328,50 @@ def logprobs_batch(logits, token=None, top_n=0, V=None, status=None):
     a.token, a.top_n, a.top_stride = _ptr(token), top_n, top_n
     a.logprob, a.lse = _ptr(out.get("logprob")), out["lse"].data_ptr()
     a.top_id, a.top_logprob = _ptr(out.get("top_id")), _ptr(out.get("top_logprob"))
-    ws = _workspace("logprobs", dev, lib.arcs_logprobs_workspace_bytes(B, V, top_n))
+    ws = _workspace("logprobs", dev, lib.arcs_logprobs_workspace_bytes(B, V, top_n), (B, V, top_n))
     a.workspace, a.workspace_bytes = ws.data_ptr(), ws.numel()
     a.status = status.data_ptr()
     _check(lib.arcs_logprobs_batch(C.byref(a), _stream(dev)), "arcs_logprobs_batch")
+    return out
+
+
+class DflashArgs(C.Structure):
+    _fields_ = [
+        ("logits", C.c_void_p), ("dtype", C.c_int32), ("slots", C.c_int32), ("nd", C.c_int32), ("V", C.c_int32),
+        ("row_stride", C.c_int64), ("hproj", C.c_void_p), ("pred", C.c_void_p), ("succ", C.c_void_p),
+        ("rank", C.c_int32), ("topk", C.c_int32), ("max_drafts", C.c_int32), ("tok", C.c_void_p), ("min_p", C.c_double),
+        ("n_out", C.c_void_p), ("out_tokens", C.c_void_p), ("out_stride", C.c_int32), ("path_p", C.c_void_p),
+        ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("status", C.c_void_p),
+    ]  # fmt: skip
+
+
+lib.arcs_dflash_workspace_bytes.restype = C.c_size_t
+lib.arcs_dflash_workspace_bytes.argtypes = [C.c_int32, C.c_int32, C.c_int32, C.c_int32]
+lib.arcs_dflash_select.restype = C.c_int
+lib.arcs_dflash_select.argtypes = [C.POINTER(DflashArgs), C.c_void_p]
+
+
+def dflash_select(logits, hproj, pred, succ, tok, topk=16, max_drafts=7, min_p=0.3, status=None):
+    """arcs_dflash_select: logits [slots, nd, >=V] fp32 / bf16, hproj [slots, nd, rank] float32,
+    pred / succ [V, rank] bf16 codebooks (int16 tensors holding the bit patterns), tok int32
+    [slots]. Returns n_out [slots], tokens [slots, nd] (-1 past n_out), path_p [slots, nd], status."""
+    dev = logits.device
+    slots, nd = logits.shape[0], logits.shape[1]
+    V, rank = pred.shape
+    assert logits.stride(2) == 1 and (slots == 1 or logits.stride(0) == nd * logits.stride(1)) and hproj.is_contiguous() and pred.is_contiguous() and succ.is_contiguous()
+    out = {"n_out": torch.zeros(slots, dtype=torch.int32, device=dev), "tokens": torch.full((slots, nd), -1, dtype=torch.int32, device=dev),
+           "path_p": torch.full((slots, nd), float("nan"), dtype=torch.float64, device=dev)}
+    if status is None:
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+    out["status"] = status
+    a = DflashArgs()
+    a.logits, a.dtype, a.slots, a.nd, a.V, a.row_stride = logits.data_ptr(), _dtype_code(logits), slots, nd, V, logits.stride(1)
+    a.hproj, a.pred, a.succ, a.rank, a.topk, a.max_drafts = hproj.data_ptr(), pred.data_ptr(), succ.data_ptr(), rank, topk, max_drafts
+    a.tok, a.min_p = tok.data_ptr(), min_p
+    a.n_out, a.out_tokens, a.out_stride, a.path_p = out["n_out"].data_ptr(), out["tokens"].data_ptr(), nd, out["path_p"].data_ptr()
+    ws = _workspace("dflash", dev, lib.arcs_dflash_workspace_bytes(slots, nd, V, topk), (slots, nd, V, topk))
+    a.workspace, a.workspace_bytes, a.status = ws.data_ptr(), ws.numel(), status.data_ptr()
+    _check(lib.arcs_dflash_select(C.byref(a), _stream(dev)), "arcs_dflash_select")
     return out
 
 

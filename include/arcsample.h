@@ -200,7 +200,7 @@ typedef struct {
   const int32_t* draft_off;  /* [slots+1] */
   int32_t* accepted;         /* [slots] */
   int32_t* next;             /* [slots] */
-  void* workspace;           /* arcs_argmax_workspace_bytes(), zeroed once before first use */
+  void* workspace;           /* arcs_argmax_workspace_bytes(), zeroed before its first use and again before a call of another shape (R, V) takes it over */
   size_t workspace_bytes;
   int32_t* status;
 } arcs_argmax_args;
@@ -301,13 +301,54 @@ typedef struct {
   double* lse;            /* [B] optional: log of the sum of exponentials */
   int32_t* top_id;        /* [B][top_stride]; entries past min(top_n, V) are not written */
   double* top_logprob;    /* [B][top_stride] */
-  void* workspace;        /* arcs_logprobs_workspace_bytes(), zeroed once before first use */
+  void* workspace;        /* arcs_logprobs_workspace_bytes(), zeroed before its first use and again before a call of another shape (B, V, top_n) takes it over */
   size_t workspace_bytes;
   int32_t* status;        /* device status word (first error wins), may be NULL */
 } arcs_logprob_args;
 
 size_t arcs_logprobs_workspace_bytes(int32_t B, int32_t V, int32_t top_n);
 int arcs_logprobs_batch(const arcs_logprob_args* args, void* stream);
+
+/* ------------------------------------------------------------------------------------------
+ * dflash_select: the candidate selector of the DFlash2 drafter (zero/engine_drafters.h:461-506),
+ * for many slots in one call. Per slot and draft position t (rows of raw logits, as the
+ * drafter's head produced them): the topk largest logits (value descending, id ascending,
+ * :476-484); score(c) = logit(c) + sum_r (pred[prev][r] * hproj[t][r]) * succ[c][r], every
+ * product a float and the sum a double built in index order (:487-493); the candidate with the
+ * best score, the first among equals, becomes the draft and the next position's `prev` (:494,
+ * :505). With min_p > 0 the drafts stop when the drafter's own probability of the path,
+ * prod exp(logit(draft) - max) / sum exp(l - max), falls below min_p; the first draft always
+ * goes (:496-503; the reference reads min_p from ARC_DFL_P, default 0.3).
+ * Drafts are bit-exact against the reference's loop; the path probability uses this library's
+ * log-sum-exp (logprobs_batch), within 1e-7 relative of the exact sum where the reference's
+ * float sums over blocks of 4096 are within about 1e-6: a path probability that close to min_p
+ * may be cut one draft apart.
+ * The first step is arcs_logprobs_batch on slots * nd rows; the second one warp per slot.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* logits;      /* [slots][nd][row_stride] device, of dtype */
+  int32_t dtype;           /* arcs_dtype */
+  int32_t slots, nd, V;
+  int64_t row_stride;      /* elements */
+  const float* hproj;      /* [slots][nd][rank] the selector's projection of the hidden states */
+  const uint16_t* pred;    /* [V][rank] bf16 bit patterns: codebook indexed by the previous token */
+  const uint16_t* succ;    /* [V][rank] bf16 bit patterns: codebook indexed by the candidate */
+  int32_t rank;            /* 1 .. 1024 */
+  int32_t topk;            /* 1 .. 64 (the reference's dfl_topk_, 16) */
+  int32_t max_drafts;      /* at most min(nd, max_drafts) drafts per slot */
+  const int32_t* tok;      /* [slots] the token before the first draft */
+  double min_p;            /* 0: no cut */
+  int32_t* n_out;          /* [slots] drafts kept */
+  int32_t* out_tokens;     /* [slots][out_stride] */
+  int32_t out_stride;      /* >= min(nd, max_drafts) */
+  double* path_p;          /* [slots][nd] optional: path probability after each position visited */
+  void* workspace;         /* arcs_dflash_workspace_bytes(), 256-byte aligned, zeroed before its first use and again before a call of another shape takes it over */
+  size_t workspace_bytes;
+  int32_t* status;         /* device status word, may be NULL */
+} arcs_dflash_args;
+
+size_t arcs_dflash_workspace_bytes(int32_t slots, int32_t nd, int32_t V, int32_t topk);
+int arcs_dflash_select(const arcs_dflash_args* args, void* stream);
 
 /* ------------------------------------------------------------------------------------------
  * Host-buffer entry points: what a host application that keeps its logits in host memory

@@ -413,6 +413,65 @@ void orc_dfa_mask(const uint16_t* table, int S, int dead, int state, const uint3
   }
 }
 
+/* ---------------------------------------------------------------- DFlash2 candidate selector */
+/* zero/engine_drafters.h:461-506: per draft position the K largest raw logits; every candidate's
+ * score is its logit plus the inner product of (pred[prev] * h) with succ[candidate] over the
+ * rank of the bf16 codebooks, each product a float, summed in index order into a double
+ * (:489-493); the best score (the first among equals, :494) is the draft; the drafts are kept
+ * while the drafter's own probability of the path stays at or above min_p (:497-503: the first
+ * draft always goes). Returns the number of drafts. path_p (optional, [positions]): the path
+ * probability after each position visited. */
+static float bf16_bits_to_float(uint16_t b) {
+  const uint32_t w = (uint32_t)b << 16;
+  float f;
+  memcpy(&f, &w, 4);
+  return f;
+}
+int orc_dflash_select(const float* logits, const float* hproj, const uint16_t* pred, const uint16_t* succ,
+                      int V, int rank, int topk, int nd, int max_drafts, int tok, double min_p,
+                      int32_t* out_tokens, double* path_p_out) {
+  const int K = topk < V ? topk : V; /* :465 */
+  int32_t* idx = (int32_t*)malloc((size_t)(K > 0 ? K : 1) * sizeof(int32_t));
+  float* ph = (float*)malloc((size_t)rank * sizeof(float));
+  int prev = tok, n_out = 0;
+  double path_p = 1.0;
+  const int steps = nd < max_drafts ? nd : max_drafts;
+  for (int t = 0; t < steps; ++t) { /* :473 */
+    const float* l = logits + (size_t)t * V;
+    top_ids(l, V, K, idx); /* :476-484 */
+    const float* h = hproj + (size_t)t * rank;
+    for (int r = 0; r < rank; ++r) ph[r] = bf16_bits_to_float(pred[(size_t)prev * rank + r]) * h[r]; /* :487 */
+    double best = -1e300;
+    int bt = idx[0];
+    for (int k = 0; k < K; ++k) { /* :490-495 */
+      const int c = idx[k];
+      double sc = l[c];
+      const uint16_t* sv = succ + (size_t)c * rank;
+      for (int r = 0; r < rank; ++r) {
+        const float prod = ph[r] * bf16_bits_to_float(sv[r]);
+        sc += prod;
+      }
+      if (sc > best) {
+        best = sc;
+        bt = c;
+      }
+    }
+    if (min_p > 0) { /* :496-503 */
+      float mx = l[idx[0]];
+      for (int k = 1; k < K; ++k) mx = mx > l[idx[k]] ? mx : l[idx[k]];
+      const double z = orc_softmax_den(l, V, mx);
+      path_p *= exp((double)l[bt] - mx) / z;
+      if (path_p_out) path_p_out[t] = path_p;
+      if (t > 0 && path_p < min_p) break;
+    }
+    out_tokens[n_out++] = bt;
+    prev = bt;
+  }
+  free(idx);
+  free(ph);
+  return n_out;
+}
+
 /* ---------------------------------------------------------------- bf16 */
 void orc_bf16_to_f32(const uint16_t* in, int64_t n, float* out) {
   for (int64_t i = 0; i < n; ++i) {

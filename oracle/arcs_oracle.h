@@ -103,6 +103,14 @@ void orc_dfa_mask(const uint16_t* table, int S, int dead, int state, const uint3
                   const uint8_t* bytes, const uint8_t* special, int special_ok, int V,
                   uint32_t* out_bits);
 
+/* The DFlash2 candidate selector (zero/engine_drafters.h:461-506) for one slot: logits [nd][V],
+ * hproj [nd][rank] fp32; pred / succ [V][rank] bf16 bit patterns. Returns the number of drafts
+ * written to out_tokens; path_p_out (optional, [nd]) receives the path probability after each
+ * position visited (only with min_p > 0). */
+int orc_dflash_select(const float* logits, const float* hproj, const uint16_t* pred, const uint16_t* succ,
+                      int V, int rank, int topk, int nd, int max_drafts, int tok, double min_p,
+                      int32_t* out_tokens, double* path_p_out);
+
 /* exact widening / round-to-nearest-even narrowing between fp32 and bf16 */
 void orc_bf16_to_f32(const uint16_t* in, int64_t n, float* out);
 void orc_f32_to_bf16(const float* in, int64_t n, uint16_t* out);

@@ -184,3 +184,28 @@ def ref_lp_entry(row, token=-1, top_n=0):
     ids, tlp = np.full(max(top_n, 1), -1, np.int32), np.full(max(top_n, 1), np.nan, np.float64)
     lse = refslices.ref_lp_entry(_p(row), len(row), int(token), int(top_n), _p(lp), _p(ids), _p(tlp))
     return lse, lp[0], ids[:top_n], tlp[:top_n]
+
+
+# ---- the DFlash2 candidate selector (zero/engine_drafters.h:461-506), one slot
+def dflash_select(logits, hproj, pred, succ, topk, max_drafts, tok, min_p):
+    """logits [nd, V] float32, hproj [nd, rank] float32, pred / succ [V, rank] uint16 (bf16 bits).
+    Returns (drafts int32 array, path probabilities float64 [nd])."""
+    logits, hproj = _f32(logits), _f32(hproj)
+    pred, succ = np.ascontiguousarray(pred, np.uint16), np.ascontiguousarray(succ, np.uint16)
+    nd, V = logits.shape
+    out, pp = np.zeros(nd, np.int32), np.full(nd, np.nan)
+    n = orc.orc_dflash_select(_p(logits), _p(hproj), _p(pred), _p(succ), V, hproj.shape[1], topk, nd, max_drafts, int(tok),
+                              C.c_double(min_p), _p(out), _p(pp))
+    return out[:n], pp
+
+
+def ref_dflash_select(logits, hproj, pred, succ, topk, max_drafts, tok, min_p):
+    """The reference's own loop (a fragment of zero/engine_drafters.h compiled by oracle/ref_slices.cpp)."""
+    assert refslices is not None
+    logits, hproj = _f32(logits), _f32(hproj)
+    pred, succ = np.ascontiguousarray(pred, np.uint16), np.ascontiguousarray(succ, np.uint16)
+    nd, V = logits.shape
+    out = np.zeros(nd, np.int32)
+    n = refslices.ref_dflash_select(_p(logits), _p(hproj), _p(pred), _p(succ), V, hproj.shape[1], topk, nd, max_drafts, int(tok),
+                                    C.c_double(min_p), _p(out))
+    return out[:n]

@@ -7,6 +7,7 @@ import numpy as np
 import pytest
 
 import orc
+from arcinfer_b200 import synth
 from cases import rand_logits, rand_mask, rand_params, rand_recent
 
 needs_ref = pytest.mark.skipif(orc.ref is None, reason="oracle/_ref/libarcs_ref.so not built")
@@ -168,3 +169,34 @@ def test_softmax_den_pinned_to_the_reference_function():
             x = rand_logits(g, V, mode)
             mx = float(x.max())
             assert orc.softmax_den(x, mx) == orc.ref_softmax_den(x, mx)
+
+
+def dflash_case(g, V, rank, nd, sharp=1.0):
+    """Inputs of the DFlash2 selector: logits with a few strong tokens per position (so that the
+    path probability is neither 0 nor 1), small codebook entries that reorder the top candidates."""
+    logits = (g.standard_normal((nd, V)) * 2.0).astype(np.float32)
+    for t in range(nd):
+        logits[t, g.integers(0, V, 3)] += np.float32(6.0 * sharp)
+    hproj = g.standard_normal((nd, rank)).astype(np.float32)
+    pred = synth.f32_to_bf16_bits((g.standard_normal((V, rank)) * 0.3).astype(np.float32))
+    succ = synth.f32_to_bf16_bits((g.standard_normal((V, rank)) * 0.3).astype(np.float32))
+    return logits, hproj, pred, succ
+
+
+@pytest.mark.skipif(orc.refslices is None, reason="oracle/_ref/libarcs_refslices.so not built (needs the reference tree)")
+def test_dflash_selector_restatement_is_the_reference_loop():
+    g = np.random.default_rng(77)
+    n_cut = 0
+    for V, rank, nd, topk, min_p, sharp in [(3000, 64, 7, 16, 0.3, 1.0), (5000, 256, 5, 16, 0.3, 0.6), (2000, 32, 7, 64, 0.0, 1.0),
+                                            (4096, 128, 3, 8, 0.9, 1.0), (40, 16, 4, 64, 0.3, 1.0), (3000, 64, 7, 16, 0.05, 0.3)]:
+        for rep in range(4):
+            logits, hproj, pred, succ = dflash_case(g, V, rank, nd, sharp)
+            if rep == 1:  # ties among the top logits: the first of equals is kept and wins
+                logits[:, 5] = logits[:, 9] = logits.max(axis=1) + 1
+            tok = int(g.integers(0, V))
+            for max_drafts in (nd, 2):
+                got, _ = orc.dflash_select(logits, hproj, pred, succ, topk, max_drafts, tok, min_p)
+                want = orc.ref_dflash_select(logits, hproj, pred, succ, topk, max_drafts, tok, min_p)
+                assert np.array_equal(got, want), (V, rank, nd, topk, min_p, rep)
+                n_cut += len(want) < min(nd, max_drafts)
+    assert n_cut > 0  # the probability cut was taken somewhere
