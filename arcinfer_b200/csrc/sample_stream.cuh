@@ -53,9 +53,6 @@ enum {
 };
 enum { L_TAU_B = 0 /* [3] */, L_TAU_A = 3 /* [3] */, L_END = 6 };
 
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
-}
 __device__ __forceinline__ int s_tiles(const SegPlan& p) { return (p.body_bytes + kSTile - 1) / kSTile; }
 __device__ __forceinline__ uint32_t s_tile_bytes(const SegPlan& p, int t) {
   const int32_t rem = p.body_bytes - t * kSTile;
