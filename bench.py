@@ -358,6 +358,86 @@ def bench_small(args):
     print(json.dumps(line), flush=True)
 
 
+def bench_dflash(args):
+    """--workload dflash (one GPU): the DFlash2 candidate selector (zero/engine_drafters.h:461-506)
+    for 8 slots x 7 draft positions of a 151936-token vocabulary, rank-256 codebooks, top-16
+    candidates, min_p 0.3. One step = arcs_dflash_select on device-resident inputs (a CUDA graph
+    replay, L2 flushed between calls); every slot's drafts are compared with the CPU checker."""
+    import numpy as np
+    import torch
+
+    import arcinfer_b200 as ab
+    from arcinfer_b200 import synth
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import orc
+
+    torch.cuda.set_device(0)
+    dev = "cuda"
+    slots, nd, V, rank, topk, min_p = 8, 7, 151936, 256, 16, 0.3
+    g = np.random.default_rng(synth.BASE_SEED + 31)
+    logits = (g.standard_normal((slots, nd, V)) * 2.0).astype(np.float32)
+    for s_ in range(slots):
+        for t in range(nd):
+            logits[s_, t, g.integers(0, V, 3)] += np.float32(5.0)
+    hproj = g.standard_normal((slots, nd, rank)).astype(np.float32)
+    pred = synth.f32_to_bf16_bits((g.standard_normal((V, rank)) * 0.3).astype(np.float32))
+    succ = synth.f32_to_bf16_bits((g.standard_normal((V, rank)) * 0.3).astype(np.float32))
+    tok = g.integers(0, V, slots).astype(np.int32)
+    d = [torch.from_numpy(a).to(dev) for a in (logits, hproj, pred.view(np.int16), succ.view(np.int16), tok)]
+    step = lambda: ab.dflash_select(d[0], d[1], d[2], d[3], d[4], topk=topk, max_drafts=nd, min_p=min_p)
+    for _ in range(max(args.warmup, 5)):
+        out = step()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        step()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            out = step()
+    torch.cuda.synchronize()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    clocks = ClockSampler(0)
+    times = []
+    for _ in range(args.steps):
+        flush.fill_(1)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    clk = clocks.stop()
+    ms = float(np.median(times))
+    assert int(out["status"].item()) == 0
+    n_out, toks = out["n_out"].cpu().numpy(), out["tokens"].cpu().numpy()
+    bad = 0
+    t0 = time.perf_counter()
+    for s_ in range(slots):
+        want, _ = orc.dflash_select(logits[s_], hproj[s_], pred, succ, topk, nd, int(tok[s_]), min_p)
+        bad += int(n_out[s_] != len(want) or not np.array_equal(toks[s_, : len(want)], want))
+    cpu_dt = time.perf_counter() - t0
+    parity = {"rows_checked": slots, "mismatches": bad, "against": "oracle/arcs_oracle.c (pinned to the reference's loop) on the same inputs"}
+    if bad:
+        print(json.dumps({"parity": parity}), flush=True)
+        sys.exit(3)
+    peak, which = measured_peak()
+    R = slots * nd
+    abytes = R * V * 4 + R * rank * 4 + R * (topk + 1) * rank * 2
+    print(json.dumps({
+        "metric": "draft_rows_per_sec", "value": R / (ms * 1e-3), "unit": "rows/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 5),
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32 logits, bf16 codebooks, fp64 scores",
+        "data": "synthetic", "config": {"workload": "dflash", "slots": slots, "positions": nd, "vocab": V, "rank": rank, "topk": topk, "min_p": min_p,
+                                        "l2": "L2 flushed (256 MiB written) between timed calls; median of the calls", "launch": "CUDA graph replay of the step"},
+        "gpu_launches": 3 * args.steps, "clocks": clk, "e2e": None,
+        "roofline": {"bound": "hbm", "kernel": "logprob_kernel", "achieved": abytes / (ms * 1e-3) / 1e9, "peak": peak, "peak_source": f"of {which}", "unit": "GB/s",
+                     "frac": abytes / (ms * 1e-3) / 1e9 / peak, "traffic": None, "algorithmic_bytes_per_launch": abytes,
+                     "note": "a latency case: 56 rows in one pass, then a sequential walk of 7 positions per slot"},
+        "cpu_baseline": {"value": R / cpu_dt, "unit": "rows/s", "cores": 1, "kind": "port", "sample": f"the whole workload ({slots} slots), once, one thread"},
+        "parity": parity}), flush=True)
+
+
 def vocab_shard_leg(ab, synth, dist, rank, world, dev, B, V, H, params, steps, warmup, check_rows=4):
     """The vocabulary-sharded step (strong scaling): every rank holds its columns of ALL B rows,
     runs the selection on them under global ids into packed records, one all-gather of
@@ -448,7 +528,7 @@ def main():
     ap.add_argument("--vocab", type=int, default=VOCAB)
     ap.add_argument("--shard", default="rows", choices=["rows", "vocab"],
                     help="how N GPUs split the work: rows (default, no collective) or vocabulary columns (one all-gather)")
-    ap.add_argument("--workload", default="wide-batch", choices=["wide-batch", "logprobs", "single-row", "multi-slot", "spec-verify", "constrained"],
+    ap.add_argument("--workload", default="wide-batch", choices=["wide-batch", "logprobs", "single-row", "multi-slot", "spec-verify", "constrained", "dflash"],
                     help="wide-batch: the sampling step (the headline); logprobs: arcs_logprobs_batch on the same logits; the other four: "
                          "the latency workloads of the measured configurations 1-4 (one GPU)")
     ap.add_argument("--no-e2e", action="store_true")
@@ -460,6 +540,10 @@ def main():
     if args.workload == "logprobs" and args.impl == "ours":
         if int(os.environ.get("RANK", "0")) == 0:
             bench_logprobs(args)
+        return
+    if args.workload == "dflash" and args.impl == "ours":
+        if int(os.environ.get("RANK", "0")) == 0:
+            bench_dflash(args)
         return
     if args.workload in ("single-row", "multi-slot", "spec-verify", "constrained") and args.impl == "ours":
         if int(os.environ.get("RANK", "0")) == 0:
