@@ -9,9 +9,10 @@
 //              aside, then tested element by element, and the survivors appended to the item's
 //              lists in the workspace;
 //   threshold  one warp keeps raising the thresholds of the items that are streaming from the
-//              coarse histograms the scanners update, and releases an item to the finish kernel
-//              when all scanners are through with it;
-//   preparing  two warps build the filters and headers of the items ahead of the stream
+//              coarse histograms the scanners update;
+//   closing    one warp hands an item over to the finish kernel when all scanners are through
+//              with it: list lengths and last thresholds to the item's header, then the release;
+//   preparing  four warps build the filters and headers of the items ahead of the stream
 //              (sample_prep.cuh), and find each item's first threshold: ahead of the stream they
 //              fetch the item's first tiles into a side buffer (the ring's own copy of those
 //              tiles then comes out of the L2 cache) and read the threshold off the maxima of

@@ -16,8 +16,16 @@ through the host-buffer entry point (pinned host logits copied in every step, to
 back); `roofline` is the dominant kernel's (the pass over the logits) algorithmic bytes over its
 average launch time, measured with CUDA events between the kernels, against the measured copy
 bandwidth (MEASURED_PEAKS.json), with the whole step's figure beside it; `parity` compares the
-tokens of 129 rows spread over the whole batch with the CPU checker after the timed region; `cpu_baseline` is the reference's own CPU sampler
-(compiled from its sources into oracle/_ref) timed on this box's host cores.
+tokens of 129 rows spread over the whole batch with the CPU checker after the timed region;
+`cpu_baseline` is the reference's own CPU sampler (compiled from its sources into oracle/_ref)
+timed on this box's host cores. With more than one rank the line also carries `vocab_shard`: the
+same 1024 rows split by vocabulary columns over the ranks (strong scaling: local pass, one
+all-gather of packed records, merge), timed after the main region.
+
+  --workload logprobs | single-row | multi-slot | spec-verify | constrained | dflash   (one GPU)
+
+print a line of their own for the other entry points and the reference's own small shapes; the
+latency shapes are timed as CUDA graph replays with L2 flushed between calls.
 """
 import argparse
 import json
