@@ -72,6 +72,28 @@ int arcs_jcon_create(const char* schema_json, int32_t object_only, const uint32_
   return ok ? ARCS_OK : ARCS_ERR_UNSUPPORTED;
 }
 
+int arcs_tcon_create(int32_t kind, const char* tools_json, const uint32_t* byte_off, const uint8_t* bytes, int32_t V, arcs_jcon** out) {
+  if (!tools_json || !out || V < 0 || (V > 0 && (!byte_off || (!bytes && byte_off[V] > 0)))) return ARCS_ERR_ARG;
+  *out = nullptr;
+  if (kind != ARCS_TCON_GEMMA) return ARCS_ERR_UNSUPPORTED;  // (the Qwen form is served by the ranked head)
+  for (int32_t t = 0; t < V; ++t)
+    if (byte_off[t + 1] < byte_off[t]) return ARCS_ERR_ARG;
+  std::unique_ptr<arcs_jcon> h(new arcs_jcon);
+  Jcon& j = h->j;
+  j.au.reset(new Automaton(tools_json, Automaton::GEMMA));
+  j.why = j.au->why_not();
+  if (V > 0) {
+    j.byte_off.assign(byte_off, byte_off + V + 1);
+    j.bytes.assign(bytes, bytes + byte_off[V]);
+  } else {
+    j.byte_off.assign(1, 0u);
+  }
+  j.vocab.reset(new Automaton::Vocab(j.byte_off.data(), j.bytes.data(), V));
+  const bool ok = j.au->supported();
+  *out = h.release();
+  return ok ? ARCS_OK : ARCS_ERR_UNSUPPORTED;
+}
+
 const char* arcs_jcon_why(const arcs_jcon* h) { return h ? h->j.why.c_str() : "null handle"; }
 
 int arcs_jcon_check(const arcs_jcon* h, const char* text, int64_t len) {

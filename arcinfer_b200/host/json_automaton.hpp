@@ -51,9 +51,13 @@ struct Frame {
 };
 using Config = std::vector<Frame>;
 
-enum FrameType : uint8_t { F_TOP = 1, F_NUM, F_STR, F_LIT, F_ENUM, F_OBJ, F_ARR };
-// F_TOP.sub
-enum : uint8_t { T_LEAD = 0, T_VALUE = 1, T_TRAIL = 2 };
+enum FrameType : uint8_t { F_TOP = 1, F_NUM, F_STR, F_LIT, F_ENUM, F_OBJ, F_ARR, F_GSTR, F_GOBJ };
+// F_TOP.sub (G_*: the Gemma tool-call form)
+enum : uint8_t { T_LEAD = 0, T_VALUE = 1, T_TRAIL = 2, G_CALL = 3, G_NAME = 4, G_CLOSE = 5, G_END = 6 };
+// F_GSTR.sub: inside the opening <|"|>, inside the text (n: how much of the closing <|"|> has been seen)
+enum : uint8_t { GS_OPEN = 0, GS_BODY = 1 };
+// F_GOBJ.sub
+enum : uint8_t { GO_OPEN = 0, GO_KEY, GO_AFTER_COLON, GO_IN_VALUE, GO_AFTER_VALUE };
 // F_NUM.sub
 enum : uint8_t { N_MINUS = 0, N_ZERO, N_INT, N_DOT, N_FRAC, N_E, N_ESIGN, N_EXP };
 // F_STR.sub
@@ -63,6 +67,8 @@ enum : uint8_t { O_OPEN = 0, O_AFTER_COMMA, O_IN_KEY, O_AFTER_KEY, O_AFTER_COLON
 // F_ARR.sub
 enum : uint8_t { A_OPEN = 0, A_IN_VALUE, A_AFTER_ELEM, A_AFTER_COMMA };
 
+constexpr const char* kGemmaQuote = "<|\"|>";       // tcon::GemmaCall::kQ
+constexpr const char* kGemmaClose = "<tool_call|>";  // tcon::GemmaCall::kClose
 constexpr const char* kOtherKey = "\x01other";  // a key no property and no used key starts with (table walks only)
 
 inline bool is_ws(uint8_t c) { return c == ' ' || c == '\n' || c == '\r' || c == '\t'; }
@@ -70,6 +76,7 @@ inline bool is_ws(uint8_t c) { return c == ' ' || c == '\n' || c == '\r' || c ==
 
 class Automaton {
  public:
+  enum Dialect { JSON = 0, GEMMA = 1 };
   // schema_json: the JSON schema as text ("{}" = any value); object_only: the value must be an
   // object (json_object mode), as jcon::Checker(schema, object_only)
   Automaton(const std::string& schema_json, bool object_only) : object_only_(object_only) {
@@ -78,7 +85,25 @@ class Automaton {
       return;
     }
     std::vector<const JVal*> path;
-    supported_ = vet(root_, path);
+    supported_ = vet(root_, path, root_);
+  }
+  // The Gemma 4 tool-call form (tcon::GemmaCall, tools/tool_constraint.h:66-280): the text after
+  // <|tool_call> is call:NAME{key:value,...}<tool_call|>, keys bare words, strings between
+  // <|"|> delimiters, no whitespace; tools_json: the request's "tools" (:45-51).
+  Automaton(const std::string& tools_json, Dialect gemma) : dialect_(gemma) {
+    if (!JVal::parse(tools_json, root_)) {
+      why_ = "the tool list is not JSON";
+      return;
+    }
+    supported_ = true;
+    for (const JVal& t : root_.a) {
+      const JVal& f = t.has("function") ? t["function"] : t;
+      if (f["name"].str().empty()) continue;
+      const JVal* params = f["parameters"].is_object() ? &f["parameters"] : &any_schema();
+      tools_.push_back({f["name"].str(), params});
+      std::vector<const JVal*> path;
+      supported_ = supported_ && vet(*params, path, *params);
+    }
   }
   bool supported() const { return supported_; }
   const std::string& why_not() const { return why_; }
@@ -86,14 +111,14 @@ class Automaton {
   Config start() const {
     Config c(1);
     c[0].type = F_TOP;
-    c[0].sub = T_LEAD;
+    c[0].sub = dialect_ == GEMMA ? G_CALL : T_LEAD;
     return c;
   }
   // one more byte of the answer; false: no continuation fits (FAIL). `walk`: the call is part of a
   // table expansion, where keys that no property and no used key starts with are folded into one.
   bool step(Config& st, uint8_t c, bool walk = false) const;
   // PARTIAL or DONE for a configuration that has not failed (tools/json_constraint.h:37-47)
-  static Res classify(const Config& st) { return st.size() == 1 && st[0].sub == T_TRAIL ? DONE : PARTIAL; }
+  Res classify(const Config& st) const { return st.size() == 1 && st[0].sub == (dialect_ == GEMMA ? G_END : T_TRAIL) ? DONE : PARTIAL; }
   // Checker::check: FAIL / PARTIAL / DONE for a whole text
   Res check(const std::string& text) const {
     Config st = start();
@@ -133,8 +158,12 @@ class Automaton {
 
  private:
   JVal root_;
+  Dialect dialect_ = JSON;
   bool object_only_ = false, supported_ = false;
   std::string why_;
+  std::vector<std::pair<std::string, const JVal*>> tools_;  // (GEMMA) name, parameters
+  // the schema `$ref`s are resolved against: the schema itself, or the parameters of the tool the call names
+  const JVal& root_of(const Config& st) const { return dialect_ == GEMMA && st[0].node >= 0 ? node(st[0].node) : root_; }
   mutable std::vector<const JVal*> nodes_;
 
   int node_id(const JVal* p) const {
@@ -153,14 +182,14 @@ class Automaton {
   }
   const JVal& node(int id) const { return id < 0 ? any_schema() : *nodes_[(size_t)id]; }
   // :53-64, one level
-  const JVal& resolve(const JVal& sc) const {
+  static const JVal& resolve(const JVal& sc, const JVal& root) {
     const std::string ref = sc["$ref"].str();
     if (ref.empty()) return sc;
     for (const char* pre : {"#/$defs/", "#/definitions/"}) {
       const std::string p = pre;
-      if (ref.compare(0, p.size(), p) == 0) return root_[p.substr(2, p.size() - 3)][ref.substr(p.size())];
+      if (ref.compare(0, p.size(), p) == 0) return root[p.substr(2, p.size() - 3)][ref.substr(p.size())];
     }
-    return root_;
+    return root;
   }
   static bool has_type(const JVal& sc, const char* t) {  // :71-80
     const JVal& ty = sc["type"];
@@ -192,10 +221,16 @@ class Automaton {
     return nullptr;
   }
   static bool is_enum(const JVal& sc) { return sc["enum"].is_array() || sc.has("const"); }
-  static std::vector<std::string> options(const JVal& sc) {  // :113-115
+  // the text an allowed value is written as: compact JSON (:113-115), or, in the Gemma form, a
+  // string between its delimiters and anything else as JSON (tools/tool_constraint.h:171-174)
+  std::string text_of(const JVal& v) const {
+    if (dialect_ == GEMMA && v.is_string()) return std::string(kGemmaQuote) + v.s + kGemmaQuote;
+    return v.dump();
+  }
+  std::vector<std::string> options(const JVal& sc) const {
     std::vector<std::string> o;
-    if (sc.has("const")) o.push_back(sc["const"].dump());
-    for (const JVal& e : sc["enum"].a) o.push_back(e.dump());
+    if (sc.has("const")) o.push_back(text_of(sc["const"]));
+    for (const JVal& e : sc["enum"].a) o.push_back(text_of(e));
     return o;
   }
   struct CharSet {
@@ -209,23 +244,23 @@ class Automaton {
     bool meets(const CharSet& o) const { return (w[0] & o.w[0]) | (w[1] & o.w[1]) | (w[2] & o.w[2]) | (w[3] & o.w[3]); }
   };
   // the characters a value of this schema can start with (a superset: a cycle of references gives all)
-  CharSet first_chars(const JVal& sc0, std::vector<const JVal*>& path) const {
+  CharSet first_chars(const JVal& sc0, std::vector<const JVal*>& path, const JVal& root) const {
     CharSet cs;
-    const JVal& sc = resolve(sc0);
+    const JVal& sc = resolve(sc0, root);
     if (std::find(path.begin(), path.end(), &sc) != path.end() || path.size() > 64) {
       cs.all();
       return cs;
     }
     path.push_back(&sc);
     if (const JVal* alt = alternatives(sc)) {
-      for (const JVal& br : alt->a) cs.join(first_chars(br, path));
+      for (const JVal& br : alt->a) cs.join(first_chars(br, path, root));
     } else if (is_enum(sc)) {
       for (const std::string& o : options(sc))
         if (!o.empty()) cs.add((unsigned char)o[0]);
     } else {
       if (has_type(sc, "object")) cs.add('{');
       if (has_type(sc, "array")) cs.add('[');
-      if (has_type(sc, "string")) cs.add('"');
+      if (has_type(sc, "string")) cs.add(dialect_ == GEMMA ? '<' : '"');
       if (has_type(sc, "number")) {
         cs.add('-');
         for (char d = '0'; d <= '9'; ++d) cs.add((unsigned char)d);
@@ -241,8 +276,8 @@ class Automaton {
   }
   // every schema node a value can be checked against: are its alternatives told apart by their
   // first character, and is no enum option a proper prefix of another?
-  bool vet(const JVal& sc0, std::vector<const JVal*>& path) {
-    const JVal& sc = resolve(sc0);
+  bool vet(const JVal& sc0, std::vector<const JVal*>& path, const JVal& root) {
+    const JVal& sc = resolve(sc0, root);
     if (std::find(path.begin(), path.end(), &sc) != path.end()) return true;
     if (path.size() > 256) {
       why_ = "schema nested too deep";
@@ -254,7 +289,7 @@ class Automaton {
       std::vector<CharSet> sets;
       for (const JVal& br : alt->a) {
         std::vector<const JVal*> p2;
-        sets.push_back(first_chars(br, p2));
+        sets.push_back(first_chars(br, p2, root));
       }
       for (size_t i = 0; i < sets.size() && ok; ++i)
         for (size_t j = i + 1; j < sets.size() && ok; ++j)
@@ -262,7 +297,7 @@ class Automaton {
             ok = false;
             why_ = "anyOf / oneOf branches that can start with the same character";
           }
-      for (const JVal& br : alt->a) ok = ok && vet(br, path);
+      for (const JVal& br : alt->a) ok = ok && vet(br, path, root);
     } else if (is_enum(sc)) {
       const std::vector<std::string> o = options(sc);
       for (size_t i = 0; i < o.size() && ok; ++i)
@@ -272,9 +307,9 @@ class Automaton {
             why_ = "an enum option that is a proper prefix of another";
           }
     } else {
-      for (const auto& kv : sc["properties"].o) ok = ok && vet(kv.second, path);
-      if (sc["additionalProperties"].is_object()) ok = ok && vet(sc["additionalProperties"], path);
-      if (sc["items"].is_object()) ok = ok && vet(sc["items"], path);
+      for (const auto& kv : sc["properties"].o) ok = ok && vet(kv.second, path, root);
+      if (sc["additionalProperties"].is_object()) ok = ok && vet(sc["additionalProperties"], path, root);
+      if (sc["items"].is_object()) ok = ok && vet(sc["items"], path, root);
     }
     path.pop_back();
     return ok;
@@ -289,6 +324,8 @@ class Automaton {
     return addl.is_object() || addl.as_bool(false) || (!props.is_object() && !addl.is_bool());
   }
   bool key_allowed(const Frame& obj, const std::string& k, bool prefix) const;
+  bool step_gemma_top(Config& st, uint8_t c) const;
+  bool step_gemma_object(Config& st, uint8_t c, bool walk) const;
 };
 
 // a configuration as a string: equal strings, equal futures

@@ -21,11 +21,12 @@ inline bool Automaton::key_allowed(const Frame& obj, const std::string& k, bool 
 // A value of schema `node` at nesting `depth` starts with byte c (tools/json_constraint.h:92-133).
 inline bool Automaton::start_value(Config& st, int node_idx, int depth, uint8_t c) const {
   if (depth > 32) return false;                                             // :93
-  const JVal& sc = resolve(node(node_idx));
+  const JVal& root = root_of(st);
+  const JVal& sc = resolve(node(node_idx), root);
   if (const JVal* alt = alternatives(sc)) {                                 // :96-108 (branches told apart by c, see vet)
     for (const JVal& br : alt->a) {
       std::vector<const JVal*> path;
-      if (first_chars(br, path).has(c)) return start_value(st, node_id(&br), depth + 1, c);
+      if (first_chars(br, path, root).has(c)) return start_value(st, node_id(&br), depth + 1, c);
     }
     return false;
   }
@@ -39,8 +40,17 @@ inline bool Automaton::start_value(Config& st, int node_idx, int depth, uint8_t 
   }
   if (c == '{') {
     if (!has_type(sc, "object")) return false;
-    f.type = F_OBJ;
-    f.sub = O_OPEN;
+    f.type = dialect_ == GEMMA ? F_GOBJ : F_OBJ;
+    f.sub = dialect_ == GEMMA ? (uint8_t)GO_OPEN : (uint8_t)O_OPEN;
+    st.push_back(f);
+    return true;
+  }
+  if (dialect_ == GEMMA && c == '<') {  // tools/tool_constraint.h:162, :183-190: <|"|> text <|"|>
+    if (!has_type(sc, "string")) return false;
+    f.type = F_GSTR;
+    f.sub = GS_OPEN;
+    f.node = -1;
+    f.n = 1;
     st.push_back(f);
     return true;
   }
@@ -51,7 +61,7 @@ inline bool Automaton::start_value(Config& st, int node_idx, int depth, uint8_t 
     st.push_back(f);
     return true;
   }
-  if (c == '"') {
+  if (c == '"' && dialect_ == JSON) {
     if (!has_type(sc, "string")) return false;
     f.type = F_STR;
     f.node = -1;
@@ -85,8 +95,13 @@ inline bool Automaton::complete(Config& st, bool walk) const {
   st.pop_back();
   Frame& p = st.back();
   if (p.type == F_TOP) {
-    p.sub = T_TRAIL;
+    p.sub = dialect_ == GEMMA ? (uint8_t)G_CLOSE : (uint8_t)T_TRAIL;  // (GEMMA: the close marker follows, :93)
     p.ws = 0;
+    p.n = 0;
+    return true;
+  }
+  if (p.type == F_GOBJ) {
+    p.sub = GO_AFTER_VALUE;
     return true;
   }
   if (p.type == F_ARR) {
@@ -126,6 +141,7 @@ inline bool Automaton::step(Config& st, uint8_t c, bool walk) const {
     Frame& f = st.back();
     switch (f.type) {
       case F_TOP:
+        if (dialect_ == GEMMA) return step_gemma_top(st, c);
         if (f.sub == T_LEAD) {                               // :38-41
           if (is_ws(c)) return true;
           if (object_only_ && c != '{') return false;
@@ -155,7 +171,7 @@ inline bool Automaton::step(Config& st, uint8_t c, bool walk) const {
               f.sub = N_DOT;
               return true;
             }
-            if (c == 'e' || c == 'E') {
+            if ((c == 'e' || c == 'E') && dialect_ == JSON) {  // (the Gemma form has no exponent, tools/tool_constraint.h:191-208)
               if (f.flag) return false;
               f.sub = N_E;
               return true;
@@ -167,7 +183,7 @@ inline bool Automaton::step(Config& st, uint8_t c, bool walk) const {
             return true;
           case N_FRAC:
             if (digit) return true;
-            if (c == 'e' || c == 'E') {
+            if ((c == 'e' || c == 'E') && dialect_ == JSON) {
               f.sub = N_E;
               return true;
             }
@@ -289,7 +305,7 @@ inline bool Automaton::step(Config& st, uint8_t c, bool walk) const {
       }
       case F_ARR: {                                          // :256-281
         const JVal& sc = node(f.node);
-        if (is_ws(c)) return f.sub != A_IN_VALUE && ++f.ws <= 8;
+        if (is_ws(c) && dialect_ == JSON) return f.sub != A_IN_VALUE && ++f.ws <= 8;
         const int64_t mn = sc["minItems"].as_int(0), mx = sc["maxItems"].as_int(1 << 30);
         if (c == ']' && (f.sub == A_OPEN || f.sub == A_AFTER_ELEM)) {
           if (f.n < mn) return false;
@@ -308,9 +324,136 @@ inline bool Automaton::step(Config& st, uint8_t c, bool walk) const {
         const JVal* items = sc["items"].is_object() ? &sc["items"] : nullptr;
         return start_value(st, items ? node_id(items) : -1, depth + 1, c);
       }
+      case F_GSTR:                                           // tools/tool_constraint.h:183-190
+        if (f.sub == GS_OPEN) {
+          if (c != (uint8_t)kGemmaQuote[f.n]) return false;
+          if (++f.n == 5) {
+            f.sub = GS_BODY;
+            f.n = 0;
+          }
+          return true;
+        }
+        // any text up to the first closing delimiter (no proper border in <|"|>: after a mismatch
+        // only a '<' can begin it again)
+        if (c == (uint8_t)kGemmaQuote[f.n]) {
+          if (++f.n == 5) return complete(st, walk);
+        } else {
+          f.n = c == '<' ? 1 : 0;
+        }
+        return true;
+      case F_GOBJ:
+        return step_gemma_object(st, c, walk);
       default:
         return false;
     }
+  }
+}
+
+// call:NAME{...}<tool_call|> (tools/tool_constraint.h:79-94)
+inline bool Automaton::step_gemma_top(Config& st, uint8_t c) const {
+  Frame& f = st.back();
+  switch (f.sub) {
+    case G_CALL:
+      if (c != (uint8_t)"call:"[f.n]) return false;
+      if (++f.n == 5) {
+        f.sub = G_NAME;
+        f.text.clear();
+      }
+      return true;
+    case G_NAME: {
+      if (c != '{') {  // :84-88: the name so far must begin some tool's name
+        f.text.push_back((char)c);
+        for (const auto& t : tools_)
+          if (t.first.compare(0, f.text.size(), f.text) == 0) return true;
+        return false;
+      }
+      const JVal* params = nullptr;  // :54-61: the last tool of that name
+      for (const auto& t : tools_)
+        if (t.first == f.text) params = t.second;
+      if (!params) return false;
+      f.node = node_id(params);  // (what $ref is resolved against from here on)
+      f.text.clear();
+      f.sub = T_VALUE;
+      const JVal& sc = resolve(*params, *params);
+      if (alternatives(sc)) return start_value(st, node_id(params), 0, c);  // :133-147 come before the "always an object" of :149
+      Frame o;
+      o.type = F_GOBJ;
+      o.sub = GO_OPEN;
+      o.node = node_id(&sc);
+      o.depth = 0;
+      st.push_back(o);
+      return true;
+    }
+    case G_CLOSE:
+      if (c != (uint8_t)kGemmaClose[f.n]) return false;
+      if (++f.n == (int32_t)std::strlen(kGemmaClose)) f.sub = G_END;
+      return true;
+    default:  // G_END: nothing may follow (:94); T_VALUE: a value frame is on top, not this one
+      return false;
+  }
+}
+
+// {key:value,...} with bare keys and no whitespace (tools/tool_constraint.h:209-257)
+inline bool Automaton::step_gemma_object(Config& st, uint8_t c, bool walk) const {
+  Frame& f = st.back();
+  const JVal& sc = node(f.node);
+  auto closes = [&]() {  // :222-226
+    for (const JVal& r : sc["required"].a)
+      if (!std::binary_search(f.seen.begin(), f.seen.end(), r.str())) return false;
+    return complete(st, walk);
+  };
+  const bool key_char = std::isalnum(c) || c == '_' || c == '-' || c == '.' || c == '$';  // :234
+  switch (f.sub) {
+    case GO_OPEN:
+      if (c == '}') return closes();
+      f.sub = GO_KEY;
+      f.text.clear();
+      [[fallthrough]];
+    case GO_KEY:
+      if (key_char) {
+        if (f.text != kOtherKey) {
+          f.text.push_back((char)c);
+          if (!key_allowed(f, f.text, true)) return false;  // :236-247 with prefix
+          if (walk && any_key_of(sc)) {  // fold, as for JSON keys
+            bool prefix_of_known = false;
+            for (const auto& kv : sc["properties"].o) prefix_of_known = prefix_of_known || kv.first.compare(0, f.text.size(), f.text) == 0;
+            for (const std::string& k : f.seen) prefix_of_known = prefix_of_known || k.compare(0, f.text.size(), f.text) == 0;
+            if (!prefix_of_known) f.text = kOtherKey;
+          }
+        }
+        return true;
+      }
+      if (c != ':') return false;  // :249
+      if (f.text == kOtherKey) {
+        if (!any_key_of(sc) || f.flag) return false;
+        f.flag = 1;
+      } else {
+        if (f.text.empty() || !key_allowed(f, f.text, false)) return false;
+        f.seen.insert(std::upper_bound(f.seen.begin(), f.seen.end(), f.text), f.text);
+      }
+      f.sub = GO_AFTER_COLON;
+      return true;
+    case GO_AFTER_COLON: {  // :251-255
+      const JVal& props = sc["properties"];
+      const JVal& addl = sc["additionalProperties"];
+      const JVal* vs = f.text == kOtherKey || props[f.text].is_null() ? (addl.is_object() ? &addl : nullptr) : &props[f.text];
+      f.sub = GO_IN_VALUE;
+      const int depth = f.depth;
+      return start_value(st, vs ? node_id(vs) : -1, depth + 1, c);
+    }
+    case GO_AFTER_VALUE:
+      if (c == '}') return closes();
+      if (c != ',') return false;  // :228
+      {
+        bool more = any_key_of(sc);  // :229: a comma only where another key can follow
+        for (const auto& kv : sc["properties"].o) more = more || !std::binary_search(f.seen.begin(), f.seen.end(), kv.first);
+        if (!more) return false;
+      }
+      f.sub = GO_KEY;
+      f.text.clear();
+      return true;
+    default:
+      return false;
   }
 }
 

@@ -50,6 +50,25 @@ class JsonConstraint:
         if rc != 0:
             raise ValueError(f"arcs_jcon_create failed with code {rc}")
 
+    @classmethod
+    def gemma_call(cls, tools_json, byte_off, bytes_):
+        """The Gemma tool-call form (tcon::GemmaCall, tools/tool_constraint.h:66-280): texts are
+        what follows <|tool_call>; tools_json: the request's "tools" array as JSON text."""
+        lib = _load()
+        self = cls.__new__(cls)
+        self._h = C.c_void_p()
+        byte_off = np.ascontiguousarray(byte_off, dtype=np.uint32)
+        bytes_ = np.ascontiguousarray(bytes_, dtype=np.uint8)
+        self.V = len(byte_off) - 1
+        rc = lib.arcs_tcon_create(0, tools_json.encode(), byte_off.ctypes.data_as(C.c_void_p), bytes_.ctypes.data_as(C.c_void_p), self.V, C.byref(self._h))
+        if rc == ERR_UNSUPPORTED:
+            why = lib.arcs_jcon_why(self._h).decode()
+            self.close()
+            raise Unsupported(why)
+        if rc != 0:
+            raise ValueError(f"arcs_tcon_create failed with code {rc}")
+        return self
+
     def close(self):
         if getattr(self, "_h", None):
             _load().arcs_jcon_destroy(self._h)

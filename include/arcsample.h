@@ -273,6 +273,18 @@ int arcs_jcon_check(const arcs_jcon* h, const char* text, int64_t len);
 int arcs_jcon_table(arcs_jcon* h, const char* text, int64_t len, const uint16_t** table, int32_t* n_states,
                     int32_t* dead, const uint8_t** done, int32_t* text_state);
 void arcs_jcon_cache_stats(const arcs_jcon* h, int64_t* hits, int64_t* misses);
+/* The same machinery for a tool call (tools/tool_constraint.h): the handle's text is what follows
+ * the call's open marker; check / table / why / destroy are the arcs_jcon_* functions above.
+ * ARCS_TCON_GEMMA: tcon::GemmaCall (:66-280), call:NAME{key:value,...}<tool_call|> with bare keys,
+ * strings between <|"|> delimiters, no whitespace, no exponents; tools_json is the request's
+ * "tools" array (:45-51). The same two schema forms are refused as for JSON. Control tokens: the
+ * reference lets the pieces <|"|> and <tool_call|> through inside a call (special_ok, :75); give
+ * arcs_dfa_mask a `special` array that leaves those two out. ARCS_TCON_QWEN (tcon::QwenCall,
+ * :285-371: raw-text parameter values ended by a marker) is not restated as an automaton:
+ * ARCS_ERR_UNSUPPORTED; such calls keep the reference's predicate over the ranked head. */
+enum { ARCS_TCON_GEMMA = 0, ARCS_TCON_QWEN = 1 };
+int arcs_tcon_create(int32_t kind, const char* tools_json, const uint32_t* byte_off, const uint8_t* bytes, int32_t V,
+                     arcs_jcon** out);
 void arcs_jcon_destroy(arcs_jcon* h);
 
 /* ------------------------------------------------------------------------------------------

@@ -28,18 +28,30 @@ def _vocab(g):
     return off, by
 
 
-def _decode(si, doc, steps, seed):
+def _decode(si, doc, steps, seed, tools=None):
     """One constrained decoding on the GPU. With `doc`, tokens that continue it are favoured so
     strongly that the answer spells it (the mask still decides what may be drawn); without, the
-    walk is free. Returns (text, ended)."""
+    walk is free. tools: a tool list, for the Gemma tool-call form instead of schema si.
+    Returns (text, ended)."""
     import arcinfer_b200 as ab
 
-    schema, obj = SCHEMAS[si]
     g = np.random.default_rng(seed)
-    off, by = _vocab(g)
+    if tools is None:
+        schema, obj = SCHEMAS[si]
+        off, by = _vocab(g)
+        jc = jcon.JsonConstraint(schema, obj, off, by)
+        check = lambda text: ref_check(schema, obj, text)
+    else:
+        import test_tcon
+
+        toks, off, by = test_tcon.call_vocab(g, 3000)
+        off2, by2 = synth.make_vocab(g, V - len(toks))
+        off = np.concatenate([off, off2[1:] + off[-1]]).astype(np.uint32)
+        by = np.concatenate([by, by2[: off2[-1]]])
+        jc = jcon.JsonConstraint.gemma_call(tools, off, by)
+        check = test_tcon.ref_check
     lens = np.diff(off.astype(np.int64))
     pieces = [by[off[t] : off[t + 1]].tobytes() for t in range(V)]
-    jc = jcon.JsonConstraint(schema, obj, off, by)
     d_off, d_by = torch.from_numpy(off.view(np.int32)).cuda(), torch.from_numpy(by).cuda()
     params = torch.from_numpy(make_params(1, temperature=0.9, top_k=40, top_p=0.95).view(np.uint8)).cuda()
     mask_row = torch.zeros(1, dtype=torch.int32, device="cuda")
@@ -74,7 +86,7 @@ def _decode(si, doc, steps, seed):
         assert 0 <= tok < V and allowed[tok], (si, step, text, tok)
         text += pieces[tok]
         if orc.ref is not None:
-            assert ref_check(schema, obj, text) != jcon.FAIL, (si, step, text)
+            assert check(text) != jcon.FAIL, (si, step, text)
     hits, misses = jc.cache_stats()
     assert hits + misses >= 1
     return text, ended
@@ -96,3 +108,15 @@ def test_constrained_decoding_spells_a_valid_document(si):
 def test_free_constrained_walk_stays_a_prefix(si):
     text, ended = _decode(si, None, 40, 900 + si)
     assert ended or len(text) > 0
+
+
+def test_tool_call_decoding_spells_a_valid_call():
+    """The Gemma tool-call form through the same pipeline (tools/tool_constraint.h:66-280)."""
+    import test_tcon
+
+    for k, call in enumerate(test_tcon.CALLS[:5]):
+        d = call.encode()
+        text, ended = _decode(0, d, 4 * len(d) + 8, 950 + k, tools=test_tcon.TOOLS)
+        assert ended and text == d, text
+        if orc.ref is not None:
+            assert test_tcon.ref_check(text) == jcon.DONE

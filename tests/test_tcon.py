@@ -1,0 +1,124 @@
+"""The Gemma tool-call form as a byte automaton (arcs_tcon_create + the arcs_jcon_* functions)
+against the reference's tcon::GemmaCall::check (oracle/_ref, tools/tool_constraint.h:66-280): every
+prefix of valid and damaged calls, and token by token over a synthetic vocabulary (the table's
+mask bit must equal check(text + piece) != FAIL). No GPU needed."""
+import json
+
+import numpy as np
+import pytest
+
+import orc
+from arcinfer_b200 import jcon
+from test_jcon import damaged
+
+F, P, D = jcon.FAIL, jcon.PARTIAL, jcon.DONE
+Q = '<|"|>'
+END = "<tool_call|>"
+
+TOOLS = json.dumps([
+    {"type": "function", "function": {"name": "get_weather", "parameters": {
+        "type": "object", "properties": {"city": {"type": "string"}, "days": {"type": "integer"}, "units": {"enum": ["c", "f", 3]},
+                                         "opts": {"type": "object", "properties": {"deep": {"type": "boolean"}}, "additionalProperties": True}},
+        "required": ["city"]}}},
+    {"type": "function", "function": {"name": "get", "parameters": {"type": "object"}}},
+    {"name": "edit.file", "parameters": {
+        "$defs": {"R": {"type": "object", "properties": {"from": {"type": "integer"}, "to": {"type": "integer"}}, "required": ["from"]}},
+        "type": "object", "properties": {"path": {"type": "string"}, "ranges": {"type": "array", "items": {"$ref": "#/$defs/R"}, "minItems": 1, "maxItems": 2},
+                                         "mode": {"anyOf": [{"type": "null"}, {"const": "fast"}, {"type": "number"}]}},
+        "required": ["path", "ranges"], "additionalProperties": False}},
+    {"type": "function", "function": {"name": "noargs"}},
+])  # fmt: skip
+
+CALLS = [
+    f"call:get_weather{{city:{Q}Oslo, NO{Q},days:3,units:{Q}c{Q}}}{END}",
+    f"call:get_weather{{units:3,opts:{{deep:true,x-1:[1,-2.5,{Q}a<|b{Q},{{}}],y:null}},city:{Q}{Q}}}{END}",
+    f"call:get{{anything:[{{k:{Q}v{Q}}},0,-0.5],$x:false}}{END}",
+    f"call:get{{}}{END}",
+    f"call:edit.file{{path:{Q}a/b.txt{Q},ranges:[{{from:1,to:2}},{{from:30}}],mode:{Q}fast{Q}}}{END}",
+    f"call:edit.file{{ranges:[{{to:5,from:0}}],path:{Q}p{Q},mode:-1.25}}{END}",
+    f"call:edit.file{{path:{Q}p{Q},ranges:[{{from:7}}],mode:null}}{END}",
+    f"call:noargs{{free:1}}{END}",
+]
+
+
+def ref_check(text):
+    return orc.ref.ref_tcon_check(0, TOOLS.encode(), text, len(text))
+
+
+needs_ref = pytest.mark.skipif(orc.ref is None, reason="oracle/_ref/libarcs_ref.so not built (needs the reference tree)")
+EMPTY_VOCAB = (np.zeros(1, np.uint32), np.zeros(0, np.uint8))
+
+
+def test_calls_without_the_reference():
+    tc = jcon.JsonConstraint.gemma_call(TOOLS, *EMPTY_VOCAB)
+    for call in CALLS:
+        assert tc.check(call) == D, call
+        assert tc.check(call[:-1]) == P and tc.check(call + "x") == F
+    for bad in ["call:nope{", "call:get_weather{}" + END, "call:get_weather{city:1", "call:get_weather{city:" + Q + "a" + Q + ",city:",
+                "call:edit.file{path:" + Q + "p" + Q + ",ranges:[]", "call:get{a: 1", "call:get{a:1e", "call:get{:"]:
+        assert tc.check(bad) == F, bad
+    with pytest.raises(jcon.Unsupported):
+        jcon.JsonConstraint.gemma_call(json.dumps([{"name": "t", "parameters": {"type": "object", "properties": {"v": {"anyOf": [{"type": "integer"}, {"type": "number"}]}}}}]), *EMPTY_VOCAB)
+    lib = jcon._load()
+    import ctypes as C
+
+    h = C.c_void_p()
+    assert lib.arcs_tcon_create(1, b"[]", None, None, 0, C.byref(h)) == jcon.ERR_UNSUPPORTED  # the Qwen form: not an automaton here
+
+
+@needs_ref
+def test_every_prefix_against_the_reference_checker():
+    rng = np.random.default_rng(21)
+    tc = jcon.JsonConstraint.gemma_call(TOOLS, *EMPTY_VOCAB)
+    n = 0
+    for call in CALLS:
+        for text in [call.encode()] + damaged(call, rng, 60):
+            for cut in range(len(text) + 1):
+                got, want = tc.check(text[:cut]), ref_check(text[:cut])
+                assert got == want, (text[:cut], got, want)
+                n += 1
+                if want == F:
+                    break
+            if cut < len(text):
+                assert tc.check(text) == ref_check(text) == F
+    assert n > 5000
+
+
+def call_vocab(rng, n_random=1200):
+    toks = [bytes([b]) for b in range(256)]
+    frag = ["call:", "call:get", "get_", "weather", "_weather{", "edit", ".file", "edit.file{", "noargs", "{}", "}" + END, END, "<tool", "_call|>", "<|", '"|>', Q, Q + ",", "," , ":" + Q,
+            "city", "city:", "days:", "days:3", "units", "opts:{", "deep:", "true", "false", "null", "tru", "path:", "ranges:[", "ranges:[{", "from:", "to:", "{from:", "mode:", "mode:" + Q + "fast" + Q,
+            "fast", "}]", "},{", "]}", "}}", "[1,", "-2.5", "0.", "12", "3}", "3,", ":[", "x-1:", "$x:", "a<|b", "<", "|", "free:1"]
+    toks += [f.encode() for f in frag]
+    src = np.frombuffer(b'call:get_wathrdi.fnos{}[],<|">-0123456789$xyzk', np.uint8)
+    printable = np.frombuffer(bytes(range(0x20, 0x7F)), np.uint8)
+    for _ in range(n_random):
+        ln = int(rng.integers(1, 8))
+        a = src if rng.random() < 0.7 else printable
+        toks.append(bytes(a[rng.integers(0, len(a), ln)]))
+    toks.append(b"")
+    off = np.zeros(len(toks) + 1, np.uint32)
+    off[1:] = np.cumsum([len(t) for t in toks])
+    return toks, off, np.frombuffer(b"".join(toks), np.uint8).copy()
+
+
+@needs_ref
+def test_table_mask_is_the_per_candidate_predicate():
+    rng = np.random.default_rng(8)
+    toks, off, by = call_vocab(rng)
+    tc = jcon.JsonConstraint.gemma_call(TOOLS, off, by)
+    steps = 0
+    for call in CALLS:
+        d = call.encode()
+        for cut in sorted(set(rng.integers(0, len(d), 16).tolist() + [0, len(d) - 1])):
+            text = d[:cut]
+            table, dead, done, ts = tc.table(text)
+            assert ts == ref_check(text) == P
+            allowed, end = jcon.walk_mask(table, dead, off, by)
+            for t, piece in enumerate(toks):
+                want = ref_check(text + piece) if piece else F
+                assert bool(allowed[t]) == (want != F), (text, piece, want)
+                if want != F:
+                    assert bool(done[end[t]]) == (want == D), (text, piece, want)
+            steps += 1
+    assert steps > 60
