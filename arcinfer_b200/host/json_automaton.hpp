@@ -76,6 +76,7 @@ inline bool is_ws(uint8_t c) { return c == ' ' || c == '\n' || c == '\r' || c ==
 
 class Automaton {
  public:
+  using State = Config;
   enum Dialect { JSON = 0, GEMMA = 1 };
   // schema_json: the JSON schema as text ("{}" = any value); object_only: the value must be an
   // object (json_object mode), as jcon::Checker(schema, object_only)
@@ -155,6 +156,9 @@ class Automaton {
     }
   };
   bool table(const Config& from, const Vocab& vocab, Table& out, int max_states = 8192) const;
+  std::string key(const Config& st) const;
+  // whether an object of this schema takes keys it does not name (tools/json_constraint.h:204)
+  static bool any_key_of_public(const JVal& sc) { return any_key_of(sc); }
 
  private:
   JVal root_;
@@ -329,6 +333,8 @@ class Automaton {
 };
 
 // a configuration as a string: equal strings, equal futures
+inline std::string config_key(const Config& st);
+inline std::string Automaton::key(const Config& st) const { return config_key(st); }
 inline std::string config_key(const Config& st) {
   std::string k;
   for (const Frame& f : st) {
@@ -352,21 +358,25 @@ inline std::string config_key(const Config& st) {
   return k;
 }
 
-inline bool Automaton::table(const Config& from, const Vocab& vocab, Table& out, int max_states) const {
+// The expansion itself, for any machine M with a state type, `bool step(State&, uint8_t, bool walk)`,
+// `std::string key(const State&)` (equal keys, equal futures) and `Res classify(const State&)`.
+template <class M>
+bool build_table(const M& m, const typename M::State& from, const Automaton::Vocab& vocab, Automaton::Table& out, int max_states) {
+  using State = typename M::State;
   if (max_states > 65534) max_states = 65534;
   std::unordered_map<std::string, int> ids;
-  std::vector<Config> cfg;
+  std::vector<State> cfg;
   std::vector<std::vector<int>> next;  // [state][256]: -2 not worked out, -1 dead
-  ids.emplace(config_key(from), 0);
+  ids.emplace(m.key(from), 0);
   cfg.push_back(from);
   next.emplace_back(256, -2);
   bool full = false;
   auto trans = [&](int s, uint8_t c) -> int {
     int& slot = next[(size_t)s][c];
     if (slot != -2) return slot;
-    Config t = cfg[(size_t)s];
-    if (!step(t, c, true)) return slot = -1;
-    const std::string key = config_key(t);
+    State t = cfg[(size_t)s];
+    if (!m.step(t, c, true)) return slot = -1;
+    const std::string key = m.key(t);
     auto it = ids.find(key);
     if (it == ids.end()) {
       if ((int)cfg.size() >= max_states) {
@@ -409,11 +419,15 @@ inline bool Automaton::table(const Config& from, const Vocab& vocab, Table& out,
   out.next.assign((size_t)(S + 1) * 256, (uint16_t)S);
   out.done.assign((size_t)S + 1, 0);
   for (int s = 0; s < S; ++s) {
-    out.done[(size_t)s] = classify(cfg[(size_t)s]) == DONE;
+    out.done[(size_t)s] = m.classify(cfg[(size_t)s]) == DONE;
     for (int c = 0; c < 256; ++c)
       if (next[(size_t)s][(size_t)c] >= 0) out.next[(size_t)s * 256 + (size_t)c] = (uint16_t)next[(size_t)s][(size_t)c];
   }
   return true;
+}
+
+inline bool Automaton::table(const Config& from, const Vocab& vocab, Table& out, int max_states) const {
+  return build_table(*this, from, vocab, out, max_states);
 }
 
 }  // namespace jcon

@@ -51,7 +51,13 @@ class JsonConstraint:
             raise ValueError(f"arcs_jcon_create failed with code {rc}")
 
     @classmethod
-    def gemma_call(cls, tools_json, byte_off, bytes_):
+    def qwen_call(cls, tools_json, byte_off, bytes_):
+        """The Qwen 3.x tool-call form (tcon::QwenCall, tools/tool_constraint.h:285-371): texts are
+        what follows <tool_call>."""
+        return cls.gemma_call(tools_json, byte_off, bytes_, kind=1)
+
+    @classmethod
+    def gemma_call(cls, tools_json, byte_off, bytes_, kind=0):
         """The Gemma tool-call form (tcon::GemmaCall, tools/tool_constraint.h:66-280): texts are
         what follows <|tool_call>; tools_json: the request's "tools" array as JSON text."""
         lib = _load()
@@ -60,7 +66,7 @@ class JsonConstraint:
         byte_off = np.ascontiguousarray(byte_off, dtype=np.uint32)
         bytes_ = np.ascontiguousarray(bytes_, dtype=np.uint8)
         self.V = len(byte_off) - 1
-        rc = lib.arcs_tcon_create(0, tools_json.encode(), byte_off.ctypes.data_as(C.c_void_p), bytes_.ctypes.data_as(C.c_void_p), self.V, C.byref(self._h))
+        rc = lib.arcs_tcon_create(kind, tools_json.encode(), byte_off.ctypes.data_as(C.c_void_p), bytes_.ctypes.data_as(C.c_void_p), self.V, C.byref(self._h))
         if rc == ERR_UNSUPPORTED:
             why = lib.arcs_jcon_why(self._h).decode()
             self.close()

@@ -279,9 +279,11 @@ void arcs_jcon_cache_stats(const arcs_jcon* h, int64_t* hits, int64_t* misses);
  * strings between <|"|> delimiters, no whitespace, no exponents; tools_json is the request's
  * "tools" array (:45-51). The same two schema forms are refused as for JSON. Control tokens: the
  * reference lets the pieces <|"|> and <tool_call|> through inside a call (special_ok, :75); give
- * arcs_dfa_mask a `special` array that leaves those two out. ARCS_TCON_QWEN (tcon::QwenCall,
- * :285-371: raw-text parameter values ended by a marker) is not restated as an automaton:
- * ARCS_ERR_UNSUPPORTED; such calls keep the reference's predicate over the ranked head. */
+ * arcs_dfa_mask a `special` array that leaves those two out.
+ * ARCS_TCON_QWEN: tcon::QwenCall (:285-371), <function=NAME> then <parameter=KEY> VALUE
+ * </parameter> blocks, </function> </tool_call>, up to two blanks between the parts; a "string"
+ * (or untyped) value is raw text without the two parameter markers, any other is JSON for its
+ * schema (its own root, as jcon::Checker(vs, false)), optionally followed by one newline. */
 enum { ARCS_TCON_GEMMA = 0, ARCS_TCON_QWEN = 1 };
 int arcs_tcon_create(int32_t kind, const char* tools_json, const uint32_t* byte_off, const uint8_t* bytes, int32_t V,
                      arcs_jcon** out);

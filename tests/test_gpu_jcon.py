@@ -28,7 +28,7 @@ def _vocab(g):
     return off, by
 
 
-def _decode(si, doc, steps, seed, tools=None):
+def _decode(si, doc, steps, seed, tools=None, qwen=False):
     """One constrained decoding on the GPU. With `doc`, tokens that continue it are favoured so
     strongly that the answer spells it (the mask still decides what may be drawn); without, the
     walk is free. tools: a tool list, for the Gemma tool-call form instead of schema si.
@@ -44,12 +44,12 @@ def _decode(si, doc, steps, seed, tools=None):
     else:
         import test_tcon
 
-        toks, off, by = test_tcon.call_vocab(g, 3000)
+        toks, off, by = (test_tcon.qwen_vocab if qwen else test_tcon.call_vocab)(g, 3000)
         off2, by2 = synth.make_vocab(g, V - len(toks))
         off = np.concatenate([off, off2[1:] + off[-1]]).astype(np.uint32)
         by = np.concatenate([by, by2[: off2[-1]]])
-        jc = jcon.JsonConstraint.gemma_call(tools, off, by)
-        check = test_tcon.ref_check
+        jc = (jcon.JsonConstraint.qwen_call if qwen else jcon.JsonConstraint.gemma_call)(tools, off, by)
+        check = test_tcon.ref_qcheck if qwen else test_tcon.ref_check
     lens = np.diff(off.astype(np.int64))
     pieces = [by[off[t] : off[t + 1]].tobytes() for t in range(V)]
     d_off, d_by = torch.from_numpy(off.view(np.int32)).cuda(), torch.from_numpy(by).cuda()
@@ -120,3 +120,15 @@ def test_tool_call_decoding_spells_a_valid_call():
         assert ended and text == d, text
         if orc.ref is not None:
             assert test_tcon.ref_check(text) == jcon.DONE
+
+
+def test_qwen_tool_call_decoding_spells_a_valid_call():
+    """The Qwen 3.x tool-call form through the same pipeline (tools/tool_constraint.h:285-371)."""
+    import test_tcon
+
+    for k, call in enumerate(test_tcon.QCALLS[:4]):
+        d = call.encode()
+        text, ended = _decode(0, d, 4 * len(d) + 8, 970 + k, tools=test_tcon.QTOOLS, qwen=True)
+        assert ended and text == d, text
+        if orc.ref is not None:
+            assert test_tcon.ref_qcheck(text) == jcon.DONE

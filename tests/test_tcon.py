@@ -63,7 +63,7 @@ def test_calls_without_the_reference():
     import ctypes as C
 
     h = C.c_void_p()
-    assert lib.arcs_tcon_create(1, b"[]", None, None, 0, C.byref(h)) == jcon.ERR_UNSUPPORTED  # the Qwen form: not an automaton here
+    assert lib.arcs_tcon_create(7, b"[]", None, None, 0, C.byref(h)) == 1  # no such form
 
 
 @needs_ref
@@ -117,6 +117,103 @@ def test_table_mask_is_the_per_candidate_predicate():
             allowed, end = jcon.walk_mask(table, dead, off, by)
             for t, piece in enumerate(toks):
                 want = ref_check(text + piece) if piece else F
+                assert bool(allowed[t]) == (want != F), (text, piece, want)
+                if want != F:
+                    assert bool(done[end[t]]) == (want == D), (text, piece, want)
+            steps += 1
+    assert steps > 60
+
+
+# ---------------------------------------------------------------- the Qwen 3.x form (tools/tool_constraint.h:285-371)
+QTOOLS = json.dumps([
+    {"type": "function", "function": {"name": "search", "parameters": {
+        "type": "object", "properties": {"query": {"type": "string"}, "limit": {"type": "integer"}, "exact": {"type": "boolean"},
+                                         "filters": {"type": "object", "properties": {"lang": {"enum": ["en", "de"]}}, "required": ["lang"]},
+                                         "tags": {"type": "array", "items": {"type": "string"}, "maxItems": 3}, "free": {}},
+        "required": ["query"]}}},
+    {"type": "function", "function": {"name": "search_all", "parameters": {"type": "object", "additionalProperties": {"type": "number"}}}},
+    {"name": "ping"},
+])  # fmt: skip
+
+# (a number at the very end of a value is still PARTIAL for jcon::Checker - more digits could follow - so the
+#  reference takes a numeric parameter only with a blank behind it, besides the one newline it strips: :364-368)
+QCALLS = [
+    "\n<function=search>\n<parameter=query>\nhello <b>world</b> 1 < 2\n</parameter>\n<parameter=limit>\n10\n\n</parameter>\n</function>\n</tool_call>",
+    "<function=search><parameter=exact>true</parameter><parameter=query>q</parameter> <parameter=filters>{\"lang\": \"de\"}\n</parameter></function></tool_call>",
+    "<function=search>\n<parameter=tags>\n[\"a<\", \"</param\", \"x\"]\n</parameter>\n<parameter=query>\n\n</parameter>\n<parameter=free>\nany {text} here</parameter>\n</function>\n</tool_call>",
+    " <function=search_all>\n<parameter=a>\n-1.5e3 \n</parameter>\n<parameter=b>2 </parameter>\n</function> </tool_call>",
+    "<function=ping>\n</function>\n</tool_call>",
+    "<function=search>\n<parameter=limit>\n 7\n\n</parameter>\n<parameter=query>\nx</parameter>\n</function>\n</tool_call>",
+]
+
+
+def ref_qcheck(text):
+    return orc.ref.ref_tcon_check(1, QTOOLS.encode(), text, len(text))
+
+
+def test_qwen_calls_without_the_reference():
+    tc = jcon.JsonConstraint.qwen_call(QTOOLS, *EMPTY_VOCAB)
+    for call in QCALLS:
+        assert tc.check(call) == D, call
+        assert tc.check(call[:-1]) == P and tc.check(call + "x") == F
+    for bad in ["<function=nope", "<function=search>\n</function>", "<function=search>\n<parameter=limit>\n1.5\n</parameter>",
+                "<function=search>\n<parameter=query>a<parameter=", "<function=search>\n<parameter=limit>1</parameter><parameter=limit>",
+                "   <function=", "<function=search>\n\n\n<", "<function=ping></function></tool_call> \n\n",
+                "<function=search>\n<parameter=limit>\n10\n</parameter>"]:
+        assert tc.check(bad) == F, bad
+
+
+@needs_ref
+def test_qwen_every_prefix_against_the_reference_checker():
+    rng = np.random.default_rng(33)
+    tc = jcon.JsonConstraint.qwen_call(QTOOLS, *EMPTY_VOCAB)
+    n = 0
+    for call in QCALLS:
+        for text in [call.encode()] + damaged(call, rng, 80):
+            for cut in range(len(text) + 1):
+                got, want = tc.check(text[:cut]), ref_qcheck(text[:cut])
+                assert got == want, (text[:cut], got, want)
+                n += 1
+                if want == F:
+                    break
+            if cut < len(text):
+                assert tc.check(text) == ref_qcheck(text) == F
+    assert n > 8000
+
+
+def qwen_vocab(rng, n_random=1200):
+    toks = [bytes([b]) for b in range(256)]
+    frag = ["<function=", "<function=search", "search", "_all", ">\n", "<parameter=", "<parameter=query>", "query", "limit", ">\n10\n", "</parameter>", "</parameter>\n", "\n</parameter>",
+            "</", "</param", "eter>", "<param", "</function>", "</function>\n", "</tool_call>", "\n</tool_call>", "<", ">", "\n", "\n\n", " ", "  ", "true", "false", "tru", "10", "-1", ".5e3",
+            '{"lang"', '": "de"}', '["a<"', ', "', '"]', "hello", " world", "<b>", "exact", "filters", "tags", "free", "ping", "a>", "b>2", "e3 \n"]
+    toks += [f.encode() for f in frag]
+    src = np.frombuffer(b'<>/=\n function parameter search query limit 0123456789-.e"{}[],:truefals', np.uint8)
+    printable = np.frombuffer(bytes(range(0x20, 0x7F)), np.uint8)
+    for _ in range(n_random):
+        ln = int(rng.integers(1, 8))
+        a = src if rng.random() < 0.7 else printable
+        toks.append(bytes(a[rng.integers(0, len(a), ln)]))
+    toks.append(b"")
+    off = np.zeros(len(toks) + 1, np.uint32)
+    off[1:] = np.cumsum([len(t) for t in toks])
+    return toks, off, np.frombuffer(b"".join(toks), np.uint8).copy()
+
+
+@needs_ref
+def test_qwen_table_mask_is_the_per_candidate_predicate():
+    rng = np.random.default_rng(9)
+    toks, off, by = qwen_vocab(rng)
+    tc = jcon.JsonConstraint.qwen_call(QTOOLS, off, by)
+    steps = 0
+    for call in QCALLS:
+        d = call.encode()
+        for cut in sorted(set(rng.integers(0, len(d), 18).tolist() + [0, len(d) - 1])):
+            text = d[:cut]
+            table, dead, done, ts = tc.table(text)
+            assert ts == ref_qcheck(text) == P
+            allowed, end = jcon.walk_mask(table, dead, off, by)
+            for t, piece in enumerate(toks):
+                want = ref_qcheck(text + piece) if piece else F
                 assert bool(allowed[t]) == (want != F), (text, piece, want)
                 if want != F:
                     assert bool(done[end[t]]) == (want == D), (text, piece, want)
