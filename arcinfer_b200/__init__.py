@@ -10,7 +10,7 @@ process that only generates inputs does not map the CUDA library.
 """
 from .params import PARAMS_DTYPE, make_params  # noqa: F401
 
-_CAPI_NAMES = ("ArcsError", "adjusted_batch", "argmax_batch", "dfa_mask", "dflash_select", "lib", "logprobs_batch", "merge_batch", "merge_records", "sample_batch")
+_CAPI_NAMES = ("ArcsError", "accept_batch", "adjusted_batch", "argmax_batch", "dfa_mask", "dflash_select", "lib", "logprobs_batch", "merge_batch", "merge_records", "sample_batch")
 
 
 def __getattr__(name):

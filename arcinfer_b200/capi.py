@@ -91,6 +91,8 @@ lib.arcs_argmax_batch.argtypes = [C.POINTER(ArgmaxArgs), C.c_void_p]
 lib.arcs_argmax_batch_static.restype = C.c_int
 lib.arcs_argmax_batch_static.argtypes = [C.POINTER(ArgmaxArgs), C.c_void_p]
 lib.arcs_argmax_static_scratch_bytes.restype = C.c_size_t
+lib.arcs_accept_batch.restype = C.c_int
+lib.arcs_accept_batch.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]
 lib.arcs_dfa_mask.restype = C.c_int
 lib.arcs_dfa_mask.argtypes = [
     C.c_void_p, C.c_int32, C.c_int32, C.c_void_p, C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p,
@@ -198,6 +200,38 @@ def sample_batch(logits, params, u, hist_off=None, hist_ids=None, bias_off=None,
     a.status = status.data_ptr()
     _check(lib.arcs_sample_batch(C.byref(a), _stream(dev)), "arcs_sample_batch")
     return out
+
+
+def accept_batch(token, row_off, draft, draft_off):
+    """arcs_accept_batch: the acceptance walk over chosen tokens (int32 device tensors): returns
+    (accepted [slots], next [slots])."""
+    slots = row_off.numel() - 1
+    dev = token.device
+    acc = torch.empty(slots, dtype=torch.int32, device=dev)
+    nxt = torch.empty(slots, dtype=torch.int32, device=dev)
+    _check(lib.arcs_accept_batch(token.data_ptr(), row_off.data_ptr(), draft.data_ptr(), draft_off.data_ptr(), slots, acc.data_ptr(), nxt.data_ptr(),
+                                 _stream(dev)), "arcs_accept_batch")
+    return acc, nxt
+
+
+def verification_histories(histories, drafts):
+    """The CSR history of every verification row when drafts are verified under sampling: row i of
+    a slot sees the slot's history followed by its first i drafts (tools/server_chat.h:593: an
+    accepted draft is appended to `gen` before the next row is sampled). histories / drafts: one
+    int32 array per slot; a slot has len(drafts) + 1 rows. Returns (hist_off, hist_ids, row_off,
+    draft_off, draft_ids) as numpy arrays."""
+    offs, ids, row_off, d_off = [0], [], [0], [0]
+    for h, d in zip(histories, drafts):
+        h, d = np.asarray(h, np.int32), np.asarray(d, np.int32)
+        for i in range(len(d) + 1):
+            ids.append(h)
+            ids.append(d[:i])
+            offs.append(offs[-1] + len(h) + i)
+        row_off.append(row_off[-1] + len(d) + 1)
+        d_off.append(d_off[-1] + len(d))
+    cat = np.concatenate(ids).astype(np.int32) if ids else np.zeros(0, np.int32)
+    dr = np.concatenate([np.asarray(d, np.int32) for d in drafts]) if drafts else np.zeros(0, np.int32)
+    return (np.asarray(offs, np.int32), cat, np.asarray(row_off, np.int32), np.asarray(d_off, np.int32), dr.astype(np.int32))
 
 
 def pack_width(records):

@@ -191,9 +191,35 @@ __global__ void __launch_bounds__(kThreads) argmax_kernel(const ArgmaxDev a) {
   }
 }
 
+// The same walk over tokens chosen by any means (sampled ones: tools/server_chat.h:578-591)
+__global__ void accept_kernel(const int32_t* __restrict__ token, const int32_t* __restrict__ row_off, const int32_t* __restrict__ draft,
+                              const int32_t* __restrict__ draft_off, int32_t slots, int32_t* __restrict__ accepted, int32_t* __restrict__ next) {
+  const int s = (int)(blockIdx.x * blockDim.x + threadIdx.x);
+  if (s >= slots) return;
+  const int32_t r0 = row_off[s], rows = row_off[s + 1] - r0;
+  const int32_t* d = draft + draft_off[s];
+  int32_t nd = draft_off[s + 1] - draft_off[s];
+  if (nd > rows - 1) nd = rows - 1;  // a draft needs a row after it for the bonus token
+  int32_t acc = 0, nx = rows > 0 ? token[r0] : -1;
+  while (acc < nd && nx == d[acc]) {
+    ++acc;
+    nx = token[r0 + acc];
+  }
+  accepted[s] = acc;
+  next[s] = nx;
+}
+
 }  // namespace arcs
 
 using namespace arcs;
+
+extern "C" int arcs_accept_batch(const int32_t* token, const int32_t* row_off, const int32_t* draft, const int32_t* draft_off,
+                                 int32_t slots, int32_t* accepted, int32_t* next, void* stream) {
+  if (int inj = fault_injected()) return inj;
+  if (!token || !row_off || !draft_off || !draft || !accepted || !next || slots <= 0) return set_error(ARCS_ERR_ARG, "accept_batch: bad argument");
+  accept_kernel<<<(unsigned)((slots + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(token, row_off, draft, draft_off, slots, accepted, next);
+  return check_launch("accept_batch");
+}
 
 extern "C" size_t arcs_argmax_workspace_bytes(int32_t R, int32_t V) {
   if (R <= 0 || V <= 0) return 0;

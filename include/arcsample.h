@@ -223,6 +223,19 @@ int arcs_argmax_batch(const arcs_argmax_args* args, void* stream);
  * and set ARCS_ERR_TIMEOUT in the status word). The set-up is guarded by a lock, so first calls
  * from several host threads enqueue the clearing once. The stream must belong to the current
  * device. No allocation is made by this call. */
+/* accept_batch: the acceptance walk over tokens chosen by any means: with sampled tokens it is
+ * the verification of drafts under sampling (tools/server_chat.h:578-591: the server samples from
+ * the row after each accepted draft, with the accepted drafts appended to the history, and stops
+ * at the first sample that differs). Because an accepted token EQUALS its draft, the history of
+ * verification row i, if the walk reaches it, is known beforehand: the slot's history followed by
+ * the first i drafts. So all rows of all slots are sampled in ONE arcs_sample_batch call (row i
+ * of a slot with that history and its own uniform number), and this call walks the result:
+ * accepted[s] = leading drafts equal to their row's token, next[s] = the token of the first row
+ * that differs (or of the row after the last draft). Rows past that point were sampled in vain;
+ * a host that draws its uniforms from a generator advances it by accepted[s] + 1 draws only. */
+int arcs_accept_batch(const int32_t* token, const int32_t* row_off, const int32_t* draft, const int32_t* draft_off,
+                      int32_t slots, int32_t* accepted, int32_t* next, void* stream);
+
 size_t arcs_argmax_static_scratch_bytes(void);
 int arcs_argmax_batch_static(const arcs_argmax_args* args, void* stream);
 
