@@ -526,6 +526,29 @@ def vocab_shard_leg(ab, synth, dist, rank, world, dev, B, V, H, params, steps, w
             "launches_per_step": 3, "launch": launch, "note": "local pass (stream + finish kernels), all_gather_into_tensor of packed records, merge kernel"}
 
 
+def bind_near_gpu(torch, local):
+    """Run this process (and allocate its pinned host memory: first touch) on the CPU cores the
+    GPU hangs off. With several ranks on a multi-socket host, a rank left on the wrong socket copies
+    its batch to its GPU across the socket link. Only the process's own CPU affinity is set (a
+    property of this process, read from NVML; nothing of the GPU is changed). Returns what was done."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        pr = torch.cuda.get_device_properties(local)
+        bus = f"{pr.pci_domain_id:08x}:{pr.pci_bus_id:02x}:{pr.pci_device_id:02x}.0"
+        h = pynvml.nvmlDeviceGetHandleByPciBusId(bus.encode())
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cpus = {64 * i + b for i, w in enumerate(words) for b in range(64) if (w >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return "no cores in common with the allowed set"
+        os.sched_setaffinity(0, cpus)
+        return f"{len(cpus)} cores near GPU {local}"
+    except Exception as e:  # (no NVML, no permission: the run goes on unbound)
+        return f"unbound ({type(e).__name__})"
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -612,6 +635,7 @@ def main():
     assert torch.cuda.is_available(), "bench.py needs a CUDA device: there is no CPU fallback"
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    bound = bind_near_gpu(torch, local) if world > 1 else "single rank: not bound"
     if world > 1:
         import torch.distributed as dist
 
@@ -722,7 +746,8 @@ def main():
                "steps": esteps, "ms_per_step": 1e3 * dt / esteps, "same_tokens_as_device_path": same,
                # every rank copies its own batch from its own pinned buffer: the step is the host-to-device
                # copy, and what N ranks reach together is bounded by the host side they share
-               "h2d_gbs_per_rank": h2d / dt * esteps / 1e9, "h2d_gbs_all_ranks": world * h2d / dt * esteps / 1e9}
+               "h2d_gbs_per_rank": h2d / dt * esteps / 1e9, "h2d_gbs_all_ranks": world * h2d / dt * esteps / 1e9,
+               "host_cores": bound}
         ctx.close()
         del h_logits
     clk = clocks.stop() if clocks else None
