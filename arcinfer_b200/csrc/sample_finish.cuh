@@ -32,9 +32,10 @@ __global__ void __launch_bounds__(G, 5) finish_kernel(const SampleDev a) {  // (
   __shared__ int misc[8];
   __shared__ int sh[12];
   __shared__ int seg_n[4][kMaxSeg];  // per segment: entries of the prepare kernel (+ flagged ones of the stream), survivors B, A, overflowed
-  __shared__ __align__(16) uint32_t fl_key[kStage];   // hot elements the filter flagged, waiting to be settled
-  __shared__ __align__(16) int32_t fl_id[kStage];     // (global id | kOkB)
-  __shared__ __align__(16) uint32_t fl_cnt[kStage];   // occurrences in the history | in the repeat window << 31 | in the bias list << 30
+  __shared__ __align__(16) uint32_t fl_all[3 * kStage];  // (one array, so that the CTA-wide fast path can take it whole as its scratch)
+  uint32_t* const fl_key = fl_all;                                              // hot elements the filter flagged, waiting to be settled
+  int32_t* const fl_id = reinterpret_cast<int32_t*>(fl_all + kStage);            // (global id | kOkB)
+  uint32_t* const fl_cnt = fl_all + 2 * kStage;                                 // occurrences in the history | in the repeat window << 31 | in the bias list << 30
   enum { L_TAU_B = 0, L_TAU_A, L_PRUNE_MIN, L_TOP, L_LOW };
   enum { S_CNT_B = 0, S_CNT_A, S_FLAGS, S_NCAND, S_BANS, S_NFLAG, S_NLIST, S_NLISTA, S_OVER, S_NPRE };
 
@@ -44,13 +45,14 @@ __global__ void __launch_bounds__(G, 5) finish_kernel(const SampleDev a) {  // (
   // ---- rows of this CTA: the warp path first, every warp its own row
   const int kRows = MASKED ? 1 : a.rows_per_cta;  // (at most G / 32)
   static_assert(G == 128 && kStage * 4 >= (int)sizeof(FastScratch) && kCapB * 4 >= (int)sizeof(FastScratch), "the warps' scratch lies in four of the arrays above");
+  static_assert(3 * kStage * 4 >= (int)sizeof(FastScratchCta), "the CTA-wide fast path's scratch is the three stage arrays together");
   __shared__ int row_rc[G / 32];
   const int b_first = (int)blockIdx.x * kRows;
   if (!MASKED) {
     const int w = gt >> 5, bw = b_first + w;
     int rc = kFastSlow;
     if (kRows == 1) {  // few rows: the whole CTA on one
-      rc = finish_row_fast<T, G>(a, b_first, *reinterpret_cast<FastScratch*>(fl_key), hist);
+      rc = finish_row_fast<T, G>(a, b_first, *reinterpret_cast<FastScratchCta*>(fl_all), hist);
       if (w > 0) rc = kFastDone;
     } else if (w >= kRows || bw >= a.B) {
       rc = kFastDone;

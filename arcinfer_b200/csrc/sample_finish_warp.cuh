@@ -15,7 +15,8 @@ namespace arcs {
 
 
 constexpr int kFastK = 64;      // most candidates a row may keep on this path
-constexpr int kFastBuf = 256;   // most survivors above the last threshold
+constexpr int kFastBuf = 256;   // most survivors above the last threshold (one warp)
+constexpr int kFastBufCta = 512;  // ... when the whole CTA works on the row
 constexpr int kFastFlag = 32;   // most flagged entries
 constexpr uint32_t kFlagWaitLimit = 1u << 21;  // bounded wait for an item's release (about a second)
 
@@ -56,8 +57,9 @@ __device__ __forceinline__ float exp_term(float xf) {
 }
 
 // one warp's scratch (carved out of shared memory by the caller, 8-byte aligned)
-struct FastScratch {
-  unsigned long long buf[kFastBuf];  // composites of the survivors above the threshold; later the running sums
+template <int BUF>
+struct FastScratchT {
+  unsigned long long buf[BUF];  // composites of the survivors above the threshold; later the running sums
   float sv[kFastK];
   int32_t sid[kFastK];
   double spr[kFastK + 1];
@@ -67,6 +69,8 @@ struct FastScratch {
   unsigned long long tau;   // the threshold the survivors must exceed
   int32_t rc, m, nf, spill, kB;
 };
+using FastScratch = FastScratchT<kFastBuf>;
+using FastScratchCta = FastScratchT<kFastBufCta>;
 static_assert(sizeof(FastScratch) <= 4096, "a warp's scratch fits one of the CTA-wide path's 4 KB arrays");
 
 enum { kFastDone = 0, kFastSlow = 1, kFastLate = 2 };
@@ -106,7 +110,8 @@ __device__ __forceinline__ void combine_mz(const SampleDev& a, int b) {
 // flagged entries, softmax, cuts, draw) the first warp does. Every thread returns the same code
 // up to the last barrier.
 template <typename T, int NT>
-__device__ __noinline__ int finish_row_fast(const SampleDev& a, int b, FastScratch& fs, uint32_t* bins) {
+__device__ __noinline__ int finish_row_fast(const SampleDev& a, int b, FastScratchT<(NT == 128 ? kFastBufCta : kFastBuf)>& fs, uint32_t* bins) {
+  constexpr int kBuf = NT == 128 ? kFastBufCta : kFastBuf;
   static_assert(NT == 32 || NT == 128, "one warp or the CTA");
   const int lane = threadIdx.x & 31;
   const int tid = NT == 32 ? lane : (int)threadIdx.x;
@@ -224,7 +229,7 @@ __device__ __noinline__ int finish_row_fast(const SampleDev& a, int b, FastScrat
   // ---- many entries (NT == 128): a tighter threshold first, read off the counts of the entries by
   // the upper 16 bits of their keys, as the stream kernel does for its own (flagged entries count
   // for nothing: what they are worth is not known yet)
-  if (NT == 128 && total > kFastBuf) {
+  if (NT == 128 && total > kBuf) {
     for (int i = tid; i < 256; i += NT) bins[i] = 0u;
     bar();
     const unsigned long long tau0 = fs.tau;
@@ -293,7 +298,7 @@ __device__ __noinline__ int finish_row_fast(const SampleDev& a, int b, FastScrat
           nf_w += __popc(bf);
         }
         if (keep) {
-          if (atk < kFastBuf) fs.buf[atk] = cm;
+          if (atk < kBuf) fs.buf[atk] = cm;
           else fs.spill = 1;
         }
         if (fl) {
@@ -360,7 +365,7 @@ __device__ __noinline__ int finish_row_fast(const SampleDev& a, int b, FastScrat
         const uint64_t cm = comp_of(ky, idf);
         p = p && cm > tau;
         if (p) {  // (warp-uniform: every lane computed the same)
-          if (m >= kFastBuf) {
+          if (m >= kBuf) {
             if (lane == 0) fs.spill = 1;
             break;
           }
@@ -398,7 +403,7 @@ __device__ __noinline__ int finish_row_fast(const SampleDev& a, int b, FastScrat
         fs.sid[rank[x]] = comp_id(mine[x]);
       }
   };
-  if (NT == 128) rank_all(IntTag<kFastBuf / 128>{});
+  if (NT == 128) rank_all(IntTag<kFastBufCta / 128>{});
   else if (m <= 64) rank_all(IntTag<2>{});
   else if (m <= 128) rank_all(IntTag<4>{});
   else rank_all(IntTag<kFastBuf / 32>{});
