@@ -211,3 +211,75 @@ def test_arguments_are_checked():
         jcon.JsonConstraint("not json", False, *EMPTY_VOCAB)
     jc = jcon.JsonConstraint(json.dumps({}), False, *EMPTY_VOCAB)
     assert jc.check("[1]") == D
+
+
+# ---- random schemas (the subset the checker knows) and documents that mostly fit them
+def _rschema(rng, d=0):
+    r=rng.random()
+    if d>3 or r<0.25:
+        t=rng.choice(["string","integer","number","boolean","null"])
+        return {"type":str(t)}
+    if r<0.35: return {}
+    if r<0.45:
+        opts=["a","bc","x y",1,25,None,True,-3.5]
+        return {"enum":[opts[int(rng.integers(0,len(opts)))] for _ in range(int(rng.integers(1,4)))]}
+    if r<0.5: return {"const": {"k":[1,"z"]}}
+    if r<0.65:
+        return {"type":"array","items":_rschema(rng, d+1),**({"minItems":int(rng.integers(0,3))} if rng.random()<0.5 else {}),**({"maxItems":int(rng.integers(1,4))} if rng.random()<0.5 else {})}
+    if r<0.9:
+        props={str(k):_rschema(rng, d+1) for k in rng.choice(["a","ab","b","name","n1"],int(rng.integers(0,4)),replace=False)}
+        s={"type":"object","properties":props}
+        if props and rng.random()<0.6: s["required"]=[str(k) for k in list(props)[:int(rng.integers(0,len(props)+1))]]
+        c=rng.random()
+        if c<0.3: s["additionalProperties"]=False
+        elif c<0.5: s["additionalProperties"]=True
+        elif c<0.7: s["additionalProperties"]=_rschema(rng, d+1)
+        return s
+    return {"anyOf":[_rschema(rng, d+1) for _ in range(int(rng.integers(1,4)))]}
+def _rvalue(rng, s, d=0):
+    # a value that often (not always) fits
+    if "enum" in s: return s["enum"][int(rng.integers(0,len(s["enum"])))]
+    if "const" in s: return s["const"]
+    if "anyOf" in s: return _rvalue(rng, s["anyOf"][int(rng.integers(0,len(s["anyOf"])))],d+1)
+    t=s.get("type")
+    if t is None: t=str(rng.choice(["string","integer","object","array","null","boolean"]))
+    if t=="string": return str(rng.choice(["","hi","a\"b","\\n x","ü"]))
+    if t=="integer": return int(rng.integers(-50,500))
+    if t=="number": return float(rng.choice([0.5,-12.25,3e5,7]))
+    if t=="boolean": return bool(rng.integers(0,2))
+    if t=="null": return None
+    if t=="array": return [_rvalue(rng, s.get("items",{}),d+1) for _ in range(int(rng.integers(0,4)))] if d<4 else []
+    if t=="object":
+        o={}
+        for k,v in s.get("properties",{}).items():
+            if rng.random()<0.8: o[k]=_rvalue(rng, v,d+1)
+        if rng.random()<0.3 and d<4: o["zz"]=_rvalue(rng, s["additionalProperties"] if isinstance(s.get("additionalProperties"),dict) else {},d+1)
+        return o
+
+
+@needs_ref
+def test_random_schemas_against_the_reference_checker():
+    rng = np.random.default_rng(123)
+    pool = b'{}[]:,"\\ \n0123456789-+.eEtruefalsnabxyz'
+    total = unsupported = 0
+    for _ in range(160):
+        s = _rschema(rng)
+        sj = json.dumps(s)
+        obj = bool(rng.integers(0, 2)) and s.get("type") == "object"
+        try:
+            jc = jcon.JsonConstraint(sj, obj, *EMPTY_VOCAB)
+        except jcon.Unsupported:
+            unsupported += 1
+            continue
+        for _rep in range(5):
+            doc = json.dumps(_rvalue(rng, s), separators=(str(rng.choice([",", ", "])), str(rng.choice([":", ": "]))), ensure_ascii=False).encode()
+            if rng.random() < 0.5 and len(doc):
+                i = int(rng.integers(0, len(doc)))
+                doc = doc[:i] + bytes([pool[int(rng.integers(0, len(pool)))]]) + doc[i + int(rng.integers(0, 2)):]
+            for cut in range(len(doc) + 1):
+                got, want = jc.check(doc[:cut]), ref_check(sj, obj, doc[:cut])
+                assert got == want, (sj, obj, doc[:cut], got, want)
+                total += 1
+                if want == F:
+                    break
+    assert total > 4000 and unsupported < 40
