@@ -283,3 +283,34 @@ def test_random_schemas_against_the_reference_checker():
                 if want == F:
                     break
     assert total > 4000 and unsupported < 40
+
+
+@needs_ref
+def test_random_schemas_table_masks_are_the_predicate():
+    rng = np.random.default_rng(77)
+    toks, off, by = json_vocab(rng, 500)
+    total = 0
+    for _ in range(60):
+        s = _rschema(rng)
+        sj = json.dumps(s)
+        obj = bool(rng.integers(0, 2)) and s.get("type") == "object"
+        try:
+            jc = jcon.JsonConstraint(sj, obj, off, by)
+        except jcon.Unsupported:
+            continue
+        doc = json.dumps(_rvalue(rng, s), separators=(str(rng.choice([",", ", "])), str(rng.choice([":", ": "]))), ensure_ascii=False).encode()
+        if ref_check(sj, obj, doc) == F:
+            continue
+        for cut in sorted(set(rng.integers(0, len(doc) + 1, 3).tolist())):
+            text = doc[:cut]
+            if ref_check(sj, obj, text) == D:
+                continue
+            table, dead, done, _ts = jc.table(text)
+            allowed, end = jcon.walk_mask(table, dead, off, by)
+            for t, piece in enumerate(toks):
+                want = ref_check(sj, obj, text + piece) if piece else F
+                assert bool(allowed[t]) == (want != F), (sj, obj, text, piece, want)
+                if want != F:
+                    assert bool(done[end[t]]) == (want == D), (sj, obj, text, piece, want)
+                total += 1
+    assert total > 30000
