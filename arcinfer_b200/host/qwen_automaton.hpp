@@ -140,6 +140,9 @@ class QwenAutomaton {
         if (p && st.text.size() == kParam.size()) {
           st.phase = Q_KEY;
           st.text.clear();
+          // (:341: a parameter can begin only where some key can still follow)
+          const JVal& ps = params(st);
+          if (!key_ok(st, ps, Automaton::any_key_of_public(ps), true)) return false;
         } else if (f && st.text.size() == kEndFn.size()) {
           st.phase = Q_TAIL;  // :325: up to two blanks, then "</tool_call>", then nothing
           st.text.clear();

@@ -219,3 +219,63 @@ def test_qwen_table_mask_is_the_per_candidate_predicate():
                     assert bool(done[end[t]]) == (want == D), (text, piece, want)
             steps += 1
     assert steps > 60
+
+
+# ---- random parameter schemas: calls written in either form, damaged, every prefix
+def _gemma_text(v):
+    if isinstance(v, str):
+        return Q + v + Q
+    if isinstance(v, bool):
+        return "true" if v else "false"
+    if v is None:
+        return "null"
+    if isinstance(v, (int, float)):
+        s = repr(v)
+        return s if "e" not in s and "E" not in s else str(int(v))
+    if isinstance(v, list):
+        return "[" + ",".join(_gemma_text(x) for x in v) + "]"
+    return "{" + ",".join(k + ":" + _gemma_text(x) for k, x in v.items()) + "}"
+
+
+def _qwen_text(name, params, args):
+    out = "<function=" + name + ">\n"
+    for k, v in args.items():
+        addl = params.get("additionalProperties")
+        vs = params.get("properties", {}).get(k, addl if isinstance(addl, dict) else {})
+        raw = vs.get("type") == "string" or "type" not in vs
+        body = (v if isinstance(v, str) else json.dumps(v)) if raw else json.dumps(v) + " "
+        out += "<parameter=" + k + ">\n" + body + "\n</parameter>\n"
+    return out + "</function>\n</tool_call>"
+
+
+@needs_ref
+@pytest.mark.parametrize("kind", [0, 1])
+def test_random_parameter_schemas_against_the_reference_checker(kind):
+    from test_jcon import _rschema, _rvalue
+
+    rng = np.random.default_rng(5 + kind)
+    pool = b'{}[]:,<|">/=\n 0123456789-.truefalsnabxyz'
+    total = done = 0
+    for _ in range(90):
+        params = _rschema(rng, 1)
+        while params.get("type") != "object":
+            params = _rschema(rng, 1)
+        tools = json.dumps([{"type": "function", "function": {"name": "tool_a", "parameters": params}}, {"name": "tool", "parameters": {"type": "object"}}])
+        try:
+            tc = (jcon.JsonConstraint.gemma_call if kind == 0 else jcon.JsonConstraint.qwen_call)(tools, *EMPTY_VOCAB)
+        except jcon.Unsupported:
+            continue
+        for _rep in range(4):
+            args = _rvalue(rng, params)
+            doc = (("call:tool_a" + _gemma_text(args) + END) if kind == 0 else _qwen_text("tool_a", params, args)).encode()
+            if rng.random() < 0.5:
+                i = int(rng.integers(0, len(doc)))
+                doc = doc[:i] + bytes([pool[int(rng.integers(0, len(pool)))]]) + doc[i + int(rng.integers(0, 2)):]
+            for cut in range(len(doc) + 1):
+                got, want = tc.check(doc[:cut]), orc.ref.ref_tcon_check(kind, tools.encode(), doc[:cut], cut)
+                assert got == want, (kind, tools, doc[:cut], got, want)
+                total += 1
+                done += want == D
+                if want == F:
+                    break
+    assert total > 5000 and done > 20
