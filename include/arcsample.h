@@ -5,7 +5,8 @@
  * single-threaded host sampler over a logits row read back from the GPU. Every entry point
  * takes plain pointers and sizes; device pointers are owned by the caller; nothing throws;
  * the return value is an arcs_status. Calls enqueue work on the caller's stream (passed as
- * void*, a cudaStream_t) and do not synchronise unless the name ends in _host.
+ * void*, a cudaStream_t) and do not synchronise unless the name ends in _host. The arcs_jcon_* and
+ * arcs_tcon_create functions are host code and enqueue nothing.
  *
  * Citations name files of the reference project (rizagp/arcinfer) by their path inside it.
  *
